@@ -1,0 +1,222 @@
+/*
+ * vkml_b200.h -- C ABI of the B200 (sm_100a) execution backend for vkML.
+ *
+ * This is the whole boundary between vkML's host framework and the CUDA
+ * backend: plain pointers, sizes and POD structs, status codes instead of
+ * exceptions, no C++ or torch types.  One `b200_ctx` is one CUDA device with
+ * one compute stream; everything submitted through a context is ordered on
+ * that stream.
+ *
+ * The only intended caller inside vkML is an adapter class deriving from
+ * `vkml::Backend` (include/vkml/backend/api/backend.h:49-125); each entry
+ * point below names the virtual it replaces.  Numeric values of `b200_op` and
+ * `b200_dtype` equal vkML's `OpKind` (include/vkml/graph/op.h:30-139) and
+ * `DType` (include/vkml/core/dtype.h:17-23) so a node is flattened by copying
+ * fields, and `params` carries the raw 64 `OpParams` bytes
+ * (include/vkml/graph/op.h:199-221).
+ */
+#ifndef VKML_B200_H
+#define VKML_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define B200_ABI_VERSION 1
+#define B200_MAX_DIMS 4   /* vkml::kMaxDims, include/vkml/core/shape.h:25 */
+#define B200_MAX_SRC 4    /* vkml::kMaxSrc,  include/vkml/graph/op.h:148 */
+#define B200_PARAM_BYTES 64
+
+/* Status codes. Each maps to one vkML exception type
+ * (include/vkml/util/error.h:7-38); the adapter rethrows. */
+typedef enum b200_status {
+    B200_OK = 0,
+    B200_SHAPE_ERROR = 1,
+    B200_DTYPE_ERROR = 2,
+    B200_DEVICE_ERROR = 3,
+    B200_INDEX_ERROR = 4,
+    B200_NOT_IMPLEMENTED = 5,
+    B200_INTERNAL_ERROR = 6,
+    B200_OUT_OF_MEMORY = 7,
+    B200_INVALID_ARGUMENT = 8,
+    B200_TIMEOUT = 9
+} b200_status;
+
+/* vkml::DType */
+typedef enum b200_dtype {
+    B200_F32 = 0,
+    B200_F16 = 1,
+    B200_I32 = 2,
+    B200_I64 = 3,
+    B200_BOOL = 4
+} b200_dtype;
+
+/* vkml::OpKind, same order and values. */
+typedef enum b200_op {
+    B200_OP_INPUT = 0, B200_OP_CONST, B200_OP_FULL, B200_OP_ARANGE, B200_OP_RAND,
+    B200_OP_RESHAPE, B200_OP_PERMUTE, B200_OP_SLICE, B200_OP_BROADCAST, B200_OP_SQUEEZE,
+    B200_OP_UNSQUEEZE, B200_OP_CONTIGUOUS, B200_OP_CAST, B200_OP_CAT, B200_OP_ADD,
+    B200_OP_SUB, B200_OP_MUL, B200_OP_SCALED_ADD, B200_OP_DIV, B200_OP_POW,
+    B200_OP_MAXIMUM, B200_OP_MINIMUM, B200_OP_EQUAL, B200_OP_LESS, B200_OP_GREATER,
+    B200_OP_LESS_EQUAL, B200_OP_GREATER_EQUAL, B200_OP_NOT_EQUAL, B200_OP_NEG, B200_OP_ABS,
+    B200_OP_SIGN, B200_OP_SQUARE, B200_OP_SQRT, B200_OP_RSQRT, B200_OP_RECIPROCAL,
+    B200_OP_EXP, B200_OP_LOG, B200_OP_ERF, B200_OP_ERFC, B200_OP_SIN,
+    B200_OP_COS, B200_OP_TANH, B200_OP_SIGMOID, B200_OP_RELU, B200_OP_GELU,
+    B200_OP_SILU, B200_OP_CLAMP, B200_OP_SUM, B200_OP_MEAN, B200_OP_MAX,
+    B200_OP_MIN, B200_OP_PROD, B200_OP_ARGMAX, B200_OP_ARGMIN, B200_OP_MATMUL,
+    B200_OP_SOFTMAX, B200_OP_LOG_SOFTMAX, B200_OP_IM2COL, B200_OP_COL2IM, B200_OP_MAX_POOL2D,
+    B200_OP_MAX_POOL2D_BACKWARD, B200_OP_INDEX_SELECT, B200_OP_SCATTER_ADD,
+    B200_OP_SLICE_BACKWARD, B200_OP_WHERE, B200_OP_TRIU, B200_OP_TRIL,
+    B200_OP_COUNT
+} b200_op;
+
+/* A strided view of device memory: vkml::Shape (byte strides, rank <= 4,
+ * stride 0 with extent > 1 marks a broadcast; include/vkml/core/shape.h:60-153)
+ * plus the node's address `storage->data() + storage_offset`
+ * (include/vkml/graph/node.h:144-149). */
+typedef struct b200_tensor {
+    void* data;
+    int64_t dims[B200_MAX_DIMS];
+    int64_t strides[B200_MAX_DIMS]; /* bytes */
+    int32_t ndim;
+    int32_t dtype; /* b200_dtype */
+} b200_tensor;
+
+/* One graph node as the backend sees it (vkml::Node, node.h:69-157). */
+typedef struct b200_node {
+    uint32_t op;    /* b200_op */
+    uint32_t n_src; /* 0..4 */
+    b200_tensor out;
+    b200_tensor src[B200_MAX_SRC];
+    uint8_t params[B200_PARAM_BYTES];
+} b200_node;
+
+/* vkml::BufferCopy (backend.h:18-24) with the storage base already added. */
+typedef struct b200_copy {
+    void* dst;
+    const void* src;
+    size_t nbytes;
+} b200_copy;
+
+/* Subset of vkml::DeviceCapabilities (capabilities.h:23-119) the adapter fills
+ * from the device. */
+typedef struct b200_caps {
+    char name[128];
+    int32_t cc_major, cc_minor;
+    uint32_t sm_count;
+    uint32_t warp_size;
+    uint32_t max_threads_per_block;
+    size_t max_shared_memory_bytes;
+    size_t total_memory_bytes;
+    size_t min_buffer_alignment;
+} b200_caps;
+
+/* Allocator and launch counters: the figures vkML's VulkanStats exposes
+ * (include/vkml/backend/vulkan/vulkan_backend.h:41-58). */
+typedef struct b200_stats {
+    uint64_t reserved_bytes;     /* held from the driver */
+    uint64_t in_use_bytes;       /* handed out and not yet freed */
+    uint64_t peak_in_use_bytes;
+    uint64_t live_allocations;
+    uint64_t total_allocations;
+    uint64_t driver_allocations; /* cudaMalloc calls: growth of the cache */
+    uint64_t compute_calls;      /* b200_compute calls (= submissions) */
+    uint64_t kernel_launches;    /* kernels launched by this library */
+    uint64_t nodes_computed;
+    uint64_t comm_bytes;         /* bytes all-reduced */
+} b200_stats;
+
+typedef struct b200_ctx b200_ctx;
+
+/* b200_compute flags */
+#define B200_COMPUTE_DEFAULT 0u
+#define B200_COMPUTE_SYNC 1u        /* synchronise before returning (eager mode, executor.cpp:134-144) */
+#define B200_COMPUTE_GRAD_SYNC 2u   /* all-reduce the span's gradient outputs listed by b200_dist_mark_grad */
+
+/* GEMM arithmetic: 3xTF32 split on the tensor cores (default), single-pass
+ * TF32 (explicit opt-in), or plain fp32 FMA on the CUDA cores. */
+typedef enum b200_gemm_precision {
+    B200_GEMM_3XTF32 = 0,
+    B200_GEMM_TF32 = 1,
+    B200_GEMM_FP32 = 2
+} b200_gemm_precision;
+
+/* -- lifetime: replaces vkml::vulkan_backend(index) (vulkan_backend.cpp:2991) -- */
+int b200_abi_version(void);
+int b200_device_count(int* count);
+int b200_create(int cuda_ordinal, b200_ctx** out);
+void b200_destroy(b200_ctx* ctx);
+
+/* Backend::capabilities() (backend.h:62). */
+int b200_get_caps(b200_ctx* ctx, b200_caps* out);
+
+/* Allocator::allocate / Storage deleter (allocator.h:44, storage.h:33).
+ * Thread-safe; memory is recycled in stream order, so a buffer may be freed
+ * while kernels that use it are still queued. nbytes == 0 yields *out = NULL. */
+int b200_alloc(b200_ctx* ctx, size_t nbytes, void** out);
+int b200_free(b200_ctx* ctx, void* ptr);
+/* Return every cached, unused block to the driver. */
+int b200_trim(b200_ctx* ctx);
+
+/* Backend::supports(const Node&) (backend.h:67). 1 = can evaluate, 0 = cannot. */
+int b200_supports(const b200_node* node);
+
+/* Backend::compute(span<Node* const>) (backend.h:79): evaluates the non-view,
+ * non-leaf nodes in order on the context's stream. Returns once the work is
+ * ordered, not finished, unless B200_COMPUTE_SYNC is set. */
+int b200_compute(b200_ctx* ctx, const b200_node* nodes, size_t n_nodes, uint32_t flags);
+
+/* Backend::copy_from_host / copy_to_host (backend.h:82-86). copy_to_host
+ * returns after the bytes are in `dst`. */
+int b200_copy_from_host(b200_ctx* ctx, void* dst_device, const void* src_host, size_t nbytes);
+int b200_copy_to_host(b200_ctx* ctx, void* dst_host, const void* src_device, size_t nbytes);
+
+/* Backend::copy_device_to_device(span<const BufferCopy>) (backend.h:108):
+ * disjoint ranges, one unit of work. */
+int b200_copy_device_to_device(b200_ctx* ctx, const b200_copy* copies, size_t n);
+
+/* Backend::synchronize() (backend.h:124). Also reports errors the device
+ * recorded since the last call (an out-of-range index in index_select /
+ * scatter_add -> B200_INDEX_ERROR; a bounded wait that ran out -> B200_TIMEOUT). */
+int b200_synchronize(b200_ctx* ctx);
+
+/* Text of the last error on this context (empty string if none). */
+const char* b200_last_error(b200_ctx* ctx);
+const char* b200_status_name(int status);
+
+int b200_get_stats(b200_ctx* ctx, b200_stats* out);
+
+/* Matmul kernel policy: replaces the VKML_GEMM_* switches
+ * (vulkan_backend.cpp:2160-2178). */
+int b200_set_gemm_precision(b200_ctx* ctx, int precision);
+int b200_get_gemm_precision(b200_ctx* ctx);
+
+/* The CUDA stream (cudaStream_t) every call on this context is ordered on, so
+ * a caller that owns other device work can order against it with events. */
+void* b200_stream(b200_ctx* ctx);
+
+/* -- data-parallel training (no counterpart in vkML, which is single-device:
+ *    src/dispatch/executor.cpp:96-103). One process per GPU. -- */
+#define B200_UNIQUE_ID_BYTES 128
+int b200_dist_unique_id(void* out_id /* B200_UNIQUE_ID_BYTES */);
+int b200_dist_init(b200_ctx* ctx, int rank, int world_size, const void* id);
+int b200_dist_destroy(b200_ctx* ctx);
+/* Average `count` f32 values in place across ranks on the communication
+ * stream; ordered after everything submitted so far and before everything
+ * submitted after b200_dist_wait. */
+int b200_dist_all_reduce_mean(b200_ctx* ctx, void* data, size_t count);
+int b200_dist_wait(b200_ctx* ctx);
+/* Register gradient buffers: a b200_compute call with B200_COMPUTE_GRAD_SYNC
+ * all-reduces each registered buffer as soon as the node that writes it has
+ * been launched, overlapping communication with the rest of the span. */
+int b200_dist_mark_grad(b200_ctx* ctx, void* data, size_t count);
+int b200_dist_clear_grads(b200_ctx* ctx);
+
+#ifdef __cplusplus
+}
+#endif
+
+#endif /* VKML_B200_H */

@@ -1,0 +1,458 @@
+"""Seeded op cases shared by the oracle-pinning tests (CPU) and the CUDA parity
+tests (GPU), with the tolerance each op is held to.
+
+The tolerance table restates vkML's own device-vs-CPU policy
+(tests/python/tolerance.py:89-278): EXACT for everything that moves bits,
+selects an element, or is one correctly-rounded IEEE operation; a ULP budget for
+the transcendental functions (libm on the CPU, CUDA's math library on the GPU);
+relative 1e-5 for softmax; a backward-error bound gamma*sum|terms| for sums,
+means and dot products whose summation ORDER differs between implementations.
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass, field
+
+import numpy as np
+
+from vkml_b200 import graph
+from vkml_b200.graph import DType, Op
+
+from helpers import ELEMENT_SIZES, layouts
+
+FP32_EPS = float(np.finfo(np.float32).eps)
+PAIRWISE_BLOCK = 32
+
+# kind, ulp, rtol, atol
+POLICY = {
+    "exact": ("exact", 0, 0, 0),
+    "div": ("ulp", 3, 0, 0), "sqrt": ("ulp", 3, 0, 0), "rsqrt": ("ulp", 3, 0, 0),
+    "reciprocal": ("ulp", 3, 0, 0), "exp": ("ulp", 8, 0, 0), "log": ("ulp", 4, 0, 2.0 ** -21),
+    "sin": ("ulp", 0, 0, 2.0 ** -11), "cos": ("ulp", 0, 0, 2.0 ** -11),
+    "erf": ("rel", 0, 1e-6, 1e-7), "erfc": ("rel", 0, 1e-5, 1e-7), "tanh": ("rel", 0, 1e-5, 1e-7),
+    "sigmoid": ("rel", 0, 1e-5, 1e-7), "gelu": ("rel", 0, 1e-5, 1e-7), "silu": ("rel", 0, 1e-5, 1e-7),
+    "pow": ("ulp", 16, 0, 0), "arange": ("ulp", 4, 0, 0),
+    "softmax": ("rel", 0, 1e-5, 1e-7), "log_softmax": ("rel", 0, 1e-5, 1e-5),
+    "sum": ("backward", 0, 0, 0), "mean": ("backward", 0, 0, 0), "matmul": ("backward", 0, 0, 0),
+}
+
+EXACT_OPS = {"full", "rand", "contiguous", "cast", "cat", "index_select", "im2col", "max_pool2d",
+             "max_pool2d_backward", "col2im", "scatter_add", "relu", "neg", "abs", "sign", "clamp",
+             "maximum", "minimum", "where", "triu", "tril", "equal", "less", "greater", "less_equal",
+             "greater_equal", "not_equal", "argmax", "argmin", "max", "min", "add", "sub", "mul",
+             "square", "scaled_add", "slice_backward"}
+
+
+def policy_for(op_name: str):
+    if op_name in EXACT_OPS:
+        return POLICY["exact"]
+    return POLICY[op_name]
+
+
+def ulp_distance(a, b):
+    ai = a.astype(np.float32).view(np.int32).astype(np.int64)
+    bi = b.astype(np.float32).view(np.int32).astype(np.int64)
+    ai = np.where(ai < 0, np.int64(0x80000000) - ai, ai)
+    bi = np.where(bi < 0, np.int64(0x80000000) - bi, bi)
+    return np.abs(ai - bi)
+
+
+def pairwise_gamma(n: int) -> float:
+    if n <= 1:
+        return 0.0
+    return (PAIRWISE_BLOCK + np.log2(max(n / PAIRWISE_BLOCK, 1.0))) * FP32_EPS
+
+
+@dataclass
+class Case:
+    name: str
+    op: int
+    srcs: list
+    out_shape: tuple
+    out_dtype: DType
+    params: bytes = b""
+    # for the backward-error bound: per-output sum|terms| and the term count
+    terms_abs_sum: object = None
+    reduction_n: int = 0
+
+    @property
+    def op_name(self) -> str:
+        return graph.op_name(self.op)
+
+
+def check(case: Case, got: np.ndarray, want: np.ndarray, exact_override: bool = False):
+    """Assert `got` matches `want` under the case's policy (or bit-exactly)."""
+    assert got.shape == want.shape, f"{case.name}: shape {got.shape} vs {want.shape}"
+    assert got.dtype == want.dtype, f"{case.name}: dtype {got.dtype} vs {want.dtype}"
+    if got.size == 0:
+        return
+    kind, ulp, rtol, atol = POLICY["exact"] if exact_override else policy_for(case.op_name)
+    floating = np.issubdtype(got.dtype, np.floating)
+    if floating:
+        nan_g, nan_w = np.isnan(got), np.isnan(want)
+        assert np.array_equal(nan_g, nan_w), f"{case.name}: NaN pattern differs"
+    if kind == "exact":
+        # value comparison, NaN placement checked above (vkML's EXACT policy)
+        bad = ((got != want) & ~nan_g) if floating else (got != want)
+    elif kind == "ulp":
+        diff = np.abs(got.astype(np.float64) - want.astype(np.float64))
+        bad = np.zeros(got.shape, dtype=bool)
+        with np.errstate(invalid="ignore"):
+            if ulp:
+                bad |= (ulp_distance(got, want) > ulp) & ~nan_g & (got != want)
+            else:
+                bad |= (got != want) & ~nan_g
+            if atol:
+                bad &= diff > atol
+    elif kind == "rel":
+        bad = ~np.isclose(got, want, rtol=rtol, atol=atol, equal_nan=True)
+    elif kind == "backward":
+        bound = pairwise_gamma(case.reduction_n) * np.asarray(case.terms_abs_sum, dtype=np.float64) * 4.0
+        with np.errstate(invalid="ignore"):
+            diff = np.abs(got.astype(np.float64) - want.astype(np.float64))
+        bad = (diff > np.broadcast_to(bound.reshape(got.shape) if np.ndim(bound) else bound, got.shape)) & ~nan_g
+        bad &= ~((got == want))
+    else:
+        raise AssertionError(kind)
+    if np.any(bad):
+        idx = np.argwhere(bad)[0]
+        raise AssertionError(
+            f"{case.name} [{kind}]: {int(bad.sum())}/{bad.size} elements differ; first at {tuple(idx)}: "
+            f"got {got[tuple(idx)]!r} want {want[tuple(idx)]!r}")
+
+
+# ---------------------------------------------------------------------------
+
+UNARY = ["neg", "abs", "sign", "square", "sqrt", "rsqrt", "reciprocal", "exp", "log", "erf", "erfc",
+         "sin", "cos", "tanh", "sigmoid", "relu", "gelu", "silu"]
+BINARY = ["add", "sub", "mul", "div", "pow", "maximum", "minimum"]
+COMPARE = ["equal", "less", "greater", "less_equal", "greater_equal", "not_equal"]
+
+
+def _unary_input(rng, name, shape):
+    x = rng.standard_normal(shape).astype(np.float32)
+    if name in ("sqrt", "rsqrt", "log"):
+        x = np.abs(x) + np.float32(0.05)
+    if name in ("exp", "sin", "cos"):
+        x = np.clip(x, -3, 3)
+    if name == "reciprocal":
+        x = np.where(np.abs(x) < 0.05, np.float32(0.5), x)
+    return x.astype(np.float32)
+
+
+def elementwise_cases(seed=1234, sizes=ELEMENT_SIZES, quick=False):
+    rng = np.random.default_rng(seed)
+    # dense 1-D at the block-edge sizes
+    for name in UNARY:
+        for n in (sizes if not quick else [257]):
+            yield Case(f"{name}/n={n}", Op[name.upper()], [_unary_input(rng, name, (n,))], (n,), DType.F32)
+    for name in BINARY:
+        for n in (sizes if not quick else [257]):
+            a = rng.standard_normal((n,)).astype(np.float32)
+            b = rng.standard_normal((n,)).astype(np.float32)
+            if name == "pow":
+                a = np.abs(a) + np.float32(0.1)
+            if name == "div":
+                b = np.where(np.abs(b) < 0.05, np.float32(0.5), b).astype(np.float32)
+            yield Case(f"{name}/n={n}", Op[name.upper()], [a, b], (n,), DType.F32)
+    for name in COMPARE:
+        n = 1000
+        a = rng.integers(-3, 4, n).astype(np.float32)
+        b = rng.integers(-3, 4, n).astype(np.float32)
+        a[::17] = np.nan
+        yield Case(f"{name}/n={n}", Op[name.upper()], [a, b], (n,), DType.BOOL)
+    # NaN rules
+    x = np.array([np.nan, -0.0, 0.0, 1.0, -1.0, np.inf, -np.inf, 1e-42, -1e-42], dtype=np.float32)
+    for name in ("relu", "sign", "neg", "abs", "square"):
+        yield Case(f"{name}/special", Op[name.upper()], [x], x.shape, DType.F32)
+    y = x[::-1].copy()
+    for name in ("maximum", "minimum", "add", "mul", "sub"):
+        yield Case(f"{name}/special", Op[name.upper()], [x, y], x.shape, DType.F32)
+    # layouts: every stride pattern, rank 2 and rank 4
+    for shape in [(33, 65), (3, 5, 17, 9), (64, 128), (255, 257)]:
+        for tag_a, a in layouts(rng, shape):
+            yield Case(f"relu/{shape}/{tag_a}", Op.RELU, [a], shape, DType.F32)
+            yield Case(f"contiguous/{shape}/{tag_a}", Op.CONTIGUOUS, [a], shape, DType.F32)
+            for tag_b, b in layouts(rng, shape):
+                yield Case(f"add/{shape}/{tag_a}+{tag_b}", Op.ADD, [a, b], shape, DType.F32)
+                yield Case(f"scaled_add/{shape}/{tag_a}+{tag_b}", Op.SCALED_ADD, [a, b], shape, DType.F32,
+                           graph.scaled_add_params(0.9, -0.1))
+    # broadcasts as stride-0 views: bias rows, columns, channels, scalars
+    a = rng.standard_normal((64, 128)).astype(np.float32)
+    row = np.broadcast_to(rng.standard_normal((128,)).astype(np.float32), (64, 128))
+    col = np.broadcast_to(rng.standard_normal((64, 1)).astype(np.float32), (64, 128))
+    scalar = np.broadcast_to(np.float32(0.25).reshape(()), (64, 128))
+    yield Case("add/row-broadcast", Op.ADD, [a, row], a.shape, DType.F32)
+    yield Case("mul/col-broadcast", Op.MUL, [a, col], a.shape, DType.F32)
+    yield Case("div/scalar-broadcast", Op.DIV, [a, scalar], a.shape, DType.F32)
+    yield Case("equal/both-broadcast", Op.EQUAL,
+               [np.broadcast_to(np.arange(64, dtype=np.float32).reshape(64, 1) % 10, (64, 10)),
+                np.broadcast_to(np.arange(10, dtype=np.float32).reshape(1, 10), (64, 10))], (64, 10), DType.BOOL)
+    img = rng.standard_normal((4, 8, 6, 6)).astype(np.float32)
+    chan = np.broadcast_to(rng.standard_normal((8, 1, 1)).astype(np.float32), (4, 8, 6, 6))
+    yield Case("add/channel-broadcast", Op.ADD, [img, chan], img.shape, DType.F32)
+    yield Case("contiguous/broadcast-materialise", Op.CONTIGUOUS,
+               [np.broadcast_to(np.float32(3.5).reshape(()), (64,))], (64,), DType.F32)
+    # where / clamp / scaled_add bit identity / tri
+    cond = (rng.random((64, 128)) < 0.5).astype(np.uint8)
+    b = rng.standard_normal((64, 128)).astype(np.float32)
+    yield Case("where/dense", Op.WHERE, [cond, a, b], a.shape, DType.F32)
+    yield Case("where/broadcast-zero", Op.WHERE, [cond, a, np.broadcast_to(np.float32(0).reshape(()), a.shape)],
+               a.shape, DType.F32)
+    yield Case("clamp/both", Op.CLAMP, [a], a.shape, DType.F32, graph.clamp_params(-0.5, 0.5))
+    yield Case("clamp/lo", Op.CLAMP, [a], a.shape, DType.F32, graph.clamp_params(0.0, None))
+    yield Case("clamp/hi", Op.CLAMP, [a], a.shape, DType.F32, graph.clamp_params(None, 0.0))
+    for d in (-2, 0, 1):
+        yield Case(f"triu/{d}", Op.TRIU, [a], a.shape, DType.F32, graph.tri_params(d))
+        yield Case(f"tril/{d}", Op.TRIL, [a], a.shape, DType.F32, graph.tri_params(d))
+    wt = np.ascontiguousarray(rng.standard_normal((784, 128)).astype(np.float32)).T  # [128,784] strides {1,128}
+    vt = np.ascontiguousarray(rng.standard_normal((784, 128)).astype(np.float32)).T
+    yield Case("scaled_add/transposed-grad", Op.SCALED_ADD, [vt, wt], (128, 784), DType.F32,
+               graph.scaled_add_params(0.9, 1.0))
+    p = rng.standard_normal((128, 784)).astype(np.float32)
+    yield Case("scaled_add/param-update", Op.SCALED_ADD, [p, wt], (128, 784), DType.F32,
+               graph.scaled_add_params(1.0, -0.1))
+
+
+def creation_cases():
+    for dt, v in [(DType.F32, 2.5), (DType.F32, 0.1), (DType.I64, 7.0), (DType.I32, -3.0),
+                  (DType.BOOL, 1.0), (DType.BOOL, 0.0), (DType.F16, 0.1)]:
+        for n in (0, 1, 257):
+            yield Case(f"full/{dt.name}/{v}/n={n}", Op.FULL, [], (n,), dt, graph.full_params(v))
+    yield Case("full/scalar", Op.FULL, [], (), DType.F32, graph.full_params(1.0))
+    yield Case("arange/f32", Op.ARANGE, [], (1000,), DType.F32, graph.arange_params(0.0, 1.0))
+    yield Case("arange/f32-frac", Op.ARANGE, [], (777,), DType.F32, graph.arange_params(-3.3, 0.37))
+    yield Case("arange/i64", Op.ARANGE, [], (100,), DType.I64, graph.arange_params(5.0, 3.0))
+    for seed, off, n in [(0, 0, 16), (20260728, 5, 1000), (2 ** 40 + 3, 2 ** 33, 257)]:
+        yield Case(f"rand/{seed}/{off}", Op.RAND, [], (n,), DType.F32, graph.rand_params(seed, off))
+
+
+def cast_cases(seed=7):
+    rng = np.random.default_rng(seed)
+    f = (rng.standard_normal(1000) * 100).astype(np.float32)
+    f[:4] = [0.0, -0.0, 0.5, -0.5]
+    i64 = rng.integers(-2 ** 40, 2 ** 40, 1000).astype(np.int64)
+    small_i64 = rng.integers(0, 1000, 1000).astype(np.int64)
+    i32 = rng.integers(-2 ** 31, 2 ** 31 - 1, 1000).astype(np.int32)
+    bl = (rng.random(1000) < 0.5).astype(np.uint8)
+    h = rng.standard_normal(1000).astype(np.float16)
+    f16src = np.concatenate([f / 100, np.array([65504, 65520, 1e30, 6e-8, 3e-8, 5.96e-8, 1e-10, np.inf, -np.inf,
+                                                np.nan, 6.1e-5, 6.0e-5, 1.0009765625, 1.00048828125],
+                                               dtype=np.float32)]).astype(np.float32)
+    yield Case("cast/f32->i32", Op.CAST, [f], f.shape, DType.I32)
+    yield Case("cast/f32->i64", Op.CAST, [f], f.shape, DType.I64)
+    yield Case("cast/f32->bool", Op.CAST, [f], f.shape, DType.BOOL)
+    yield Case("cast/f32->f16", Op.CAST, [f16src], f16src.shape, DType.F16)
+    yield Case("cast/f16->f32", Op.CAST, [h], h.shape, DType.F32)
+    yield Case("cast/i32->f32", Op.CAST, [i32], i32.shape, DType.F32)
+    yield Case("cast/i32->i64", Op.CAST, [i32], i32.shape, DType.I64)
+    yield Case("cast/i64->f32", Op.CAST, [i64], i64.shape, DType.F32)
+    yield Case("cast/labels->f32", Op.CAST, [small_i64], small_i64.shape, DType.F32)
+    yield Case("cast/i64->i32", Op.CAST, [small_i64], small_i64.shape, DType.I32)
+    yield Case("cast/bool->f32", Op.CAST, [bl], bl.shape, DType.F32)
+    yield Case("cast/bool->i64", Op.CAST, [bl], bl.shape, DType.I64)
+    yield Case("cast/f32->f32", Op.CAST, [f], f.shape, DType.F32)
+    m = rng.standard_normal((16, 24)).astype(np.float32)
+    yield Case("cast/f32->i64/transposed", Op.CAST, [np.ascontiguousarray(m.T).T], m.shape, DType.I64)
+
+
+def reduce_cases(seed=99, quick=False):
+    rng = np.random.default_rng(seed)
+
+    def mk(name, x, axes, keepdim=False, tag=""):
+        nd = x.ndim
+        axes_n = [a % nd for a in axes] if axes else list(range(nd))
+        out_shape = tuple((1 if i in axes_n else d) for i, d in enumerate(x.shape) if keepdim or i not in axes_n)
+        is_arg = name in ("argmax", "argmin")
+        n_red = int(np.prod([x.shape[a] for a in axes_n])) if axes_n else 1
+        tas = np.sum(np.abs(x.astype(np.float64)), axis=tuple(axes_n), keepdims=keepdim)
+        if name == "mean" and n_red:
+            tas = tas / n_red
+        return Case(f"{name}/{x.shape}/axes={axes}/{tag}", Op[name.upper()], [x], out_shape,
+                    DType.I64 if is_arg else DType.F32, graph.reduce_params(axes, nd, keepdim),
+                    terms_abs_sum=tas, reduction_n=n_red)
+
+    shapes = [((6,), [[]]), ((2, 3), [[], [0], [1], [-1]]), ((64, 10), [[1], [0]]), ((64, 128), [[0], [1], []]),
+              ((4, 8, 6, 6), [[0, 2, 3], [1], [3], [0]]), ((3, 5, 300), [[2], [0, 1]]),
+              ((1, 7, 40, 27), [[1]]), ((100000,), [[]]), ((2, 70000), [[1]]), ((9, 1031), [[1], [0]]),
+              ((3000, 33), [[0]])]
+    if quick:
+        shapes = shapes[:5]
+    for shape, axes_list in shapes:
+        for axes in axes_list:
+            for tag, x in layouts(rng, shape):
+                if tag in ("strided", "offset") and len(shape) == 1 and shape[0] > 1000:
+                    continue
+                for name in ("sum", "mean", "max", "min", "argmax", "argmin"):
+                    if name in ("argmax", "argmin") and len(axes) != 1:
+                        continue
+                    yield mk(name, x, axes, keepdim=False, tag=tag)
+            yield mk("sum", rng.standard_normal(shape).astype(np.float32), axes, keepdim=True, tag="keepdim")
+    # ties, NaN and infinities: first extremum, NaN rules
+    t = np.array([[1, 5, 5, 4], [2, 2, 1, 1], [np.nan, 3, 3, np.nan], [-np.inf, -np.inf, -np.inf, -np.inf],
+                  [np.nan, np.nan, np.nan, np.nan], [np.inf, 1, np.inf, 0]], dtype=np.float32)
+    for name in ("max", "min", "argmax", "argmin", "sum"):
+        yield mk(name, t, [1], tag="ties-nan")
+    wide = rng.integers(0, 4, (5, 5000)).astype(np.float32)  # many ties across lanes
+    for name in ("argmax", "argmin", "max", "min"):
+        yield mk(name, wide, [1], tag="many-ties")
+        yield mk(name, np.ascontiguousarray(wide.T), [0], tag="many-ties-col")
+    ones = np.ones((100000,), dtype=np.float32)
+    yield mk("sum", ones, [], tag="ones")
+    mixed = ones.copy()
+    mixed[0] = 1e7
+    yield mk("sum", mixed, [], tag="mixed-magnitude")
+    yield mk("sum", np.zeros((0, 5), dtype=np.float32), [0], tag="empty-reduced")
+    yield mk("mean", np.zeros((0, 5), dtype=np.float32), [0], tag="empty-reduced")
+    yield mk("max", np.zeros((0, 5), dtype=np.float32), [0], tag="empty-reduced")
+
+
+def softmax_cases(seed=5, quick=False):
+    rng = np.random.default_rng(seed)
+    shapes = [((64, 10), 1), ((256, 100), 1), ((7, 1000), 1), ((3, 4099), 1), ((2, 32000), 1), ((2, 50000), 1),
+              ((33, 65), 0), ((4, 8, 6, 6), 1), ((5, 300, 7), 1), ((3,), 0), ((512, 33), 1)]
+    if quick:
+        shapes = shapes[:4]
+    for shape, axis in shapes:
+        for tag, x in layouts(rng, shape, scale=2.0):
+            if tag != "dense" and np.prod(shape) > 200000:
+                continue
+            for name in ("softmax", "log_softmax"):
+                yield Case(f"{name}/{shape}/axis={axis}/{tag}", Op[name.upper()], [x], shape, DType.F32,
+                           graph.axis_params(axis))
+    for vals in ([1000.0, 1001.0, 1002.0], [0.0, -200.0, -400.0], [-1e30, 0.0, 1e30],
+                 [np.nan, 1.0, 2.0], [-np.inf, -np.inf, -np.inf], [np.inf, 1.0, 2.0], [88.0, 89.0, -104.0]):
+        x = np.array([vals], dtype=np.float32)
+        for name in ("softmax", "log_softmax"):
+            yield Case(f"{name}/extreme/{vals}", Op[name.upper()], [x], x.shape, DType.F32, graph.axis_params(1))
+    big = np.full((2, 2000), 1000.0, dtype=np.float32)
+    big[:, ::7] = 1002.0
+    yield Case("softmax/large-logits-wide", Op.SOFTMAX, [big], big.shape, DType.F32, graph.axis_params(1))
+
+
+def matmul_cases(seed=11, quick=False):
+    rng = np.random.default_rng(seed)
+
+    def mk(tag, a, b):
+        a4 = a.reshape((1,) * (4 - a.ndim) + a.shape) if a.ndim < 4 else a
+        b4 = b.reshape((1,) * (4 - b.ndim) + b.shape) if b.ndim < 4 else b
+        bshape = np.broadcast_shapes(a4.shape[:2], b4.shape[:2])
+        a4 = np.broadcast_to(a4, bshape + a4.shape[2:])
+        b4 = np.broadcast_to(b4, bshape + b4.shape[2:])
+        m, k, n = a4.shape[2], a4.shape[3], b4.shape[3]
+        tas = np.abs(a4.astype(np.float64)) @ np.abs(b4.astype(np.float64))
+        return Case(f"matmul/{tag}/{m}x{k}x{n}/batch={bshape}", Op.MATMUL, [a4, b4], bshape + (m, n), DType.F32,
+                    terms_abs_sum=tas, reduction_n=k)
+
+    def rnd(*shape):
+        return rng.standard_normal(shape).astype(np.float32)
+
+    yield mk("known", np.array([[1, 2, 3], [4, 5, 6]], np.float32), np.array([[7, 8], [9, 10], [11, 12]], np.float32))
+    edge = [1, 2, 15, 16, 17, 31, 32, 33, 63, 64, 65, 127, 128, 129, 255, 257]
+    if quick:
+        edge = [1, 17, 33, 64, 129]
+    for s in edge:
+        yield mk("square", rnd(s, s), rnd(s, s))
+    for m, k, n in [(1, 1, 1), (31, 33, 31), (33, 31, 33), (64, 784, 128), (64, 128, 10), (64, 10, 128),
+                    (784, 64, 128), (128, 64, 10), (5, 1000, 3), (130, 70, 260), (64, 4096, 64), (3, 2500, 200)]:
+        yield mk("nn", rnd(m, k), rnd(k, n))
+        yield mk("nt", rnd(m, k), np.ascontiguousarray(rnd(n, k)).T)
+        yield mk("tn", np.ascontiguousarray(rnd(k, m)).T, rnd(k, n))
+        if not quick:
+            yield mk("tt", np.ascontiguousarray(rnd(k, m)).T, np.ascontiguousarray(rnd(n, k)).T)
+    # batched: weights broadcast over the batch (conv forward), per-sample dW, sliced operand
+    yield mk("conv-fwd", rnd(1, 1, 16, 27), rnd(1, 6, 27, 64))
+    yield mk("conv-dw", rnd(1, 6, 16, 64), np.ascontiguousarray(rnd(1, 6, 27, 64)).transpose(0, 1, 3, 2))
+    yield mk("conv-dcols", np.broadcast_to(np.ascontiguousarray(rnd(16, 27)).T.reshape(1, 1, 27, 16), (1, 6, 27, 16)),
+             rnd(1, 6, 16, 64))
+    yield mk("batch2", rnd(2, 3, 20, 30), rnd(2, 3, 30, 10))
+    yield mk("batch-bcast-b", rnd(2, 2, 2, 2), np.eye(2, dtype=np.float32).reshape(1, 1, 2, 2))
+    big = rnd(40, 100)
+    yield mk("sliced", big[3:35, 10:74:2], rnd(32, 50))
+    yield mk("empty-k", np.zeros((4, 0), np.float32), np.zeros((0, 5), np.float32))
+    yield mk("empty-m", np.zeros((0, 4), np.float32), rnd(4, 5))
+
+
+def movement_cases(seed=21, quick=False):
+    rng = np.random.default_rng(seed)
+
+    def unfold(n, c, h, w, k, s, p, d):
+        oh = (h + 2 * p[0] - (d[0] * (k[0] - 1) + 1)) // s[0] + 1
+        ow = (w + 2 * p[1] - (d[1] * (k[1] - 1) + 1)) // s[1] + 1
+        return oh, ow, graph.unfold_params(k, s, p, d, (h, w))
+
+    geos = [(2, 3, 8, 8, (3, 3), (1, 1), (1, 1), (1, 1)), (2, 4, 9, 7, (3, 2), (2, 1), (1, 0), (1, 1)),
+            (1, 2, 10, 10, (3, 3), (1, 1), (2, 2), (2, 2)), (3, 1, 5, 5, (1, 1), (1, 1), (0, 0), (1, 1)),
+            (2, 3, 6, 6, (2, 2), (2, 2), (0, 0), (1, 1)), (4, 3, 32, 32, (3, 3), (1, 1), (1, 1), (1, 1))]
+    if quick:
+        geos = geos[:3]
+    for n, c, h, w, k, s, p, d in geos:
+        oh, ow, params = unfold(n, c, h, w, k, s, p, d)
+        for tag, x in layouts(rng, (n, c, h, w)):
+            yield Case(f"im2col/{(n, c, h, w)}/k={k}s={s}p={p}d={d}/{tag}", Op.IM2COL, [x],
+                       (n, c * k[0] * k[1], oh * ow), DType.F32, params)
+        for tag, cols in layouts(rng, (n, c * k[0] * k[1], oh * ow)):
+            yield Case(f"col2im/{(n, c, h, w)}/k={k}s={s}p={p}d={d}/{tag}", Op.COL2IM, [cols], (n, c, h, w),
+                       DType.F32, params)
+    pools = [(2, 3, 8, 8, (2, 2), (2, 2), (0, 0), (1, 1)), (2, 2, 9, 9, (3, 3), (2, 2), (1, 1), (1, 1)),
+             (1, 4, 7, 6, (3, 2), (1, 1), (1, 1), (1, 1)), (4, 8, 32, 32, (2, 2), (2, 2), (0, 0), (1, 1))]
+    for n, c, h, w, k, s, p, d in pools:
+        oh, ow, params = unfold(n, c, h, w, k, s, p, d)
+        x = rng.integers(0, 5, (n, c, h, w)).astype(np.float32)  # many ties: first-max rule matters
+        g = rng.standard_normal((n, c, oh, ow)).astype(np.float32)
+        for tag, xv in layouts(rng, (n, c, h, w)):
+            xv[...] = x
+            yield Case(f"max_pool2d/{(n, c, h, w)}/k={k}s={s}p={p}/{tag}", Op.MAX_POOL2D, [xv], (n, c, oh, ow),
+                       DType.F32, params)
+        yield Case(f"max_pool2d_backward/{(n, c, h, w)}/k={k}s={s}p={p}", Op.MAX_POOL2D_BACKWARD, [g, x],
+                   (n, c, h, w), DType.F32, params)
+        xr = rng.standard_normal((n, c, h, w)).astype(np.float32)
+        yield Case(f"max_pool2d_backward/random/{(n, c, h, w)}/k={k}", Op.MAX_POOL2D_BACKWARD, [g, xr],
+                   (n, c, h, w), DType.F32, params)
+    # index_select / scatter_add: every axis, duplicates, strided index
+    table = rng.standard_normal((50, 16)).astype(np.float32)
+    idx = rng.integers(0, 50, 200).astype(np.int64)
+    yield Case("index_select/rows", Op.INDEX_SELECT, [table, idx], (200, 16), DType.F32, graph.axis_params(0))
+    idx_c = rng.integers(0, 16, 9).astype(np.int64)
+    yield Case("index_select/cols", Op.INDEX_SELECT, [table, idx_c], (50, 9), DType.F32, graph.axis_params(1))
+    yield Case("index_select/strided-index", Op.INDEX_SELECT, [table, np.repeat(idx, 2)[::2]], (200, 16), DType.F32,
+               graph.axis_params(0))
+    t3 = rng.standard_normal((4, 10, 6)).astype(np.float32)
+    idx3 = rng.integers(0, 10, 7).astype(np.int64)
+    yield Case("index_select/middle", Op.INDEX_SELECT, [t3, idx3], (4, 7, 6), DType.F32, graph.axis_params(1))
+    yield Case("index_select/transposed", Op.INDEX_SELECT, [np.ascontiguousarray(table.T).T, idx], (200, 16),
+               DType.F32, graph.axis_params(0))
+    yield Case("index_select/i64-values", Op.INDEX_SELECT, [np.arange(50, dtype=np.int64) * 3, idx], (200,),
+               DType.I64, graph.axis_params(0))
+    src = rng.standard_normal((200, 16)).astype(np.float32)
+    yield Case("scatter_add/rows", Op.SCATTER_ADD, [src, idx], (50, 16), DType.F32, graph.axis_params(0))
+    dup = np.zeros(200, dtype=np.int64)  # every source into one destination: order-sensitive sum
+    yield Case("scatter_add/all-duplicates", Op.SCATTER_ADD, [src * 1e3, dup], (3, 16), DType.F32,
+               graph.axis_params(0))
+    src3 = rng.standard_normal((4, 7, 6)).astype(np.float32)
+    yield Case("scatter_add/middle", Op.SCATTER_ADD, [src3, idx3], (4, 10, 6), DType.F32, graph.axis_params(1))
+    yield Case("scatter_add/empty", Op.SCATTER_ADD, [np.zeros((0, 16), np.float32), np.zeros((0,), np.int64)],
+               (5, 16), DType.F32, graph.axis_params(0))
+    # cat / slice_backward
+    a = rng.standard_normal((3, 4, 5)).astype(np.float32)
+    for axis, other in [(0, (2, 4, 5)), (1, (3, 6, 5)), (2, (3, 4, 1))]:
+        b = rng.standard_normal(other).astype(np.float32)
+        out = list(a.shape)
+        out[axis] += other[axis]
+        yield Case(f"cat/axis={axis}", Op.CAT, [a, b], tuple(out), DType.F32, graph.axis_params(axis))
+    yield Case("cat/transposed", Op.CAT, [np.ascontiguousarray(a.transpose(0, 2, 1)).transpose(0, 2, 1), a], (6, 4, 5),
+               DType.F32, graph.axis_params(0))
+    g = rng.standard_normal((3, 4, 5)).astype(np.float32)
+    yield Case("slice_backward/axis1", Op.SLICE_BACKWARD, [g], (3, 11, 5), DType.F32, graph.slice_params(1, 2, 10, 2))
+    yield Case("slice_backward/axis0", Op.SLICE_BACKWARD, [g], (5, 4, 5), DType.F32, graph.slice_params(0, 1, 4, 1))
+    yield Case("slice_backward/axis2-strided-g", Op.SLICE_BACKWARD, [np.ascontiguousarray(g.transpose(0, 2, 1)).transpose(0, 2, 1)],
+               (3, 4, 15), DType.F32, graph.slice_params(2, 0, 15, 3))
+
+
+def all_cases(quick=False):
+    yield from elementwise_cases(quick=quick)
+    yield from creation_cases()
+    yield from cast_cases()
+    yield from reduce_cases(quick=quick)
+    yield from softmax_cases(quick=quick)
+    yield from matmul_cases(quick=quick)
+    yield from movement_cases(quick=quick)

@@ -1,0 +1,222 @@
+"""CUDA path vs the CPU oracle on identical seeded inputs, through the C ABI.
+
+Integer, index and ordering ops are compared bit-exactly; floating ops under the
+tolerance vkML itself applies between its GPU and CPU backends (tests/cases.py).
+"""
+import json
+import os
+
+import numpy as np
+import pytest
+
+import cases
+from helpers import CudaImpl, OracleImpl
+from vkml_b200 import graph
+from vkml_b200.graph import DType, Op
+
+pytestmark = pytest.mark.gpu
+
+GOLDEN = os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden")
+
+
+@pytest.fixture(scope="module")
+def oracle():
+    return OracleImpl()
+
+
+@pytest.fixture(scope="module")
+def cuda(backend):
+    return CudaImpl(backend)
+
+
+def _run_family(gen, cuda, oracle, backend):
+    n = 0
+    failures = []
+    for case in gen:
+        want = oracle.run(case.op, case.srcs, case.out_shape, case.out_dtype, case.params)
+        got = cuda.run(case.op, case.srcs, case.out_shape, case.out_dtype, case.params, sync_check=False)
+        try:
+            cases.check(case, got, want)
+        except AssertionError as e:
+            failures.append(str(e))
+        n += 1
+    backend.synchronize()
+    assert not failures, f"{len(failures)}/{n} cases failed:\n" + "\n".join(failures[:20])
+    return n
+
+
+def test_elementwise(cuda, oracle, backend):
+    assert _run_family(cases.elementwise_cases(), cuda, oracle, backend) > 400
+
+
+def test_creation(cuda, oracle, backend):
+    assert _run_family(cases.creation_cases(), cuda, oracle, backend) > 20
+
+
+def test_cast(cuda, oracle, backend):
+    assert _run_family(cases.cast_cases(), cuda, oracle, backend) >= 14
+
+
+def test_reduce(cuda, oracle, backend):
+    assert _run_family(cases.reduce_cases(), cuda, oracle, backend) > 300
+
+
+def test_softmax(cuda, oracle, backend):
+    assert _run_family(cases.softmax_cases(), cuda, oracle, backend) > 60
+
+
+def test_matmul_fp32(cuda, oracle, backend):
+    backend.set_gemm_precision(2)
+    try:
+        assert _run_family(cases.matmul_cases(), cuda, oracle, backend) > 60
+    finally:
+        backend.set_gemm_precision(0)
+
+
+def test_matmul_default_precision(cuda, oracle, backend):
+    """3xTF32 on the tensor cores where the shape is eligible, fp32 FMA elsewhere:
+    both inside the backward-error bound of the fp32 dot product."""
+    assert _run_family(cases.matmul_cases(), cuda, oracle, backend) > 60
+
+
+def test_movement(cuda, oracle, backend):
+    assert _run_family(cases.movement_cases(), cuda, oracle, backend) > 80
+
+
+def test_golden_fixtures(cuda, backend):
+    """Committed outputs of the reference CPU build: the GPU agrees with the
+    reference itself, not only with the restatement."""
+    data = np.load(os.path.join(GOLDEN, "reference_outputs.npz"))
+    names = json.loads(str(data["__index__"]))
+    by_name = {c.name: c for c in cases.all_cases(quick=True)}
+    for i, name in enumerate(names):
+        case = by_name[name]
+        if case.op == Op.PROD:
+            continue
+        got = cuda.run(case.op, case.srcs, case.out_shape, case.out_dtype, case.params, sync_check=False)
+        cases.check(case, got, data[f"out_{i}"])
+    backend.synchronize()
+
+
+def test_known_answers(cuda, backend):
+    from test_oracle import _params
+    with open(os.path.join(GOLDEN, "known_answers.json")) as f:
+        table = json.load(f)
+    for spec in table:
+        if spec["op"] == "prod":
+            continue
+        srcs = []
+        for s in spec["srcs"]:
+            if s.get("values") is None:
+                a = np.full(s["shape"], s["fill"], dtype=np.float32)
+                a.reshape(-1)[0] = s.get("first", s["fill"])
+            else:
+                a = np.array(s["values"], dtype=DType[s.get("dtype", "F32")].numpy).reshape(s["shape"])
+            if s.get("transpose"):
+                a = np.ascontiguousarray(a).T
+            if "broadcast" in s:
+                a = np.broadcast_to(a, s["broadcast"])
+            srcs.append(a)
+        out_dt = DType[spec.get("out_dtype", "F32")]
+        got = cuda.run(Op[spec["op"].upper()], srcs, tuple(spec["out_shape"]), out_dt, _params(spec))
+        want = np.array(spec["want"], dtype=out_dt.numpy).reshape(spec["out_shape"])
+        np.testing.assert_allclose(got, want, rtol=spec.get("rtol", 1e-6), atol=spec.get("atol", 0),
+                                   err_msg=spec["name"])
+
+
+def test_out_of_range_index_is_reported(cuda, backend):
+    """The CPU backend throws IndexError (kernels_movement.cpp:362,419); the device
+    clamps, records it, and the next synchronize reports an index error."""
+    table = np.arange(12, dtype=np.float32).reshape(4, 3)
+    idx = np.array([0, 4], dtype=np.int64)
+    cuda.run(Op.INDEX_SELECT, [table, idx], (2, 3), DType.F32, graph.axis_params(0), sync_check=False)
+    with pytest.raises(IndexError):
+        backend.synchronize()
+    backend.synchronize()  # the word is cleared: the context stays usable
+    cuda.run(Op.SCATTER_ADD, [table[:2], np.array([0, -1], dtype=np.int64)], (4, 3), DType.F32,
+             graph.axis_params(0), sync_check=False)
+    with pytest.raises(IndexError):
+        backend.synchronize()
+    got = cuda.run(Op.INDEX_SELECT, [table, np.array([3, 0], dtype=np.int64)], (2, 3), DType.F32,
+                   graph.axis_params(0))
+    np.testing.assert_array_equal(got, table[[3, 0]])
+
+
+def test_repeated_execution_is_byte_identical(cuda, backend):
+    rng = np.random.default_rng(0)
+    x = rng.standard_normal((300, 5000)).astype(np.float32)
+    p = graph.reduce_params([1], 2)
+    a = cuda.run(Op.SUM, [x], (300,), DType.F32, p)
+    for _ in range(3):
+        assert np.array_equal(a.view(np.uint32), cuda.run(Op.SUM, [x], (300,), DType.F32, p).view(np.uint32))
+    a2 = np.ascontiguousarray(rng.standard_normal((64, 512)).astype(np.float32))
+    b2 = np.ascontiguousarray(rng.standard_normal((512, 96)).astype(np.float32))
+    m = cuda.run(Op.MATMUL, [a2.reshape(1, 1, 64, 512), b2.reshape(1, 1, 512, 96)], (1, 1, 64, 96), DType.F32)
+    for _ in range(3):
+        again = cuda.run(Op.MATMUL, [a2.reshape(1, 1, 64, 512), b2.reshape(1, 1, 512, 96)], (1, 1, 64, 96), DType.F32)
+        assert np.array_equal(m.view(np.uint32), again.view(np.uint32))
+
+
+def test_scaled_add_is_bit_identical_to_the_composed_form(cuda, backend):
+    rng = np.random.default_rng(1)
+    a = rng.standard_normal(100_001).astype(np.float32)
+    b = rng.standard_normal(100_001).astype(np.float32)
+    alpha, beta = np.float32(0.9), np.float32(-0.1)
+    fused = cuda.run(Op.SCALED_ADD, [a, b], a.shape, DType.F32, graph.scaled_add_params(alpha, beta))
+    al = np.broadcast_to(alpha.reshape(()), a.shape)
+    be = np.broadcast_to(beta.reshape(()), a.shape)
+    pa = cuda.run(Op.MUL, [a, al], a.shape, DType.F32)
+    pb = cuda.run(Op.MUL, [b, be], a.shape, DType.F32)
+    composed = cuda.run(Op.ADD, [pa, pb], a.shape, DType.F32)
+    assert np.array_equal(fused.view(np.uint32), composed.view(np.uint32))
+    assert np.array_equal(fused.view(np.uint32), (a * alpha + b * beta).view(np.uint32))
+
+
+def test_a_span_is_ordered(backend):
+    """RAW and WAR hazards inside one compute() span: later nodes read what earlier
+    nodes wrote, and a buffer freed mid-span and handed out again is not clobbered
+    (the checks of vkML's tests/cpp/test_aliasing.cpp, on the stream model)."""
+    import vkml_b200 as V
+    from vkml_b200 import DeviceTensor, NodeDesc
+    n = 1 << 20
+    x = np.arange(n, dtype=np.float32)
+    tx = DeviceTensor.from_host(backend, x)
+    t1 = DeviceTensor.empty(backend, (n,))
+    t2 = DeviceTensor.empty(backend, (n,))
+    t3 = DeviceTensor.empty(backend, (n,))
+    span = [NodeDesc(Op.ADD, t1.desc, [tx.desc, tx.desc]),      # t1 = 2x
+            NodeDesc(Op.MUL, t2.desc, [t1.desc, t1.desc]),      # t2 = 4x^2   (RAW on t1)
+            NodeDesc(Op.NEG, t1.desc, [tx.desc]),               # t1 = -x     (WAR on t1)
+            NodeDesc(Op.ADD, t3.desc, [t1.desc, t2.desc])]      # t3 = 4x^2 - x
+    backend.compute(span)
+    want = (x + x) * (x + x) + (-x)
+    np.testing.assert_array_equal(t3.numpy(), want)
+    # free a buffer while its consumer is queued, reallocate, overwrite
+    t4 = DeviceTensor.empty(backend, (n,))
+    backend.compute([NodeDesc(Op.RELU, t4.desc, [t3.desc])])
+    addr = t3.storage.data
+    del t3
+    t5 = DeviceTensor.empty(backend, (n,))
+    backend.compute([NodeDesc(Op.FULL, t5.desc, [], graph.full_params(-7.0))])
+    np.testing.assert_array_equal(t4.numpy(), np.maximum(want, 0))
+    assert t5.storage.data == addr  # the cache really did hand the block out again
+    st = backend.stats()
+    assert st["kernel_launches"] > 0 and st["compute_calls"] > 0
+
+
+def test_device_copies(backend):
+    from vkml_b200 import DeviceTensor
+    rng = np.random.default_rng(4)
+    a = rng.standard_normal(1000).astype(np.float32)
+    ta = DeviceTensor.from_host(backend, a)
+    tb = DeviceTensor.empty(backend, (1000,))
+    tc = DeviceTensor.empty(backend, (500,))
+    backend.copy_device_to_device([(tb.storage, 0, ta.storage, 0, 4000), (tc.storage, 0, ta.storage, 2000, 2000)])
+    np.testing.assert_array_equal(tb.numpy(), a)
+    np.testing.assert_array_equal(tc.numpy(), a[500:])
+    with pytest.raises(IndexError):
+        backend.copy_device_to_device([(tc.storage, 0, ta.storage, 0, 4000)])
+    with pytest.raises(IndexError):
+        backend.copy_from_host(tc.storage, 1999, a)
+    z = backend.allocate(0)
+    assert z.data == 0 and z.nbytes == 0

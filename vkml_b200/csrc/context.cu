@@ -1,0 +1,579 @@
+// C-ABI entry points, the caching allocator and the per-node dispatch.
+#include "context.h"
+#include "gemm.h"
+
+#include <algorithm>
+#include <new>
+
+namespace b200 {
+
+void check_last_launch(const char* what) {
+    const cudaError_t err = cudaPeekAtLastError();
+    if (err != cudaSuccess) {
+        cudaGetLastError();  // clear the sticky launch error so the context stays usable
+        fail(B200_DEVICE_ERROR, std::string(what) + ": launch failed: " + cudaGetErrorString(err));
+    }
+}
+
+// ---------------------------------------------------------------------------
+// CachingAllocator
+// ---------------------------------------------------------------------------
+
+size_t CachingAllocator::round_size(size_t n) {
+    // 512-byte classes up to 1 MiB, 2 MiB classes above: a freed activation
+    // buffer is then reusable by the next step's buffer of the same shape, and
+    // near-equal shapes share a class.
+    if (n <= (size_t(1) << 20)) {
+        return (n + 511) & ~size_t(511);
+    }
+    const size_t mb2 = size_t(2) << 20;
+    return (n + mb2 - 1) / mb2 * mb2;
+}
+
+void* CachingAllocator::allocate(size_t nbytes) {
+    if (nbytes == 0) {
+        return nullptr;
+    }
+    const size_t size = round_size(nbytes);
+    std::lock_guard<std::mutex> lock(mu_);
+    void* ptr = nullptr;
+    auto it = free_.lower_bound(size);
+    // accept a cached block up to 25 % larger than needed
+    if (it != free_.end() && it->first <= size + size / 4) {
+        ptr = it->second;
+        free_.erase(it);
+    } else {
+        cudaError_t err = cudaMalloc(&ptr, size);
+        if (err != cudaSuccess) {
+            // give the cache back to the driver and try once more
+            cudaGetLastError();
+            for (auto& kv : free_) {
+                cudaFree(kv.second);
+                reserved -= kv.first;
+                sizes_.erase(kv.second);
+            }
+            free_.clear();
+            err = cudaMalloc(&ptr, size);
+            if (err != cudaSuccess) {
+                cudaGetLastError();
+                fail(B200_OUT_OF_MEMORY, "device allocation of " + std::to_string(size) +
+                                             " bytes failed: " + cudaGetErrorString(err));
+            }
+        }
+        sizes_[ptr] = size;
+        reserved += size;
+        ++driver_allocs;
+    }
+    const size_t got = sizes_[ptr];
+    live_[ptr] = got;
+    in_use += got;
+    peak = std::max(peak, in_use);
+    ++live;
+    ++total;
+    return ptr;
+}
+
+void CachingAllocator::release(void* ptr) {
+    if (ptr == nullptr) {
+        return;
+    }
+    std::lock_guard<std::mutex> lock(mu_);
+    auto it = live_.find(ptr);
+    if (it == live_.end()) {
+        fail(B200_INVALID_ARGUMENT, "b200_free: pointer was not allocated by this context");
+    }
+    in_use -= it->second;
+    --live;
+    free_.emplace(it->second, ptr);
+    live_.erase(it);
+}
+
+void CachingAllocator::trim() {
+    std::lock_guard<std::mutex> lock(mu_);
+    for (auto& kv : free_) {
+        cudaFree(kv.second);
+        reserved -= kv.first;
+        sizes_.erase(kv.second);
+    }
+    free_.clear();
+}
+
+CachingAllocator::~CachingAllocator() {
+    for (auto& kv : sizes_) {
+        cudaFree(kv.first);
+    }
+}
+
+// ---------------------------------------------------------------------------
+// supports / dispatch
+// ---------------------------------------------------------------------------
+
+namespace {
+
+bool is_view_or_leaf(uint32_t op) {
+    return op == B200_OP_INPUT || op == B200_OP_CONST ||
+           (op >= B200_OP_RESHAPE && op <= B200_OP_UNSQUEEZE);
+}
+
+bool dense(const b200_tensor& t) {
+    int64_t numel = 1;
+    for (int i = 0; i < t.ndim; ++i) numel *= t.dims[i];
+    if (numel == 0) return true;
+    int64_t expected = static_cast<int64_t>(dtype_size(t.dtype));
+    for (int i = t.ndim - 1; i >= 0; --i) {
+        if (t.dims[i] == 1) continue;
+        if (t.strides[i] != expected) return false;
+        expected *= t.dims[i];
+    }
+    return true;
+}
+
+bool srcs_f32(const b200_node& n, int count) {
+    if (static_cast<int>(n.n_src) < count) return false;
+    for (int i = 0; i < count; ++i) {
+        if (n.src[i].dtype != B200_F32) return false;
+    }
+    return true;
+}
+
+bool cast_pair_ok(int from, int to) {
+    if (from == to) return true;
+    switch (from) {
+        case B200_F32: return to == B200_I32 || to == B200_I64 || to == B200_BOOL || to == B200_F16;
+        case B200_F16: return to == B200_F32;
+        case B200_I32: return to == B200_F32 || to == B200_I64;
+        case B200_I64: return to == B200_F32 || to == B200_I32;
+        case B200_BOOL: return to == B200_F32 || to == B200_I64;
+        default: return false;
+    }
+}
+
+void dispatch_matmul(b200_ctx* ctx, const b200_node& node) {
+    const View out = make_view(node.out);
+    const View a = make_view(node.src[0]);
+    const View b = make_view(node.src[1]);
+    if (node.out.ndim != 4 || node.src[0].ndim != 4 || node.src[1].ndim != 4) {
+        fail(B200_SHAPE_ERROR, "matmul expects rank-4 operands");
+    }
+    if (out.dtype != B200_F32 || a.dtype != B200_F32 || b.dtype != B200_F32) {
+        fail(B200_DTYPE_ERROR, "matmul: only f32 is implemented");
+    }
+    if (!out.contiguous) {
+        fail(B200_NOT_IMPLEMENTED, "matmul output must be contiguous");
+    }
+    GemmProblem p{};
+    p.a = reinterpret_cast<const float*>(a.data);
+    p.b = reinterpret_cast<const float*>(b.data);
+    p.out = reinterpret_cast<float*>(out.data);
+    p.b0 = out.dim[0];
+    p.b1 = out.dim[1];
+    p.m = out.dim[2];
+    p.n = out.dim[3];
+    p.k = a.dim[3];
+    if (b.dim[2] != p.k || a.dim[2] != p.m || b.dim[3] != p.n || a.dim[0] != p.b0 ||
+        a.dim[1] != p.b1 || b.dim[0] != p.b0 || b.dim[1] != p.b1) {
+        fail(B200_SHAPE_ERROR, "matmul: operand extents disagree");
+    }
+    for (int i = 0; i < 4; ++i) {
+        p.a_s[i] = a.stride[i];
+        p.b_s[i] = b.stride[i];
+    }
+    if (ctx->gemm_precision != B200_GEMM_FP32 && gemm_tc_eligible(ctx, p)) {
+        gemm_tc(ctx, p, ctx->gemm_precision == B200_GEMM_3XTF32);
+    } else {
+        gemm_simt(ctx, p);
+    }
+}
+
+void dispatch_node(b200_ctx* ctx, const b200_node& node) {
+    const uint32_t op = node.op;
+    if (op == B200_OP_MATMUL) {
+        dispatch_matmul(ctx, node);
+    } else if (op == B200_OP_SOFTMAX || op == B200_OP_LOG_SOFTMAX) {
+        launch_softmax(ctx, node);
+    } else if (op >= B200_OP_SUM && op <= B200_OP_ARGMIN) {
+        if (op == B200_OP_PROD) {
+            fail(B200_NOT_IMPLEMENTED, "prod is not implemented on this backend");
+        }
+        launch_reduce(ctx, node);
+    } else if (op == B200_OP_IM2COL || op == B200_OP_COL2IM || op == B200_OP_MAX_POOL2D ||
+               op == B200_OP_MAX_POOL2D_BACKWARD || op == B200_OP_INDEX_SELECT ||
+               op == B200_OP_SCATTER_ADD) {
+        launch_movement(ctx, node);
+    } else {
+        launch_elementwise(ctx, node);
+    }
+}
+
+void set_error(b200_ctx* ctx, const std::string& msg) {
+    if (ctx == nullptr) return;
+    std::lock_guard<std::mutex> lock(ctx->err_mu);
+    ctx->last_error = msg;
+}
+
+// Runs `fn`, converting Error / bad_alloc into a status code and message.
+template <typename Fn>
+int guarded(b200_ctx* ctx, Fn&& fn) {
+    try {
+        if (ctx != nullptr) {
+            cudaError_t err = cudaSetDevice(ctx->device);
+            if (err != cudaSuccess) {
+                set_error(ctx, std::string("cudaSetDevice: ") + cudaGetErrorString(err));
+                return B200_DEVICE_ERROR;
+            }
+        }
+        fn();
+        return B200_OK;
+    } catch (const Error& e) {
+        set_error(ctx, e.message);
+        return e.status;
+    } catch (const std::bad_alloc&) {
+        set_error(ctx, "host allocation failed");
+        return B200_OUT_OF_MEMORY;
+    } catch (const std::exception& e) {
+        set_error(ctx, e.what());
+        return B200_INTERNAL_ERROR;
+    }
+}
+
+}  // namespace
+
+// Mirrors VulkanBackend::supports (src/backend/vulkan/vulkan_backend.cpp:1012-1187)
+// for f32; f16 appears only as a cast endpoint.  Honest rather than optimistic:
+// a false here becomes NotImplementedError at realize, there is no fallback.
+bool supports_node(const b200_node& n) {
+    const uint32_t op = n.op;
+    if (is_view_or_leaf(op)) return true;
+    if (op >= B200_OP_COUNT) return false;
+    if (n.n_src > B200_MAX_SRC) return false;
+    if (!dense(n.out)) return false;
+    const int dt = n.out.dtype;
+    switch (op) {
+        case B200_OP_FULL: return dt == B200_F32 || dt == B200_F16 || dt == B200_I64 || dt == B200_I32 || dt == B200_BOOL;
+        case B200_OP_ARANGE: return dt == B200_F32 || dt == B200_I64;
+        case B200_OP_RAND: return dt == B200_F32;
+        case B200_OP_CONTIGUOUS: return n.n_src >= 1 && n.src[0].dtype == dt;
+        case B200_OP_CAST: return n.n_src >= 1 && cast_pair_ok(n.src[0].dtype, dt);
+        case B200_OP_CAT: return dt == B200_F32 && srcs_f32(n, 2);
+        case B200_OP_SCALED_ADD:
+        case B200_OP_ADD: case B200_OP_SUB: case B200_OP_MUL: case B200_OP_DIV: case B200_OP_POW:
+        case B200_OP_MAXIMUM: case B200_OP_MINIMUM:
+            return dt == B200_F32 && srcs_f32(n, 2);
+        case B200_OP_EQUAL: case B200_OP_LESS: case B200_OP_GREATER: case B200_OP_LESS_EQUAL:
+        case B200_OP_GREATER_EQUAL: case B200_OP_NOT_EQUAL:
+            return dt == B200_BOOL && srcs_f32(n, 2);
+        case B200_OP_WHERE:
+            return dt == B200_F32 && n.n_src >= 3 && n.src[0].dtype == B200_BOOL &&
+                   n.src[1].dtype == B200_F32 && n.src[2].dtype == B200_F32;
+        case B200_OP_TRIU: case B200_OP_TRIL: return dt == B200_F32 && srcs_f32(n, 1) && n.out.ndim >= 2;
+        case B200_OP_SUM: case B200_OP_MEAN: case B200_OP_MAX: case B200_OP_MIN:
+            return dt == B200_F32 && srcs_f32(n, 1);
+        case B200_OP_PROD: return false;  // declined by vkML's GPU backend as well (vulkan_backend.cpp:1137-1154)
+        case B200_OP_ARGMAX: case B200_OP_ARGMIN: return dt == B200_I64 && srcs_f32(n, 1);
+        case B200_OP_MATMUL: return dt == B200_F32 && srcs_f32(n, 2) && n.out.ndim == 4;
+        case B200_OP_SOFTMAX: case B200_OP_LOG_SOFTMAX: return dt == B200_F32 && srcs_f32(n, 1);
+        case B200_OP_IM2COL: case B200_OP_COL2IM: case B200_OP_MAX_POOL2D:
+            return dt == B200_F32 && srcs_f32(n, 1);
+        case B200_OP_MAX_POOL2D_BACKWARD: return dt == B200_F32 && srcs_f32(n, 2);
+        case B200_OP_INDEX_SELECT:
+            return (dtype_size(dt) == 4 || dtype_size(dt) == 8) && n.n_src >= 2 &&
+                   n.src[0].dtype == dt && n.src[1].dtype == B200_I64;
+        case B200_OP_SCATTER_ADD:
+            return dt == B200_F32 && n.n_src >= 2 && n.src[0].dtype == B200_F32 &&
+                   n.src[1].dtype == B200_I64;
+        case B200_OP_SLICE_BACKWARD: return dt == B200_F32 && srcs_f32(n, 1);
+        default:
+            if (op >= B200_OP_NEG && op <= B200_OP_CLAMP) return dt == B200_F32 && srcs_f32(n, 1);
+            return false;
+    }
+}
+
+}  // namespace b200
+
+void* b200_ctx::ensure_workspace(size_t nbytes) {
+    if (nbytes <= workspace_bytes) {
+        return workspace;
+    }
+    // Work already queued may still be using the old buffer; the stream is
+    // in-order, so freeing it through the stream-ordered cache is safe.
+    if (workspace != nullptr) {
+        alloc.release(workspace);
+        workspace = nullptr;
+        workspace_bytes = 0;
+    }
+    const size_t want = std::max(nbytes, size_t(8) << 20);
+    workspace = alloc.allocate(want);
+    workspace_bytes = want;
+    return workspace;
+}
+
+using namespace b200;
+
+extern "C" {
+
+int b200_abi_version(void) { return B200_ABI_VERSION; }
+
+const char* b200_status_name(int status) {
+    switch (status) {
+        case B200_OK: return "ok";
+        case B200_SHAPE_ERROR: return "shape error";
+        case B200_DTYPE_ERROR: return "dtype error";
+        case B200_DEVICE_ERROR: return "device error";
+        case B200_INDEX_ERROR: return "index error";
+        case B200_NOT_IMPLEMENTED: return "not implemented";
+        case B200_INTERNAL_ERROR: return "internal error";
+        case B200_OUT_OF_MEMORY: return "out of memory";
+        case B200_INVALID_ARGUMENT: return "invalid argument";
+        case B200_TIMEOUT: return "timeout";
+        default: return "unknown status";
+    }
+}
+
+int b200_device_count(int* count) {
+    if (count == nullptr) return B200_INVALID_ARGUMENT;
+    int n = 0;
+    const cudaError_t err = cudaGetDeviceCount(&n);
+    if (err != cudaSuccess) {
+        cudaGetLastError();
+        *count = 0;
+        return B200_DEVICE_ERROR;
+    }
+    *count = n;
+    return B200_OK;
+}
+
+int b200_create(int cuda_ordinal, b200_ctx** out) {
+    if (out == nullptr) return B200_INVALID_ARGUMENT;
+    *out = nullptr;
+    int n = 0;
+    if (cudaGetDeviceCount(&n) != cudaSuccess || cuda_ordinal < 0 || cuda_ordinal >= n) {
+        cudaGetLastError();
+        return B200_DEVICE_ERROR;  // no CUDA device: there is no CPU fallback in this library
+    }
+    b200_ctx* ctx = new (std::nothrow) b200_ctx();
+    if (ctx == nullptr) return B200_OUT_OF_MEMORY;
+    ctx->device = cuda_ordinal;
+    const int rc = guarded(ctx, [&] {
+        B200_CUDA_CHECK(cudaGetDeviceProperties(&ctx->prop, cuda_ordinal));
+        if (ctx->prop.major != 10) {
+            fail(B200_DEVICE_ERROR, std::string("device '") + ctx->prop.name +
+                                        "' is not compute capability 10.x; this library is built for sm_100a only");
+        }
+        B200_CUDA_CHECK(cudaStreamCreateWithFlags(&ctx->stream, cudaStreamNonBlocking));
+        B200_CUDA_CHECK(cudaMalloc(&ctx->d_status, sizeof(uint32_t)));
+        B200_CUDA_CHECK(cudaMemset(ctx->d_status, 0, sizeof(uint32_t)));
+        B200_CUDA_CHECK(cudaMallocHost(&ctx->h_status, sizeof(uint32_t)));
+        *ctx->h_status = 0;
+    });
+    if (rc != B200_OK) {
+        b200_destroy(ctx);
+        return rc;
+    }
+    *out = ctx;
+    return B200_OK;
+}
+
+void b200_destroy(b200_ctx* ctx) {
+    if (ctx == nullptr) return;
+    cudaSetDevice(ctx->device);
+    if (ctx->stream != nullptr) cudaStreamSynchronize(ctx->stream);
+    dist_destroy(ctx);
+    if (ctx->stream != nullptr) cudaStreamDestroy(ctx->stream);
+    if (ctx->d_status != nullptr) cudaFree(ctx->d_status);
+    if (ctx->h_status != nullptr) cudaFreeHost(ctx->h_status);
+    if (ctx->staging != nullptr) cudaFreeHost(ctx->staging);
+    cudaGetLastError();
+    delete ctx;
+}
+
+int b200_get_caps(b200_ctx* ctx, b200_caps* out) {
+    if (ctx == nullptr || out == nullptr) return B200_INVALID_ARGUMENT;
+    std::memset(out, 0, sizeof(*out));
+    std::snprintf(out->name, sizeof(out->name), "%s", ctx->prop.name);
+    out->cc_major = ctx->prop.major;
+    out->cc_minor = ctx->prop.minor;
+    out->sm_count = static_cast<uint32_t>(ctx->prop.multiProcessorCount);
+    out->warp_size = static_cast<uint32_t>(ctx->prop.warpSize);
+    out->max_threads_per_block = static_cast<uint32_t>(ctx->prop.maxThreadsPerBlock);
+    out->max_shared_memory_bytes = ctx->prop.sharedMemPerBlockOptin;
+    out->total_memory_bytes = ctx->prop.totalGlobalMem;
+    out->min_buffer_alignment = 512;
+    return B200_OK;
+}
+
+int b200_alloc(b200_ctx* ctx, size_t nbytes, void** out) {
+    if (ctx == nullptr || out == nullptr) return B200_INVALID_ARGUMENT;
+    *out = nullptr;
+    return guarded(ctx, [&] { *out = ctx->alloc.allocate(nbytes); });
+}
+
+int b200_free(b200_ctx* ctx, void* ptr) {
+    if (ctx == nullptr) return B200_INVALID_ARGUMENT;
+    return guarded(ctx, [&] { ctx->alloc.release(ptr); });
+}
+
+int b200_trim(b200_ctx* ctx) {
+    if (ctx == nullptr) return B200_INVALID_ARGUMENT;
+    return guarded(ctx, [&] {
+        B200_CUDA_CHECK(cudaStreamSynchronize(ctx->stream));
+        ctx->alloc.trim();
+    });
+}
+
+int b200_supports(const b200_node* node) {
+    if (node == nullptr) return 0;
+    return supports_node(*node) ? 1 : 0;
+}
+
+int b200_compute(b200_ctx* ctx, const b200_node* nodes, size_t n_nodes, uint32_t flags) {
+    if (ctx == nullptr || (nodes == nullptr && n_nodes != 0)) return B200_INVALID_ARGUMENT;
+    return guarded(ctx, [&] {
+        ctx->compute_calls.fetch_add(1, std::memory_order_relaxed);
+        const bool grad_sync = (flags & B200_COMPUTE_GRAD_SYNC) != 0 && ctx->dist != nullptr;
+        for (size_t i = 0; i < n_nodes; ++i) {
+            const b200_node& node = nodes[i];
+            if (is_view_or_leaf(node.op)) {
+                continue;  // resolved by the executor through aliasing (backend.h:34-45)
+            }
+            if (node.op >= B200_OP_COUNT) {
+                fail(B200_NOT_IMPLEMENTED, "unknown op " + std::to_string(node.op));
+            }
+            // zero-element tensors are legal and need no work (vulkan_backend.cpp:1233-1236)
+            int64_t numel = 1;
+            for (int d = 0; d < node.out.ndim; ++d) numel *= node.out.dims[d];
+            if (numel == 0) {
+                continue;
+            }
+            if (node.out.data == nullptr) {
+                fail(B200_INVALID_ARGUMENT, "node has no storage");
+            }
+            for (uint32_t s = 0; s < node.n_src && s < B200_MAX_SRC; ++s) {
+                int64_t sn = 1;
+                for (int d = 0; d < node.src[s].ndim; ++d) sn *= node.src[s].dims[d];
+                if (sn != 0 && node.src[s].data == nullptr) {
+                    fail(B200_INVALID_ARGUMENT, "source " + std::to_string(s) + " has no storage");
+                }
+            }
+            dispatch_node(ctx, node);
+            ctx->nodes_computed.fetch_add(1, std::memory_order_relaxed);
+            if (grad_sync) {
+                dist_after_node(ctx, node);
+            }
+        }
+        if (grad_sync) {
+            dist_join(ctx);
+        }
+        if (flags & B200_COMPUTE_SYNC) {
+            B200_CUDA_CHECK(cudaStreamSynchronize(ctx->stream));
+        }
+    });
+}
+
+int b200_copy_from_host(b200_ctx* ctx, void* dst_device, const void* src_host, size_t nbytes) {
+    if (ctx == nullptr) return B200_INVALID_ARGUMENT;
+    if (nbytes == 0) return B200_OK;
+    if (dst_device == nullptr || src_host == nullptr) return B200_INVALID_ARGUMENT;
+    return guarded(ctx, [&] {
+        // For pageable memory the runtime stages the bytes before returning, so
+        // the caller may reuse `src_host` immediately; pinned memory is read
+        // asynchronously, in stream order.
+        B200_CUDA_CHECK(cudaMemcpyAsync(dst_device, src_host, nbytes, cudaMemcpyHostToDevice, ctx->stream));
+        cudaPointerAttributes attr{};
+        const cudaError_t e = cudaPointerGetAttributes(&attr, src_host);
+        if (e != cudaSuccess) cudaGetLastError();
+        if (e == cudaSuccess && attr.type == cudaMemoryTypeHost) {
+            // pinned source: the copy is truly asynchronous; wait so the
+            // "caller may reuse the buffer" contract of copy_from_host holds
+            B200_CUDA_CHECK(cudaStreamSynchronize(ctx->stream));
+        }
+    });
+}
+
+static int report_device_status(b200_ctx* ctx) {
+    const uint32_t bits = *ctx->h_status;
+    if (bits == 0) return B200_OK;
+    *ctx->h_status = 0;
+    cudaMemsetAsync(ctx->d_status, 0, sizeof(uint32_t), ctx->stream);
+    if (bits & kStatusIndexOutOfRange) {
+        set_error(ctx, "an index passed to index_select / scatter_add was out of range");
+        return B200_INDEX_ERROR;
+    }
+    if (bits & kStatusWaitTimedOut) {
+        set_error(ctx, "a bounded device-side wait ran out");
+        return B200_TIMEOUT;
+    }
+    set_error(ctx, "a kernel reported an internal error (status bits " + std::to_string(bits) + ")");
+    return B200_INTERNAL_ERROR;
+}
+
+int b200_copy_to_host(b200_ctx* ctx, void* dst_host, const void* src_device, size_t nbytes) {
+    if (ctx == nullptr) return B200_INVALID_ARGUMENT;
+    if (nbytes == 0) return B200_OK;
+    if (dst_host == nullptr || src_device == nullptr) return B200_INVALID_ARGUMENT;
+    return guarded(ctx, [&] {
+        B200_CUDA_CHECK(cudaMemcpyAsync(dst_host, src_device, nbytes, cudaMemcpyDeviceToHost, ctx->stream));
+        B200_CUDA_CHECK(cudaStreamSynchronize(ctx->stream));
+    });
+}
+
+int b200_copy_device_to_device(b200_ctx* ctx, const b200_copy* copies, size_t n) {
+    if (ctx == nullptr || (copies == nullptr && n != 0)) return B200_INVALID_ARGUMENT;
+    return guarded(ctx, [&] {
+        for (size_t i = 0; i < n; ++i) {
+            if (copies[i].nbytes == 0) continue;
+            if (copies[i].dst == nullptr || copies[i].src == nullptr) {
+                fail(B200_INVALID_ARGUMENT, "null pointer in copy_device_to_device");
+            }
+            B200_CUDA_CHECK(cudaMemcpyAsync(copies[i].dst, copies[i].src, copies[i].nbytes,
+                                            cudaMemcpyDeviceToDevice, ctx->stream));
+        }
+    });
+}
+
+int b200_synchronize(b200_ctx* ctx) {
+    if (ctx == nullptr) return B200_INVALID_ARGUMENT;
+    int device_rc = B200_OK;
+    const int rc = guarded(ctx, [&] {
+        B200_CUDA_CHECK(cudaMemcpyAsync(ctx->h_status, ctx->d_status, sizeof(uint32_t),
+                                        cudaMemcpyDeviceToHost, ctx->stream));
+        B200_CUDA_CHECK(cudaStreamSynchronize(ctx->stream));
+        device_rc = report_device_status(ctx);
+    });
+    return rc != B200_OK ? rc : device_rc;
+}
+
+const char* b200_last_error(b200_ctx* ctx) {
+    if (ctx == nullptr) return "";
+    std::lock_guard<std::mutex> lock(ctx->err_mu);
+    // the string lives in the context until the next error replaces it
+    return ctx->last_error.c_str();
+}
+
+int b200_get_stats(b200_ctx* ctx, b200_stats* out) {
+    if (ctx == nullptr || out == nullptr) return B200_INVALID_ARGUMENT;
+    out->reserved_bytes = ctx->alloc.reserved;
+    out->in_use_bytes = ctx->alloc.in_use;
+    out->peak_in_use_bytes = ctx->alloc.peak;
+    out->live_allocations = ctx->alloc.live;
+    out->total_allocations = ctx->alloc.total;
+    out->driver_allocations = ctx->alloc.driver_allocs;
+    out->compute_calls = ctx->compute_calls.load();
+    out->kernel_launches = ctx->kernel_launches.load();
+    out->nodes_computed = ctx->nodes_computed.load();
+    out->comm_bytes = ctx->comm_bytes.load();
+    return B200_OK;
+}
+
+int b200_set_gemm_precision(b200_ctx* ctx, int precision) {
+    if (ctx == nullptr || precision < B200_GEMM_3XTF32 || precision > B200_GEMM_FP32) {
+        return B200_INVALID_ARGUMENT;
+    }
+    ctx->gemm_precision = precision;
+    return B200_OK;
+}
+
+int b200_get_gemm_precision(b200_ctx* ctx) { return ctx == nullptr ? -1 : ctx->gemm_precision; }
+
+void* b200_stream(b200_ctx* ctx) { return ctx == nullptr ? nullptr : ctx->stream; }
+
+}  // extern "C"

@@ -1,0 +1,101 @@
+// The backend context: one CUDA device, one compute stream, a caching
+// allocator, a device status word and counters.
+#pragma once
+
+#include "common.cuh"
+
+#include <atomic>
+#include <map>
+#include <mutex>
+#include <unordered_map>
+#include <vector>
+
+namespace b200 {
+
+// Caching device allocator.
+//
+// vkML allocates a fresh buffer for every computed node
+// (src/dispatch/executor.cpp:40-45) and drops it whenever the last handle goes
+// away, possibly while kernels that use it are still queued.  All work of a
+// context runs on ONE in-order stream, so a block that is freed and handed out
+// again is only ever touched by later work on the same stream: recycling needs
+// no events.  Blocks come from cudaMalloc in size classes and return to
+// per-size free lists; nothing goes back to the driver until trim().
+class CachingAllocator {
+public:
+    void* allocate(size_t nbytes);
+    void release(void* ptr);
+    void trim();
+    ~CachingAllocator();
+
+    uint64_t reserved = 0, in_use = 0, peak = 0, live = 0, total = 0, driver_allocs = 0;
+
+private:
+    static size_t round_size(size_t n);
+    std::mutex mu_;
+    std::multimap<size_t, void*> free_;           // size -> block
+    std::unordered_map<void*, size_t> sizes_;     // every block ever handed out
+    std::unordered_map<void*, size_t> live_;      // blocks currently out (ptr -> size)
+};
+
+struct DistState;  // dist.cu
+
+struct GradBuffer {
+    void* data;
+    size_t count;
+};
+
+}  // namespace b200
+
+struct b200_ctx {
+    int device = 0;
+    cudaStream_t stream = nullptr;
+    cudaDeviceProp prop{};
+    b200::CachingAllocator alloc;
+
+    uint32_t* d_status = nullptr;  // device status word (DeviceStatusBits)
+    uint32_t* h_status = nullptr;  // pinned mirror
+
+    // Scratch the library owns (GEMM operand splits, reduction partials). Grown
+    // on demand, never shrunk; reused by every launch on the stream.
+    void* workspace = nullptr;
+    size_t workspace_bytes = 0;
+
+    // Pinned staging for host copies.
+    void* staging = nullptr;
+    size_t staging_bytes = 0;
+
+    int gemm_precision = B200_GEMM_3XTF32;
+
+    std::atomic<uint64_t> compute_calls{0}, kernel_launches{0}, nodes_computed{0}, comm_bytes{0};
+
+    std::mutex err_mu;
+    std::string last_error;
+
+    b200::DistState* dist = nullptr;
+    std::vector<b200::GradBuffer> grads;
+
+    void* ensure_workspace(size_t nbytes);
+    void count_launch(uint64_t n = 1) { kernel_launches.fetch_add(n, std::memory_order_relaxed); }
+};
+
+namespace b200 {
+
+// Per-family launchers (one translation unit each). Each reads the node, picks a
+// kernel from the operand layouts, and launches on ctx->stream.
+void launch_elementwise(b200_ctx* ctx, const b200_node& node);  // unary, binary, compare, where, scaled_add, cast, contiguous, full, arange, rand, tri, cat, slice_backward
+void launch_reduce(b200_ctx* ctx, const b200_node& node);       // sum, mean, max, min, argmax, argmin
+void launch_softmax(b200_ctx* ctx, const b200_node& node);      // softmax, log_softmax
+void launch_movement(b200_ctx* ctx, const b200_node& node);     // im2col, col2im, max_pool2d(+backward), index_select, scatter_add
+void launch_matmul(b200_ctx* ctx, const b200_node& node);       // matmul (all kernels)
+
+bool supports_node(const b200_node& node);
+
+// dist.cu
+void dist_destroy(b200_ctx* ctx);
+void dist_after_node(b200_ctx* ctx, const b200_node& node);  // all-reduce a registered gradient once its producer is queued
+void dist_join(b200_ctx* ctx);                                // make the compute stream wait for outstanding all-reduces
+
+void check_last_launch(const char* what);
+
+}  // namespace b200

@@ -1,0 +1,956 @@
+// Memory-bound elementwise family: unary, binary, compare, where, scaled_add,
+// cast, contiguous, full, arange, rand, triu/tril, cat, slice_backward.
+//
+// Arithmetic follows vkML's CPU backend (src/backend/cpu/kernels_elementwise.cpp,
+// src/backend/cpu/kernels_movement.cpp) operation for operation; this file is
+// compiled with -fmad=false so no multiply-add pair is contracted, which is what
+// keeps scaled_add bit-identical to the composed mul/mul/add
+// (kernels_elementwise.cpp:256-259).
+//
+// Three execution shapes, picked from the operand strides:
+//   flat     -- every operand dense: 128-bit loads/stores, grid-stride.
+//   strided  -- rank<=4 collapsed index walk; vectorised along the innermost axis
+//               when every operand is unit-stride or broadcast (stride 0) there.
+//   tiled    -- an operand whose unit stride lies on the second-innermost axis
+//               (a transposed view) goes through a 32x33 shared-memory tile so
+//               both the global read and the global write stay coalesced.
+#include "context.h"
+
+#include <cuda_fp16.h>
+
+namespace b200 {
+namespace {
+
+constexpr int kThreads = 256;
+
+template <typename T, int N>
+struct alignas(sizeof(T) * N) Vec {
+    T v[N];
+};
+
+// ---------------------------------------------------------------------------
+// Functors. In0/In1/In2 and Out are the storage types; apply() is the CPU
+// backend's lambda.
+// ---------------------------------------------------------------------------
+
+struct NoParams {};
+
+#define UNARY_F32(NAME, EXPR)                                                      \
+    struct NAME {                                                                   \
+        static constexpr int NIN = 1;                                               \
+        using In0 = float;                                                          \
+        using In1 = float;                                                          \
+        using In2 = float;                                                          \
+        using Out = float;                                                          \
+        using P = NoParams;                                                         \
+        __device__ __forceinline__ static float apply(const P&, float x, float, float) { \
+            return EXPR;                                                            \
+        }                                                                           \
+    };
+
+__device__ __forceinline__ float sigmoid_ref(float x) {
+    // kernels_elementwise.cpp:25-31: the branch keeps exp's argument non-positive.
+    if (x >= 0.0F) {
+        return 1.0F / (1.0F + expf(-x));
+    }
+    const float e = expf(x);
+    return e / (1.0F + e);
+}
+
+__device__ __forceinline__ float sign_ref(float x) {
+    return x > 0.0F ? 1.0F : (x < 0.0F ? -1.0F : 0.0F);  // NaN and -0 give +0 (:75-83)
+}
+
+UNARY_F32(FNeg, -x)
+UNARY_F32(FAbs, fabsf(x))
+UNARY_F32(FSign, sign_ref(x))
+UNARY_F32(FSquare, x * x)
+UNARY_F32(FSqrt, sqrtf(x))
+UNARY_F32(FRsqrt, 1.0F / sqrtf(x))
+UNARY_F32(FReciprocal, 1.0F / x)
+UNARY_F32(FExp, expf(x))
+UNARY_F32(FLog, logf(x))
+UNARY_F32(FErf, erff(x))
+UNARY_F32(FErfc, erfcf(x))
+UNARY_F32(FSin, sinf(x))
+UNARY_F32(FCos, cosf(x))
+UNARY_F32(FTanh, tanhf(x))
+UNARY_F32(FSigmoid, sigmoid_ref(x))
+UNARY_F32(FRelu, (x <= 0.0F ? 0.0F : x))  // NaN propagates (:223-231)
+UNARY_F32(FGelu, 0.5F * x * erfcf(-x * 0.70710678118654752440F))
+UNARY_F32(FSilu, x * sigmoid_ref(x))
+
+struct FClamp {
+    static constexpr int NIN = 1;
+    using In0 = float;
+    using In1 = float;
+    using In2 = float;
+    using Out = float;
+    using P = ClampParams;
+    __device__ __forceinline__ static float apply(const P& p, float v, float, float) {
+        if (p.has_lo && v < p.lo) {
+            return p.lo;
+        }
+        if (p.has_hi && v > p.hi) {
+            return p.hi;
+        }
+        return v;
+    }
+};
+
+#define BINARY_F32(NAME, EXPR)                                                     \
+    struct NAME {                                                                   \
+        static constexpr int NIN = 2;                                               \
+        using In0 = float;                                                          \
+        using In1 = float;                                                          \
+        using In2 = float;                                                          \
+        using Out = float;                                                          \
+        using P = NoParams;                                                         \
+        __device__ __forceinline__ static float apply(const P&, float x, float y, float) { \
+            return EXPR;                                                            \
+        }                                                                           \
+    };
+
+BINARY_F32(FAdd, __fadd_rn(x, y))
+BINARY_F32(FSub, __fsub_rn(x, y))
+BINARY_F32(FMul, __fmul_rn(x, y))
+BINARY_F32(FDiv, __fdiv_rn(x, y))
+BINARY_F32(FPow, powf(x, y))
+BINARY_F32(FMaximum, ((isnan(x) || isnan(y)) ? __int_as_float(0x7fc00000) : (x > y ? x : y)))
+BINARY_F32(FMinimum, ((isnan(x) || isnan(y)) ? __int_as_float(0x7fc00000) : (x < y ? x : y)))
+
+struct FScaledAdd {
+    static constexpr int NIN = 2;
+    using In0 = float;
+    using In1 = float;
+    using In2 = float;
+    using Out = float;
+    using P = ScaledAddParams;
+    __device__ __forceinline__ static float apply(const P& p, float x, float y, float) {
+        // two rounded products, then one rounded sum: never an FMA
+        return __fadd_rn(__fmul_rn(x, p.alpha), __fmul_rn(y, p.beta));
+    }
+};
+
+#define COMPARE_F32(NAME, EXPR)                                                    \
+    struct NAME {                                                                   \
+        static constexpr int NIN = 2;                                               \
+        using In0 = float;                                                          \
+        using In1 = float;                                                          \
+        using In2 = float;                                                          \
+        using Out = uint8_t;                                                        \
+        using P = NoParams;                                                         \
+        __device__ __forceinline__ static uint8_t apply(const P&, float x, float y, float) { \
+            return (EXPR) ? 1 : 0;                                                  \
+        }                                                                           \
+    };
+
+COMPARE_F32(FEqual, x == y)
+COMPARE_F32(FLess, x < y)
+COMPARE_F32(FGreater, x > y)
+COMPARE_F32(FLessEqual, x <= y)
+COMPARE_F32(FGreaterEqual, x >= y)
+COMPARE_F32(FNotEqual, x != y)
+
+struct FWhere {
+    static constexpr int NIN = 3;
+    using In0 = uint8_t;
+    using In1 = float;
+    using In2 = float;
+    using Out = float;
+    using P = NoParams;
+    __device__ __forceinline__ static float apply(const P&, uint8_t c, float a, float b) {
+        return c != 0 ? a : b;
+    }
+};
+
+// Same-type copy by element width (Contiguous, and Cast with from == to).
+template <typename T>
+struct FCopy {
+    static constexpr int NIN = 1;
+    using In0 = T;
+    using In1 = T;
+    using In2 = T;
+    using Out = T;
+    using P = NoParams;
+    __device__ __forceinline__ static T apply(const P&, T x, T, T) { return x; }
+};
+
+// fp32 -> fp16 bits, round to nearest even; NaN becomes a quiet NaN with the
+// input's sign and an otherwise empty payload, as vkML's software conversion
+// produces (src/core/dtype.cpp:47-70).
+__device__ __forceinline__ uint16_t f32_to_f16_bits(float f) {
+    if (isnan(f)) {
+        return static_cast<uint16_t>(((__float_as_uint(f) >> 16) & 0x8000U) | 0x7E00U);
+    }
+    return __half_as_ushort(__float2half_rn(f));
+}
+
+template <typename From, typename To>
+struct FCast {
+    static constexpr int NIN = 1;
+    using In0 = From;
+    using In1 = From;
+    using In2 = From;
+    using Out = To;
+    using P = NoParams;
+    __device__ __forceinline__ static To apply(const P&, From x, From, From) {
+        return static_cast<To>(x);
+    }
+};
+struct FCastF32Bool {
+    static constexpr int NIN = 1;
+    using In0 = float;
+    using In1 = float;
+    using In2 = float;
+    using Out = uint8_t;
+    using P = NoParams;
+    __device__ __forceinline__ static uint8_t apply(const P&, float x, float, float) {
+        return x != 0.0F ? 1 : 0;
+    }
+};
+struct FCastF32F16 {
+    static constexpr int NIN = 1;
+    using In0 = float;
+    using In1 = float;
+    using In2 = float;
+    using Out = uint16_t;
+    using P = NoParams;
+    __device__ __forceinline__ static uint16_t apply(const P&, float x, float, float) {
+        return f32_to_f16_bits(x);
+    }
+};
+struct FCastF16F32 {
+    static constexpr int NIN = 1;
+    using In0 = uint16_t;
+    using In1 = uint16_t;
+    using In2 = uint16_t;
+    using Out = float;
+    using P = NoParams;
+    __device__ __forceinline__ static float apply(const P&, uint16_t x, uint16_t, uint16_t) {
+        return __half2float(__ushort_as_half(x));
+    }
+};
+template <typename To>
+struct FCastBool {
+    static constexpr int NIN = 1;
+    using In0 = uint8_t;
+    using In1 = uint8_t;
+    using In2 = uint8_t;
+    using Out = To;
+    using P = NoParams;
+    __device__ __forceinline__ static To apply(const P&, uint8_t x, uint8_t, uint8_t) {
+        return x != 0 ? To(1) : To(0);
+    }
+};
+
+// ---------------------------------------------------------------------------
+// Kernels
+// ---------------------------------------------------------------------------
+
+// Every operand dense and 16-byte-friendly: VEC elements per thread per trip.
+template <typename F, int VEC>
+__global__ void __launch_bounds__(kThreads)
+flat_kernel(typename F::Out* __restrict__ out, const typename F::In0* __restrict__ a,
+            const typename F::In1* __restrict__ b, const typename F::In2* __restrict__ c,
+            int64_t n, typename F::P p) {
+    const int64_t nvec = n / VEC;
+    const int64_t stride = int64_t(gridDim.x) * blockDim.x;
+    for (int64_t i = int64_t(blockIdx.x) * blockDim.x + threadIdx.x; i < nvec; i += stride) {
+        Vec<typename F::In0, VEC> va = reinterpret_cast<const Vec<typename F::In0, VEC>*>(a)[i];
+        Vec<typename F::In1, VEC> vb{};
+        Vec<typename F::In2, VEC> vc{};
+        if constexpr (F::NIN >= 2) {
+            vb = reinterpret_cast<const Vec<typename F::In1, VEC>*>(b)[i];
+        }
+        if constexpr (F::NIN >= 3) {
+            vc = reinterpret_cast<const Vec<typename F::In2, VEC>*>(c)[i];
+        }
+        Vec<typename F::Out, VEC> vo;
+#pragma unroll
+        for (int k = 0; k < VEC; ++k) {
+            vo.v[k] = F::apply(p, va.v[k], vb.v[k], vc.v[k]);
+        }
+        reinterpret_cast<Vec<typename F::Out, VEC>*>(out)[i] = vo;
+    }
+    // tail (n % VEC elements) by the first threads of block 0
+    if (blockIdx.x == 0) {
+        const int64_t i = nvec * VEC + threadIdx.x;
+        if (i < n) {
+            typename F::In1 y{};
+            typename F::In2 z{};
+            if constexpr (F::NIN >= 2) {
+                y = b[i];
+            }
+            if constexpr (F::NIN >= 3) {
+                z = c[i];
+            }
+            out[i] = F::apply(p, a[i], y, z);
+        }
+    }
+}
+
+// General strided walk. L.stride[0..2] are the inputs, the output is dense.
+// With VEC > 1 the innermost extent has been divided by VEC and every input's
+// innermost stride is VEC (unit stride, vector load) or 0 (broadcast, splat).
+template <typename F, int VEC>
+__global__ void __launch_bounds__(kThreads)
+strided_kernel(typename F::Out* __restrict__ out, const typename F::In0* __restrict__ a,
+               const typename F::In1* __restrict__ b, const typename F::In2* __restrict__ c,
+               int64_t nvec, Layout4 L, typename F::P p) {
+    const int64_t stride = int64_t(gridDim.x) * blockDim.x;
+    const int inner = kMaxDims - 1;
+    for (int64_t i = int64_t(blockIdx.x) * blockDim.x + threadIdx.x; i < nvec; i += stride) {
+        int64_t off[3];
+        offsets_of<3>(L, i, off);
+        Vec<typename F::In0, VEC> va;
+        Vec<typename F::In1, VEC> vb{};
+        Vec<typename F::In2, VEC> vc{};
+        if (VEC > 1 && L.stride[0][inner] != 0) {
+            va = *reinterpret_cast<const Vec<typename F::In0, VEC>*>(a + off[0]);
+        } else {
+            const typename F::In0 s = a[off[0]];
+#pragma unroll
+            for (int k = 0; k < VEC; ++k) {
+                va.v[k] = s;
+            }
+        }
+        if constexpr (F::NIN >= 2) {
+            if (VEC > 1 && L.stride[1][inner] != 0) {
+                vb = *reinterpret_cast<const Vec<typename F::In1, VEC>*>(b + off[1]);
+            } else {
+                const typename F::In1 s = b[off[1]];
+#pragma unroll
+                for (int k = 0; k < VEC; ++k) {
+                    vb.v[k] = s;
+                }
+            }
+        }
+        if constexpr (F::NIN >= 3) {
+            if (VEC > 1 && L.stride[2][inner] != 0) {
+                vc = *reinterpret_cast<const Vec<typename F::In2, VEC>*>(c + off[2]);
+            } else {
+                const typename F::In2 s = c[off[2]];
+#pragma unroll
+                for (int k = 0; k < VEC; ++k) {
+                    vc.v[k] = s;
+                }
+            }
+        }
+        Vec<typename F::Out, VEC> vo;
+#pragma unroll
+        for (int k = 0; k < VEC; ++k) {
+            vo.v[k] = F::apply(p, va.v[k], vb.v[k], vc.v[k]);
+        }
+        reinterpret_cast<Vec<typename F::Out, VEC>*>(out)[i] = vo;
+    }
+}
+
+// Transposed operands. Iteration space [batch, R, C], output dense row-major.
+// Each input is read either along C (its stride on C is 1 or 0) or, when
+// `transposed` is set for it, along R through a padded shared tile. 4-byte types.
+struct TileArgs {
+    int64_t batch, rows, cols;
+    int64_t sb[3], sr[3], sc[3];  // per-input element strides over (batch, R, C)
+    int transposed[3];
+};
+
+template <typename F>
+__global__ void __launch_bounds__(256)
+tiled_kernel(typename F::Out* __restrict__ out, const typename F::In0* __restrict__ a,
+             const typename F::In1* __restrict__ b, const typename F::In2* __restrict__ c,
+             TileArgs t, typename F::P p) {
+    __shared__ typename F::In0 ta[32][33];
+    __shared__ typename F::In1 tb[32][33];
+    const int64_t tiles_c = (t.cols + 31) / 32;
+    const int64_t tiles_r = (t.rows + 31) / 32;
+    const int64_t n_tiles = tiles_c * tiles_r * t.batch;
+    const int tx = threadIdx.x & 31;
+    const int ty = threadIdx.x >> 5;  // 0..7
+    for (int64_t tile = blockIdx.x; tile < n_tiles; tile += gridDim.x) {
+        const int64_t tc = tile % tiles_c;
+        const int64_t tr = (tile / tiles_c) % tiles_r;
+        const int64_t bi = tile / (tiles_c * tiles_r);
+        const int64_t r0 = tr * 32;
+        const int64_t c0 = tc * 32;
+        // stage transposed inputs: thread (tx,ty) reads row r0+tx (unit stride), col c0+ty+8j
+        if (t.transposed[0]) {
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                const int64_t r = r0 + tx;
+                const int64_t cc = c0 + ty + 8 * j;
+                if (r < t.rows && cc < t.cols) {
+                    ta[tx][ty + 8 * j] = a[bi * t.sb[0] + r * t.sr[0] + cc * t.sc[0]];
+                }
+            }
+        }
+        if constexpr (F::NIN >= 2) {
+            if (t.transposed[1]) {
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                    const int64_t r = r0 + tx;
+                    const int64_t cc = c0 + ty + 8 * j;
+                    if (r < t.rows && cc < t.cols) {
+                        tb[tx][ty + 8 * j] = b[bi * t.sb[1] + r * t.sr[1] + cc * t.sc[1]];
+                    }
+                }
+            }
+        }
+        __syncthreads();
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            const int64_t r = r0 + ty + 8 * j;
+            const int64_t cc = c0 + tx;
+            if (r < t.rows && cc < t.cols) {
+                const typename F::In0 x = t.transposed[0]
+                                              ? ta[ty + 8 * j][tx]
+                                              : a[bi * t.sb[0] + r * t.sr[0] + cc * t.sc[0]];
+                typename F::In1 y{};
+                if constexpr (F::NIN >= 2) {
+                    y = t.transposed[1] ? tb[ty + 8 * j][tx]
+                                        : b[bi * t.sb[1] + r * t.sr[1] + cc * t.sc[1]];
+                }
+                out[(bi * t.rows + r) * t.cols + cc] = F::apply(p, x, y, typename F::In2{});
+            }
+        }
+        __syncthreads();
+    }
+}
+
+// ---------------------------------------------------------------------------
+// Layout analysis
+// ---------------------------------------------------------------------------
+
+// Collapse the shared iteration space of `n` views (all already broadcast to the
+// same extents): drop extents of 1, merge neighbours that every operand walks as
+// one run.
+Layout4 collapse(const View* views, int n) {
+    int64_t dim[kMaxDims];
+    int64_t st[4][kMaxDims];
+    int rank = 0;
+    for (int a = 0; a < kMaxDims; ++a) {
+        const int64_t d = views[0].dim[a];
+        if (d == 1) {
+            continue;
+        }
+        bool merged = false;
+        if (rank > 0) {
+            merged = true;
+            for (int o = 0; o < n; ++o) {
+                if (st[o][rank - 1] != views[o].stride[a] * d) {
+                    merged = false;
+                    break;
+                }
+            }
+        }
+        if (merged) {
+            dim[rank - 1] *= d;
+            for (int o = 0; o < n; ++o) {
+                st[o][rank - 1] = views[o].stride[a];
+            }
+        } else {
+            dim[rank] = d;
+            for (int o = 0; o < n; ++o) {
+                st[o][rank] = views[o].stride[a];
+            }
+            ++rank;
+        }
+    }
+    if (rank == 0) {
+        dim[0] = 1;
+        for (int o = 0; o < n; ++o) {
+            st[o][0] = 0;
+        }
+        rank = 1;
+    }
+    Layout4 L{};
+    L.ndim = rank;
+    for (int a = 0; a < kMaxDims; ++a) {
+        L.dim[a] = 1;
+        for (int o = 0; o < 4; ++o) {
+            L.stride[o][a] = 0;
+        }
+    }
+    for (int r = 0; r < rank; ++r) {
+        const int a = kMaxDims - rank + r;
+        L.dim[a] = dim[r];
+        for (int o = 0; o < n; ++o) {
+            L.stride[o][a] = st[o][r];
+        }
+    }
+    return L;
+}
+
+template <typename T>
+bool aligned_for(const void* p, int vec) {
+    return reinterpret_cast<uintptr_t>(p) % (sizeof(T) * vec) == 0;
+}
+
+template <typename F>
+void run(b200_ctx* ctx, const b200_node& node, const typename F::P& p) {
+    const View out = make_view(node.out);
+    if (out.numel == 0) {
+        return;
+    }
+    if (!out.contiguous) {
+        fail(B200_NOT_IMPLEMENTED, "elementwise output must be contiguous");
+    }
+    if (static_cast<int>(node.n_src) < F::NIN) {
+        fail(B200_INVALID_ARGUMENT, "elementwise node is missing a source");
+    }
+    View in[3];
+    for (int i = 0; i < F::NIN; ++i) {
+        in[i] = make_view(node.src[i]);
+        for (int a = 0; a < kMaxDims; ++a) {
+            if (in[i].dim[a] != out.dim[a]) {
+                fail(B200_SHAPE_ERROR, "elementwise operand extents differ from the output's");
+            }
+        }
+    }
+    auto* o = reinterpret_cast<typename F::Out*>(out.data);
+    auto* a = reinterpret_cast<const typename F::In0*>(in[0].data);
+    auto* b = F::NIN >= 2 ? reinterpret_cast<const typename F::In1*>(in[1].data) : nullptr;
+    auto* c = F::NIN >= 3 ? reinterpret_cast<const typename F::In2*>(in[2].data) : nullptr;
+    const int64_t n = out.numel;
+
+    bool dense = true;
+    for (int i = 0; i < F::NIN; ++i) {
+        dense = dense && in[i].contiguous;
+    }
+    constexpr int kVec = sizeof(typename F::Out) == 8 ? 2 : 4;
+    if (dense) {
+        bool al = aligned_for<typename F::Out>(o, kVec) && aligned_for<typename F::In0>(a, kVec);
+        if (F::NIN >= 2) {
+            al = al && aligned_for<typename F::In1>(b, kVec);
+        }
+        if (F::NIN >= 3) {
+            al = al && aligned_for<typename F::In2>(c, kVec);
+        }
+        if (al) {
+            flat_kernel<F, kVec><<<grid_for(n / kVec + 1, kThreads), kThreads, 0, ctx->stream>>>(
+                o, a, b, c, n, p);
+        } else {
+            flat_kernel<F, 1><<<grid_for(n, kThreads), kThreads, 0, ctx->stream>>>(o, a, b, c, n, p);
+        }
+        ctx->count_launch();
+        check_last_launch("elementwise flat");
+        return;
+    }
+
+    Layout4 L = collapse(in, F::NIN);
+    const int inner = kMaxDims - 1;
+
+    // transposed-operand path: 4-byte types, <= 2 inputs, collapsed rank 2 or 3
+    if constexpr (F::NIN <= 2 && sizeof(typename F::In0) == 4 && sizeof(typename F::In1) == 4 &&
+                  sizeof(typename F::Out) == 4) {
+        if (L.ndim >= 2 && L.ndim <= 3) {
+            const int rax = kMaxDims - 2;
+            bool any_t = false;
+            bool ok = true;
+            TileArgs t{};
+            t.cols = L.dim[inner];
+            t.rows = L.dim[rax];
+            t.batch = L.ndim == 3 ? L.dim[kMaxDims - 3] : 1;
+            for (int i = 0; i < F::NIN; ++i) {
+                t.sc[i] = L.stride[i][inner];
+                t.sr[i] = L.stride[i][rax];
+                t.sb[i] = L.ndim == 3 ? L.stride[i][kMaxDims - 3] : 0;
+                if (t.sc[i] == 1 || t.sc[i] == 0) {
+                    t.transposed[i] = 0;
+                } else if (t.sr[i] == 1) {
+                    t.transposed[i] = 1;
+                    any_t = true;
+                } else {
+                    ok = false;
+                }
+            }
+            if (ok && any_t && t.rows >= 8 && t.cols >= 8) {
+                const int64_t tiles = ceil_div(t.rows, 32) * ceil_div(t.cols, 32) * t.batch;
+                tiled_kernel<F><<<grid_for(tiles, 1, 16), 256, 0, ctx->stream>>>(o, a, b, c, t, p);
+                ctx->count_launch();
+                check_last_launch("elementwise tiled");
+                return;
+            }
+        }
+    }
+
+    // vectorise along the innermost axis when every input is unit-stride or broadcast there
+    bool vec_ok = L.dim[inner] % kVec == 0 && aligned_for<typename F::Out>(o, kVec);
+    const void* ptrs[3] = {a, b, c};
+    const size_t esz[3] = {sizeof(typename F::In0), sizeof(typename F::In1), sizeof(typename F::In2)};
+    for (int i = 0; i < F::NIN && vec_ok; ++i) {
+        const int64_t si = L.stride[i][inner];
+        if (si == 0) {
+            continue;
+        }
+        if (si != 1 || reinterpret_cast<uintptr_t>(ptrs[i]) % (esz[i] * kVec) != 0) {
+            vec_ok = false;
+            break;
+        }
+        for (int ax = kMaxDims - L.ndim; ax < inner; ++ax) {
+            if (L.stride[i][ax] % kVec != 0) {
+                vec_ok = false;
+            }
+        }
+    }
+    if (vec_ok) {
+        Layout4 V = L;
+        V.dim[inner] /= kVec;
+        for (int i = 0; i < F::NIN; ++i) {
+            V.stride[i][inner] *= kVec;
+        }
+        const int64_t nvec = n / kVec;
+        strided_kernel<F, kVec><<<grid_for(nvec, kThreads), kThreads, 0, ctx->stream>>>(o, a, b, c,
+                                                                                       nvec, V, p);
+    } else {
+        strided_kernel<F, 1><<<grid_for(n, kThreads), kThreads, 0, ctx->stream>>>(o, a, b, c, n, L,
+                                                                                  p);
+    }
+    ctx->count_launch();
+    check_last_launch("elementwise strided");
+}
+
+// ---------------------------------------------------------------------------
+// Creation and index-pattern ops (outputs are dense)
+// ---------------------------------------------------------------------------
+
+template <typename T>
+__global__ void __launch_bounds__(kThreads) fill_kernel(T* __restrict__ out, int64_t n, T value) {
+    const int64_t stride = int64_t(gridDim.x) * blockDim.x;
+    for (int64_t i = int64_t(blockIdx.x) * blockDim.x + threadIdx.x; i < n; i += stride) {
+        out[i] = value;
+    }
+}
+
+// start + i*step evaluated in double with two roundings, then narrowed
+// (kernels_movement.cpp:175-197).
+template <typename T>
+__global__ void __launch_bounds__(kThreads)
+arange_kernel(T* __restrict__ out, int64_t n, double start, double step) {
+    const int64_t stride = int64_t(gridDim.x) * blockDim.x;
+    for (int64_t i = int64_t(blockIdx.x) * blockDim.x + threadIdx.x; i < n; i += stride) {
+        out[i] = static_cast<T>(__dadd_rn(start, __dmul_rn(static_cast<double>(i), step)));
+    }
+}
+
+// Philox4x32-10 keyed by the seed, counter = (index, offset); the first output
+// word's top 24 bits scaled by 2^-24 (src/backend/cpu/philox.h:47-89).
+__global__ void __launch_bounds__(kThreads)
+rand_kernel(float* __restrict__ out, int64_t n, uint64_t seed, uint64_t offset) {
+    const int64_t stride = int64_t(gridDim.x) * blockDim.x;
+    for (int64_t i = int64_t(blockIdx.x) * blockDim.x + threadIdx.x; i < n; i += stride) {
+        uint32_t c0 = static_cast<uint32_t>(i), c1 = static_cast<uint32_t>(uint64_t(i) >> 32);
+        uint32_t c2 = static_cast<uint32_t>(offset), c3 = static_cast<uint32_t>(offset >> 32);
+        uint32_t k0 = static_cast<uint32_t>(seed), k1 = static_cast<uint32_t>(seed >> 32);
+#pragma unroll
+        for (int r = 0; r < 10; ++r) {
+            const uint32_t hi0 = __umulhi(0xD2511F53U, c0), lo0 = 0xD2511F53U * c0;
+            const uint32_t hi1 = __umulhi(0xCD9E8D57U, c2), lo1 = 0xCD9E8D57U * c2;
+            c0 = hi1 ^ c1 ^ k0;
+            c1 = lo1;
+            c2 = hi0 ^ c3 ^ k1;
+            c3 = lo0;
+            k0 += 0x9E3779B9U;
+            k1 += 0xBB67AE85U;
+        }
+        out[i] = static_cast<float>(c0 >> 8) * (1.0F / 16777216.0F);
+    }
+}
+
+// triu/tril over the last two axes (kernels_elementwise.cpp:326-352).
+__global__ void __launch_bounds__(kThreads)
+tri_kernel(float* __restrict__ out, const float* __restrict__ in, Geo gin, int64_t n, int64_t width,
+           int64_t height, int diagonal, int upper) {
+    const int64_t stride = int64_t(gridDim.x) * blockDim.x;
+    for (int64_t i = int64_t(blockIdx.x) * blockDim.x + threadIdx.x; i < n; i += stride) {
+        const int64_t col = i % width;
+        const int64_t row = (i / width) % height;
+        const int64_t d = col - row;
+        const bool keep = upper ? d >= diagonal : d <= diagonal;
+        out[i] = keep ? in[geo_offset(gin, i)] : 0.0F;
+    }
+}
+
+// Two-input concatenation along `axis` (kernels_movement.cpp:272-317).
+template <typename T>
+__global__ void __launch_bounds__(kThreads)
+cat_kernel(T* __restrict__ out, const T* __restrict__ a, const T* __restrict__ b, Geo ga, Geo gb,
+           int64_t n, int64_t inner, int64_t out_extent, int64_t a_extent, int64_t b_extent) {
+    const int64_t stride = int64_t(gridDim.x) * blockDim.x;
+    for (int64_t i = int64_t(blockIdx.x) * blockDim.x + threadIdx.x; i < n; i += stride) {
+        const int64_t rest = i % inner;
+        const int64_t along = (i / inner) % out_extent;
+        const int64_t outer = i / (inner * out_extent);
+        if (along < a_extent) {
+            out[i] = a[geo_offset(ga, (outer * a_extent + along) * inner + rest)];
+        } else {
+            out[i] = b[geo_offset(gb, (outer * b_extent + (along - a_extent)) * inner + rest)];
+        }
+    }
+}
+
+// Adjoint of a strided slice, pull form: every element of the zero-padded result
+// looks up whether a gradient element lands on it (kernels_movement.cpp:226-262).
+__global__ void __launch_bounds__(kThreads)
+slice_backward_kernel(float* __restrict__ out, const float* __restrict__ g, Geo gout, Geo gg,
+                      int64_t n, int axis, int64_t start, int64_t step) {
+    const int64_t stride = int64_t(gridDim.x) * blockDim.x;
+    for (int64_t i = int64_t(blockIdx.x) * blockDim.x + threadIdx.x; i < n; i += stride) {
+        int64_t rem = i;
+        int64_t goff = 0;
+        bool hit = true;
+#pragma unroll
+        for (int a = kMaxDims - 1; a >= 0; --a) {
+            const int64_t idx = rem % gout.dim[a];
+            rem /= gout.dim[a];
+            if (a == axis) {
+                const int64_t rel = idx - start;
+                if (rel < 0 || rel % step != 0 || rel / step >= gg.dim[a]) {
+                    hit = false;
+                } else {
+                    goff += (rel / step) * gg.stride[a];
+                }
+            } else {
+                goff += idx * gg.stride[a];
+            }
+        }
+        out[i] = hit ? g[goff] : 0.0F;
+    }
+}
+
+void run_full(b200_ctx* ctx, const b200_node& node) {
+    const View out = make_view(node.out);
+    const auto p = get_params<FullParams>(node);
+    const int64_t n = out.numel;
+    if (n == 0) {
+        return;
+    }
+    const unsigned g = grid_for(n, kThreads);
+    switch (out.dtype) {
+        case B200_F32:
+            fill_kernel<float><<<g, kThreads, 0, ctx->stream>>>(reinterpret_cast<float*>(out.data), n,
+                                                               static_cast<float>(p.value));
+            break;
+        case B200_F16: {
+            // narrow on the host with the same rule as the device cast
+            const float f = static_cast<float>(p.value);
+            uint16_t bits;
+            if (f != f) {
+                uint32_t w;
+                std::memcpy(&w, &f, 4);
+                bits = static_cast<uint16_t>(((w >> 16) & 0x8000U) | 0x7E00U);
+            } else {
+                const __half h = __float2half_rn(f);
+                std::memcpy(&bits, &h, 2);
+            }
+            fill_kernel<uint16_t><<<g, kThreads, 0, ctx->stream>>>(
+                reinterpret_cast<uint16_t*>(out.data), n, bits);
+            break;
+        }
+        case B200_I64:
+            fill_kernel<int64_t><<<g, kThreads, 0, ctx->stream>>>(
+                reinterpret_cast<int64_t*>(out.data), n, static_cast<int64_t>(p.value));
+            break;
+        case B200_I32:
+            fill_kernel<int32_t><<<g, kThreads, 0, ctx->stream>>>(
+                reinterpret_cast<int32_t*>(out.data), n, static_cast<int32_t>(p.value));
+            break;
+        case B200_BOOL:
+            fill_kernel<uint8_t><<<g, kThreads, 0, ctx->stream>>>(
+                reinterpret_cast<uint8_t*>(out.data), n, static_cast<uint8_t>(p.value != 0.0 ? 1 : 0));
+            break;
+        default: fail(B200_DTYPE_ERROR, "full: unsupported dtype");
+    }
+    ctx->count_launch();
+    check_last_launch("full");
+}
+
+void run_cast(b200_ctx* ctx, const b200_node& node) {
+    const int from = node.src[0].dtype;
+    const int to = node.out.dtype;
+    if (from == to) {
+        switch (dtype_size(to)) {
+            case 1: run<FCopy<uint8_t>>(ctx, node, {}); return;
+            case 2: run<FCopy<uint16_t>>(ctx, node, {}); return;
+            case 4: run<FCopy<uint32_t>>(ctx, node, {}); return;
+            case 8: run<FCopy<uint64_t>>(ctx, node, {}); return;
+        }
+    }
+    // the conversions vkML's CPU backend defines (kernels_movement.cpp:52-123)
+    if (from == B200_F32 && to == B200_I32) return run<FCast<float, int32_t>>(ctx, node, {});
+    if (from == B200_F32 && to == B200_I64) return run<FCast<float, int64_t>>(ctx, node, {});
+    if (from == B200_F32 && to == B200_BOOL) return run<FCastF32Bool>(ctx, node, {});
+    if (from == B200_F32 && to == B200_F16) return run<FCastF32F16>(ctx, node, {});
+    if (from == B200_F16 && to == B200_F32) return run<FCastF16F32>(ctx, node, {});
+    if (from == B200_I32 && to == B200_F32) return run<FCast<int32_t, float>>(ctx, node, {});
+    if (from == B200_I32 && to == B200_I64) return run<FCast<int32_t, int64_t>>(ctx, node, {});
+    if (from == B200_I64 && to == B200_F32) return run<FCast<int64_t, float>>(ctx, node, {});
+    if (from == B200_I64 && to == B200_I32) return run<FCast<int64_t, int32_t>>(ctx, node, {});
+    if (from == B200_BOOL && to == B200_F32) return run<FCastBool<float>>(ctx, node, {});
+    if (from == B200_BOOL && to == B200_I64) return run<FCastBool<int64_t>>(ctx, node, {});
+    fail(B200_DTYPE_ERROR, "cast: unsupported conversion");
+}
+
+void require_f32(const b200_node& node, const char* what) {
+    if (node.out.dtype != B200_F32) {
+        fail(B200_DTYPE_ERROR, std::string(what) + ": only f32 is implemented");
+    }
+}
+
+}  // namespace
+
+void launch_elementwise(b200_ctx* ctx, const b200_node& node) {
+    switch (node.op) {
+        case B200_OP_FULL: run_full(ctx, node); return;
+        case B200_OP_ARANGE: {
+            const View out = make_view(node.out);
+            const auto p = get_params<ArangeParams>(node);
+            if (out.numel == 0) return;
+            if (out.dtype == B200_F32) {
+                arange_kernel<float><<<grid_for(out.numel, kThreads), kThreads, 0, ctx->stream>>>(
+                    reinterpret_cast<float*>(out.data), out.numel, p.start, p.step);
+            } else if (out.dtype == B200_I64) {
+                arange_kernel<int64_t><<<grid_for(out.numel, kThreads), kThreads, 0, ctx->stream>>>(
+                    reinterpret_cast<int64_t*>(out.data), out.numel, p.start, p.step);
+            } else {
+                fail(B200_DTYPE_ERROR, "arange: unsupported dtype");
+            }
+            ctx->count_launch();
+            check_last_launch("arange");
+            return;
+        }
+        case B200_OP_RAND: {
+            require_f32(node, "rand");
+            const View out = make_view(node.out);
+            const auto p = get_params<RandParams>(node);
+            if (out.numel == 0) return;
+            rand_kernel<<<grid_for(out.numel, kThreads), kThreads, 0, ctx->stream>>>(
+                reinterpret_cast<float*>(out.data), out.numel, p.seed, p.offset);
+            ctx->count_launch();
+            check_last_launch("rand");
+            return;
+        }
+        case B200_OP_CONTIGUOUS:
+            if (node.src[0].dtype != node.out.dtype) {
+                fail(B200_DTYPE_ERROR, "contiguous must not change dtype");
+            }
+            switch (dtype_size(node.out.dtype)) {
+                case 1: run<FCopy<uint8_t>>(ctx, node, {}); return;
+                case 2: run<FCopy<uint16_t>>(ctx, node, {}); return;
+                case 4: run<FCopy<uint32_t>>(ctx, node, {}); return;
+                case 8: run<FCopy<uint64_t>>(ctx, node, {}); return;
+            }
+            fail(B200_DTYPE_ERROR, "contiguous: unknown dtype");
+        case B200_OP_CAST: run_cast(ctx, node); return;
+        case B200_OP_TRIU:
+        case B200_OP_TRIL: {
+            require_f32(node, "triu/tril");
+            const View out = make_view(node.out);
+            const View in = make_view(node.src[0]);
+            if (out.numel == 0) return;
+            const auto p = get_params<TriParams>(node);
+            tri_kernel<<<grid_for(out.numel, kThreads), kThreads, 0, ctx->stream>>>(
+                reinterpret_cast<float*>(out.data), reinterpret_cast<const float*>(in.data),
+                geo_of(in), out.numel, out.dim[3], out.dim[2], p.diagonal,
+                node.op == B200_OP_TRIU ? 1 : 0);
+            ctx->count_launch();
+            check_last_launch("tri");
+            return;
+        }
+        case B200_OP_CAT: {
+            const View out = make_view(node.out);
+            const View a = make_view(node.src[0]);
+            const View b = make_view(node.src[1]);
+            if (out.numel == 0) return;
+            const int axis = get_params<AxisParams>(node).axis + (kMaxDims - node.out.ndim);
+            int64_t inner = 1;
+            for (int i = axis + 1; i < kMaxDims; ++i) inner *= out.dim[i];
+            const unsigned g = grid_for(out.numel, kThreads);
+            if (dtype_size(out.dtype) == 4) {
+                cat_kernel<uint32_t><<<g, kThreads, 0, ctx->stream>>>(
+                    reinterpret_cast<uint32_t*>(out.data), reinterpret_cast<const uint32_t*>(a.data),
+                    reinterpret_cast<const uint32_t*>(b.data), geo_of(a), geo_of(b), out.numel, inner,
+                    out.dim[axis], a.dim[axis], b.dim[axis]);
+            } else {
+                fail(B200_DTYPE_ERROR, "cat: only 4-byte dtypes are implemented");
+            }
+            ctx->count_launch();
+            check_last_launch("cat");
+            return;
+        }
+        case B200_OP_SLICE_BACKWARD: {
+            require_f32(node, "slice_backward");
+            const View out = make_view(node.out);
+            const View g = make_view(node.src[0]);
+            if (out.numel == 0) return;
+            const auto p = get_params<SliceParams>(node);
+            slice_backward_kernel<<<grid_for(out.numel, kThreads), kThreads, 0, ctx->stream>>>(
+                reinterpret_cast<float*>(out.data), reinterpret_cast<const float*>(g.data),
+                geo_of(out), geo_of(g), out.numel, p.axis + (kMaxDims - node.out.ndim), p.start,
+                p.step);
+            ctx->count_launch();
+            check_last_launch("slice_backward");
+            return;
+        }
+        case B200_OP_WHERE:
+            require_f32(node, "where");
+            run<FWhere>(ctx, node, {});
+            return;
+        case B200_OP_SCALED_ADD:
+            require_f32(node, "scaled_add");
+            run<FScaledAdd>(ctx, node, get_params<ScaledAddParams>(node));
+            return;
+        case B200_OP_CLAMP:
+            require_f32(node, "clamp");
+            run<FClamp>(ctx, node, get_params<ClampParams>(node));
+            return;
+        default: break;
+    }
+
+    if (node.op >= B200_OP_EQUAL && node.op <= B200_OP_NOT_EQUAL) {
+        if (node.out.dtype != B200_BOOL || node.src[0].dtype != B200_F32 ||
+            node.src[1].dtype != B200_F32) {
+            fail(B200_DTYPE_ERROR, "comparison: expects f32 operands and a bool result");
+        }
+        switch (node.op) {
+            case B200_OP_EQUAL: run<FEqual>(ctx, node, {}); return;
+            case B200_OP_LESS: run<FLess>(ctx, node, {}); return;
+            case B200_OP_GREATER: run<FGreater>(ctx, node, {}); return;
+            case B200_OP_LESS_EQUAL: run<FLessEqual>(ctx, node, {}); return;
+            case B200_OP_GREATER_EQUAL: run<FGreaterEqual>(ctx, node, {}); return;
+            case B200_OP_NOT_EQUAL: run<FNotEqual>(ctx, node, {}); return;
+        }
+    }
+
+    require_f32(node, "elementwise");
+    switch (node.op) {
+        case B200_OP_ADD: run<FAdd>(ctx, node, {}); return;
+        case B200_OP_SUB: run<FSub>(ctx, node, {}); return;
+        case B200_OP_MUL: run<FMul>(ctx, node, {}); return;
+        case B200_OP_DIV: run<FDiv>(ctx, node, {}); return;
+        case B200_OP_POW: run<FPow>(ctx, node, {}); return;
+        case B200_OP_MAXIMUM: run<FMaximum>(ctx, node, {}); return;
+        case B200_OP_MINIMUM: run<FMinimum>(ctx, node, {}); return;
+        case B200_OP_NEG: run<FNeg>(ctx, node, {}); return;
+        case B200_OP_ABS: run<FAbs>(ctx, node, {}); return;
+        case B200_OP_SIGN: run<FSign>(ctx, node, {}); return;
+        case B200_OP_SQUARE: run<FSquare>(ctx, node, {}); return;
+        case B200_OP_SQRT: run<FSqrt>(ctx, node, {}); return;
+        case B200_OP_RSQRT: run<FRsqrt>(ctx, node, {}); return;
+        case B200_OP_RECIPROCAL: run<FReciprocal>(ctx, node, {}); return;
+        case B200_OP_EXP: run<FExp>(ctx, node, {}); return;
+        case B200_OP_LOG: run<FLog>(ctx, node, {}); return;
+        case B200_OP_ERF: run<FErf>(ctx, node, {}); return;
+        case B200_OP_ERFC: run<FErfc>(ctx, node, {}); return;
+        case B200_OP_SIN: run<FSin>(ctx, node, {}); return;
+        case B200_OP_COS: run<FCos>(ctx, node, {}); return;
+        case B200_OP_TANH: run<FTanh>(ctx, node, {}); return;
+        case B200_OP_SIGMOID: run<FSigmoid>(ctx, node, {}); return;
+        case B200_OP_RELU: run<FRelu>(ctx, node, {}); return;
+        case B200_OP_GELU: run<FGelu>(ctx, node, {}); return;
+        case B200_OP_SILU: run<FSilu>(ctx, node, {}); return;
+        default: fail(B200_NOT_IMPLEMENTED, "elementwise: unhandled op");
+    }
+}
+
+}  // namespace b200

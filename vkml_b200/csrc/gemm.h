@@ -1,0 +1,28 @@
+// Batched GEMM problem as vkML's matmul node presents it
+// (src/backend/cpu/kernels_matmul.cpp:35-87): rank-4 operands
+// a[B0,B1,M,K], b[B0,B1,K,N] with arbitrary element strides (stride 0 on a batch
+// axis = broadcast, transposed views = swapped inner strides), dense output
+// out[B0,B1,M,N].
+#pragma once
+
+#include "context.h"
+
+namespace b200 {
+
+struct GemmProblem {
+    const float* a;
+    const float* b;
+    float* out;
+    int64_t b0, b1, m, n, k;
+    int64_t a_s[4];  // element strides of a over (b0, b1, m, k)
+    int64_t b_s[4];  // element strides of b over (b0, b1, k, n)
+};
+
+// fp32 FMA on the CUDA cores; any strides, any size. gemm_simt.cu
+void gemm_simt(b200_ctx* ctx, const GemmProblem& p);
+
+// tcgen05 tensor-core path (3xTF32 or single-pass TF32). gemm_tc.cu
+bool gemm_tc_eligible(const b200_ctx* ctx, const GemmProblem& p);
+void gemm_tc(b200_ctx* ctx, const GemmProblem& p, bool three_pass);
+
+}  // namespace b200
