@@ -1,0 +1,356 @@
+#!/usr/bin/env python
+"""Benchmark of the backend hot path: fp32 GEMM C = A.B at 8192^3 through
+vkML's matmul node (3xTF32 on the tcgen05 tensor cores), as whole-job TFLOP/s.
+
+    python bench.py --gpus N --steps K --warmup W            (N > 1: under torchrun)
+    python bench.py --impl reference ...                     the reference CPU path
+
+One step = one matmul node through Backend.compute(): operand split pre-pass
+(A and B), the tensor-core kernel, nothing skipped.  A, B ~ N(0,1) from a fixed
+seed, generated on the host and uploaded once; operands (268 MB each) exceed L2.
+`value` times K steps with the inputs resident in HBM, on the device, max over
+ranks.  `e2e` times the same call with HOST buffers: pinned A and B are copied
+up and C is copied back inside every timed step.  `roofline` is the tensor-core
+kernel alone, from CUDA events around each launch on the launching stream.
+`cpu_baseline` is the reference CPU backend's matmul kernel (compiled from the
+reference's own sources into oracle/_ref/) on a bounded row slab of the same
+product, on all host cores.  At N > 1 every rank runs the same GEMM on its own
+operands (independent replicas: a GEMM node has no exchange step).
+"""
+from __future__ import annotations
+
+import argparse
+import ctypes as C
+import json
+import os
+import sys
+import threading
+import time
+
+import numpy as np
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+SEED_DATA = 20260728
+# dram__bytes_read.sum + dram__bytes_write.sum of one launch of the tensor-core kernel,
+# from profiles/ (None until a capture of this kernel has been taken).
+TRAFFIC_BYTES_PER_LAUNCH = None
+
+
+def parse():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
+    ap.add_argument("--size", type=int, default=8192, help="M = N = K")
+    ap.add_argument("--precision", default="3xtf32", choices=["3xtf32", "tf32", "fp32"])
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-e2e", action="store_true")
+    return ap.parse_args()
+
+
+def peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        with open(path) as f:
+            p = json.load(f)
+        return {"hbm_gbs": p["hbm_gbs"], "bf16_tflops": p["bf16_tflops"],
+                "bf16_tflops_sustained": p.get("bf16_tflops_sustained"), "source": "measured"}
+    return {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0, "source": "fallback"}
+
+
+class ClockSampler(threading.Thread):
+    """Samples SM clock and throttle reasons through NVML while the timed region runs (read-only)."""
+
+    def __init__(self, index: int):
+        super().__init__(daemon=True)
+        self.index, self.samples, self.reasons, self.max_mhz = index, [], set(), None
+        self._stop_evt = threading.Event()
+        try:
+            import pynvml
+            pynvml.nvmlInit()
+            self.nv = pynvml
+            self.h = pynvml.nvmlDeviceGetHandleByIndex(index)
+            self.max_mhz = pynvml.nvmlDeviceGetMaxClockInfo(self.h, pynvml.NVML_CLOCK_SM)
+        except Exception:
+            self.nv = None
+
+    def run(self):
+        if self.nv is None:
+            return
+        nv = self.nv
+        names = {"hw_slowdown": getattr(nv, "nvmlClocksThrottleReasonHwSlowdown", 0x8),
+                 "hw_thermal_slowdown": getattr(nv, "nvmlClocksThrottleReasonHwThermalSlowdown", 0x40),
+                 "sw_thermal_slowdown": getattr(nv, "nvmlClocksThrottleReasonSwThermalSlowdown", 0x20),
+                 "sw_power_cap": getattr(nv, "nvmlClocksThrottleReasonSwPowerCap", 0x4)}
+        while not self._stop_evt.is_set():
+            try:
+                self.samples.append(nv.nvmlDeviceGetClockInfo(self.h, nv.NVML_CLOCK_SM))
+                bits = nv.nvmlDeviceGetCurrentClocksThrottleReasons(self.h)
+                for k, v in names.items():
+                    if bits & v:
+                        self.reasons.add(k)
+            except Exception:
+                pass
+            time.sleep(0.004)
+
+    def stop(self):
+        self._stop_evt.set()
+        self.join(timeout=2)
+        med = float(np.median(self.samples)) if self.samples else None
+        return {"sm_mhz": med, "sm_max_mhz": self.max_mhz, "reasons": sorted(self.reasons),
+                "samples": len(self.samples)}
+
+
+def make_operands(size: int, rank: int):
+    rng = np.random.default_rng(SEED_DATA + rank)
+    a = rng.standard_normal((size, size), dtype=np.float32)
+    b = rng.standard_normal((size, size), dtype=np.float32)
+    return a, b
+
+
+# ---------------------------------------------------------------------------
+# reference CPU path (oracle/_ref): used by --impl reference and by cpu_baseline
+# ---------------------------------------------------------------------------
+
+def reference_lib():
+    from vkml_b200 import _abi
+    path = os.path.join(ROOT, "oracle", "_ref", "libvkml_ref.so")
+    if not os.path.exists(path):
+        return None
+    lib = C.CDLL(path)
+    lib.vkml_ref_matmul_mt.restype = C.c_int
+    lib.vkml_ref_matmul_mt.argtypes = [C.POINTER(_abi.Node), C.c_int]
+    return lib
+
+
+def reference_slab_seconds(lib, a, b, rows: int, threads: int) -> float:
+    """Seconds the reference matmul kernel takes for A[:rows] . B on `threads` host threads."""
+    from vkml_b200.graph import DType, NodeDesc, Op, TensorDesc
+    k, n = b.shape
+    out = np.empty((rows, n), dtype=np.float32)
+    node = NodeDesc(int(Op.MATMUL), TensorDesc.contiguous(out.ctypes.data, (1, 1, rows, n), DType.F32),
+                    [TensorDesc.contiguous(a.ctypes.data, (1, 1, rows, k), DType.F32),
+                     TensorDesc.contiguous(b.ctypes.data, (1, 1, k, n), DType.F32)])
+    c = node.to_c()
+    t0 = time.perf_counter()
+    rc = lib.vkml_ref_matmul_mt(C.byref(c), threads)
+    dt = time.perf_counter() - t0
+    if rc != 0:
+        raise RuntimeError(f"reference matmul failed with status {rc}")
+    return dt
+
+
+def cpu_baseline(a, b, budget_s: float = 12.0):
+    lib = reference_lib()
+    cores = os.cpu_count() or 1
+    size = a.shape[0]
+    if lib is None:
+        return None
+    probe_rows = cores
+    t = reference_slab_seconds(lib, a, b, probe_rows, cores)
+    rows = int(max(cores, min(size, probe_rows * budget_s / max(t, 1e-6))))
+    rows = max(cores, rows // cores * cores)
+    t = reference_slab_seconds(lib, a, b, rows, cores)
+    flops = 2.0 * rows * size * size
+    return {"value": flops / t / 1e12, "unit": "TFLOP/s", "cores": cores, "kind": "reference",
+            "sample": f"rows 0..{rows} of A: a {rows}x{size}x{size} slab of the {size}^3 product through the "
+                      f"reference matmul kernel, {cores} host threads over row slabs, {t:.1f} s",
+            "seconds": t, "full_size_seconds_extrapolated": t * size / rows}
+
+
+def run_reference(args, rank, world):
+    if rank != 0:
+        return
+    a, b = make_operands(args.size, 0)
+    lib = reference_lib()
+    base = {"impl": "reference", "metric": "fp32_gemm_tflops", "unit": "TFLOP/s", "n_gpus": args.gpus,
+            "steps": args.steps, "warmup": args.warmup, "higher_is_better": True, "scaling": "weak",
+            "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+            "config": {"workload": f"fp32 GEMM {args.size}^3, A,B ~ N(0,1)", "m": args.size, "n": args.size,
+                       "k": args.size}}
+    if lib is None:
+        print(json.dumps({"impl": "reference", "unavailable": "oracle/_ref/libvkml_ref.so is not built"}))
+        return
+    cores = os.cpu_count() or 1
+    # size one step at ~2 s of CPU work so steps+warmup stay within minutes
+    t_probe = reference_slab_seconds(lib, a, b, cores, cores)
+    total = max(1, args.steps + args.warmup)
+    rows = int(max(cores, min(args.size, cores * min(2.0, 150.0 / total) / max(t_probe, 1e-6))))
+    rows = max(cores, rows // cores * cores)
+    for _ in range(args.warmup):
+        reference_slab_seconds(lib, a, b, rows, cores)
+    t = 0.0
+    for _ in range(args.steps):
+        t += reference_slab_seconds(lib, a, b, rows, cores)
+    flops = 2.0 * rows * args.size * args.size * args.steps
+    v = flops / t / 1e12
+    base.update({"value": v, "ms_per_step": t / args.steps * 1e3,
+                 "cpu_baseline": {"value": v, "unit": "TFLOP/s", "cores": cores, "kind": "reference",
+                                  "sample": f"each step: rows 0..{rows} of A ({rows}x{args.size}x{args.size} slab) "
+                                            f"through the reference CPU matmul kernel on {cores} threads"},
+                 "e2e": {"value": v, "unit": "TFLOP/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}})
+    print(json.dumps(base))
+
+
+# ---------------------------------------------------------------------------
+# B200 arm
+# ---------------------------------------------------------------------------
+
+def run_b200(args, rank, local_rank, world):
+    import vkml_b200
+    from vkml_b200 import DeviceTensor, NodeDesc, Op, graph
+    dist = None
+    if world > 1:
+        import torch
+        import torch.distributed as td
+        torch.cuda.set_device(local_rank)
+        td.init_process_group(backend="nccl", device_id=torch.device("cuda", local_rank))
+        dist = td
+
+    backend = vkml_b200.Backend(local_rank)  # raises without the CUDA library or a device
+    backend.set_gemm_precision({"3xtf32": 0, "tf32": 1, "fp32": 2}[args.precision])
+    size = args.size
+    a_host, b_host = make_operands(size, rank)
+    a = DeviceTensor.from_host(backend, a_host).reshape((1, 1, size, size))
+    b = DeviceTensor.from_host(backend, b_host).reshape((1, 1, size, size))
+    c = DeviceTensor.empty(backend, (1, 1, size, size))
+    node = NodeDesc(int(Op.MATMUL), c.desc, [a.desc, b.desc])
+    packed = graph.pack_nodes([node])
+    flops_per_step = 2.0 * size ** 3
+
+    def barrier():
+        backend.synchronize()
+        if dist is not None:
+            import torch
+            torch.cuda.synchronize()
+            dist.barrier()
+
+    def max_over_ranks(ms: float) -> float:
+        if dist is None:
+            return ms
+        import torch
+        t = torch.tensor([ms], dtype=torch.float64, device="cuda")
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t.item())
+
+    # ---- device-resident timing ----
+    for _ in range(max(args.warmup, 3)):
+        backend.compute_packed(packed, 1)
+    barrier()
+    sampler = ClockSampler(local_rank)
+    sampler.start()
+    backend.set_profiling(True)
+    launches0 = backend.stats()["kernel_launches"]
+    backend.timer_begin()
+    for _ in range(args.steps):
+        backend.compute_packed(packed, 1)
+    ms = backend.timer_end()
+    barrier()
+    launches = backend.stats()["kernel_launches"] - launches0
+    records = backend.last_profile()
+    backend.set_profiling(False)
+    clocks = sampler.stop()
+    ms = max_over_ranks(ms)
+    value = flops_per_step * args.steps * world / (ms * 1e-3) / 1e12
+
+    # ---- roofline of the dominant kernel ----
+    pk = peaks()
+    by_label = {}
+    for label, t in records:
+        by_label.setdefault(label, []).append(t)
+    main_label = max(by_label, key=lambda k: sum(by_label[k])) if by_label else None
+    roofline = None
+    kernel_share = {k: {"launches": len(v), "total_ms": sum(v)} for k, v in by_label.items()}
+    if main_label is not None:
+        avg_ms = sum(by_label[main_label]) / len(by_label[main_label])
+        achieved = flops_per_step / (avg_ms * 1e-3) / 1e12
+        passes = 3 if args.precision == "3xtf32" else 1
+        # TF32 issues at half the bf16 rate; MEASURED_PEAKS.json has no TF32 entry, so the
+        # denominator is half the measured bf16 burst figure.
+        peak = pk["bf16_tflops"] / 2.0
+        roofline = {"bound": "tensor", "kernel": main_label, "achieved": achieved, "peak": peak,
+                    "unit": "TFLOP/s", "frac": achieved / peak,
+                    "traffic": TRAFFIC_BYTES_PER_LAUNCH, "avg_launch_ms": avg_ms,
+                    "tensor_pipe_tflops": achieved * passes, "tensor_pipe_frac": achieved * passes / peak,
+                    "peak_source": f"{pk['source']}: bf16_tflops/2 (TF32 runs at half the bf16 rate)",
+                    "note": "achieved counts the algorithmic 2*M*N*K once; 3xTF32 issues it three times on "
+                            "the tensor pipe (tensor_pipe_*), so frac cannot exceed 1/3"}
+        if args.precision == "fp32":
+            roofline["bound"] = "fp32-simt"
+
+    # ---- end to end with host buffers ----
+    e2e = None
+    if not args.no_e2e:
+        nbytes = size * size * 4
+        pin_a, pin_b, pin_c = backend.alloc_host(nbytes), backend.alloc_host(nbytes), backend.alloc_host(nbytes)
+        pin_a[:] = a_host.view(np.uint8).reshape(-1)
+        pin_b[:] = b_host.view(np.uint8).reshape(-1)
+        e_steps = max(3, min(args.steps, 10))
+
+        def e2e_step():
+            backend.copy_from_host(a.storage, 0, pin_a.ctypes.data, nbytes)
+            backend.copy_from_host(b.storage, 0, pin_b.ctypes.data, nbytes)
+            backend.compute_packed(packed, 1)
+            backend.copy_to_host(pin_c, c.storage, 0, nbytes)
+
+        for _ in range(2):
+            e2e_step()
+        barrier()
+        backend.timer_begin()
+        t0 = time.perf_counter()
+        for _ in range(e_steps):
+            e2e_step()
+        e_ms = backend.timer_end()
+        wall_ms = (time.perf_counter() - t0) * 1e3
+        barrier()
+        e_ms = max_over_ranks(max(e_ms, wall_ms))
+        e2e = {"value": flops_per_step * e_steps * world / (e_ms * 1e-3) / 1e12, "unit": "TFLOP/s",
+               "h2d_bytes_per_step": 2 * nbytes, "d2h_bytes_per_step": nbytes, "steps": e_steps,
+               "ms_per_step": e_ms / e_steps}
+        checksum = float(np.frombuffer(pin_c, dtype=np.float32)[:1024].sum())
+        e2e["result_checksum_first_1024"] = checksum
+        for p in (pin_a, pin_b, pin_c):
+            backend.free_host(p)
+
+    cpu = None
+    if rank == 0 and world == 1 and not args.no_cpu_baseline:
+        cpu = cpu_baseline(a_host, b_host)
+
+    if rank == 0:
+        line = {
+            "metric": "fp32_gemm_tflops", "value": value, "unit": "TFLOP/s", "n_gpus": world, "steps": args.steps,
+            "warmup": max(args.warmup, 3), "ms_per_step": ms / args.steps, "higher_is_better": True,
+            "scaling": "weak", "vs_baseline": None,
+            "dtype": {"3xtf32": "f32 (3xTF32 split on tcgen05, fp32 accumulate)", "tf32": "tf32",
+                      "fp32": "f32"}[args.precision],
+            "data": "synthetic",
+            "config": {"workload": f"fp32 GEMM C=A.B, M=N=K={size}, A,B ~ N(0,1) seed {SEED_DATA}, one matmul node "
+                                   "through Backend.compute (operand split + tensor-core kernel)",
+                       "m": size, "n": size, "k": size, "precision": args.precision,
+                       "cache": "operands (268 MB each at 8192) exceed L2; no flush needed",
+                       "parallelism": "independent replicas" if world > 1 else "single GPU"},
+            "roofline": roofline, "cpu_baseline": cpu, "e2e": e2e, "gpu_launches": launches,
+            "kernels": kernel_share, "clocks": clocks,
+        }
+        print(json.dumps(line))
+    if dist is not None:
+        dist.barrier()
+        dist.destroy_process_group()
+
+
+def main():
+    args = parse()
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    if args.impl == "reference":
+        run_reference(args, rank, world)
+    else:
+        run_b200(args, rank, local_rank, world)
+
+
+if __name__ == "__main__":
+    main()

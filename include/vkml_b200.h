@@ -189,6 +189,30 @@ const char* b200_status_name(int status);
 
 int b200_get_stats(b200_ctx* ctx, b200_stats* out);
 
+/* Per-dispatch device timing, the counterpart of the Vulkan backend's timestamp
+ * queries and last_profile() (include/vkml/backend/vulkan/vulkan_backend.h:163-203):
+ * while enabled, every kernel launch is bracketed by CUDA events on the
+ * context's stream. b200_profile_read synchronises, resolves the events into
+ * (label, milliseconds) records in launch order and clears the list. */
+typedef struct b200_profile_record {
+    char label[48];
+    float ms;
+    uint32_t op; /* b200_op of the node the launch belongs to */
+} b200_profile_record;
+int b200_profile_enable(b200_ctx* ctx, int on);
+int b200_profile_read(b200_ctx* ctx, b200_profile_record* out, size_t capacity, size_t* count);
+
+/* A stopwatch on the context's stream: begin records a CUDA event, end records
+ * a second one, waits for it and returns the device time between them. */
+int b200_timer_begin(b200_ctx* ctx);
+int b200_timer_end(b200_ctx* ctx, float* milliseconds);
+
+/* Page-locked host memory for uploads and downloads that should run at full
+ * PCIe rate (the role of the Vulkan backend's staging buffers,
+ * src/backend/vulkan/vulkan_backend.cpp:2720-2793). */
+int b200_alloc_host(b200_ctx* ctx, size_t nbytes, void** out);
+int b200_free_host(b200_ctx* ctx, void* ptr);
+
 /* Matmul kernel policy: replaces the VKML_GEMM_* switches
  * (vulkan_backend.cpp:2160-2178). */
 int b200_set_gemm_precision(b200_ctx* ctx, int precision);

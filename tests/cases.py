@@ -87,6 +87,7 @@ def check(case: Case, got: np.ndarray, want: np.ndarray, exact_override: bool = 
         return
     kind, ulp, rtol, atol = POLICY["exact"] if exact_override else policy_for(case.op_name)
     floating = np.issubdtype(got.dtype, np.floating)
+    nan_g = np.zeros(got.shape, dtype=bool)
     if floating:
         nan_g, nan_w = np.isnan(got), np.isnan(want)
         assert np.array_equal(nan_g, nan_w), f"{case.name}: NaN pattern differs"
@@ -370,6 +371,46 @@ def matmul_cases(seed=11, quick=False):
     yield mk("sliced", big[3:35, 10:74:2], rnd(32, 50))
     yield mk("empty-k", np.zeros((4, 0), np.float32), np.zeros((0, 5), np.float32))
     yield mk("empty-m", np.zeros((0, 4), np.float32), rnd(4, 5))
+
+
+def matmul_tc_cases(seed=12):
+    """Shapes large enough for the tensor-core path, with every operand-major
+    combination, ragged edges in M, N and K, batches and broadcast batches."""
+    rng = np.random.default_rng(seed)
+
+    def rnd(*shape):
+        return rng.standard_normal(shape).astype(np.float32)
+
+    def mk(tag, a4, b4):
+        bshape = np.broadcast_shapes(a4.shape[:2], b4.shape[:2])
+        a4 = np.broadcast_to(a4, bshape + a4.shape[2:])
+        b4 = np.broadcast_to(b4, bshape + b4.shape[2:])
+        m, k, n = a4.shape[2], a4.shape[3], b4.shape[3]
+        tas = np.abs(a4.astype(np.float64)) @ np.abs(b4.astype(np.float64))
+        return Case(f"matmul-tc/{tag}/{m}x{k}x{n}/batch={bshape}", Op.MATMUL, [a4, b4], bshape + (m, n), DType.F32,
+                    terms_abs_sum=tas, reduction_n=k)
+
+    def t(x):  # same values, transposed storage
+        return np.ascontiguousarray(np.swapaxes(x, -1, -2)).swapaxes(-1, -2)
+
+    m, k, n = 300, 1000, 520
+    yield mk("nn", rnd(1, 1, m, k), rnd(1, 1, k, n))
+    yield mk("nt", rnd(1, 1, m, k), t(rnd(1, 1, k, n)))
+    yield mk("tn", t(rnd(1, 1, m, k)), rnd(1, 1, k, n))
+    yield mk("tt", t(rnd(1, 1, m, k)), t(rnd(1, 1, k, n)))
+    yield mk("bn64", rnd(1, 1, 257, 777), rnd(1, 1, 777, 50))
+    yield mk("bn128", rnd(1, 1, 129, 513), rnd(1, 1, 513, 100))
+    yield mk("bn256", rnd(1, 1, 2100, 96), rnd(1, 1, 96, 2500))
+    yield mk("k33", rnd(1, 1, 1024, 33), rnd(1, 1, 33, 1024))
+    yield mk("split-k", rnd(1, 1, 128, 8192), rnd(1, 1, 8192, 128))
+    yield mk("skinny", rnd(1, 1, 64, 2048), t(rnd(1, 1, 2048, 512)))
+    yield mk("batched", rnd(2, 3, 150, 200), rnd(2, 3, 200, 130))
+    yield mk("conv-fwd-bcast-a", rnd(1, 1, 128, 576), rnd(1, 8, 576, 256))
+    yield mk("conv-dw", rnd(1, 8, 128, 256), t(rnd(1, 8, 256, 576)))
+    yield mk("conv-dcols-bcast-a", t(rnd(1, 1, 576, 128)), rnd(1, 8, 128, 256))
+    yield mk("bcast-b", rnd(4, 1, 100, 300), rnd(1, 1, 300, 200))
+    big = rnd(1, 1, 700, 1200)
+    yield mk("sliced", big[:, :, 5:605, 16:1016], rnd(1, 1, 1000, 300))
 
 
 def movement_cases(seed=21, quick=False):

@@ -65,6 +65,11 @@ class Stats(C.Structure):
         "nodes_computed", "comm_bytes")]
 
 
+class ProfileRecord(C.Structure):
+    """b200_profile_record"""
+    _fields_ = [("label", C.c_char * 48), ("ms", C.c_float), ("op", C.c_uint32)]
+
+
 # Every symbol include/vkml_b200.h declares: name -> (restype, argtypes).
 _P = C.c_void_p
 SYMBOLS = {
@@ -85,6 +90,12 @@ SYMBOLS = {
     "b200_last_error": (C.c_char_p, [_P]),
     "b200_status_name": (C.c_char_p, [C.c_int]),
     "b200_get_stats": (C.c_int, [_P, C.POINTER(Stats)]),
+    "b200_profile_enable": (C.c_int, [_P, C.c_int]),
+    "b200_profile_read": (C.c_int, [_P, C.POINTER(ProfileRecord), C.c_size_t, C.POINTER(C.c_size_t)]),
+    "b200_timer_begin": (C.c_int, [_P]),
+    "b200_timer_end": (C.c_int, [_P, C.POINTER(C.c_float)]),
+    "b200_alloc_host": (C.c_int, [_P, C.c_size_t, C.POINTER(_P)]),
+    "b200_free_host": (C.c_int, [_P, _P]),
     "b200_set_gemm_precision": (C.c_int, [_P, C.c_int]),
     "b200_get_gemm_precision": (C.c_int, [_P]),
     "b200_stream": (_P, [_P]),

@@ -174,6 +174,40 @@ class Backend:
         self._check(self._lib.b200_get_stats(self._ctx, C.byref(s)), "stats")
         return {name: getattr(s, name) for name, _ in s._fields_}
 
+    def set_profiling(self, enabled: bool) -> None:
+        """Bracket every kernel launch with device timestamps (VulkanBackend::set_profiling)."""
+        self._check(self._lib.b200_profile_enable(self._ctx, 1 if enabled else 0), "profile_enable")
+
+    def last_profile(self, capacity: int = 65536) -> list:
+        """[(label, gpu_ms)] in launch order since the last read; synchronises."""
+        buf = (_abi.ProfileRecord * capacity)()
+        n = C.c_size_t(0)
+        self._check(self._lib.b200_profile_read(self._ctx, buf, capacity, C.byref(n)), "profile_read")
+        return [(buf[i].label.decode(), float(buf[i].ms)) for i in range(n.value)]
+
+    def timer_begin(self) -> None:
+        self._check(self._lib.b200_timer_begin(self._ctx), "timer_begin")
+
+    def timer_end(self) -> float:
+        """Device milliseconds since timer_begin, on the context's stream; synchronises."""
+        ms = C.c_float(0)
+        self._check(self._lib.b200_timer_end(self._ctx, C.byref(ms)), "timer_end")
+        return float(ms.value)
+
+    def alloc_host(self, nbytes: int) -> np.ndarray:
+        """Page-locked host bytes as a uint8 array (freed with free_host)."""
+        ptr = C.c_void_p()
+        self._check(self._lib.b200_alloc_host(self._ctx, nbytes, C.byref(ptr)), "alloc_host")
+        arr = np.ctypeslib.as_array((C.c_uint8 * nbytes).from_address(ptr.value))
+        self._pinned = getattr(self, "_pinned", {})
+        self._pinned[arr.ctypes.data] = ptr.value
+        return arr
+
+    def free_host(self, arr: np.ndarray) -> None:
+        ptr = getattr(self, "_pinned", {}).pop(arr.ctypes.data, None)
+        if ptr is not None:
+            self._check(self._lib.b200_free_host(self._ctx, ptr), "free_host")
+
     def trim(self) -> None:
         self._check(self._lib.b200_trim(self._ctx), "trim")
 

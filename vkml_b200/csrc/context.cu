@@ -3,6 +3,7 @@
 #include "gemm.h"
 
 #include <algorithm>
+#include <cstdlib>
 #include <new>
 
 namespace b200 {
@@ -13,6 +14,40 @@ void check_last_launch(const char* what) {
         cudaGetLastError();  // clear the sticky launch error so the context stays usable
         fail(B200_DEVICE_ERROR, std::string(what) + ": launch failed: " + cudaGetErrorString(err));
     }
+}
+
+ProfScope::ProfScope(b200_ctx* ctx, const char* label) : ctx_(ctx) {
+    if (!ctx->profiling) {
+        return;
+    }
+    ProfEntry e{};
+    std::snprintf(e.label, sizeof(e.label), "%s", label);
+    e.op = ctx->current_op;
+    if (cudaEventCreate(&e.begin) != cudaSuccess || cudaEventCreate(&e.end) != cudaSuccess) {
+        cudaGetLastError();
+        return;
+    }
+    cudaEventRecord(e.begin, ctx->stream);
+    ctx->prof.push_back(e);
+    index_ = static_cast<int>(ctx->prof.size()) - 1;
+}
+
+ProfScope::~ProfScope() {
+    if (index_ >= 0) {
+        cudaEventRecord(ctx_->prof[static_cast<size_t>(index_)].end, ctx_->stream);
+    }
+}
+
+const char* op_label(uint32_t op) {
+    static const char* const names[B200_OP_COUNT] = {
+        "input", "const", "full", "arange", "rand", "reshape", "permute", "slice", "broadcast", "squeeze",
+        "unsqueeze", "contiguous", "cast", "cat", "add", "sub", "mul", "scaled_add", "div", "pow", "maximum",
+        "minimum", "equal", "less", "greater", "less_equal", "greater_equal", "not_equal", "neg", "abs", "sign",
+        "square", "sqrt", "rsqrt", "reciprocal", "exp", "log", "erf", "erfc", "sin", "cos", "tanh", "sigmoid",
+        "relu", "gelu", "silu", "clamp", "sum", "mean", "max", "min", "prod", "argmax", "argmin", "matmul",
+        "softmax", "log_softmax", "im2col", "col2im", "max_pool2d", "max_pool2d_backward", "index_select",
+        "scatter_add", "slice_backward", "where", "triu", "tril"};
+    return op < B200_OP_COUNT ? names[op] : "?";
 }
 
 // ---------------------------------------------------------------------------
@@ -187,9 +222,13 @@ void dispatch_matmul(b200_ctx* ctx, const b200_node& node) {
 
 void dispatch_node(b200_ctx* ctx, const b200_node& node) {
     const uint32_t op = node.op;
+    ctx->current_op = op;
     if (op == B200_OP_MATMUL) {
-        dispatch_matmul(ctx, node);
-    } else if (op == B200_OP_SOFTMAX || op == B200_OP_LOG_SOFTMAX) {
+        dispatch_matmul(ctx, node);  // times its kernels one by one
+        return;
+    }
+    ProfScope scope(ctx, op_label(op));
+    if (op == B200_OP_SOFTMAX || op == B200_OP_LOG_SOFTMAX) {
         launch_softmax(ctx, node);
     } else if (op >= B200_OP_SUM && op <= B200_OP_ARGMIN) {
         if (op == B200_OP_PROD) {
@@ -364,6 +403,15 @@ int b200_create(int cuda_ordinal, b200_ctx** out) {
         B200_CUDA_CHECK(cudaMemset(ctx->d_status, 0, sizeof(uint32_t)));
         B200_CUDA_CHECK(cudaMallocHost(&ctx->h_status, sizeof(uint32_t)));
         *ctx->h_status = 0;
+        // VKML_B200_GEMM_PRECISION = 3xtf32 (default) | tf32 | fp32, read once per context:
+        // the counterpart of the VKML_GEMM_* switches (vulkan_backend.cpp:2160-2178)
+        if (const char* e = std::getenv("VKML_B200_GEMM_PRECISION")) {
+            const std::string v(e);
+            if (v == "tf32") ctx->gemm_precision = B200_GEMM_TF32;
+            else if (v == "fp32") ctx->gemm_precision = B200_GEMM_FP32;
+            else if (v == "3xtf32" || v.empty()) ctx->gemm_precision = B200_GEMM_3XTF32;
+            else fail(B200_INVALID_ARGUMENT, "VKML_B200_GEMM_PRECISION must be 3xtf32, tf32 or fp32");
+        }
     });
     if (rc != B200_OK) {
         b200_destroy(ctx);
@@ -382,6 +430,8 @@ void b200_destroy(b200_ctx* ctx) {
     if (ctx->d_status != nullptr) cudaFree(ctx->d_status);
     if (ctx->h_status != nullptr) cudaFreeHost(ctx->h_status);
     if (ctx->staging != nullptr) cudaFreeHost(ctx->staging);
+    if (ctx->timer_begin != nullptr) cudaEventDestroy(ctx->timer_begin);
+    if (ctx->timer_end != nullptr) cudaEventDestroy(ctx->timer_end);
     cudaGetLastError();
     delete ctx;
 }
@@ -562,6 +612,78 @@ int b200_get_stats(b200_ctx* ctx, b200_stats* out) {
     out->nodes_computed = ctx->nodes_computed.load();
     out->comm_bytes = ctx->comm_bytes.load();
     return B200_OK;
+}
+
+int b200_profile_enable(b200_ctx* ctx, int on) {
+    if (ctx == nullptr) return B200_INVALID_ARGUMENT;
+    return guarded(ctx, [&] {
+        B200_CUDA_CHECK(cudaStreamSynchronize(ctx->stream));
+        for (ProfEntry& e : ctx->prof) {
+            cudaEventDestroy(e.begin);
+            cudaEventDestroy(e.end);
+        }
+        ctx->prof.clear();
+        ctx->profiling = on != 0;
+    });
+}
+
+int b200_profile_read(b200_ctx* ctx, b200_profile_record* out, size_t capacity, size_t* count) {
+    if (ctx == nullptr || count == nullptr || (out == nullptr && capacity != 0)) return B200_INVALID_ARGUMENT;
+    return guarded(ctx, [&] {
+        B200_CUDA_CHECK(cudaStreamSynchronize(ctx->stream));
+        size_t n = 0;
+        for (ProfEntry& e : ctx->prof) {
+            if (n < capacity) {
+                float ms = 0.0F;
+                if (cudaEventElapsedTime(&ms, e.begin, e.end) != cudaSuccess) {
+                    cudaGetLastError();
+                    ms = -1.0F;
+                }
+                std::memcpy(out[n].label, e.label, sizeof(out[n].label));
+                out[n].ms = ms;
+                out[n].op = e.op;
+                ++n;
+            }
+            cudaEventDestroy(e.begin);
+            cudaEventDestroy(e.end);
+        }
+        ctx->prof.clear();
+        *count = n;
+    });
+}
+
+int b200_timer_begin(b200_ctx* ctx) {
+    if (ctx == nullptr) return B200_INVALID_ARGUMENT;
+    return guarded(ctx, [&] {
+        if (ctx->timer_begin == nullptr) {
+            B200_CUDA_CHECK(cudaEventCreate(&ctx->timer_begin));
+            B200_CUDA_CHECK(cudaEventCreate(&ctx->timer_end));
+        }
+        B200_CUDA_CHECK(cudaEventRecord(ctx->timer_begin, ctx->stream));
+    });
+}
+
+int b200_timer_end(b200_ctx* ctx, float* milliseconds) {
+    if (ctx == nullptr || milliseconds == nullptr) return B200_INVALID_ARGUMENT;
+    return guarded(ctx, [&] {
+        if (ctx->timer_begin == nullptr) fail(B200_INVALID_ARGUMENT, "b200_timer_end without b200_timer_begin");
+        B200_CUDA_CHECK(cudaEventRecord(ctx->timer_end, ctx->stream));
+        B200_CUDA_CHECK(cudaEventSynchronize(ctx->timer_end));
+        B200_CUDA_CHECK(cudaEventElapsedTime(milliseconds, ctx->timer_begin, ctx->timer_end));
+    });
+}
+
+int b200_alloc_host(b200_ctx* ctx, size_t nbytes, void** out) {
+    if (ctx == nullptr || out == nullptr) return B200_INVALID_ARGUMENT;
+    *out = nullptr;
+    if (nbytes == 0) return B200_OK;
+    return guarded(ctx, [&] { B200_CUDA_CHECK(cudaMallocHost(out, nbytes)); });
+}
+
+int b200_free_host(b200_ctx* ctx, void* ptr) {
+    if (ctx == nullptr) return B200_INVALID_ARGUMENT;
+    if (ptr == nullptr) return B200_OK;
+    return guarded(ctx, [&] { B200_CUDA_CHECK(cudaFreeHost(ptr)); });
 }
 
 int b200_set_gemm_precision(b200_ctx* ctx, int precision) {

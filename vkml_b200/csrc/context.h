@@ -40,6 +40,12 @@ private:
 
 struct DistState;  // dist.cu
 
+struct ProfEntry {
+    char label[48];
+    uint32_t op;
+    cudaEvent_t begin, end;
+};
+
 struct GradBuffer {
     void* data;
     size_t count;
@@ -72,6 +78,11 @@ struct b200_ctx {
     std::mutex err_mu;
     std::string last_error;
 
+    cudaEvent_t timer_begin = nullptr, timer_end = nullptr;
+    bool profiling = false;
+    uint32_t current_op = 0;
+    std::vector<b200::ProfEntry> prof;
+
     b200::DistState* dist = nullptr;
     std::vector<b200::GradBuffer> grads;
 
@@ -97,5 +108,20 @@ void dist_after_node(b200_ctx* ctx, const b200_node& node);  // all-reduce a reg
 void dist_join(b200_ctx* ctx);                                // make the compute stream wait for outstanding all-reduces
 
 void check_last_launch(const char* what);
+
+// Brackets the launches made inside its lifetime with CUDA events when profiling is on.
+class ProfScope {
+public:
+    ProfScope(b200_ctx* ctx, const char* label);
+    ~ProfScope();
+    ProfScope(const ProfScope&) = delete;
+    ProfScope& operator=(const ProfScope&) = delete;
+
+private:
+    b200_ctx* ctx_;
+    int index_ = -1;
+};
+
+const char* op_label(uint32_t op);
 
 }  // namespace b200

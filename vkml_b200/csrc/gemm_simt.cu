@@ -148,6 +148,7 @@ void gemm_simt(b200_ctx* ctx, const GemmProblem& p) {
         dst = static_cast<float*>(ctx->ensure_workspace(sizeof(float) * out_elems * splits));
     }
     dim3 grid(static_cast<unsigned>(tiles), 1, static_cast<unsigned>(splits));
+    ProfScope scope(ctx, "matmul.fp32_simt");
     gemm_simt_kernel<<<grid, 256, 0, ctx->stream>>>(p, dst, k_chunk, out_elems);
     ctx->count_launch();
     if (splits > 1) {
