@@ -46,6 +46,9 @@ def parse():
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--size", type=int, default=8192, help="M = N = K")
     ap.add_argument("--precision", default="3xtf32", choices=["3xtf32", "tf32", "fp32"])
+    ap.add_argument("--workload", default="gemm", choices=["gemm", "ops"],
+                    help="gemm: the contract line; ops: per-kernel HBM table of the memory-bound family")
+    ap.add_argument("--filter", default="", help="ops workload: substring of the case names to run")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true")
     return ap.parse_args()
@@ -341,12 +344,152 @@ def run_b200(args, rank, local_rank, world):
         dist.destroy_process_group()
 
 
+# ---------------------------------------------------------------------------
+# memory-bound family: achieved HBM GB/s per kernel at the BASELINE shapes
+# ---------------------------------------------------------------------------
+
+def run_ops(args, local_rank):
+    """One JSON line per case: algorithmic bytes / device time, against the measured HBM
+    peak.  Every case rotates over enough independent buffer sets that consecutive
+    launches cannot be served from the 126 MB L2."""
+    import vkml_b200
+    from vkml_b200 import DeviceTensor, NodeDesc, Op, graph
+    from vkml_b200.graph import DType
+    backend = vkml_b200.Backend(local_rank)
+    pk = peaks()
+    rng = np.random.default_rng(SEED_DATA)
+    F32, I64, BOOL = DType.F32, DType.I64, DType.BOOL
+
+    def dev(shape, dtype=F32, kind="normal"):
+        n = int(np.prod(shape)) if len(shape) else 1
+        if dtype == F32:
+            host = rng.standard_normal(n, dtype=np.float32) if kind == "normal" else rng.random(n, dtype=np.float32)
+        elif dtype == I64:
+            host = rng.integers(0, 10, n).astype(np.int64)
+        else:
+            host = (rng.random(n) < 0.5).astype(np.uint8)
+        return DeviceTensor.from_host(backend, host.reshape(shape))
+
+    cases = []
+
+    def case(name, op, out_shape, out_dtype, make_srcs, params=b"", bytes_alg=None):
+        cases.append((name, op, out_shape, out_dtype, make_srcs, params, bytes_alg))
+
+    def T(t):  # transposed view of a 2-D tensor
+        return t.transpose(0, 1)
+
+    B, H = 2048, 8192
+    case("add dense [2048,8192]", Op.ADD, (B, H), F32, lambda: [dev((B, H)), dev((B, H))], bytes_alg=12 * B * H)
+    case("add bias row-broadcast [2048,8192]+[8192]", Op.ADD, (B, H), F32,
+         lambda: [dev((B, H)), dev((H,)).broadcast_to((B, H))], bytes_alg=8 * B * H + 4 * H)
+    case("add bias channel-broadcast [256,64,32,32]+[64,1,1]", Op.ADD, (256, 64, 32, 32), F32,
+         lambda: [dev((256, 64, 32, 32)), dev((64, 1, 1)).broadcast_to((256, 64, 32, 32))],
+         bytes_alg=8 * 256 * 64 * 1024)
+    case("relu [2048,8192]", Op.RELU, (B, H), F32, lambda: [dev((B, H))], bytes_alg=8 * B * H)
+    case("less_equal vs scalar [2048,8192] -> bool", Op.LESS_EQUAL, (B, H), BOOL,
+         lambda: [dev((B, H)), dev(()).broadcast_to((B, H))], bytes_alg=5 * B * H)
+    case("where(mask, g, 0) [2048,8192]", Op.WHERE, (B, H), F32,
+         lambda: [dev((B, H), BOOL), dev((B, H)), dev(()).broadcast_to((B, H))], bytes_alg=9 * B * H)
+    case("mul col-broadcast [2048,1000]*[2048,1]", Op.MUL, (B, 1000), F32,
+         lambda: [dev((B, 1000)), dev((B, 1)).broadcast_to((B, 1000))], bytes_alg=8 * B * 1000)
+    case("exp [8192,1000]", Op.EXP, (8192, 1000), F32, lambda: [dev((8192, 1000))], bytes_alg=8 * 8192 * 1000)
+    case("full zeros [2048,8192]", Op.FULL, (B, H), F32, lambda: [], graph.full_params(0.0), bytes_alg=4 * B * H)
+    case("cast bool->f32 [8192,1000]", Op.CAST, (8192, 1000), F32, lambda: [dev((8192, 1000), BOOL)],
+         bytes_alg=5 * 8192 * 1000)
+    case("cast i64->f32 [1<<24]", Op.CAST, (1 << 24,), F32, lambda: [dev((1 << 24,), I64)], bytes_alg=12 * (1 << 24))
+    case("scaled_add dense [8192,8192]", Op.SCALED_ADD, (H, H), F32, lambda: [dev((H, H)), dev((H, H))],
+         graph.scaled_add_params(0.9, 1.0), bytes_alg=12 * H * H)
+    case("scaled_add one transposed operand [8192,8192]", Op.SCALED_ADD, (H, H), F32,
+         lambda: [dev((H, H)), T(dev((H, H)))], graph.scaled_add_params(1.0, -0.1), bytes_alg=12 * H * H)
+    case("scaled_add both transposed [8192,4096]", Op.SCALED_ADD, (H, 4096), F32,
+         lambda: [T(dev((4096, H))), T(dev((4096, H)))], graph.scaled_add_params(0.9, 1.0), bytes_alg=12 * H * 4096)
+    case("contiguous of transposed [8192,8192]", Op.CONTIGUOUS, (H, H), F32, lambda: [T(dev((H, H)))],
+         bytes_alg=8 * H * H)
+    case("contiguous of transposed [8200,8200] (pitch not a power of two)", Op.CONTIGUOUS, (8200, 8200), F32,
+         lambda: [T(dev((8200, 8200)))], bytes_alg=8 * 8200 * 8200)
+    case("sum columns [2048,8200]->[8200] (pitch not a power of two)", Op.SUM, (1, 8200), F32,
+         lambda: [dev((B, 8200))], graph.reduce_params([0], 2, True), bytes_alg=4 * B * 8200)
+    case("sum columns [16384,8192]->[8192] (537 MB)", Op.SUM, (1, H), F32, lambda: [dev((16384, H))],
+         graph.reduce_params([0], 2, True), bytes_alg=4 * 16384 * H)
+    case("relu [8192,8192] (537 MB)", Op.RELU, (H, H), F32, lambda: [dev((H, H))], bytes_alg=8 * H * H)
+    case("softmax [8192,8000] (524 MB)", Op.SOFTMAX, (8192, 8000), F32, lambda: [dev((8192, 8000))],
+         graph.axis_params(1), bytes_alg=8 * 8192 * 8000)
+    case("sum rows [16384,8000]->[16384] (524 MB)", Op.SUM, (16384,), F32, lambda: [dev((16384, 8000))],
+         graph.reduce_params([1], 2), bytes_alg=4 * 16384 * 8000)
+    for (b, c) in [(65536, 10), (8192, 1000), (1024, 32000)]:
+        case(f"sum rows [{b},{c}]->[{b}]", Op.SUM, (b,), F32, lambda b=b, c=c: [dev((b, c))],
+             graph.reduce_params([1], 2), bytes_alg=4 * b * c + 4 * b)
+        case(f"softmax [{b},{c}]", Op.SOFTMAX, (b, c), F32, lambda b=b, c=c: [dev((b, c), kind="normal")],
+             graph.axis_params(1), bytes_alg=8 * b * c)
+        case(f"log_softmax [{b},{c}]", Op.LOG_SOFTMAX, (b, c), F32, lambda b=b, c=c: [dev((b, c))],
+             graph.axis_params(1), bytes_alg=8 * b * c)
+        case(f"argmax rows [{b},{c}]", Op.ARGMAX, (b,), I64, lambda b=b, c=c: [dev((b, c))],
+             graph.reduce_params([1], 2), bytes_alg=4 * b * c + 8 * b)
+    case("sum columns [2048,8192]->[8192] (bias grad)", Op.SUM, (1, H), F32, lambda: [dev((B, H))],
+         graph.reduce_params([0], 2, True), bytes_alg=4 * B * H + 4 * H)
+    case("sum batch axis [1,256,128,576]->[1,1,128,576] (conv dW)", Op.SUM, (1, 1, 128, 576), F32,
+         lambda: [dev((1, 256, 128, 576))], graph.reduce_params([1], 4, True), bytes_alg=4 * 256 * 128 * 576)
+    case("sum N,H,W [256,64,32,32]->[1,64,1,1] (conv bias grad)", Op.SUM, (1, 64, 1, 1), F32,
+         lambda: [dev((256, 64, 32, 32))], graph.reduce_params([0, 2, 3], 4, True), bytes_alg=4 * 256 * 64 * 1024)
+    case("mean all [1<<26]", Op.MEAN, (), F32, lambda: [dev((1 << 26,))], graph.reduce_params([], 1),
+         bytes_alg=4 * (1 << 26))
+    up = graph.unfold_params
+    case("im2col [256,64,16,16] k3 p1 -> [256,576,256]", Op.IM2COL, (256, 576, 256), F32,
+         lambda: [dev((256, 64, 16, 16))], up((3, 3), (1, 1), (1, 1), (1, 1), (16, 16)),
+         bytes_alg=4 * (256 * 64 * 256 + 256 * 576 * 256))
+    case("col2im [256,576,256] -> [256,64,16,16]", Op.COL2IM, (256, 64, 16, 16), F32,
+         lambda: [dev((256, 576, 256))], up((3, 3), (1, 1), (1, 1), (1, 1), (16, 16)),
+         bytes_alg=4 * (256 * 64 * 256 + 256 * 576 * 256))
+    case("max_pool2d 2x2 [256,64,32,32]", Op.MAX_POOL2D, (256, 64, 16, 16), F32,
+         lambda: [dev((256, 64, 32, 32))], up((2, 2), (2, 2), (0, 0), (1, 1), (32, 32)),
+         bytes_alg=4 * 256 * 64 * (1024 + 256))
+    case("max_pool2d_backward 2x2 [256,64,32,32]", Op.MAX_POOL2D_BACKWARD, (256, 64, 32, 32), F32,
+         lambda: [dev((256, 64, 16, 16)), dev((256, 64, 32, 32))], up((2, 2), (2, 2), (0, 0), (1, 1), (32, 32)),
+         bytes_alg=4 * 256 * 64 * (1024 + 256 + 1024))
+    case("index_select rows [50000,1024][8192]", Op.INDEX_SELECT, (8192, 1024), F32,
+         lambda: [dev((50000, 1024)), DeviceTensor.from_host(backend, rng.integers(0, 50000, 8192).astype(np.int64))],
+         graph.axis_params(0), bytes_alg=8 * 8192 * 1024)
+
+    results = []
+    for name, op, out_shape, out_dtype, make_srcs, params, bytes_alg in cases:
+        if args.filter and args.filter not in name:
+            continue
+        probe = make_srcs()
+        set_bytes = sum(t.storage.nbytes for t in probe) + int(np.prod(out_shape) if len(out_shape) else 1) * out_dtype.itemsize
+        n_sets = int(min(24, max(2, np.ceil(300e6 / max(set_bytes, 1)))))
+        sets = [probe] + [make_srcs() for _ in range(n_sets - 1)]
+        outs = [DeviceTensor.empty(backend, out_shape, out_dtype) for _ in range(n_sets)]
+        packed = [graph.pack_nodes([NodeDesc(int(op), o.desc, [t.desc for t in srcs], params)])
+                  for srcs, o in zip(sets, outs)]
+        reps = max(args.steps, 20)
+        for i in range(max(args.warmup, 3)):
+            backend.compute_packed(packed[i % n_sets], 1)
+        backend.synchronize()
+        l0 = backend.stats()["kernel_launches"]
+        backend.timer_begin()
+        for i in range(reps):
+            backend.compute_packed(packed[i % n_sets], 1)
+        ms = backend.timer_end()
+        launches = (backend.stats()["kernel_launches"] - l0) / reps
+        us = ms * 1e3 / reps
+        gbs = bytes_alg / (us * 1e-6) / 1e9
+        row = {"op": name, "us": round(us, 2), "algorithmic_MB": round(bytes_alg / 1e6, 2), "GBps": round(gbs, 1),
+               "frac_of_hbm": round(gbs / pk["hbm_gbs"], 3), "launches_per_call": launches, "buffer_sets": n_sets}
+        results.append(row)
+        print(json.dumps(row), flush=True)
+        del sets, outs, packed, probe
+        backend.trim()
+    return results
+
+
 def main():
     args = parse()
     rank = int(os.environ.get("RANK", "0"))
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
-    if args.impl == "reference":
+    if args.workload == "ops":
+        run_ops(args, local_rank)
+    elif args.impl == "reference":
         run_reference(args, rank, world)
     else:
         run_b200(args, rank, local_rank, world)

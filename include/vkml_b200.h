@@ -134,7 +134,9 @@ typedef struct b200_ctx b200_ctx;
 /* b200_compute flags */
 #define B200_COMPUTE_DEFAULT 0u
 #define B200_COMPUTE_SYNC 1u        /* synchronise before returning (eager mode, executor.cpp:134-144) */
-#define B200_COMPUTE_GRAD_SYNC 2u   /* all-reduce the span's gradient outputs listed by b200_dist_mark_grad */
+#define B200_COMPUTE_GRAD_SYNC 2u   /* all-reduce (average) the span's gradients across ranks: the buffers
+                                       registered with b200_dist_mark_grad, or, when none are registered,
+                                       every f32 output of the span that no later node of the span reads */
 
 /* GEMM arithmetic: 3xTF32 split on the tensor cores (default), single-pass
  * TF32 (explicit opt-in), or plain fp32 FMA on the CUDA cores. */

@@ -18,6 +18,13 @@
 //                         built with WITH_B200 -- the B200 adapter registered as
 //                         Device::vulkan(0).  Same graphs, same bytes, two
 //                         devices: the loss curves are the training parity test.
+//                         With device 2 nothing is computed: a recording backend
+//                         writes every call the framework makes on its device
+//                         (allocations, uploads, compute spans with their node
+//                         descriptors, device copies, downloads) to a JSON-lines
+//                         file, which vkml_b200/replay.py plays back through the C
+//                         ABI -- the exact submissions of the real framework, at
+//                         any size, without the CPU having to execute them.
 #include "vkml_b200.h"
 
 #include "vkml/api/ops.h"
@@ -34,6 +41,7 @@
 
 #include <cstdio>
 #include <cstring>
+#include <mutex>
 #include <string>
 #include <thread>
 #include <vector>
@@ -87,12 +95,176 @@ vkml::NodePtr rebuild(const b200_node& d) {
     return out;
 }
 
+// ---------------------------------------------------------------------------
+// Recording backend: vkml::Backend registered as Device::vulkan(9).  Memory is
+// virtual (addresses are never dereferenced), compute() only logs.
+// ---------------------------------------------------------------------------
+constexpr uint64_t kArenaBase = uint64_t(1) << 44;
+constexpr int kArenaShift = 38;  // 256 GiB of address space per allocation
+
+class RecordingBackend final : public vkml::Backend {
+public:
+    RecordingBackend() : alloc_(this) {
+        caps_.asynchronous = true;
+        caps_.host_accessible_buffers = false;
+        caps_.total_memory_bytes = size_t(180) << 30;
+    }
+    void open(const char* path) {
+        if (file_ != nullptr) std::fclose(file_);
+        file_ = std::fopen(path, "w");
+        if (file_ == nullptr) throw vkml::DeviceError(std::string("cannot open ") + path);
+    }
+    void close() {
+        if (file_ != nullptr) std::fclose(file_);
+        file_ = nullptr;
+    }
+    void mark(const char* what, int index) {
+        if (file_ != nullptr) std::fprintf(file_, "{\"ev\":\"%s\",\"index\":%d}\n", what, index);
+    }
+    void arm_grad_sync() { grad_sync_ = true; }
+
+    std::string_view name() const noexcept override { return "recorder"; }
+    vkml::Device device() const noexcept override { return vkml::Device::vulkan(9); }
+    const vkml::DeviceCapabilities& capabilities() const noexcept override { return caps_; }
+    vkml::Allocator& allocator() override { return alloc_; }
+    bool supports(const vkml::Node&) const override { return true; }
+
+    void compute(std::span<vkml::Node* const> nodes) override {
+        if (file_ == nullptr) return;
+        std::fprintf(file_, "{\"ev\":\"compute\",\"grad_sync\":%s,\"nodes\":[", grad_sync_ ? "true" : "false");
+        grad_sync_ = false;
+        bool first = true;
+        for (vkml::Node* n : nodes) {
+            if (vkml::is_view_op(n->op) || n->is_leaf()) continue;
+            std::fprintf(file_, "%s{\"op\":%d,\"params\":\"", first ? "" : ",", static_cast<int>(n->op));
+            first = false;
+            for (std::byte b : n->params.raw) std::fprintf(file_, "%02x", static_cast<unsigned>(b));
+            std::fprintf(file_, "\",\"out\":");
+            tensor(*n);
+            std::fprintf(file_, ",\"src\":[");
+            for (int i = 0; i < n->n_src; ++i) {
+                if (i) std::fputc(',', file_);
+                tensor(*n->src[static_cast<size_t>(i)]);
+            }
+            std::fprintf(file_, "]}");
+        }
+        std::fprintf(file_, "]}\n");
+    }
+    void copy_from_host(vkml::Storage& dst, int64_t off, const void*, size_t nbytes) override {
+        if (file_ != nullptr && nbytes != 0)
+            std::fprintf(file_, "{\"ev\":\"h2d\",\"id\":%llu,\"off\":%lld,\"bytes\":%zu}\n", id_of(dst.data()),
+                         static_cast<long long>(off), nbytes);
+    }
+    void copy_to_host(void* dst, const vkml::Storage& src, int64_t off, size_t nbytes) override {
+        std::memset(dst, 0, nbytes);
+        if (file_ != nullptr && nbytes != 0)
+            std::fprintf(file_, "{\"ev\":\"d2h\",\"id\":%llu,\"off\":%lld,\"bytes\":%zu}\n", id_of(src.data()),
+                         static_cast<long long>(off), nbytes);
+    }
+    void copy_device_to_device(std::span<const vkml::BufferCopy> copies) override {
+        if (file_ == nullptr) return;
+        std::fprintf(file_, "{\"ev\":\"d2d\",\"copies\":[");
+        bool first = true;
+        for (const vkml::BufferCopy& c : copies) {
+            if (c.nbytes == 0) continue;
+            std::fprintf(file_, "%s[%llu,%lld,%llu,%lld,%zu]", first ? "" : ",", id_of(c.dst->data()),
+                         static_cast<long long>(c.dst_offset), id_of(c.src->data()),
+                         static_cast<long long>(c.src_offset), c.nbytes);
+            first = false;
+        }
+        std::fprintf(file_, "]}\n");
+    }
+    using vkml::Backend::copy_device_to_device;
+    void synchronize() override {
+        if (file_ != nullptr) std::fprintf(file_, "{\"ev\":\"sync\"}\n");
+    }
+
+private:
+    class FakeAllocator final : public vkml::Allocator {
+    public:
+        explicit FakeAllocator(RecordingBackend* owner) : owner_(owner) {}
+        std::shared_ptr<vkml::Storage> allocate(size_t nbytes) override {
+            RecordingBackend* o = owner_;
+            if (nbytes == 0) {
+                return std::make_shared<vkml::Storage>(nullptr, 0, o->device(), vkml::Storage::Deleter{});
+            }
+            const uint64_t id = o->next_id_++;
+            void* fake = reinterpret_cast<void*>(kArenaBase + (id << kArenaShift));
+            if (o->file_ != nullptr)
+                std::fprintf(o->file_, "{\"ev\":\"alloc\",\"id\":%llu,\"bytes\":%zu}\n",
+                             static_cast<unsigned long long>(id), nbytes);
+            live_ += nbytes;
+            return std::make_shared<vkml::Storage>(fake, nbytes, o->device(), [o, id, this](void*, size_t n) {
+                live_ -= n;
+                if (o->file_ != nullptr)
+                    std::fprintf(o->file_, "{\"ev\":\"free\",\"id\":%llu}\n", static_cast<unsigned long long>(id));
+            });
+        }
+        std::string_view name() const noexcept override { return "recorder"; }
+        vkml::Device device() const noexcept override { return vkml::Device::vulkan(9); }
+        size_t live_bytes() const noexcept override { return live_; }
+
+    private:
+        RecordingBackend* owner_;
+        size_t live_ = 0;
+    };
+
+    static unsigned long long id_of(const void* p) {
+        return (reinterpret_cast<uint64_t>(p) - kArenaBase) >> kArenaShift;
+    }
+    void tensor(const vkml::Node& n) {
+        const uint64_t addr = reinterpret_cast<uint64_t>(n.data());
+        if (n.data() == nullptr) {
+            std::fprintf(file_, "{\"id\":-1,\"off\":0");
+        } else {
+            std::fprintf(file_, "{\"id\":%llu,\"off\":%llu", static_cast<unsigned long long>((addr - kArenaBase) >> kArenaShift),
+                         static_cast<unsigned long long>((addr - kArenaBase) & ((uint64_t(1) << kArenaShift) - 1)));
+        }
+        std::fprintf(file_, ",\"dtype\":%d,\"dims\":[", static_cast<int>(n.dtype));
+        for (int i = 0; i < n.shape.ndim(); ++i) std::fprintf(file_, "%s%lld", i ? "," : "", static_cast<long long>(n.shape.dim(i)));
+        std::fprintf(file_, "],\"strides\":[");
+        for (int i = 0; i < n.shape.ndim(); ++i) std::fprintf(file_, "%s%lld", i ? "," : "", static_cast<long long>(n.shape.stride(i)));
+        std::fprintf(file_, "]}");
+    }
+
+    vkml::DeviceCapabilities caps_;
+    FakeAllocator alloc_;
+    std::FILE* file_ = nullptr;
+    uint64_t next_id_ = 0;
+    bool grad_sync_ = false;
+};
+
+RecordingBackend& recorder() {
+    static RecordingBackend* r = [] {
+        auto* b = new RecordingBackend();  // process lifetime, like every backend
+        vkml::register_backend(*b);
+        return b;
+    }();
+    return *r;
+}
+
+// Tells the device that the next compute span is backward()'s: its sinks are the
+// parameter gradients a data-parallel run all-reduces.
+void before_backward(int device) {
+    if (device == 2) recorder().arm_grad_sync();
+#ifdef WITH_B200
+    if (device == 1) vkml_b200::b200_backend(0).arm_grad_sync();
+#endif
+}
+
+void mark_step(int device, int index) {
+    if (device == 2) recorder().mark("step", index);
+}
+
 vkml::Device pick_device(int which) {
 #ifdef WITH_B200
     if (which == 1) {
         return vkml_b200::b200_backend(0).device();
     }
 #endif
+    if (which == 2) {
+        return recorder().device();
+    }
     if (which != 0) {
         throw vkml::DeviceError("this build of the harness has no B200 adapter");
     }
@@ -132,6 +304,25 @@ struct Sgd {
     }
 };
 
+// Host-side gradient exchange for the N-rank CPU oracle of data-parallel training: after
+// backward(), every parameter gradient is brought to the host, handed to `hook` (which
+// averages it across ranks, e.g. with a gloo all-reduce) and put back.
+using GradHook = void (*)(float* data, int64_t count, void* user);
+thread_local GradHook g_hook = nullptr;
+thread_local void* g_hook_user = nullptr;
+
+void exchange_grads(std::vector<vkml::Tensor>& params) {
+    if (g_hook == nullptr) return;
+    for (auto& p : params) {
+        vkml::Tensor g = p.grad().contiguous();
+        std::vector<float> host(static_cast<size_t>(g.numel()));
+        g.to_host(host.data());
+        g_hook(host.data(), g.numel(), g_hook_user);
+        const std::vector<int64_t> dims = g.shape();
+        p.set_grad(vkml::Tensor::from_host(host.data(), std::span<const int64_t>{dims}, vkml::DType::F32, g.device()));
+    }
+}
+
 void zero_grad(std::vector<vkml::Tensor>& params) {
     for (auto& p : params) p.set_grad(vkml::Tensor{});
 }
@@ -148,6 +339,41 @@ int vkml_ref_has_b200(void) {
 #else
     return 0;
 #endif
+}
+
+// Install (or clear, with NULL) the host-side gradient exchange used by the trainers below.
+void vkml_ref_set_grad_hook(void (*hook)(float*, int64_t, void*), void* user) {
+    g_hook = hook;
+    g_hook_user = user;
+}
+
+// Join a data-parallel job on the B200 adapter's context (NCCL communicator).
+int vkml_ref_b200_dist_init(int rank, int world, const void* unique_id) {
+#ifdef WITH_B200
+    try {
+        return b200_dist_init(vkml_b200::b200_backend(0).context(), rank, world, unique_id);
+    } catch (const std::exception& e) {
+        return status_of(e);
+    }
+#else
+    (void)rank; (void)world; (void)unique_id;
+    return B200_NOT_IMPLEMENTED;
+#endif
+}
+
+// Start / stop writing the recording backend's log (device 2 of the trainers).
+int vkml_ref_record_begin(const char* path) {
+    try {
+        recorder().open(path);
+        return B200_OK;
+    } catch (const std::exception& e) {
+        return status_of(e);
+    }
+}
+
+int vkml_ref_record_end(void) {
+    recorder().close();
+    return B200_OK;
 }
 
 int vkml_ref_compute(const b200_node* nodes, size_t n_nodes) {
@@ -213,17 +439,20 @@ int vkml_ref_train_mlp(int device, const int64_t* widths, int n_layers, float* w
         for (auto& p : params) p.set_requires_grad(true);
         Sgd opt{lr, momentum, {}};
         for (int s = 0; s < steps; ++s) {
-            vkml::Tensor h = vkml::Tensor::from_host(x + static_cast<size_t>(s) * batch * widths[0],
-                                                     {batch, widths[0]}, vkml::DType::F32, dev);
-            const vkml::Tensor labels = vkml::Tensor::from_host(y + static_cast<size_t>(s) * batch, {batch},
-                                                                vkml::DType::I64, dev);
+            mark_step(device, s);
+            const size_t at = device == 2 ? 0 : static_cast<size_t>(s);  // the recorder never reads the data
+            vkml::Tensor h = vkml::Tensor::from_host(x + at * batch * widths[0], {batch, widths[0]},
+                                                     vkml::DType::F32, dev);
+            const vkml::Tensor labels = vkml::Tensor::from_host(y + at * batch, {batch}, vkml::DType::I64, dev);
             for (int l = 0; l < n_layers; ++l) {
                 h = vkml::matmul(h, params[2 * l].transpose(-2, -1)) + params[2 * l + 1];
                 if (l + 1 < n_layers) h = vkml::relu(h);
             }
             const vkml::Tensor loss = vkml::cross_entropy(h, labels);
             zero_grad(params);
+            before_backward(device);
             vkml::backward(loss);
+            exchange_grads(params);
             opt.step(params);
             losses[s] = loss.item();
         }
@@ -263,10 +492,11 @@ int vkml_ref_train_cnn(int device, int64_t cin, int64_t hw, int64_t c1, int64_t 
         for (auto& p : params) p.set_requires_grad(true);
         Sgd opt{lr, momentum, {}};
         for (int s = 0; s < steps; ++s) {
-            vkml::Tensor h = vkml::Tensor::from_host(x + static_cast<size_t>(s) * batch * cin * hw * hw,
-                                                     {batch, cin, hw, hw}, vkml::DType::F32, dev);
-            const vkml::Tensor labels = vkml::Tensor::from_host(y + static_cast<size_t>(s) * batch, {batch},
-                                                                vkml::DType::I64, dev);
+            mark_step(device, s);
+            const size_t at = device == 2 ? 0 : static_cast<size_t>(s);
+            vkml::Tensor h = vkml::Tensor::from_host(x + at * batch * cin * hw * hw, {batch, cin, hw, hw},
+                                                     vkml::DType::F32, dev);
+            const vkml::Tensor labels = vkml::Tensor::from_host(y + at * batch, {batch}, vkml::DType::I64, dev);
             for (int l = 0; l < 3; ++l) {
                 h = vkml::conv2d(h, params[2 * l], params[2 * l + 1], {1, 1}, {1, 1});
                 h = vkml::relu(h);
@@ -276,7 +506,9 @@ int vkml_ref_train_cnn(int device, int64_t cin, int64_t hw, int64_t c1, int64_t 
             h = vkml::matmul(h, params[6].transpose(-2, -1)) + params[7];
             const vkml::Tensor loss = vkml::cross_entropy(h, labels);
             zero_grad(params);
+            before_backward(device);
             vkml::backward(loss);
+            exchange_grads(params);
             opt.step(params);
             losses[s] = loss.item();
         }

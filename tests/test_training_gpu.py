@@ -66,3 +66,49 @@ def test_cnn_10_steps(lib):
     assert np.all(np.isfinite(cpu_l))
     assert rel(gpu_l, cpu_l) < 1e-4, (gpu_l, cpu_l)
     np.testing.assert_allclose(gpu_p, cpu_p, rtol=0, atol=1e-4)
+
+
+def _replay_mlp(backend, name, widths, batch, steps, ws, bs, x, y):
+    """Replays a recorded program through the C ABI with real data; returns the loss curve."""
+    import os
+    from vkml_b200.replay import Replayer, load_program
+    program = load_program(os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden", "programs",
+                                        name + ".json.gz"))
+    assert program["meta"]["widths"] == widths and program["meta"]["batch"] == batch
+    params = [p for pair in zip(ws, bs) for p in pair]
+    state = {"step": 0}
+
+    def feed(tag, nbytes):
+        if tag[0] == "pro":
+            arr = params[tag[1]]
+        else:
+            s = state["step"]
+            arr = x[s * batch:(s + 1) * batch] if tag[1] == 0 else y[s * batch:(s + 1) * batch]
+        assert arr.nbytes == nbytes, (tag, arr.nbytes, nbytes)
+        return arr
+
+    r = Replayer(backend, program, feed)
+    for s in range(steps):
+        state["step"] = s
+        r.step()
+    backend.synchronize()
+    losses = np.array([d.view(np.float32)[0] for _, d in r.downloads if d.nbytes == 4], dtype=np.float32)
+    return losses, r
+
+
+def test_recorded_program_replays_to_the_same_loss_curve(lib, backend):
+    """The MNIST MLP step recorded from the reference framework (its compute spans,
+    copies and allocations, captured by a logging backend) and replayed through the C
+    ABI gives the CPU backend's loss curve: the replay IS the framework's traffic."""
+    widths, batch, steps = [784, 128, 10], 64, 100
+    ws, bs, x, y = training.mlp_problem(widths, batch, steps)
+    cpu_l, _, _ = training.train_mlp(lib, training.CPU, widths, ws, bs, x, y, batch, steps)
+    gpu_l, r = _replay_mlp(backend, "mlp_784_128_10_b64", widths, batch, steps, ws, bs, x, y)
+    assert len(gpu_l) == steps
+    assert rel(gpu_l, cpu_l) < 1e-4, (gpu_l[:5], cpu_l[:5])
+    # steady state allocates nothing new from the driver: every buffer comes from the cache
+    before = backend.stats()["driver_allocations"]
+    for _ in range(5):
+        r.step()
+    backend.synchronize()
+    assert backend.stats()["driver_allocations"] == before

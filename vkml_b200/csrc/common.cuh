@@ -241,6 +241,55 @@ __device__ __forceinline__ int64_t geo_offset(const Geo& g, int64_t linear) {
     return view_offset(g.dim, g.stride, linear);
 }
 
+// Index arithmetic is the whole cost of the strided kernels, and a 64-bit divide is
+// several times a 32-bit one.  Kernels are therefore templated on the index type and
+// the host picks uint32_t whenever every linear index and element offset fits.
+template <typename I>
+struct GeoT {
+    I dim[kMaxDims];
+    I stride[kMaxDims];
+};
+
+template <typename I>
+inline GeoT<I> geo_t(const View& v) {
+    GeoT<I> g;
+    for (int i = 0; i < kMaxDims; ++i) {
+        g.dim[i] = static_cast<I>(v.dim[i]);
+        g.stride[i] = static_cast<I>(v.stride[i]);
+    }
+    return g;
+}
+
+template <typename I>
+__device__ __forceinline__ I geo_off(const GeoT<I>& g, I linear) {
+    I off = 0;
+#pragma unroll
+    for (int a = kMaxDims - 1; a >= 0; --a) {
+        const I q = linear / g.dim[a];
+        off += (linear - q * g.dim[a]) * g.stride[a];
+        linear = q;
+    }
+    return off;
+}
+
+// True when a view can be walked with 32-bit unsigned indices: non-negative strides and
+// both its element count and its largest element offset below 2^31.
+inline bool fits32(const View& v) {
+    if (v.numel >= (int64_t(1) << 31)) {
+        return false;
+    }
+    int64_t last = 0;
+    for (int i = 0; i < kMaxDims; ++i) {
+        if (v.stride[i] < 0) {
+            return false;
+        }
+        if (v.dim[i] > 0) {
+            last += (v.dim[i] - 1) * v.stride[i];
+        }
+    }
+    return last < (int64_t(1) << 31);
+}
+
 inline int64_t ceil_div(int64_t a, int64_t b) { return (a + b - 1) / b; }
 
 // Grid for a grid-stride loop over `work` items: enough blocks to cover the work,

@@ -401,6 +401,8 @@ int b200_create(int cuda_ordinal, b200_ctx** out) {
         B200_CUDA_CHECK(cudaStreamCreateWithFlags(&ctx->stream, cudaStreamNonBlocking));
         B200_CUDA_CHECK(cudaMalloc(&ctx->d_status, sizeof(uint32_t)));
         B200_CUDA_CHECK(cudaMemset(ctx->d_status, 0, sizeof(uint32_t)));
+        B200_CUDA_CHECK(cudaMalloc(&ctx->d_counters, sizeof(unsigned) * 4096));
+        B200_CUDA_CHECK(cudaMemset(ctx->d_counters, 0, sizeof(unsigned) * 4096));
         B200_CUDA_CHECK(cudaMallocHost(&ctx->h_status, sizeof(uint32_t)));
         *ctx->h_status = 0;
         // VKML_B200_GEMM_PRECISION = 3xtf32 (default) | tf32 | fp32, read once per context:
@@ -428,6 +430,7 @@ void b200_destroy(b200_ctx* ctx) {
     dist_destroy(ctx);
     if (ctx->stream != nullptr) cudaStreamDestroy(ctx->stream);
     if (ctx->d_status != nullptr) cudaFree(ctx->d_status);
+    if (ctx->d_counters != nullptr) cudaFree(ctx->d_counters);
     if (ctx->h_status != nullptr) cudaFreeHost(ctx->h_status);
     if (ctx->staging != nullptr) cudaFreeHost(ctx->staging);
     if (ctx->timer_begin != nullptr) cudaEventDestroy(ctx->timer_begin);
@@ -480,6 +483,35 @@ int b200_compute(b200_ctx* ctx, const b200_node* nodes, size_t n_nodes, uint32_t
     return guarded(ctx, [&] {
         ctx->compute_calls.fetch_add(1, std::memory_order_relaxed);
         const bool grad_sync = (flags & B200_COMPUTE_GRAD_SYNC) != 0 && ctx->dist != nullptr;
+        // With no buffers registered, the gradients are the span's SINKS: f32 outputs that
+        // no later node of the span reads.  backward() realises exactly the leaf gradients
+        // (src/autograd/autograd.cpp:627-666), so every other output is consumed in-span.
+        std::vector<char> is_sink;
+        if (grad_sync && ctx->grads.empty()) {
+            is_sink.assign(n_nodes, 0);
+            auto bytes_of = [](const b200_tensor& t) {
+                size_t n = dtype_size(t.dtype);
+                for (int d = 0; d < t.ndim; ++d) n *= static_cast<size_t>(t.dims[d]);
+                return n;
+            };
+            for (size_t i = 0; i < n_nodes; ++i) {
+                const b200_node& node = nodes[i];
+                if (is_view_or_leaf(node.op) || node.out.dtype != B200_F32 || node.out.data == nullptr) continue;
+                const char* lo = static_cast<const char*>(node.out.data);
+                const char* hi = lo + bytes_of(node.out);
+                bool consumed = false;
+                for (size_t j = i + 1; j < n_nodes && !consumed; ++j) {
+                    for (uint32_t k = 0; k < nodes[j].n_src && k < B200_MAX_SRC; ++k) {
+                        const char* p = static_cast<const char*>(nodes[j].src[k].data);
+                        if (p >= lo && p < hi) {
+                            consumed = true;
+                            break;
+                        }
+                    }
+                }
+                is_sink[i] = consumed ? 0 : 1;
+            }
+        }
         for (size_t i = 0; i < n_nodes; ++i) {
             const b200_node& node = nodes[i];
             if (is_view_or_leaf(node.op)) {
@@ -507,7 +539,13 @@ int b200_compute(b200_ctx* ctx, const b200_node* nodes, size_t n_nodes, uint32_t
             dispatch_node(ctx, node);
             ctx->nodes_computed.fetch_add(1, std::memory_order_relaxed);
             if (grad_sync) {
-                dist_after_node(ctx, node);
+                if (!is_sink.empty()) {
+                    if (is_sink[i]) {
+                        dist_all_reduce_now(ctx, node.out.data, static_cast<size_t>(numel));
+                    }
+                } else {
+                    dist_after_node(ctx, node);
+                }
             }
         }
         if (grad_sync) {

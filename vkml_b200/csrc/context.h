@@ -61,6 +61,7 @@ struct b200_ctx {
 
     uint32_t* d_status = nullptr;  // device status word (DeviceStatusBits)
     uint32_t* h_status = nullptr;  // pinned mirror
+    unsigned* d_counters = nullptr;  // arrival counters of split reductions (self-resetting)
 
     // Scratch the library owns (GEMM operand splits, reduction partials). Grown
     // on demand, never shrunk; reused by every launch on the stream.
@@ -105,6 +106,7 @@ bool supports_node(const b200_node& node);
 // dist.cu
 void dist_destroy(b200_ctx* ctx);
 void dist_after_node(b200_ctx* ctx, const b200_node& node);  // all-reduce a registered gradient once its producer is queued
+void dist_all_reduce_now(b200_ctx* ctx, void* data, size_t count);  // average across ranks on the comm stream
 void dist_join(b200_ctx* ctx);                                // make the compute stream wait for outstanding all-reduces
 
 void check_last_launch(const char* what);

@@ -96,6 +96,12 @@ static void all_reduce_mean(b200_ctx* ctx, void* data, size_t count) {
     ctx->comm_bytes.fetch_add(count * sizeof(float), std::memory_order_relaxed);
 }
 
+void dist_all_reduce_now(b200_ctx* ctx, void* data, size_t count) {
+    if (ctx->dist != nullptr && count != 0) {
+        all_reduce_mean(ctx, data, count);
+    }
+}
+
 void dist_after_node(b200_ctx* ctx, const b200_node& node) {
     DistState* d = ctx->dist;
     if (d == nullptr || ctx->grads.empty()) {

@@ -12,11 +12,14 @@
 //   strided  -- rank<=4 collapsed index walk; vectorised along the innermost axis
 //               when every operand is unit-stride or broadcast (stride 0) there.
 //   tiled    -- an operand whose unit stride lies on the second-innermost axis
-//               (a transposed view) goes through a 32x33 shared-memory tile so
+//               (a transposed view) goes through a 64x65 shared-memory tile so
 //               both the global read and the global write stay coalesced.
+// Strided index arithmetic runs in 32 bits whenever every offset fits.
 #include "context.h"
 
 #include <cuda_fp16.h>
+
+#include <algorithm>
 
 namespace b200 {
 namespace {
@@ -248,30 +251,66 @@ struct FCastBool {
 // Kernels
 // ---------------------------------------------------------------------------
 
-// Every operand dense and 16-byte-friendly: VEC elements per thread per trip.
+// Independent vectors in flight per thread: four, or two for the 8-wide vectors of
+// the mixed-width ops so the kernel stays under 64 registers.
+template <int VEC>
+__host__ __device__ constexpr int unroll_for() {
+    return VEC >= 8 ? 2 : 4;
+}
+
+template <typename F, int VEC>
+__device__ __forceinline__ Vec<typename F::Out, VEC> apply_vec(const typename F::P& p,
+                                                               const Vec<typename F::In0, VEC>& a,
+                                                               const Vec<typename F::In1, VEC>& b,
+                                                               const Vec<typename F::In2, VEC>& c) {
+    Vec<typename F::Out, VEC> o;
+#pragma unroll
+    for (int k = 0; k < VEC; ++k) {
+        o.v[k] = F::apply(p, a.v[k], b.v[k], c.v[k]);
+    }
+    return o;
+}
+
+// Every operand dense and aligned: VEC elements per vector, kUnroll vectors per
+// thread per trip, all loads issued before the first use.
 template <typename F, int VEC>
 __global__ void __launch_bounds__(kThreads)
 flat_kernel(typename F::Out* __restrict__ out, const typename F::In0* __restrict__ a,
             const typename F::In1* __restrict__ b, const typename F::In2* __restrict__ c,
             int64_t n, typename F::P p) {
+    using VA = Vec<typename F::In0, VEC>;
+    using VB = Vec<typename F::In1, VEC>;
+    using VC = Vec<typename F::In2, VEC>;
+    using VO = Vec<typename F::Out, VEC>;
+    constexpr int kUnroll = unroll_for<VEC>();
     const int64_t nvec = n / VEC;
-    const int64_t stride = int64_t(gridDim.x) * blockDim.x;
-    for (int64_t i = int64_t(blockIdx.x) * blockDim.x + threadIdx.x; i < nvec; i += stride) {
-        Vec<typename F::In0, VEC> va = reinterpret_cast<const Vec<typename F::In0, VEC>*>(a)[i];
-        Vec<typename F::In1, VEC> vb{};
-        Vec<typename F::In2, VEC> vc{};
-        if constexpr (F::NIN >= 2) {
-            vb = reinterpret_cast<const Vec<typename F::In1, VEC>*>(b)[i];
-        }
-        if constexpr (F::NIN >= 3) {
-            vc = reinterpret_cast<const Vec<typename F::In2, VEC>*>(c)[i];
-        }
-        Vec<typename F::Out, VEC> vo;
+    const int64_t step = int64_t(gridDim.x) * kThreads * kUnroll;
+    for (int64_t base = int64_t(blockIdx.x) * kThreads * kUnroll + threadIdx.x; base < nvec; base += step) {
+        VA va[kUnroll];
+        VB vb[kUnroll];
+        VC vc[kUnroll];
 #pragma unroll
-        for (int k = 0; k < VEC; ++k) {
-            vo.v[k] = F::apply(p, va.v[k], vb.v[k], vc.v[k]);
+        for (int u = 0; u < kUnroll; ++u) {
+            const int64_t i = base + int64_t(u) * kThreads;
+            vb[u] = VB{};
+            vc[u] = VC{};
+            if (i < nvec) {
+                va[u] = reinterpret_cast<const VA*>(a)[i];
+                if constexpr (F::NIN >= 2) {
+                    vb[u] = reinterpret_cast<const VB*>(b)[i];
+                }
+                if constexpr (F::NIN >= 3) {
+                    vc[u] = reinterpret_cast<const VC*>(c)[i];
+                }
+            }
         }
-        reinterpret_cast<Vec<typename F::Out, VEC>*>(out)[i] = vo;
+#pragma unroll
+        for (int u = 0; u < kUnroll; ++u) {
+            const int64_t i = base + int64_t(u) * kThreads;
+            if (i < nvec) {
+                reinterpret_cast<VO*>(out)[i] = apply_vec<F, VEC>(p, va[u], vb[u], vc[u]);
+            }
+        }
     }
     // tail (n % VEC elements) by the first threads of block 0
     if (blockIdx.x == 0) {
@@ -290,127 +329,207 @@ flat_kernel(typename F::Out* __restrict__ out, const typename F::In0* __restrict
     }
 }
 
-// General strided walk. L.stride[0..2] are the inputs, the output is dense.
-// With VEC > 1 the innermost extent has been divided by VEC and every input's
-// innermost stride is VEC (unit stride, vector load) or 0 (broadcast, splat).
-template <typename F, int VEC>
+// Strides of up to three inputs over one collapsed iteration space, in index type I.
+template <typename I>
+struct LayoutT {
+    I dim[kMaxDims];
+    I stride[3][kMaxDims];
+    int ndim;
+};
+
+template <typename I>
+__device__ __forceinline__ void offsets3(const LayoutT<I>& L, I linear, I (&off)[3]) {
+    off[0] = off[1] = off[2] = 0;
+#pragma unroll
+    for (int a = kMaxDims - 1; a >= 0; --a) {
+        if (a >= kMaxDims - L.ndim) {
+            I idx;
+            if (a == kMaxDims - L.ndim) {
+                idx = linear;
+            } else {
+                const I q = linear / L.dim[a];
+                idx = linear - q * L.dim[a];
+                linear = q;
+            }
+            off[0] += idx * L.stride[0][a];
+            off[1] += idx * L.stride[1][a];
+            off[2] += idx * L.stride[2][a];
+        }
+    }
+}
+
+template <typename T, int VEC, typename I>
+__device__ __forceinline__ Vec<T, VEC> load_or_splat(const T* p, I off, I inner_stride) {
+    Vec<T, VEC> v;
+    if (VEC > 1 && inner_stride != 0) {
+        v = *reinterpret_cast<const Vec<T, VEC>*>(p + off);
+    } else {
+        const T s = p[off];
+#pragma unroll
+        for (int k = 0; k < VEC; ++k) {
+            v.v[k] = s;
+        }
+    }
+    return v;
+}
+
+// General strided walk; the output is dense.  With VEC > 1 the innermost extent has
+// been divided by VEC and every input's innermost stride is VEC (unit stride: vector
+// load) or 0 (broadcast: one load, splat).
+template <typename F, int VEC, typename I>
 __global__ void __launch_bounds__(kThreads)
 strided_kernel(typename F::Out* __restrict__ out, const typename F::In0* __restrict__ a,
                const typename F::In1* __restrict__ b, const typename F::In2* __restrict__ c,
-               int64_t nvec, Layout4 L, typename F::P p) {
-    const int64_t stride = int64_t(gridDim.x) * blockDim.x;
+               I nvec, LayoutT<I> L, typename F::P p) {
+    constexpr int kUnroll = unroll_for<VEC>();
     const int inner = kMaxDims - 1;
-    for (int64_t i = int64_t(blockIdx.x) * blockDim.x + threadIdx.x; i < nvec; i += stride) {
-        int64_t off[3];
-        offsets_of<3>(L, i, off);
-        Vec<typename F::In0, VEC> va;
-        Vec<typename F::In1, VEC> vb{};
-        Vec<typename F::In2, VEC> vc{};
-        if (VEC > 1 && L.stride[0][inner] != 0) {
-            va = *reinterpret_cast<const Vec<typename F::In0, VEC>*>(a + off[0]);
-        } else {
-            const typename F::In0 s = a[off[0]];
+    const int64_t step = int64_t(gridDim.x) * kThreads * kUnroll;
+    for (int64_t base = int64_t(blockIdx.x) * kThreads * kUnroll + threadIdx.x; base < int64_t(nvec);
+         base += step) {
+        Vec<typename F::In0, VEC> va[kUnroll];
+        Vec<typename F::In1, VEC> vb[kUnroll];
+        Vec<typename F::In2, VEC> vc[kUnroll];
 #pragma unroll
-            for (int k = 0; k < VEC; ++k) {
-                va.v[k] = s;
-            }
-        }
-        if constexpr (F::NIN >= 2) {
-            if (VEC > 1 && L.stride[1][inner] != 0) {
-                vb = *reinterpret_cast<const Vec<typename F::In1, VEC>*>(b + off[1]);
-            } else {
-                const typename F::In1 s = b[off[1]];
-#pragma unroll
-                for (int k = 0; k < VEC; ++k) {
-                    vb.v[k] = s;
+        for (int u = 0; u < kUnroll; ++u) {
+            const int64_t i = base + int64_t(u) * kThreads;
+            vb[u] = Vec<typename F::In1, VEC>{};
+            vc[u] = Vec<typename F::In2, VEC>{};
+            if (i < int64_t(nvec)) {
+                I off[3];
+                offsets3<I>(L, static_cast<I>(i), off);
+                va[u] = load_or_splat<typename F::In0, VEC, I>(a, off[0], L.stride[0][inner]);
+                if constexpr (F::NIN >= 2) {
+                    vb[u] = load_or_splat<typename F::In1, VEC, I>(b, off[1], L.stride[1][inner]);
+                }
+                if constexpr (F::NIN >= 3) {
+                    vc[u] = load_or_splat<typename F::In2, VEC, I>(c, off[2], L.stride[2][inner]);
                 }
             }
         }
-        if constexpr (F::NIN >= 3) {
-            if (VEC > 1 && L.stride[2][inner] != 0) {
-                vc = *reinterpret_cast<const Vec<typename F::In2, VEC>*>(c + off[2]);
-            } else {
-                const typename F::In2 s = c[off[2]];
 #pragma unroll
-                for (int k = 0; k < VEC; ++k) {
-                    vc.v[k] = s;
-                }
+        for (int u = 0; u < kUnroll; ++u) {
+            const int64_t i = base + int64_t(u) * kThreads;
+            if (i < int64_t(nvec)) {
+                reinterpret_cast<Vec<typename F::Out, VEC>*>(out)[i] = apply_vec<F, VEC>(p, va[u], vb[u], vc[u]);
             }
         }
-        Vec<typename F::Out, VEC> vo;
-#pragma unroll
-        for (int k = 0; k < VEC; ++k) {
-            vo.v[k] = F::apply(p, va.v[k], vb.v[k], vc.v[k]);
-        }
-        reinterpret_cast<Vec<typename F::Out, VEC>*>(out)[i] = vo;
     }
 }
 
 // Transposed operands. Iteration space [batch, R, C], output dense row-major.
 // Each input is read either along C (its stride on C is 1 or 0) or, when
-// `transposed` is set for it, along R through a padded shared tile. 4-byte types.
+// `transposed` is set for it, along R -- its unit-stride axis -- into a padded
+// 64x64 shared tile that is then read back along C.  16 elements per thread are in
+// flight per phase; global reads and writes are both 256-byte runs.  4-byte types.
 struct TileArgs {
     int64_t batch, rows, cols;
     int64_t sb[3], sr[3], sc[3];  // per-input element strides over (batch, R, C)
     int transposed[3];
 };
 
+constexpr int kTile = 64;
+
 template <typename F>
 __global__ void __launch_bounds__(256)
 tiled_kernel(typename F::Out* __restrict__ out, const typename F::In0* __restrict__ a,
              const typename F::In1* __restrict__ b, const typename F::In2* __restrict__ c,
              TileArgs t, typename F::P p) {
-    __shared__ typename F::In0 ta[32][33];
-    __shared__ typename F::In1 tb[32][33];
-    const int64_t tiles_c = (t.cols + 31) / 32;
-    const int64_t tiles_r = (t.rows + 31) / 32;
+    __shared__ typename F::In0 ta[kTile][kTile + 1];
+    __shared__ typename F::In1 tb[kTile][kTile + 1];
+    const int64_t tiles_c = (t.cols + kTile - 1) / kTile;
+    const int64_t tiles_r = (t.rows + kTile - 1) / kTile;
     const int64_t n_tiles = tiles_c * tiles_r * t.batch;
-    const int tx = threadIdx.x & 31;
-    const int ty = threadIdx.x >> 5;  // 0..7
-    for (int64_t tile = blockIdx.x; tile < n_tiles; tile += gridDim.x) {
-        const int64_t tc = tile % tiles_c;
-        const int64_t tr = (tile / tiles_c) % tiles_r;
-        const int64_t bi = tile / (tiles_c * tiles_r);
-        const int64_t r0 = tr * 32;
-        const int64_t c0 = tc * 32;
-        // stage transposed inputs: thread (tx,ty) reads row r0+tx (unit stride), col c0+ty+8j
+    const int fast = threadIdx.x & 63;  // position along the unit-stride axis of the phase
+    const int slow = threadIdx.x >> 6;  // 0..3
+    // Tiles are numbered so that 16 consecutive ones form a 4x4 super-tile: blocks
+    // that run at the same time then touch 1 KB runs of both the transposed source and
+    // the destination instead of 256-byte fragments of 16 different DRAM pages.
+    const int64_t super_c = (tiles_c + 3) / 4;
+    const int64_t super_r = (tiles_r + 3) / 4;
+    const int64_t n_slots = super_c * super_r * 16 * t.batch;
+    (void)n_tiles;
+    for (int64_t slot = blockIdx.x; slot < n_slots; slot += gridDim.x) {
+        const int64_t within = slot & 15;
+        const int64_t sup = slot >> 4;
+        const int64_t sc_i = sup % super_c;
+        const int64_t sr_i = (sup / super_c) % super_r;
+        const int64_t bi = sup / (super_c * super_r);
+        const int64_t tc = sc_i * 4 + (within & 3);
+        const int64_t tr = sr_i * 4 + (within >> 2);
+        if (tc >= tiles_c || tr >= tiles_r) {
+            continue;  // block-uniform
+        }
+        const int64_t r0 = tr * kTile;
+        const int64_t c0 = tc * kTile;
+        const bool full = r0 + kTile <= t.rows && c0 + kTile <= t.cols;  // block-uniform
+        // phase 1: transposed inputs, threads run along R (their unit-stride axis)
         if (t.transposed[0]) {
+            const typename F::In0* src = a + bi * t.sb[0] + (r0 + fast) * t.sr[0] + (c0 + slow) * t.sc[0];
+            const int64_t step = 4 * t.sc[0];
+            if (full) {
 #pragma unroll
-            for (int j = 0; j < 4; ++j) {
-                const int64_t r = r0 + tx;
-                const int64_t cc = c0 + ty + 8 * j;
-                if (r < t.rows && cc < t.cols) {
-                    ta[tx][ty + 8 * j] = a[bi * t.sb[0] + r * t.sr[0] + cc * t.sc[0]];
+                for (int j = 0; j < kTile / 4; ++j) {
+                    ta[fast][slow + 4 * j] = src[j * step];
+                }
+            } else if (r0 + fast < t.rows) {
+#pragma unroll
+                for (int j = 0; j < kTile / 4; ++j) {
+                    if (c0 + slow + 4 * j < t.cols) {
+                        ta[fast][slow + 4 * j] = src[j * step];
+                    }
                 }
             }
         }
         if constexpr (F::NIN >= 2) {
             if (t.transposed[1]) {
+                const typename F::In1* src = b + bi * t.sb[1] + (r0 + fast) * t.sr[1] + (c0 + slow) * t.sc[1];
+                const int64_t step = 4 * t.sc[1];
+                if (full) {
 #pragma unroll
-                for (int j = 0; j < 4; ++j) {
-                    const int64_t r = r0 + tx;
-                    const int64_t cc = c0 + ty + 8 * j;
-                    if (r < t.rows && cc < t.cols) {
-                        tb[tx][ty + 8 * j] = b[bi * t.sb[1] + r * t.sr[1] + cc * t.sc[1]];
+                    for (int j = 0; j < kTile / 4; ++j) {
+                        tb[fast][slow + 4 * j] = src[j * step];
+                    }
+                } else if (r0 + fast < t.rows) {
+#pragma unroll
+                    for (int j = 0; j < kTile / 4; ++j) {
+                        if (c0 + slow + 4 * j < t.cols) {
+                            tb[fast][slow + 4 * j] = src[j * step];
+                        }
                     }
                 }
             }
         }
         __syncthreads();
+        // phase 2: threads run along C; row r0 + slow + 4j for j = 0..15
+        typename F::Out* dst = out + (bi * t.rows + r0 + slow) * t.cols + c0 + fast;
+        const int64_t dstep = 4 * t.cols;
+        const typename F::In0* ap = a + bi * t.sb[0] + (r0 + slow) * t.sr[0] + (c0 + fast) * t.sc[0];
+        const int64_t astep = 4 * t.sr[0];
+        const typename F::In1* bp = nullptr;
+        int64_t bstep = 0;
+        if constexpr (F::NIN >= 2) {
+            bp = b + bi * t.sb[1] + (r0 + slow) * t.sr[1] + (c0 + fast) * t.sc[1];
+            bstep = 4 * t.sr[1];
+        }
+        const bool col_ok = c0 + fast < t.cols;
+        typename F::In0 xs[kTile / 4];
+        typename F::In1 ys[kTile / 4];
 #pragma unroll
-        for (int j = 0; j < 4; ++j) {
-            const int64_t r = r0 + ty + 8 * j;
-            const int64_t cc = c0 + tx;
-            if (r < t.rows && cc < t.cols) {
-                const typename F::In0 x = t.transposed[0]
-                                              ? ta[ty + 8 * j][tx]
-                                              : a[bi * t.sb[0] + r * t.sr[0] + cc * t.sc[0]];
-                typename F::In1 y{};
+        for (int j = 0; j < kTile / 4; ++j) {
+            const bool ok = full || (col_ok && r0 + slow + 4 * j < t.rows);
+            xs[j] = typename F::In0{};
+            ys[j] = typename F::In1{};
+            if (ok) {
+                xs[j] = t.transposed[0] ? ta[slow + 4 * j][fast] : ap[j * astep];
                 if constexpr (F::NIN >= 2) {
-                    y = t.transposed[1] ? tb[ty + 8 * j][tx]
-                                        : b[bi * t.sb[1] + r * t.sr[1] + cc * t.sc[1]];
+                    ys[j] = t.transposed[1] ? tb[slow + 4 * j][fast] : bp[j * bstep];
                 }
-                out[(bi * t.rows + r) * t.cols + cc] = F::apply(p, x, y, typename F::In2{});
+            }
+        }
+#pragma unroll
+        for (int j = 0; j < kTile / 4; ++j) {
+            if (full || (col_ok && r0 + slow + 4 * j < t.rows)) {
+                dst[j * dstep] = F::apply(p, xs[j], ys[j], typename F::In2{});
             }
         }
         __syncthreads();
@@ -481,9 +600,36 @@ Layout4 collapse(const View* views, int n) {
     return L;
 }
 
+template <typename I>
+LayoutT<I> narrow(const Layout4& L) {
+    LayoutT<I> r;
+    r.ndim = L.ndim;
+    for (int a = 0; a < kMaxDims; ++a) {
+        r.dim[a] = static_cast<I>(L.dim[a]);
+        for (int o = 0; o < 3; ++o) {
+            r.stride[o][a] = static_cast<I>(L.stride[o][a]);
+        }
+    }
+    return r;
+}
+
 template <typename T>
 bool aligned_for(const void* p, int vec) {
     return reinterpret_cast<uintptr_t>(p) % (sizeof(T) * vec) == 0;
+}
+
+template <typename F, int VEC>
+void launch_strided(b200_ctx* ctx, typename F::Out* o, const typename F::In0* a, const typename F::In1* b,
+                    const typename F::In2* c, int64_t nvec, const Layout4& L, bool small_index,
+                    const typename F::P& p) {
+    const unsigned grid = grid_for(ceil_div(nvec, unroll_for<VEC>()), kThreads);
+    if (small_index) {
+        strided_kernel<F, VEC, uint32_t><<<grid, kThreads, 0, ctx->stream>>>(
+            o, a, b, c, static_cast<uint32_t>(nvec), narrow<uint32_t>(L), p);
+    } else {
+        strided_kernel<F, VEC, int64_t><<<grid, kThreads, 0, ctx->stream>>>(o, a, b, c, nvec,
+                                                                            narrow<int64_t>(L), p);
+    }
 }
 
 template <typename F>
@@ -499,6 +645,7 @@ void run(b200_ctx* ctx, const b200_node& node, const typename F::P& p) {
         fail(B200_INVALID_ARGUMENT, "elementwise node is missing a source");
     }
     View in[3];
+    bool small_index = out.numel < (int64_t(1) << 31);
     for (int i = 0; i < F::NIN; ++i) {
         in[i] = make_view(node.src[i]);
         for (int a = 0; a < kMaxDims; ++a) {
@@ -506,6 +653,7 @@ void run(b200_ctx* ctx, const b200_node& node, const typename F::P& p) {
                 fail(B200_SHAPE_ERROR, "elementwise operand extents differ from the output's");
             }
         }
+        small_index = small_index && fits32(in[i]);
     }
     auto* o = reinterpret_cast<typename F::Out*>(out.data);
     auto* a = reinterpret_cast<const typename F::In0*>(in[0].data);
@@ -517,7 +665,12 @@ void run(b200_ctx* ctx, const b200_node& node, const typename F::P& p) {
     for (int i = 0; i < F::NIN; ++i) {
         dense = dense && in[i].contiguous;
     }
-    constexpr int kVec = sizeof(typename F::Out) == 8 ? 2 : 4;
+    // 16 bytes per vector of the NARROWEST type involved (capped at 8 elements)
+    constexpr size_t kMinSize =
+        std::min(std::min(sizeof(typename F::In0), sizeof(typename F::Out)),
+                 std::min(F::NIN >= 2 ? sizeof(typename F::In1) : size_t(8),
+                          F::NIN >= 3 ? sizeof(typename F::In2) : size_t(8)));
+    constexpr int kVec = kMinSize >= 8 ? 2 : (kMinSize == 4 ? 4 : 8);
     if (dense) {
         bool al = aligned_for<typename F::Out>(o, kVec) && aligned_for<typename F::In0>(a, kVec);
         if (F::NIN >= 2) {
@@ -527,10 +680,11 @@ void run(b200_ctx* ctx, const b200_node& node, const typename F::P& p) {
             al = al && aligned_for<typename F::In2>(c, kVec);
         }
         if (al) {
-            flat_kernel<F, kVec><<<grid_for(n / kVec + 1, kThreads), kThreads, 0, ctx->stream>>>(
+            flat_kernel<F, kVec><<<grid_for(ceil_div(n / kVec + 1, unroll_for<kVec>()), kThreads), kThreads, 0, ctx->stream>>>(
                 o, a, b, c, n, p);
         } else {
-            flat_kernel<F, 1><<<grid_for(n, kThreads), kThreads, 0, ctx->stream>>>(o, a, b, c, n, p);
+            flat_kernel<F, 1><<<grid_for(ceil_div(n, unroll_for<1>()), kThreads), kThreads, 0, ctx->stream>>>(o, a, b, c, n,
+                                                                                                   p);
         }
         ctx->count_launch();
         check_last_launch("elementwise flat");
@@ -565,8 +719,9 @@ void run(b200_ctx* ctx, const b200_node& node, const typename F::P& p) {
                 }
             }
             if (ok && any_t && t.rows >= 8 && t.cols >= 8) {
-                const int64_t tiles = ceil_div(t.rows, 32) * ceil_div(t.cols, 32) * t.batch;
-                tiled_kernel<F><<<grid_for(tiles, 1, 16), 256, 0, ctx->stream>>>(o, a, b, c, t, p);
+                const int64_t tiles = ceil_div(ceil_div(t.rows, kTile), 4) * ceil_div(ceil_div(t.cols, kTile), 4) * 16 *
+                                      t.batch;
+                tiled_kernel<F><<<grid_for(tiles, 1, 8), 256, 0, ctx->stream>>>(o, a, b, c, t, p);
                 ctx->count_launch();
                 check_last_launch("elementwise tiled");
                 return;
@@ -599,12 +754,9 @@ void run(b200_ctx* ctx, const b200_node& node, const typename F::P& p) {
         for (int i = 0; i < F::NIN; ++i) {
             V.stride[i][inner] *= kVec;
         }
-        const int64_t nvec = n / kVec;
-        strided_kernel<F, kVec><<<grid_for(nvec, kThreads), kThreads, 0, ctx->stream>>>(o, a, b, c,
-                                                                                       nvec, V, p);
+        launch_strided<F, kVec>(ctx, o, a, b, c, n / kVec, V, small_index, p);
     } else {
-        strided_kernel<F, 1><<<grid_for(n, kThreads), kThreads, 0, ctx->stream>>>(o, a, b, c, n, L,
-                                                                                  p);
+        launch_strided<F, 1>(ctx, o, a, b, c, n, L, small_index, p);
     }
     ctx->count_launch();
     check_last_launch("elementwise strided");
@@ -614,10 +766,22 @@ void run(b200_ctx* ctx, const b200_node& node, const typename F::P& p) {
 // Creation and index-pattern ops (outputs are dense)
 // ---------------------------------------------------------------------------
 
+// 16-byte stores; the pointer comes from the allocator, so it is 512-byte aligned.
 template <typename T>
 __global__ void __launch_bounds__(kThreads) fill_kernel(T* __restrict__ out, int64_t n, T value) {
+    constexpr int V = 16 / sizeof(T);
+    Vec<T, V> v;
+#pragma unroll
+    for (int k = 0; k < V; ++k) {
+        v.v[k] = value;
+    }
+    const bool aligned = reinterpret_cast<uintptr_t>(out) % 16 == 0;
+    const int64_t nvec = aligned ? n / V : 0;
     const int64_t stride = int64_t(gridDim.x) * blockDim.x;
-    for (int64_t i = int64_t(blockIdx.x) * blockDim.x + threadIdx.x; i < n; i += stride) {
+    for (int64_t i = int64_t(blockIdx.x) * blockDim.x + threadIdx.x; i < nvec; i += stride) {
+        reinterpret_cast<Vec<T, V>*>(out)[i] = v;
+    }
+    for (int64_t i = nvec * V + int64_t(blockIdx.x) * blockDim.x + threadIdx.x; i < n; i += stride) {
         out[i] = value;
     }
 }
@@ -725,7 +889,7 @@ void run_full(b200_ctx* ctx, const b200_node& node) {
     if (n == 0) {
         return;
     }
-    const unsigned g = grid_for(n, kThreads);
+    const unsigned g = grid_for(ceil_div(n, 4), kThreads);
     switch (out.dtype) {
         case B200_F32:
             fill_kernel<float><<<g, kThreads, 0, ctx->stream>>>(reinterpret_cast<float*>(out.data), n,

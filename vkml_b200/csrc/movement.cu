@@ -1,13 +1,19 @@
 // Window and index movement ops: im2col, col2im, max_pool2d (+backward),
 // index_select, scatter_add.
 //
-// Every kernel is one thread per OUTPUT element and accumulates in the same
-// order as vkML's CPU backend (src/backend/cpu/kernels_movement.cpp), so
-// results are bit-identical: col2im and max_pool2d_backward pull their window
-// terms in (ki, kj) order (:501-542, :629-680); scatter_add folds the sources
-// of one destination in ascending index position (:381-429); max_pool2d takes
-// the first maximum under a strict compare (:557-580).  Inputs may be strided
-// views; outputs are dense.
+// Every kernel is one thread per OUTPUT element (or per pooling window) and
+// accumulates in the same order as vkML's CPU backend
+// (src/backend/cpu/kernels_movement.cpp), so results are bit-identical: col2im and
+// max_pool2d_backward pull their window terms in (ki, kj) order (:501-542,
+// :629-680); scatter_add folds the sources of one destination in ascending index
+// position (:381-429); max_pool2d takes the first maximum under a strict compare
+// (:557-580).  Inputs may be strided views; outputs are dense.
+//
+// These ops move 8-40 bytes per element, so index arithmetic decides the speed:
+// the block owns one (image, row) or one plane, the per-thread work is one 32-bit
+// divide, and the unit-stride / non-overlapping-window cases are compiled without
+// any divide by the window stride.  Tensors too large for 32-bit indices take the
+// generic 64-bit kernels.
 #include "context.h"
 
 namespace b200 {
@@ -17,7 +23,8 @@ constexpr int kThreads = 256;
 
 struct Win {
     int kh, kw, sh, sw, ph, pw, dh, dw;
-    int64_t image_h, image_w, out_h, out_w, channels;
+    int image_h, image_w, out_h, out_w;
+    int64_t channels;
 };
 
 // window_of (kernels_movement.cpp:438-447)
@@ -25,6 +32,10 @@ Win make_win(const UnfoldParams& p, int64_t channels_times_patch) {
     auto span = [](int64_t extent, int k, int s, int pad, int d) {
         return (extent + 2LL * pad - (static_cast<int64_t>(d) * (k - 1) + 1)) / s + 1;
     };
+    if (p.kernel_h <= 0 || p.kernel_w <= 0 || p.stride_h <= 0 || p.stride_w <= 0 || p.dilation_h <= 0 ||
+        p.dilation_w <= 0 || p.image_h < 0 || p.image_w < 0) {
+        fail(B200_SHAPE_ERROR, "window geometry must be positive");
+    }
     Win w;
     w.kh = p.kernel_h;
     w.kw = p.kernel_w;
@@ -36,100 +47,127 @@ Win make_win(const UnfoldParams& p, int64_t channels_times_patch) {
     w.dw = p.dilation_w;
     w.image_h = p.image_h;
     w.image_w = p.image_w;
-    w.out_h = span(p.image_h, p.kernel_h, p.stride_h, p.pad_h, p.dilation_h);
-    w.out_w = span(p.image_w, p.kernel_w, p.stride_w, p.pad_w, p.dilation_w);
+    w.out_h = static_cast<int>(span(p.image_h, p.kernel_h, p.stride_h, p.pad_h, p.dilation_h));
+    w.out_w = static_cast<int>(span(p.image_w, p.kernel_w, p.stride_w, p.pad_w, p.dilation_w));
     w.channels = channels_times_patch / (static_cast<int64_t>(p.kernel_h) * p.kernel_w);
     return w;
 }
 
-template <bool DENSE>
-__device__ __forceinline__ float load_lin(const float* p, const Geo& g, int64_t linear) {
-    return DENSE ? p[linear] : p[geo_offset(g, linear)];
+// Element strides of a rank-4 [N, C, H, W] (or [N, R, L] padded) view.
+struct Strides4 {
+    int64_t s[4];
+};
+
+Strides4 strides_of(const View& v) {
+    Strides4 r;
+    for (int i = 0; i < 4; ++i) r.s[i] = v.stride[i];
+    return r;
 }
 
-// out[n, c*kh*kw + ki*kw + kj, oh*out_w + ow] = in[n, c, h, x] or 0 outside.
-template <bool DENSE>
+// ---------------------------------------------------------------------------
+// im2col: out[n, c*kh*kw + ki*kw + kj, oh*out_w + ow] = in[n, c, h, x] or 0 outside.
+// One block per (n, c, chunk of positions) writes all kh*kw rows of that channel:
+// the rows re-read the same input plane, so it is fetched from HBM once.
+// ---------------------------------------------------------------------------
 __global__ void __launch_bounds__(kThreads)
-im2col_kernel(float* __restrict__ out, const float* __restrict__ in, Geo gin, Win w, int64_t rows,
-              int64_t total) {
-    const int64_t positions = w.out_h * w.out_w;
-    const int64_t patch = int64_t(w.kh) * w.kw;
-    const int64_t stride = int64_t(gridDim.x) * blockDim.x;
-    for (int64_t i = int64_t(blockIdx.x) * blockDim.x + threadIdx.x; i < total; i += stride) {
-        const int64_t pos = i % positions;
-        const int64_t row = (i / positions) % rows;
-        const int64_t n = i / (positions * rows);
-        const int64_t c = row / patch;
-        const int64_t ki = (row % patch) / w.kw;
-        const int64_t kj = (row % patch) % w.kw;
-        const int64_t oh = pos / w.out_w;
-        const int64_t ow = pos % w.out_w;
-        const int64_t h = oh * w.sh - w.ph + ki * w.dh;
-        const int64_t x = ow * w.sw - w.pw + kj * w.dw;
-        float v = 0.0F;
-        if (h >= 0 && h < w.image_h && x >= 0 && x < w.image_w) {
-            v = load_lin<DENSE>(in, gin, ((n * w.channels + c) * w.image_h + h) * w.image_w + x);
+im2col_kernel(float* __restrict__ out, const float* __restrict__ in, Strides4 is, Win w, int positions,
+              int chunks) {
+    const unsigned b = blockIdx.x;
+    const unsigned chunk = b % chunks;
+    const unsigned nc = b / chunks;  // n * channels + c
+    const unsigned c = nc % static_cast<unsigned>(w.channels);
+    const unsigned n = nc / static_cast<unsigned>(w.channels);
+    const int pos = chunk * blockDim.x + threadIdx.x;
+    if (pos >= positions) {
+        return;
+    }
+    const int oh = pos / w.out_w;
+    const int ow = pos - oh * w.out_w;
+    const float* plane = in + int64_t(n) * is.s[0] + int64_t(c) * is.s[1];
+    float* dst = out + int64_t(nc) * (w.kh * w.kw) * positions + pos;
+    const int h0 = oh * w.sh - w.ph;
+    const int x0 = ow * w.sw - w.pw;
+    for (int ki = 0; ki < w.kh; ++ki) {
+        const int h = h0 + ki * w.dh;
+        const bool row_ok = h >= 0 && h < w.image_h;
+        for (int kj = 0; kj < w.kw; ++kj) {
+            const int x = x0 + kj * w.dw;
+            float v = 0.0F;
+            if (row_ok && x >= 0 && x < w.image_w) {
+                v = plane[int64_t(h) * is.s[2] + int64_t(x) * is.s[3]];
+            }
+            dst[int64_t(ki * w.kw + kj) * positions] = v;
         }
-        out[i] = v;
     }
 }
 
-template <bool DENSE>
+// ---------------------------------------------------------------------------
+// col2im: pull form, one thread per image element, one block per chunk of a plane.
+// UNIT: stride 1 and dilation 1 in both directions (no divide by the stride);
+// KH, KW > 0: window extents known at compile time, taps fully unrolled.
+// ---------------------------------------------------------------------------
+template <bool UNIT, int KH, int KW>
 __global__ void __launch_bounds__(kThreads)
-col2im_kernel(float* __restrict__ out, const float* __restrict__ cols, Geo gcols, Win w,
-              int64_t rows, int64_t total) {
-    const int64_t positions = w.out_h * w.out_w;
-    const int64_t patch = int64_t(w.kh) * w.kw;
-    const int64_t stride = int64_t(gridDim.x) * blockDim.x;
-    for (int64_t i = int64_t(blockIdx.x) * blockDim.x + threadIdx.x; i < total; i += stride) {
-        const int64_t x = i % w.image_w;
-        const int64_t h = (i / w.image_w) % w.image_h;
-        const int64_t c = (i / (w.image_w * w.image_h)) % w.channels;
-        const int64_t n = i / (w.image_w * w.image_h * w.channels);
-        float acc = 0.0F;
-        for (int ki = 0; ki < w.kh; ++ki) {
-            const int64_t top = h + w.ph - int64_t(ki) * w.dh;
-            if (top < 0 || top % w.sh != 0) {
-                continue;
+col2im_kernel(float* __restrict__ out, const float* __restrict__ cols, Strides4 cs, Win w, int chunks) {
+    const unsigned b = blockIdx.x;
+    const unsigned chunk = b % chunks;
+    const unsigned plane = b / chunks;  // n * channels + c
+    const unsigned c = plane % static_cast<unsigned>(w.channels);
+    const unsigned n = plane / static_cast<unsigned>(w.channels);
+    const int hw = chunk * blockDim.x + threadIdx.x;
+    if (hw >= w.image_h * w.image_w) {
+        return;
+    }
+    const int h = hw / w.image_w;
+    const int x = hw - h * w.image_w;
+    const int kh = KH > 0 ? KH : w.kh;
+    const int kw = KW > 0 ? KW : w.kw;
+    const float* base = cols + int64_t(n) * cs.s[1] + int64_t(c) * (kh * kw) * cs.s[2];
+    float acc = 0.0F;
+#pragma unroll
+    for (int ki = 0; ki < kh; ++ki) {
+        const int top = h + w.ph - (UNIT ? ki : ki * w.dh);
+        int oh = top;
+        bool ok_h = top >= 0;
+        if (!UNIT) {
+            ok_h = ok_h && top % w.sh == 0;
+            oh = top / w.sh;
+        }
+        ok_h = ok_h && oh < w.out_h;
+#pragma unroll
+        for (int kj = 0; kj < kw; ++kj) {
+            const int left = x + w.pw - (UNIT ? kj : kj * w.dw);
+            int ow = left;
+            bool ok = ok_h && left >= 0;
+            if (!UNIT) {
+                ok = ok && left % w.sw == 0;
+                ow = left / w.sw;
             }
-            const int64_t oh = top / w.sh;
-            if (oh >= w.out_h) {
-                continue;
-            }
-            for (int kj = 0; kj < w.kw; ++kj) {
-                const int64_t left = x + w.pw - int64_t(kj) * w.dw;
-                if (left < 0 || left % w.sw != 0) {
-                    continue;
-                }
-                const int64_t ow = left / w.sw;
-                if (ow >= w.out_w) {
-                    continue;
-                }
-                const int64_t row = c * patch + int64_t(ki) * w.kw + kj;
-                acc += load_lin<DENSE>(cols, gcols, (n * rows + row) * positions + oh * w.out_w + ow);
+            ok = ok && ow < w.out_w;
+            if (ok) {
+                acc += base[int64_t(ki * kw + kj) * cs.s[2] + int64_t(oh * w.out_w + ow) * cs.s[3]];
             }
         }
-        out[i] = acc;
     }
+    out[int64_t(plane) * (w.image_h * w.image_w) + hw] = acc;
 }
 
 // First strict maximum of one window; -1 if nothing beat -inf.
-template <bool DENSE>
-__device__ __forceinline__ int argmax_in_window(const float* in, const Geo& gin, const Win& w,
-                                                int64_t base, int64_t oh, int64_t ow, float& best) {
+__device__ __forceinline__ int argmax_in_window(const float* plane, int64_t sh_, int64_t sw_, const Win& w,
+                                                int oh, int ow, float& best) {
     best = -INFINITY;
     int best_offset = -1;
     for (int ki = 0; ki < w.kh; ++ki) {
-        const int64_t h = oh * w.sh - w.ph + int64_t(ki) * w.dh;
+        const int h = oh * w.sh - w.ph + ki * w.dh;
         if (h < 0 || h >= w.image_h) {
             continue;
         }
         for (int kj = 0; kj < w.kw; ++kj) {
-            const int64_t x = ow * w.sw - w.pw + int64_t(kj) * w.dw;
+            const int x = ow * w.sw - w.pw + kj * w.dw;
             if (x < 0 || x >= w.image_w) {
                 continue;
             }
-            const float v = load_lin<DENSE>(in, gin, base + h * w.image_w + x);
+            const float v = plane[int64_t(h) * sh_ + int64_t(x) * sw_];
             if (v > best) {
                 best = v;
                 best_offset = ki * w.kw + kj;
@@ -139,103 +177,249 @@ __device__ __forceinline__ int argmax_in_window(const float* in, const Geo& gin,
     return best_offset;
 }
 
-template <bool DENSE>
+// One thread per output element, one block per chunk of an output plane.
 __global__ void __launch_bounds__(kThreads)
-max_pool2d_kernel(float* __restrict__ out, const float* __restrict__ in, Geo gin, Win w,
-                  int64_t out_h, int64_t out_w, int64_t total, uint32_t* status) {
-    const int64_t stride = int64_t(gridDim.x) * blockDim.x;
-    for (int64_t i = int64_t(blockIdx.x) * blockDim.x + threadIdx.x; i < total; i += stride) {
-        const int64_t ow = i % out_w;
-        const int64_t oh = (i / out_w) % out_h;
-        const int64_t plane = i / (out_w * out_h);
-        float best;
-        const int off = argmax_in_window<DENSE>(in, gin, w, plane * w.image_h * w.image_w, oh, ow, best);
-        if (off < 0) {
-            // the CPU backend asserts here: a window with no element above -inf
-            atomicOr(status, kStatusInternal);
-            best = __int_as_float(0x7fc00000);
+max_pool2d_kernel(float* __restrict__ out, const float* __restrict__ in, Strides4 is, Win w, int out_h,
+                  int out_w, int channels, int chunks, uint32_t* status) {
+    const unsigned b = blockIdx.x;
+    const unsigned chunk = b % chunks;
+    const unsigned plane = b / chunks;
+    const unsigned c = plane % channels;
+    const unsigned n = plane / channels;
+    const int p = chunk * blockDim.x + threadIdx.x;
+    if (p >= out_h * out_w) {
+        return;
+    }
+    const int oh = p / out_w;
+    const int ow = p - oh * out_w;
+    float best;
+    const int off = argmax_in_window(in + int64_t(n) * is.s[0] + int64_t(c) * is.s[1], is.s[2], is.s[3], w, oh, ow,
+                                     best);
+    if (off < 0) {
+        // the CPU backend asserts here: a window with no element above -inf
+        atomicOr(status, kStatusInternal);
+        best = __int_as_float(0x7fc00000);
+    }
+    out[int64_t(plane) * (out_h * out_w) + p] = best;
+}
+
+// Non-overlapping windows (stride == kernel, no padding or dilation): one thread per
+// window with compile-time extents, rows read as one KW-wide vector when aligned.
+template <int KH, int KW>
+__global__ void __launch_bounds__(kThreads)
+max_pool2d_tiled_kernel(float* __restrict__ out, const float* __restrict__ in, Strides4 is, int out_h, int out_w,
+                        int channels, int chunks, int vec_ok, uint32_t* status) {
+    const unsigned b = blockIdx.x;
+    const unsigned chunk = b % chunks;
+    const unsigned plane = b / chunks;
+    const unsigned c = plane % channels;
+    const unsigned n = plane / channels;
+    const int p = chunk * blockDim.x + threadIdx.x;
+    if (p >= out_h * out_w) {
+        return;
+    }
+    const int oh = p / out_w;
+    const int ow = p - oh * out_w;
+    const float* src = in + int64_t(n) * is.s[0] + int64_t(c) * is.s[1] + int64_t(oh * KH) * is.s[2] +
+                       int64_t(ow * KW) * is.s[3];
+    float best = -INFINITY;
+    bool any = false;
+#pragma unroll
+    for (int ki = 0; ki < KH; ++ki) {
+        float v[KW];
+        if (KW == 2 && vec_ok) {
+            const float2 t = *reinterpret_cast<const float2*>(src + int64_t(ki) * is.s[2]);
+            v[0] = t.x;
+            v[KW - 1] = t.y;
+        } else {
+#pragma unroll
+            for (int kj = 0; kj < KW; ++kj) {
+                v[kj] = src[int64_t(ki) * is.s[2] + int64_t(kj) * is.s[3]];
+            }
         }
-        out[i] = best;
+#pragma unroll
+        for (int kj = 0; kj < KW; ++kj) {
+            if (v[kj] > best) {
+                best = v[kj];
+                any = true;
+            }
+        }
+    }
+    if (!any) {
+        atomicOr(status, kStatusInternal);
+        best = __int_as_float(0x7fc00000);
+    }
+    out[int64_t(plane) * (out_h * out_w) + p] = best;
+}
+
+// Pull form of the pooling adjoint (any geometry): every input element sums the
+// gradients of the windows whose first maximum it is, in (ki, kj) order.
+__global__ void __launch_bounds__(kThreads)
+max_pool2d_backward_kernel(float* __restrict__ out, const float* __restrict__ grad, const float* __restrict__ in,
+                           Strides4 gs, Strides4 is, Win w, int out_h, int out_w, int channels, int chunks) {
+    const unsigned b = blockIdx.x;
+    const unsigned chunk = b % chunks;
+    const unsigned plane = b / chunks;
+    const unsigned c = plane % channels;
+    const unsigned n = plane / channels;
+    const int hw = chunk * blockDim.x + threadIdx.x;
+    if (hw >= w.image_h * w.image_w) {
+        return;
+    }
+    const int h = hw / w.image_w;
+    const int x = hw - h * w.image_w;
+    const float* in_plane = in + int64_t(n) * is.s[0] + int64_t(c) * is.s[1];
+    const float* g_plane = grad + int64_t(n) * gs.s[0] + int64_t(c) * gs.s[1];
+    float acc = 0.0F;
+    for (int ki = 0; ki < w.kh; ++ki) {
+        const int top = h + w.ph - ki * w.dh;
+        if (top < 0 || top % w.sh != 0) {
+            continue;
+        }
+        const int oh = top / w.sh;
+        if (oh >= out_h) {
+            continue;
+        }
+        for (int kj = 0; kj < w.kw; ++kj) {
+            const int left = x + w.pw - kj * w.dw;
+            if (left < 0 || left % w.sw != 0) {
+                continue;
+            }
+            const int ow = left / w.sw;
+            if (ow >= out_w) {
+                continue;
+            }
+            float best;
+            if (argmax_in_window(in_plane, is.s[2], is.s[3], w, oh, ow, best) == ki * w.kw + kj) {
+                acc += g_plane[int64_t(oh) * gs.s[2] + int64_t(ow) * gs.s[3]];
+            }
+        }
+    }
+    out[int64_t(plane) * (w.image_h * w.image_w) + hw] = acc;
+}
+
+// Non-overlapping windows (stride == kernel, no padding, no dilation): every input
+// element lies in at most one window, so one thread per WINDOW finds the first
+// maximum once and writes its kh x kw patch: the gradient at the maximum (as
+// 0 + g, the value the pull form accumulates), zero elsewhere.  Rows and columns
+// past the last whole window belong to no window and are written as zero by the
+// threads of the extra, partial windows.
+template <int KH, int KW>
+__global__ void __launch_bounds__(kThreads)
+max_pool2d_backward_tiled_kernel(float* __restrict__ out, const float* __restrict__ grad,
+                                 const float* __restrict__ in, Strides4 gs, Strides4 is, Win w, int out_h,
+                                 int out_w, int cover_h, int cover_w, int channels, int chunks) {
+    const unsigned b = blockIdx.x;
+    const unsigned chunk = b % chunks;
+    const unsigned plane = b / chunks;
+    const unsigned c = plane % channels;
+    const unsigned n = plane / channels;
+    const int p = chunk * blockDim.x + threadIdx.x;
+    if (p >= cover_h * cover_w) {
+        return;
+    }
+    const int oh = p / cover_w;
+    const int ow = p - oh * cover_w;
+    const float* in_plane = in + int64_t(n) * is.s[0] + int64_t(c) * is.s[1];
+    float* out_plane = out + int64_t(plane) * (w.image_h * w.image_w);
+    const bool real = oh < out_h && ow < out_w;
+    int best_offset = -1;
+    float g = 0.0F;
+    if (real) {
+        float best = -INFINITY;
+#pragma unroll
+        for (int ki = 0; ki < KH; ++ki) {
+#pragma unroll
+            for (int kj = 0; kj < KW; ++kj) {
+                const float v = in_plane[int64_t(oh * KH + ki) * is.s[2] + int64_t(ow * KW + kj) * is.s[3]];
+                if (v > best) {
+                    best = v;
+                    best_offset = ki * KW + kj;
+                }
+            }
+        }
+        g = 0.0F + grad[int64_t(n) * gs.s[0] + int64_t(c) * gs.s[1] + int64_t(oh) * gs.s[2] + int64_t(ow) * gs.s[3]];
+    }
+#pragma unroll
+    for (int ki = 0; ki < KH; ++ki) {
+        const int h = oh * KH + ki;
+        if (h >= w.image_h) {
+            continue;
+        }
+#pragma unroll
+        for (int kj = 0; kj < KW; ++kj) {
+            const int x = ow * KW + kj;
+            if (x < w.image_w) {
+                out_plane[h * w.image_w + x] = (ki * KW + kj == best_offset) ? g : 0.0F;
+            }
+        }
     }
 }
 
-template <bool DENSE_IN, bool DENSE_G>
-__global__ void __launch_bounds__(kThreads)
-max_pool2d_backward_kernel(float* __restrict__ out, const float* __restrict__ grad,
-                           const float* __restrict__ in, Geo ggrad, Geo gin, Win w, int64_t out_h,
-                           int64_t out_w, int64_t total) {
-    const int64_t stride = int64_t(gridDim.x) * blockDim.x;
-    for (int64_t i = int64_t(blockIdx.x) * blockDim.x + threadIdx.x; i < total; i += stride) {
-        const int64_t x = i % w.image_w;
-        const int64_t h = (i / w.image_w) % w.image_h;
-        const int64_t plane = i / (w.image_w * w.image_h);
-        const int64_t base = plane * w.image_h * w.image_w;
-        float acc = 0.0F;
-        for (int ki = 0; ki < w.kh; ++ki) {
-            const int64_t top = h + w.ph - int64_t(ki) * w.dh;
-            if (top < 0 || top % w.sh != 0) {
-                continue;
-            }
-            const int64_t oh = top / w.sh;
-            if (oh >= out_h) {
-                continue;
-            }
-            for (int kj = 0; kj < w.kw; ++kj) {
-                const int64_t left = x + w.pw - int64_t(kj) * w.dw;
-                if (left < 0 || left % w.sw != 0) {
-                    continue;
-                }
-                const int64_t ow = left / w.sw;
-                if (ow >= out_w) {
-                    continue;
-                }
-                float best;
-                if (argmax_in_window<DENSE_IN>(in, gin, w, base, oh, ow, best) == ki * w.kw + kj) {
-                    acc += load_lin<DENSE_G>(grad, ggrad, (plane * out_h + oh) * out_w + ow);
-                }
-            }
-        }
-        out[i] = acc;
-    }
-}
+// ---------------------------------------------------------------------------
+// index_select / scatter_add
+// ---------------------------------------------------------------------------
 
 // out[outer, k, rest] = a[outer, idx[k], rest]  (kernels_movement.cpp:339-369).
 // An out-of-range index is recorded in the status word and clamped; the host
 // reports it as an index error at the next synchronize.
-template <typename T>
+template <typename T, typename I>
 __global__ void __launch_bounds__(kThreads)
-index_select_kernel(T* __restrict__ out, const T* __restrict__ a, const int64_t* __restrict__ idx,
-                    Geo ga, Geo gidx, int64_t inner, int64_t extent, int64_t a_extent, int64_t total,
-                    uint32_t* status) {
+index_select_kernel(T* __restrict__ out, const T* __restrict__ a, const int64_t* __restrict__ idx, GeoT<I> ga,
+                    I idx_stride, I inner, I extent, I a_extent, I total, uint32_t* status) {
     const int64_t stride = int64_t(gridDim.x) * blockDim.x;
-    for (int64_t i = int64_t(blockIdx.x) * blockDim.x + threadIdx.x; i < total; i += stride) {
-        const int64_t rest = i % inner;
-        const int64_t k = (i / inner) % extent;
-        const int64_t outer = i / (inner * extent);
-        int64_t j = idx[geo_offset(gidx, k)];
-        if (j < 0 || j >= a_extent) {
+    for (int64_t li = int64_t(blockIdx.x) * blockDim.x + threadIdx.x; li < int64_t(total); li += stride) {
+        const I i = static_cast<I>(li);
+        const I q = i / inner;
+        const I rest = i - q * inner;
+        const I outer = q / extent;
+        const I k = q - outer * extent;
+        int64_t j = idx[k * idx_stride];
+        if (j < 0 || j >= int64_t(a_extent)) {
             atomicOr(status, kStatusIndexOutOfRange);
-            j = j < 0 ? 0 : a_extent - 1;
+            j = j < 0 ? 0 : int64_t(a_extent) - 1;
         }
-        out[i] = a[geo_offset(ga, (outer * a_extent + j) * inner + rest)];
+        out[i] = a[geo_off<I>(ga, (outer * a_extent + static_cast<I>(j)) * inner + rest)];
+    }
+}
+
+// Dense source rows of 16-byte multiples: one thread per 16 bytes.
+__global__ void __launch_bounds__(kThreads)
+index_select_rows_kernel(uint4* __restrict__ out, const uint4* __restrict__ a, const int64_t* __restrict__ idx,
+                         int64_t idx_stride, unsigned inner16, unsigned extent, unsigned a_extent,
+                         unsigned total16, uint32_t* status) {
+    const int64_t stride = int64_t(gridDim.x) * blockDim.x;
+    for (int64_t li = int64_t(blockIdx.x) * blockDim.x + threadIdx.x; li < int64_t(total16); li += stride) {
+        const unsigned i = static_cast<unsigned>(li);
+        const unsigned q = i / inner16;
+        const unsigned rest = i - q * inner16;
+        const unsigned outer = q / extent;
+        const unsigned k = q - outer * extent;
+        int64_t j = idx[int64_t(k) * idx_stride];
+        if (j < 0 || j >= int64_t(a_extent)) {
+            atomicOr(status, kStatusIndexOutOfRange);
+            j = j < 0 ? 0 : int64_t(a_extent) - 1;
+        }
+        out[i] = a[(int64_t(outer) * a_extent + j) * inner16 + rest];
     }
 }
 
 // out[outer, j, rest] = sum over k with idx[k] == j of src[outer, k, rest], k ascending.
+template <typename I>
 __global__ void __launch_bounds__(kThreads)
-scatter_add_kernel(float* __restrict__ out, const float* __restrict__ src,
-                   const int64_t* __restrict__ idx, Geo gsrc, Geo gidx, int64_t inner,
-                   int64_t src_extent, int64_t out_extent, int64_t total, uint32_t* status) {
+scatter_add_kernel(float* __restrict__ out, const float* __restrict__ src, const int64_t* __restrict__ idx,
+                   GeoT<I> gsrc, I idx_stride, I inner, I src_extent, I out_extent, I total) {
     const int64_t stride = int64_t(gridDim.x) * blockDim.x;
-    for (int64_t i = int64_t(blockIdx.x) * blockDim.x + threadIdx.x; i < total; i += stride) {
-        const int64_t rest = i % inner;
-        const int64_t j = (i / inner) % out_extent;
-        const int64_t outer = i / (inner * out_extent);
+    for (int64_t li = int64_t(blockIdx.x) * blockDim.x + threadIdx.x; li < int64_t(total); li += stride) {
+        const I i = static_cast<I>(li);
+        const I q = i / inner;
+        const I rest = i - q * inner;
+        const I outer = q / out_extent;
+        const int64_t j = int64_t(q - outer * out_extent);
         float acc = 0.0F;
-        for (int64_t k = 0; k < src_extent; ++k) {
-            const int64_t t = idx[geo_offset(gidx, k)];
-            if (t == j) {
-                acc += src[geo_offset(gsrc, (outer * src_extent + k) * inner + rest)];
+        for (I k = 0; k < src_extent; ++k) {
+            if (idx[k * idx_stride] == j) {
+                acc += src[geo_off<I>(gsrc, (outer * src_extent + k) * inner + rest)];
             }
         }
         out[i] = acc;
@@ -245,11 +429,11 @@ scatter_add_kernel(float* __restrict__ out, const float* __restrict__ src,
 // Flags any index outside [0, extent): scatter_add's pull form would otherwise
 // just never match it.
 __global__ void __launch_bounds__(kThreads)
-index_range_kernel(const int64_t* __restrict__ idx, Geo gidx, int64_t n, int64_t extent,
+index_range_kernel(const int64_t* __restrict__ idx, int64_t idx_stride, int64_t n, int64_t extent,
                    uint32_t* status) {
     const int64_t k = int64_t(blockIdx.x) * blockDim.x + threadIdx.x;
     if (k < n) {
-        const int64_t t = idx[geo_offset(gidx, k)];
+        const int64_t t = idx[k * idx_stride];
         if (t < 0 || t >= extent) {
             atomicOr(status, kStatusIndexOutOfRange);
         }
@@ -268,13 +452,41 @@ void require_dense(const View& v, const char* what) {
     }
 }
 
+// Block size for a per-plane loop of `n` items: a whole number of warps, at most 256.
+int block_for(int64_t n) {
+    if (n >= 256) return 256;
+    return static_cast<int>(std::max<int64_t>(32, (n + 31) / 32 * 32));
+}
+
+void check_grid(int64_t blocks, const char* what) {
+    if (blocks <= 0 || blocks > 0x7fffffffLL) {
+        fail(B200_NOT_IMPLEMENTED, std::string(what) + ": tensor too large for one launch");
+    }
+}
+
+// The index tensor of index_select / scatter_add is one-dimensional (any stride).
+int64_t index_stride(const View& idx) {
+    int64_t stride = 0;
+    int live = 0;
+    for (int i = 0; i < kMaxDims; ++i) {
+        if (idx.dim[i] > 1) {
+            stride = idx.stride[i];
+            ++live;
+        }
+    }
+    if (live > 1) {
+        fail(B200_SHAPE_ERROR, "index tensor must be one-dimensional");
+    }
+    return stride;
+}
+
 }  // namespace
 
 void launch_movement(b200_ctx* ctx, const b200_node& node) {
     const View out = make_view(node.out);
     const int64_t total = out.numel;
-    const unsigned grid = grid_for(total, kThreads);
     float* o = reinterpret_cast<float*>(out.data);
+    constexpr int64_t kMax32 = int64_t(1) << 31;
 
     switch (node.op) {
         case B200_OP_IM2COL: {
@@ -282,21 +494,23 @@ void launch_movement(b200_ctx* ctx, const b200_node& node) {
             require_f32(out, "im2col");
             require_f32(in, "im2col");
             require_dense(out, "im2col");
-            if (node.out.ndim != 3) fail(B200_SHAPE_ERROR, "im2col: output must be [N, C*kh*kw, L]");
+            if (node.out.ndim != 3 || node.src[0].ndim != 4) {
+                fail(B200_SHAPE_ERROR, "im2col: expects [N,C,H,W] -> [N, C*kh*kw, L]");
+            }
             if (total == 0) return;
             const Win w = make_win(get_params<UnfoldParams>(node), node.out.dims[1]);
-            if (w.out_h * w.out_w != node.out.dims[2] ||
-                in.numel != node.out.dims[0] * w.channels * w.image_h * w.image_w) {
+            const int64_t rows = node.out.dims[1], positions = node.out.dims[2], n = node.out.dims[0];
+            if (int64_t(w.out_h) * w.out_w != positions || in.dim[0] != n || in.dim[1] != w.channels ||
+                in.dim[2] != w.image_h || in.dim[3] != w.image_w || rows != w.channels * w.kh * w.kw) {
                 fail(B200_SHAPE_ERROR, "im2col: geometry does not match the tensors");
             }
-            const float* src = reinterpret_cast<const float*>(in.data);
-            if (in.contiguous) {
-                im2col_kernel<true><<<grid, kThreads, 0, ctx->stream>>>(o, src, geo_of(in), w,
-                                                                       node.out.dims[1], total);
-            } else {
-                im2col_kernel<false><<<grid, kThreads, 0, ctx->stream>>>(o, src, geo_of(in), w,
-                                                                        node.out.dims[1], total);
-            }
+            if (positions >= kMax32 || rows >= kMax32) fail(B200_NOT_IMPLEMENTED, "im2col: extent too large");
+            const int block = block_for(positions);
+            const int64_t chunks = ceil_div(positions, block);
+            check_grid(n * w.channels * chunks, "im2col");
+            im2col_kernel<<<static_cast<unsigned>(n * w.channels * chunks), block, 0, ctx->stream>>>(
+                o, reinterpret_cast<const float*>(in.data), strides_of(in), w, static_cast<int>(positions),
+                static_cast<int>(chunks));
             break;
         }
         case B200_OP_COL2IM: {
@@ -307,17 +521,28 @@ void launch_movement(b200_ctx* ctx, const b200_node& node) {
             if (node.src[0].ndim != 3) fail(B200_SHAPE_ERROR, "col2im: input must be [N, C*kh*kw, L]");
             if (total == 0) return;
             const Win w = make_win(get_params<UnfoldParams>(node), node.src[0].dims[1]);
-            if (w.out_h * w.out_w != node.src[0].dims[2] ||
-                total != node.src[0].dims[0] * w.channels * w.image_h * w.image_w) {
+            const int64_t n = node.src[0].dims[0];
+            const int64_t plane = int64_t(w.image_h) * w.image_w;
+            if (int64_t(w.out_h) * w.out_w != node.src[0].dims[2] || total != n * w.channels * plane ||
+                node.src[0].dims[1] != w.channels * w.kh * w.kw) {
                 fail(B200_SHAPE_ERROR, "col2im: geometry does not match the tensors");
             }
+            if (plane >= kMax32 || w.channels >= kMax32) fail(B200_NOT_IMPLEMENTED, "col2im: extent too large");
+            const int block = block_for(plane);
+            const int64_t chunks = ceil_div(plane, block);
+            check_grid(n * w.channels * chunks, "col2im");
+            const unsigned grid = static_cast<unsigned>(n * w.channels * chunks);
             const float* src = reinterpret_cast<const float*>(cols.data);
-            if (cols.contiguous) {
-                col2im_kernel<true><<<grid, kThreads, 0, ctx->stream>>>(o, src, geo_of(cols), w,
-                                                                       node.src[0].dims[1], total);
+            const bool unit = w.sh == 1 && w.sw == 1 && w.dh == 1 && w.dw == 1;
+            if (unit && w.kh == 3 && w.kw == 3) {
+                col2im_kernel<true, 3, 3><<<grid, block, 0, ctx->stream>>>(o, src, strides_of(cols), w,
+                                                                           static_cast<int>(chunks));
+            } else if (unit) {
+                col2im_kernel<true, 0, 0><<<grid, block, 0, ctx->stream>>>(o, src, strides_of(cols), w,
+                                                                           static_cast<int>(chunks));
             } else {
-                col2im_kernel<false><<<grid, kThreads, 0, ctx->stream>>>(o, src, geo_of(cols), w,
-                                                                        node.src[0].dims[1], total);
+                col2im_kernel<false, 0, 0><<<grid, block, 0, ctx->stream>>>(o, src, strides_of(cols), w,
+                                                                            static_cast<int>(chunks));
             }
             break;
         }
@@ -326,17 +551,41 @@ void launch_movement(b200_ctx* ctx, const b200_node& node) {
             require_f32(out, "max_pool2d");
             require_f32(in, "max_pool2d");
             require_dense(out, "max_pool2d");
-            if (node.out.ndim != 4) fail(B200_SHAPE_ERROR, "max_pool2d: output must be rank 4");
+            if (node.out.ndim != 4 || node.src[0].ndim != 4) {
+                fail(B200_SHAPE_ERROR, "max_pool2d: tensors must be rank 4");
+            }
             if (total == 0) return;
             const Win w = make_win(get_params<UnfoldParams>(node), 1);
-            const float* src = reinterpret_cast<const float*>(in.data);
-            if (in.contiguous) {
-                max_pool2d_kernel<true><<<grid, kThreads, 0, ctx->stream>>>(
-                    o, src, geo_of(in), w, out.dim[2], out.dim[3], total, ctx->d_status);
-            } else {
-                max_pool2d_kernel<false><<<grid, kThreads, 0, ctx->stream>>>(
-                    o, src, geo_of(in), w, out.dim[2], out.dim[3], total, ctx->d_status);
+            if (in.dim[2] != w.image_h || in.dim[3] != w.image_w || in.dim[0] != out.dim[0] ||
+                in.dim[1] != out.dim[1]) {
+                fail(B200_SHAPE_ERROR, "max_pool2d: geometry does not match the tensors");
             }
+            const int64_t plane = out.dim[2] * out.dim[3];
+            if (plane >= kMax32 || out.dim[1] >= kMax32) fail(B200_NOT_IMPLEMENTED, "max_pool2d: extent too large");
+            const int block = block_for(plane);
+            const int64_t chunks = ceil_div(plane, block);
+            check_grid(out.dim[0] * out.dim[1] * chunks, "max_pool2d");
+            const bool tiled = w.sh == w.kh && w.sw == w.kw && w.ph == 0 && w.pw == 0 && w.dh == 1 && w.dw == 1 &&
+                               ((w.kh == 2 && w.kw == 2) || (w.kh == 3 && w.kw == 3));
+            if (tiled) {
+                const unsigned grid = static_cast<unsigned>(out.dim[0] * out.dim[1] * chunks);
+                const float* src = reinterpret_cast<const float*>(in.data);
+                const int vec_ok = in.stride[3] == 1 && in.stride[2] % 2 == 0 && in.stride[1] % 2 == 0 &&
+                                   in.stride[0] % 2 == 0 && reinterpret_cast<uintptr_t>(src) % 8 == 0;
+                if (w.kh == 2) {
+                    max_pool2d_tiled_kernel<2, 2><<<grid, block, 0, ctx->stream>>>(
+                        o, src, strides_of(in), static_cast<int>(out.dim[2]), static_cast<int>(out.dim[3]),
+                        static_cast<int>(out.dim[1]), static_cast<int>(chunks), vec_ok, ctx->d_status);
+                } else {
+                    max_pool2d_tiled_kernel<3, 3><<<grid, block, 0, ctx->stream>>>(
+                        o, src, strides_of(in), static_cast<int>(out.dim[2]), static_cast<int>(out.dim[3]),
+                        static_cast<int>(out.dim[1]), static_cast<int>(chunks), 0, ctx->d_status);
+                }
+                break;
+            }
+            max_pool2d_kernel<<<static_cast<unsigned>(out.dim[0] * out.dim[1] * chunks), block, 0, ctx->stream>>>(
+                o, reinterpret_cast<const float*>(in.data), strides_of(in), w, static_cast<int>(out.dim[2]),
+                static_cast<int>(out.dim[3]), static_cast<int>(out.dim[1]), static_cast<int>(chunks), ctx->d_status);
             break;
         }
         case B200_OP_MAX_POOL2D_BACKWARD: {
@@ -346,19 +595,50 @@ void launch_movement(b200_ctx* ctx, const b200_node& node) {
             require_f32(in, "max_pool2d_backward");
             require_f32(grad, "max_pool2d_backward");
             require_dense(out, "max_pool2d_backward");
-            if (node.out.ndim != 4 || node.src[0].ndim != 4) {
+            if (node.out.ndim != 4 || node.src[0].ndim != 4 || node.src[1].ndim != 4) {
                 fail(B200_SHAPE_ERROR, "max_pool2d_backward: tensors must be rank 4");
             }
             if (total == 0) return;
             const Win w = make_win(get_params<UnfoldParams>(node), 1);
+            if (in.dim[2] != w.image_h || in.dim[3] != w.image_w || out.dim[2] != w.image_h ||
+                out.dim[3] != w.image_w || in.dim[0] != out.dim[0] || in.dim[1] != out.dim[1] ||
+                grad.dim[0] != out.dim[0] || grad.dim[1] != out.dim[1]) {
+                fail(B200_SHAPE_ERROR, "max_pool2d_backward: geometry does not match the tensors");
+            }
+            const int out_h = static_cast<int>(grad.dim[2]), out_w = static_cast<int>(grad.dim[3]);
+            const int64_t planes = out.dim[0] * out.dim[1];
             const float* g = reinterpret_cast<const float*>(grad.data);
             const float* src = reinterpret_cast<const float*>(in.data);
-            if (in.contiguous && grad.contiguous) {
-                max_pool2d_backward_kernel<true, true><<<grid, kThreads, 0, ctx->stream>>>(
-                    o, g, src, geo_of(grad), geo_of(in), w, grad.dim[2], grad.dim[3], total);
+            const bool tiled = w.sh == w.kh && w.sw == w.kw && w.ph == 0 && w.pw == 0 && w.dh == 1 && w.dw == 1 &&
+                               ((w.kh == 2 && w.kw == 2) || (w.kh == 3 && w.kw == 3));
+            if (out.dim[1] >= kMax32 || int64_t(w.image_h) * w.image_w >= kMax32) {
+                fail(B200_NOT_IMPLEMENTED, "max_pool2d_backward: extent too large");
+            }
+            if (tiled) {
+                const int cover_h = static_cast<int>(ceil_div(w.image_h, w.kh));
+                const int cover_w = static_cast<int>(ceil_div(w.image_w, w.kw));
+                const int64_t per_plane = int64_t(cover_h) * cover_w;
+                const int block = block_for(per_plane);
+                const int64_t chunks = ceil_div(per_plane, block);
+                check_grid(planes * chunks, "max_pool2d_backward");
+                const unsigned grid = static_cast<unsigned>(planes * chunks);
+                if (w.kh == 2) {
+                    max_pool2d_backward_tiled_kernel<2, 2><<<grid, block, 0, ctx->stream>>>(
+                        o, g, src, strides_of(grad), strides_of(in), w, out_h, out_w, cover_h, cover_w,
+                        static_cast<int>(out.dim[1]), static_cast<int>(chunks));
+                } else {
+                    max_pool2d_backward_tiled_kernel<3, 3><<<grid, block, 0, ctx->stream>>>(
+                        o, g, src, strides_of(grad), strides_of(in), w, out_h, out_w, cover_h, cover_w,
+                        static_cast<int>(out.dim[1]), static_cast<int>(chunks));
+                }
             } else {
-                max_pool2d_backward_kernel<false, false><<<grid, kThreads, 0, ctx->stream>>>(
-                    o, g, src, geo_of(grad), geo_of(in), w, grad.dim[2], grad.dim[3], total);
+                const int64_t per_plane = int64_t(w.image_h) * w.image_w;
+                const int block = block_for(per_plane);
+                const int64_t chunks = ceil_div(per_plane, block);
+                check_grid(planes * chunks, "max_pool2d_backward");
+                max_pool2d_backward_kernel<<<static_cast<unsigned>(planes * chunks), block, 0, ctx->stream>>>(
+                    o, g, src, strides_of(grad), strides_of(in), w, out_h, out_w, static_cast<int>(out.dim[1]),
+                    static_cast<int>(chunks));
             }
             break;
         }
@@ -374,17 +654,36 @@ void launch_movement(b200_ctx* ctx, const b200_node& node) {
             int64_t inner = 1;
             for (int i = axis + 1; i < kMaxDims; ++i) inner *= out.dim[i];
             const auto* ip = reinterpret_cast<const int64_t*>(idx.data);
-            if (dtype_size(out.dtype) == 4) {
-                index_select_kernel<uint32_t><<<grid, kThreads, 0, ctx->stream>>>(
-                    reinterpret_cast<uint32_t*>(out.data), reinterpret_cast<const uint32_t*>(a.data), ip,
-                    geo_of(a), geo_of(idx), inner, out.dim[axis], a.dim[axis], total, ctx->d_status);
-            } else if (dtype_size(out.dtype) == 8) {
-                index_select_kernel<uint64_t><<<grid, kThreads, 0, ctx->stream>>>(
-                    reinterpret_cast<uint64_t*>(out.data), reinterpret_cast<const uint64_t*>(a.data), ip,
-                    geo_of(a), geo_of(idx), inner, out.dim[axis], a.dim[axis], total, ctx->d_status);
+            const int64_t istride = index_stride(idx);
+            const size_t esz = dtype_size(out.dtype);
+            const int64_t row_bytes = inner * static_cast<int64_t>(esz);
+            const bool small = total < kMax32 && fits32(a) && idx.numel < kMax32 && istride >= 0 &&
+                               istride * idx.numel < kMax32;
+            if (a.contiguous && row_bytes % 16 == 0 && small && reinterpret_cast<uintptr_t>(a.data) % 16 == 0 &&
+                reinterpret_cast<uintptr_t>(out.data) % 16 == 0) {
+                const int64_t total16 = total * static_cast<int64_t>(esz) / 16;
+                index_select_rows_kernel<<<grid_for(total16, kThreads), kThreads, 0, ctx->stream>>>(
+                    reinterpret_cast<uint4*>(out.data), reinterpret_cast<const uint4*>(a.data), ip, istride,
+                    static_cast<unsigned>(row_bytes / 16), static_cast<unsigned>(out.dim[axis]),
+                    static_cast<unsigned>(a.dim[axis]), static_cast<unsigned>(total16), ctx->d_status);
+                break;
+            }
+            const unsigned grid = grid_for(total, kThreads);
+#define B200_INDEX_SELECT(T, I)                                                                              \
+    index_select_kernel<T, I><<<grid, kThreads, 0, ctx->stream>>>(                                           \
+        reinterpret_cast<T*>(out.data), reinterpret_cast<const T*>(a.data), ip, geo_t<I>(a),                 \
+        static_cast<I>(istride), static_cast<I>(inner), static_cast<I>(out.dim[axis]),                       \
+        static_cast<I>(a.dim[axis]), static_cast<I>(total), ctx->d_status)
+            if (esz == 4) {
+                if (small) B200_INDEX_SELECT(uint32_t, uint32_t);
+                else B200_INDEX_SELECT(uint32_t, int64_t);
+            } else if (esz == 8) {
+                if (small) B200_INDEX_SELECT(uint64_t, uint32_t);
+                else B200_INDEX_SELECT(uint64_t, int64_t);
             } else {
                 fail(B200_DTYPE_ERROR, "index_select: unsupported element width");
             }
+#undef B200_INDEX_SELECT
             break;
         }
         case B200_OP_SCATTER_ADD: {
@@ -400,16 +699,24 @@ void launch_movement(b200_ctx* ctx, const b200_node& node) {
             int64_t inner = 1;
             for (int i = axis + 1; i < kMaxDims; ++i) inner *= out.dim[i];
             const auto* ip = reinterpret_cast<const int64_t*>(idx.data);
-            const int64_t n_idx = src.dim[axis];
-            if (n_idx > 0 && src.numel > 0) {
-                index_range_kernel<<<static_cast<unsigned>(ceil_div(n_idx, kThreads)), kThreads, 0,
-                                     ctx->stream>>>(ip, geo_of(idx), n_idx, out.dim[axis],
-                                                    ctx->d_status);
+            const int64_t istride = index_stride(idx);
+            const int64_t n_idx = src.numel == 0 ? 0 : src.dim[axis];
+            if (n_idx > 0) {
+                index_range_kernel<<<static_cast<unsigned>(ceil_div(n_idx, kThreads)), kThreads, 0, ctx->stream>>>(
+                    ip, istride, n_idx, out.dim[axis], ctx->d_status);
                 ctx->count_launch();
             }
-            scatter_add_kernel<<<grid, kThreads, 0, ctx->stream>>>(
-                o, reinterpret_cast<const float*>(src.data), ip, geo_of(src), geo_of(idx), inner,
-                src.numel == 0 ? 0 : n_idx, out.dim[axis], total, ctx->d_status);
+            const unsigned grid = grid_for(total, kThreads);
+            const float* sp = reinterpret_cast<const float*>(src.data);
+            const bool small = total < kMax32 && fits32(src) && istride >= 0 && istride * std::max<int64_t>(n_idx, 1) < kMax32;
+            if (small) {
+                scatter_add_kernel<uint32_t><<<grid, kThreads, 0, ctx->stream>>>(
+                    o, sp, ip, geo_t<uint32_t>(src), static_cast<uint32_t>(istride), static_cast<uint32_t>(inner),
+                    static_cast<uint32_t>(n_idx), static_cast<uint32_t>(out.dim[axis]), static_cast<uint32_t>(total));
+            } else {
+                scatter_add_kernel<int64_t><<<grid, kThreads, 0, ctx->stream>>>(
+                    o, sp, ip, geo_t<int64_t>(src), istride, inner, n_idx, out.dim[axis], total);
+            }
             break;
         }
         default: fail(B200_NOT_IMPLEMENTED, "movement: unhandled op");

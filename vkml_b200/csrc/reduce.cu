@@ -16,7 +16,8 @@
 //   thread -- one lane per output, lanes on consecutive outputs (column sums such
 //             as [B,N]->[N], batch-axis sums, and very short rows).
 //   Both split a long reduction across blocks into partials held in the
-//   context's scratch buffer; `finalize` folds the partials in split order.
+//   context's scratch buffer; the block that finishes last folds them in split
+//   order inside the same launch.
 #include "context.h"
 
 #include <cfloat>
@@ -25,22 +26,24 @@
 namespace b200 {
 namespace {
 
-struct RedGeo {
-    int64_t kdim[kMaxDims], kstride[kMaxDims];  // kept axes (input strides), padded in front
-    int64_t rdim[kMaxDims], rstride[kMaxDims];  // reduced axes
+template <typename I>
+struct RedGeoT {
+    I kdim[kMaxDims], kstride[kMaxDims];  // kept axes (input strides), padded in front
+    I rdim[kMaxDims], rstride[kMaxDims];  // reduced axes
     int krank, rrank;
 };
+using RedGeo = RedGeoT<int64_t>;
 
-__device__ __forceinline__ int64_t walk(const int64_t* dim, const int64_t* stride, int rank,
-                                        int64_t linear) {
+template <typename I>
+__device__ __forceinline__ I walk(const I* dim, const I* stride, int rank, I linear) {
     if (rank == 1) {
         return linear * stride[kMaxDims - 1];
     }
-    int64_t off = 0;
+    I off = 0;
 #pragma unroll
     for (int a = kMaxDims - 1; a >= 0; --a) {
         if (a >= kMaxDims - rank) {
-            const int64_t q = linear / dim[a];
+            const I q = linear / dim[a];
             off += (linear - q * dim[a]) * stride[a];
             linear = q;
         }
@@ -155,81 +158,238 @@ __device__ __forceinline__ void write_result(void* out, int64_t o, typename P::A
     }
 }
 
-// grid = (outputs / groups-per-block, splits). `partial` non-null when splits > 1.
-template <typename P, int GROUP, bool VEC4>
+constexpr int kMaxCounters = 4096;
+
+// Splits of one output (or of one block of outputs) hand their partials to whichever
+// block arrives LAST, which folds them in split order: one launch instead of two,
+// and the order of the fold does not depend on which block that was.  The counter
+// wraps back to zero on the last arrival (atomicInc with the split count as bound),
+// so the counter array needs no clearing between launches.
+__device__ __forceinline__ bool last_block_of(unsigned* counter, unsigned splits, int* flag_smem) {
+    __threadfence();  // this block's partials are visible before the ticket is taken
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        const unsigned ticket = atomicInc(counter, splits - 1);
+        *flag_smem = ticket == splits - 1;
+    }
+    __syncthreads();
+    const bool last = *flag_smem != 0;
+    if (last) {
+        __threadfence();  // and the other blocks' partials are visible to this one
+    }
+    return last;
+}
+
+// grid = (outputs / groups-per-block, splits). `partial` ([split][output]) non-null
+// when splits > 1; then split s owns the units k with (k / (GROUP*U)) % splits == s, so
+// the blocks of one launch sweep memory side by side instead of in distant chunks.
+// With VEC4 the innermost reduced axis is a dense run whose length is a multiple of 4
+// and every row start is 16-byte aligned: the reduced index space is walked in float4
+// units (g.rdim / g.rstride of the innermost axis already divided / multiplied by 4).
+template <typename P, int GROUP, bool VEC4, typename I>
 __global__ void __launch_bounds__(256)
-reduce_group_kernel(void* out, typename P::Acc* partial, const float* __restrict__ in, RedGeo g,
-                    int64_t n_out, int64_t n_red, int64_t chunk, int post) {
+reduce_group_kernel(void* out, typename P::Acc* partial, unsigned* counters, const float* __restrict__ in,
+                    RedGeoT<I> g, int64_t n_out, I n_units, int post, int64_t n_red) {
     __shared__ typename P::Acc smem[8];
+    __shared__ int last_flag;
     constexpr int kGroups = 256 / GROUP;
+    constexpr int U = 4;
     const int gid = threadIdx.x / GROUP;
     const int lane = threadIdx.x % GROUP;
     const int64_t o = int64_t(blockIdx.x) * kGroups + gid;
-    const int64_t split = blockIdx.y;
+    const I split = blockIdx.y;
+    const I splits = gridDim.y;
     typename P::Acc acc = P::init();
     const bool live = o < n_out;
     if (live) {
-        const int64_t base = walk(g.kdim, g.kstride, g.krank, o);
-        const int64_t k0 = split * chunk;
-        const int64_t k1 = min(k0 + chunk, n_red);
-        if constexpr (VEC4) {
-            // reduced run is dense and 16-byte aligned; chunk is a multiple of 4
-            const float4* p = reinterpret_cast<const float4*>(in + base);
-            for (int64_t k = k0 / 4 + lane; k < k1 / 4; k += GROUP) {
-                const float4 v = p[k];
-                acc = P::step(acc, v.x, 4 * k);
-                acc = P::step(acc, v.y, 4 * k + 1);
-                acc = P::step(acc, v.z, 4 * k + 2);
-                acc = P::step(acc, v.w, 4 * k + 3);
-            }
-        } else {
-            for (int64_t k = k0 + lane; k < k1; k += GROUP) {
-                acc = P::step(acc, in[base + walk(g.rdim, g.rstride, g.rrank, k)], k);
+        const I base = walk<I>(g.kdim, g.kstride, g.krank, static_cast<I>(o));
+        for (int64_t kb64 = int64_t(split) * (GROUP * U) + lane; kb64 < int64_t(n_units);
+             kb64 += int64_t(splits) * (GROUP * U)) {
+            const I kb = static_cast<I>(kb64);
+            if constexpr (VEC4) {
+                float4 v[U];
+#pragma unroll
+                for (int u = 0; u < U; ++u) {
+                    const I k = kb + u * GROUP;
+                    if (k < n_units) {
+                        v[u] = *reinterpret_cast<const float4*>(in + base + walk<I>(g.rdim, g.rstride, g.rrank, k));
+                    }
+                }
+#pragma unroll
+                for (int u = 0; u < U; ++u) {
+                    const I k = kb + u * GROUP;
+                    if (k < n_units) {
+                        // element index of v.x in reduced (row-major) order, for argmax / argmin
+                        const int64_t e = int64_t(k) * 4;
+                        acc = P::step(acc, v[u].x, e);
+                        acc = P::step(acc, v[u].y, e + 1);
+                        acc = P::step(acc, v[u].z, e + 2);
+                        acc = P::step(acc, v[u].w, e + 3);
+                    }
+                }
+            } else {
+                float v[U];
+#pragma unroll
+                for (int u = 0; u < U; ++u) {
+                    const I k = kb + u * GROUP;
+                    if (k < n_units) {
+                        v[u] = in[base + walk<I>(g.rdim, g.rstride, g.rrank, k)];
+                    }
+                }
+#pragma unroll
+                for (int u = 0; u < U; ++u) {
+                    const I k = kb + u * GROUP;
+                    if (k < n_units) {
+                        acc = P::step(acc, v[u], int64_t(k));
+                    }
+                }
             }
         }
     }
     acc = group_fold<P, GROUP>(acc, smem);
-    if (live && lane == 0) {
-        if (partial != nullptr) {
-            partial[o * gridDim.y + split] = acc;
-        } else {
+    if (partial == nullptr) {
+        if (live && lane == 0) {
             write_result<P>(out, o, acc, post, n_red);
         }
-    }
-}
-
-// One lane per (output, split); consecutive lanes own consecutive outputs.
-template <typename P>
-__global__ void __launch_bounds__(256)
-reduce_thread_kernel(void* out, typename P::Acc* partial, const float* __restrict__ in, RedGeo g,
-                     int64_t n_out, int64_t n_red, int64_t chunk, int post) {
-    const int64_t o = int64_t(blockIdx.x) * blockDim.x + threadIdx.x;
-    const int64_t split = blockIdx.y;
-    if (o >= n_out) {
         return;
     }
-    const int64_t base = walk(g.kdim, g.kstride, g.krank, o);
-    const int64_t k0 = split * chunk;
-    const int64_t k1 = min(k0 + chunk, n_red);
-    typename P::Acc acc = P::init();
-    if (g.rrank == 1) {
-        const int64_t s = g.rstride[kMaxDims - 1];
-        const float* p = in + base + k0 * s;
-        for (int64_t k = k0; k < k1; ++k, p += s) {
-            acc = P::step(acc, *p, k);
-        }
-    } else {
-        for (int64_t k = k0; k < k1; ++k) {
-            acc = P::step(acc, in[base + walk(g.rdim, g.rstride, g.rrank, k)], k);
-        }
+    // splits > 1 only with one output per block (GROUP == 256)
+    if (live && lane == 0) {
+        partial[int64_t(split) * n_out + o] = acc;
     }
-    if (partial != nullptr) {
-        partial[o * gridDim.y + split] = acc;
-    } else {
-        write_result<P>(out, o, acc, post, n_red);
+    if (counters == nullptr || !last_block_of(counters + blockIdx.x, splits, &last_flag)) {
+        return;
+    }
+    typename P::Acc total = P::init();
+    for (I s = threadIdx.x; s < splits; s += 256) {
+        total = P::merge(total, partial[int64_t(s) * n_out + o]);
+    }
+    total = group_fold<P, 256>(total, smem);
+    if (threadIdx.x == 0) {
+        write_result<P>(out, o, total, post, n_red);
     }
 }
 
+// One lane per (output, split); consecutive lanes own consecutive outputs, split s owns
+// the reduced indices k with (k / U) % splits == s.
+template <typename P, typename I>
+__global__ void __launch_bounds__(256)
+reduce_thread_kernel(void* out, typename P::Acc* partial, unsigned* counters, const float* __restrict__ in,
+                     RedGeoT<I> g, int64_t n_out, I n_red, int post) {
+    __shared__ int last_flag;
+    constexpr int U = 4;
+    const int64_t o = int64_t(blockIdx.x) * blockDim.x + threadIdx.x;
+    const I split = blockIdx.y;
+    const I splits = gridDim.y;
+    const bool live = o < n_out;
+    typename P::Acc acc = P::init();
+    if (live) {
+        const I base = walk<I>(g.kdim, g.kstride, g.krank, static_cast<I>(o));
+        for (int64_t kb64 = int64_t(split) * U; kb64 < int64_t(n_red); kb64 += int64_t(splits) * U) {
+            const I kb = static_cast<I>(kb64);
+            float v[U];
+#pragma unroll
+            for (int u = 0; u < U; ++u) {
+                if (kb + u < n_red) {
+                    v[u] = in[base + walk<I>(g.rdim, g.rstride, g.rrank, kb + u)];
+                }
+            }
+#pragma unroll
+            for (int u = 0; u < U; ++u) {
+                if (kb + u < n_red) {
+                    acc = P::step(acc, v[u], int64_t(kb + u));
+                }
+            }
+        }
+    }
+    if (partial == nullptr) {
+        if (live) {
+            write_result<P>(out, o, acc, post, int64_t(n_red));
+        }
+        return;
+    }
+    if (live) {
+        partial[int64_t(split) * n_out + o] = acc;
+    }
+    if (counters == nullptr || !last_block_of(counters + blockIdx.x, splits, &last_flag)) {
+        return;
+    }
+    if (live) {
+        typename P::Acc total = P::init();
+        for (I s = 0; s < splits; ++s) {
+            total = P::merge(total, partial[int64_t(s) * n_out + o]);
+        }
+        write_result<P>(out, o, total, post, int64_t(n_red));
+    }
+}
+
+// Column sums with a dense kept axis: each lane owns FOUR adjacent outputs and reads one
+// float4 per reduced index (float accumulators only: sum, mean, max, min).
+template <typename P, typename I>
+__global__ void __launch_bounds__(256)
+reduce_thread4_kernel(float* out, float4* partial, unsigned* counters, const float* __restrict__ in,
+                      RedGeoT<I> g, int64_t n_out4, I n_red, int post) {
+    __shared__ int last_flag;
+    constexpr int U = 4;
+    const int64_t o4 = int64_t(blockIdx.x) * blockDim.x + threadIdx.x;
+    const I split = blockIdx.y;
+    const I splits = gridDim.y;
+    const bool live = o4 < n_out4;
+    float acc[4] = {P::init(), P::init(), P::init(), P::init()};
+    if (live) {
+        const I base = walk<I>(g.kdim, g.kstride, g.krank, static_cast<I>(o4));
+        for (int64_t kb64 = int64_t(split) * U; kb64 < int64_t(n_red); kb64 += int64_t(splits) * U) {
+            const I kb = static_cast<I>(kb64);
+            float4 v[U];
+#pragma unroll
+            for (int u = 0; u < U; ++u) {
+                if (kb + u < n_red) {
+                    v[u] = *reinterpret_cast<const float4*>(in + base + walk<I>(g.rdim, g.rstride, g.rrank, kb + u));
+                }
+            }
+#pragma unroll
+            for (int u = 0; u < U; ++u) {
+                if (kb + u < n_red) {
+                    acc[0] = P::step(acc[0], v[u].x, 0);
+                    acc[1] = P::step(acc[1], v[u].y, 0);
+                    acc[2] = P::step(acc[2], v[u].z, 0);
+                    acc[3] = P::step(acc[3], v[u].w, 0);
+                }
+            }
+        }
+    }
+    auto finish = [&](float v) {
+        if (post == kPostMean) {
+            return n_red == 0 ? __int_as_float(0x7fc00000) : v / static_cast<float>(n_red);
+        }
+        return v;
+    };
+    if (partial == nullptr) {
+        if (live) {
+            reinterpret_cast<float4*>(out)[o4] = make_float4(finish(acc[0]), finish(acc[1]), finish(acc[2]), finish(acc[3]));
+        }
+        return;
+    }
+    if (live) {
+        partial[int64_t(split) * n_out4 + o4] = make_float4(acc[0], acc[1], acc[2], acc[3]);
+    }
+    if (!last_block_of(counters + blockIdx.x, splits, &last_flag)) {
+        return;
+    }
+    if (live) {
+        float t[4] = {P::init(), P::init(), P::init(), P::init()};
+        for (I s = 0; s < splits; ++s) {
+            const float4 q = partial[int64_t(s) * n_out4 + o4];
+            t[0] = P::merge(t[0], q.x);
+            t[1] = P::merge(t[1], q.y);
+            t[2] = P::merge(t[2], q.z);
+            t[3] = P::merge(t[3], q.w);
+        }
+        reinterpret_cast<float4*>(out)[o4] = make_float4(finish(t[0]), finish(t[1]), finish(t[2]), finish(t[3]));
+    }
+}
+
+// Fallback fold for launches with more blocks than counters. partial is [split][output].
 template <typename P>
 __global__ void __launch_bounds__(256)
 reduce_finalize_kernel(void* out, const typename P::Acc* __restrict__ partial, int64_t n_out,
@@ -240,7 +400,7 @@ reduce_finalize_kernel(void* out, const typename P::Acc* __restrict__ partial, i
     }
     typename P::Acc acc = P::init();
     for (int s = 0; s < splits; ++s) {
-        acc = P::merge(acc, partial[o * splits + s]);
+        acc = P::merge(acc, partial[int64_t(s) * n_out + o]);
     }
     write_result<P>(out, o, acc, post, n_red);
 }
@@ -279,6 +439,145 @@ int pack_axes(const int64_t* d, const int64_t* s, int n, int64_t* dim, int64_t* 
     return r;
 }
 
+template <typename I>
+RedGeoT<I> narrow_geo(const RedGeo& g) {
+    RedGeoT<I> r;
+    r.krank = g.krank;
+    r.rrank = g.rrank;
+    for (int a = 0; a < kMaxDims; ++a) {
+        r.kdim[a] = static_cast<I>(g.kdim[a]);
+        r.kstride[a] = static_cast<I>(g.kstride[a]);
+        r.rdim[a] = static_cast<I>(g.rdim[a]);
+        r.rstride[a] = static_cast<I>(g.rstride[a]);
+    }
+    return r;
+}
+
+template <typename P, typename I>
+void launch_reduce_kernels(b200_ctx* ctx, const View& out, const float* src, const RedGeo& g64, int64_t n_out,
+                           int64_t n_red, int post) {
+    using Acc = typename P::Acc;
+    RedGeoT<I> g = narrow_geo<I>(g64);
+    const int64_t r_inner = g64.rstride[kMaxDims - 1];
+    const int64_t k_inner = g64.kstride[kMaxDims - 1];
+    const bool column = (n_red <= 16) || (k_inner == 1 && r_inner != 1 && n_out >= 32);
+
+    if (column) {
+        int64_t splits = 1;
+        if (n_red >= 64) {
+            splits = ceil_div(int64_t(kSmCount) * 2048, n_out);
+            splits = std::min<int64_t>(splits, n_red / 16);
+            splits = std::max<int64_t>(1, std::min<int64_t>(splits, 1024));
+        }
+        if constexpr (sizeof(Acc) == sizeof(float)) {
+            // four adjacent outputs per lane when the kept axis is dense and everything is 16-byte aligned
+            const int64_t k_run = g64.kdim[kMaxDims - 1];
+            bool v4 = k_inner == 1 && k_run % 4 == 0 && reinterpret_cast<uintptr_t>(src) % 16 == 0 &&
+                      reinterpret_cast<uintptr_t>(out.data) % 16 == 0 && n_out >= 1024;
+            for (int a = 0; a < kMaxDims && v4; ++a) {
+                if (g64.rdim[a] > 1 && g64.rstride[a] % 4 != 0) v4 = false;
+                if (a < kMaxDims - 1 && g64.kdim[a] > 1 && g64.kstride[a] % 4 != 0) v4 = false;
+            }
+            const int64_t n_out4 = n_out / 4;
+            const int64_t bx = ceil_div(n_out4, 256);
+            if (v4 && bx <= kMaxCounters) {
+                int64_t sp = 1;
+                if (n_red >= 64) {
+                    sp = ceil_div(int64_t(kSmCount) * 1024, n_out4);
+                    sp = std::max<int64_t>(1, std::min<int64_t>(std::min<int64_t>(sp, n_red / 16), 1024));
+                }
+                RedGeoT<I> g4 = g;
+                g4.kdim[kMaxDims - 1] = static_cast<I>(k_run / 4);
+                g4.kstride[kMaxDims - 1] = 4;
+                float4* part = nullptr;
+                if (sp > 1) {
+                    part = static_cast<float4*>(ctx->ensure_workspace(sizeof(float4) * n_out4 * sp));
+                }
+                dim3 grid4(static_cast<unsigned>(bx), static_cast<unsigned>(sp));
+                reduce_thread4_kernel<P, I><<<grid4, 256, 0, ctx->stream>>>(
+                    reinterpret_cast<float*>(out.data), part, ctx->d_counters, src, g4, n_out4, static_cast<I>(n_red),
+                    post);
+                ctx->count_launch();
+                check_last_launch("reduce (thread x4)");
+                return;
+            }
+        }
+        const int64_t blocks_x = ceil_div(n_out, 256);
+        Acc* partial = nullptr;
+        unsigned* counters = nullptr;
+        if (splits > 1) {
+            partial = static_cast<Acc*>(ctx->ensure_workspace(sizeof(Acc) * n_out * splits));
+            counters = blocks_x <= kMaxCounters ? ctx->d_counters : nullptr;
+        }
+        dim3 grid(static_cast<unsigned>(blocks_x), static_cast<unsigned>(splits));
+        reduce_thread_kernel<P, I><<<grid, 256, 0, ctx->stream>>>(out.data, partial, counters, src, g, n_out,
+                                                                  static_cast<I>(n_red), post);
+        ctx->count_launch();
+        if (splits > 1 && counters == nullptr) {
+            reduce_finalize_kernel<P><<<static_cast<unsigned>(blocks_x), 256, 0, ctx->stream>>>(
+                out.data, partial, n_out, static_cast<int>(splits), post, n_red);
+            ctx->count_launch();
+        }
+        check_last_launch("reduce (thread)");
+        return;
+    }
+
+    // float4 walk: innermost reduced run dense, a multiple of 4 long, every start aligned
+    const int64_t inner_run = g64.rdim[kMaxDims - 1];
+    bool vec4 = r_inner == 1 && inner_run % 4 == 0 && reinterpret_cast<uintptr_t>(src) % 16 == 0;
+    for (int a = 0; a < kMaxDims && vec4; ++a) {
+        if (g64.kdim[a] > 1 && g64.kstride[a] % 4 != 0) vec4 = false;
+        if (a < kMaxDims - 1 && g64.rdim[a] > 1 && g64.rstride[a] % 4 != 0) vec4 = false;
+    }
+    int64_t n_units = n_red;
+    if (vec4) {
+        g.rdim[kMaxDims - 1] = static_cast<I>(inner_run / 4);
+        g.rstride[kMaxDims - 1] = 4;
+        n_units = n_red / 4;
+    }
+    const bool warp = n_units <= 1024 && n_out >= 1024;
+    const int64_t groups_per_block = warp ? 8 : 1;
+    int64_t splits = 1;
+    if (!warp && n_out < int64_t(kSmCount) * 8 && n_units >= 4096) {
+        splits = ceil_div(int64_t(kSmCount) * 8, n_out);
+        splits = std::min<int64_t>(splits, n_units / 2048);
+        splits = std::max<int64_t>(1, std::min<int64_t>(splits, 65535));
+    }
+    const int64_t blocks_x = ceil_div(n_out, groups_per_block);
+    Acc* partial = nullptr;
+    unsigned* counters = nullptr;
+    if (splits > 1) {
+        partial = static_cast<Acc*>(ctx->ensure_workspace(sizeof(Acc) * n_out * splits));
+        counters = blocks_x <= kMaxCounters ? ctx->d_counters : nullptr;
+    }
+    dim3 grid(static_cast<unsigned>(blocks_x), static_cast<unsigned>(splits));
+    const I nu = static_cast<I>(n_units);
+    if (warp) {
+        if (vec4) {
+            reduce_group_kernel<P, 32, true, I><<<grid, 256, 0, ctx->stream>>>(out.data, partial, counters, src, g,
+                                                                               n_out, nu, post, n_red);
+        } else {
+            reduce_group_kernel<P, 32, false, I><<<grid, 256, 0, ctx->stream>>>(out.data, partial, counters, src, g,
+                                                                                n_out, nu, post, n_red);
+        }
+    } else {
+        if (vec4) {
+            reduce_group_kernel<P, 256, true, I><<<grid, 256, 0, ctx->stream>>>(out.data, partial, counters, src, g,
+                                                                                n_out, nu, post, n_red);
+        } else {
+            reduce_group_kernel<P, 256, false, I><<<grid, 256, 0, ctx->stream>>>(out.data, partial, counters, src,
+                                                                                 g, n_out, nu, post, n_red);
+        }
+    }
+    ctx->count_launch();
+    if (splits > 1 && counters == nullptr) {
+        reduce_finalize_kernel<P><<<static_cast<unsigned>(ceil_div(n_out, 256)), 256, 0, ctx->stream>>>(
+            out.data, partial, n_out, static_cast<int>(splits), post, n_red);
+        ctx->count_launch();
+    }
+    check_last_launch("reduce (group)");
+}
+
 template <typename P>
 void run_reduce(b200_ctx* ctx, const View& out, const View& in, uint32_t mask4, int post) {
     int64_t kd[kMaxDims], ks[kMaxDims], rd[kMaxDims], rs[kMaxDims];
@@ -307,90 +606,11 @@ void run_reduce(b200_ctx* ctx, const View& out, const View& in, uint32_t mask4, 
     g.krank = pack_axes(kd, ks, nk, g.kdim, g.kstride);
     g.rrank = pack_axes(rd, rs, nr, g.rdim, g.rstride);
     const float* src = reinterpret_cast<const float*>(in.data);
-    using Acc = typename P::Acc;
-
-    const int64_t r_inner = g.rstride[kMaxDims - 1];
-    const int64_t k_inner = g.kstride[kMaxDims - 1];
-    const bool column = (n_red <= 16) || (k_inner == 1 && r_inner != 1 && n_out >= 32);
-
-    if (column) {
-        int64_t splits = 1;
-        if (n_red >= 64) {
-            splits = ceil_div(int64_t(kSmCount) * 1024, n_out);
-            splits = std::min<int64_t>(splits, n_red / 32);
-            splits = std::max<int64_t>(1, std::min<int64_t>(splits, 1024));
-        }
-        const int64_t chunk = ceil_div(n_red, splits);
-        splits = n_red == 0 ? 1 : ceil_div(n_red, chunk);
-        Acc* partial = nullptr;
-        if (splits > 1) {
-            partial = static_cast<Acc*>(ctx->ensure_workspace(sizeof(Acc) * n_out * splits));
-        }
-        dim3 grid(static_cast<unsigned>(ceil_div(n_out, 256)), static_cast<unsigned>(splits));
-        reduce_thread_kernel<P><<<grid, 256, 0, ctx->stream>>>(out.data, partial, src, g, n_out, n_red,
-                                                             chunk, post);
-        ctx->count_launch();
-        if (splits > 1) {
-            reduce_finalize_kernel<P><<<static_cast<unsigned>(ceil_div(n_out, 256)), 256, 0,
-                                        ctx->stream>>>(out.data, partial, n_out,
-                                                       static_cast<int>(splits), post, n_red);
-            ctx->count_launch();
-        }
-        check_last_launch("reduce (thread)");
-        return;
-    }
-
-    const bool warp = n_red <= 1024 && n_out >= 1024;
-    const int64_t groups_per_block = warp ? 8 : 1;
-    int64_t splits = 1;
-    if (!warp) {
-        const int64_t blocks = n_out;
-        if (blocks < int64_t(kSmCount) * 4 && n_red >= 16384) {
-            splits = ceil_div(int64_t(kSmCount) * 4, blocks);
-            splits = std::min<int64_t>(splits, n_red / 8192);
-            splits = std::max<int64_t>(1, std::min<int64_t>(splits, 65535));
-        }
-    }
-    int64_t chunk = ceil_div(n_red, splits);
-    chunk = ceil_div(chunk, 4) * 4;
-    splits = n_red == 0 ? 1 : ceil_div(n_red, chunk);
-    Acc* partial = nullptr;
-    if (splits > 1) {
-        partial = static_cast<Acc*>(ctx->ensure_workspace(sizeof(Acc) * n_out * splits));
-    }
-    // dense, aligned rows take the 128-bit path
-    bool vec4 = g.rrank == 1 && r_inner == 1 && n_red % 4 == 0 &&
-                reinterpret_cast<uintptr_t>(src) % 16 == 0;
-    for (int a = 0; a < kMaxDims && vec4; ++a) {
-        if (g.kdim[a] > 1 && g.kstride[a] % 4 != 0) {
-            vec4 = false;
-        }
-    }
-    dim3 grid(static_cast<unsigned>(ceil_div(n_out, groups_per_block)), static_cast<unsigned>(splits));
-    if (warp) {
-        if (vec4) {
-            reduce_group_kernel<P, 32, true><<<grid, 256, 0, ctx->stream>>>(out.data, partial, src, g,
-                                                                            n_out, n_red, chunk, post);
-        } else {
-            reduce_group_kernel<P, 32, false><<<grid, 256, 0, ctx->stream>>>(
-                out.data, partial, src, g, n_out, n_red, chunk, post);
-        }
+    if (fits32(in) && n_out < (int64_t(1) << 31) && n_red < (int64_t(1) << 31)) {
+        launch_reduce_kernels<P, uint32_t>(ctx, out, src, g, n_out, n_red, post);
     } else {
-        if (vec4) {
-            reduce_group_kernel<P, 256, true><<<grid, 256, 0, ctx->stream>>>(
-                out.data, partial, src, g, n_out, n_red, chunk, post);
-        } else {
-            reduce_group_kernel<P, 256, false><<<grid, 256, 0, ctx->stream>>>(
-                out.data, partial, src, g, n_out, n_red, chunk, post);
-        }
+        launch_reduce_kernels<P, int64_t>(ctx, out, src, g, n_out, n_red, post);
     }
-    ctx->count_launch();
-    if (splits > 1) {
-        reduce_finalize_kernel<P><<<static_cast<unsigned>(ceil_div(n_out, 256)), 256, 0, ctx->stream>>>(
-            out.data, partial, n_out, static_cast<int>(splits), post, n_red);
-        ctx->count_launch();
-    }
-    check_last_launch("reduce (group)");
 }
 
 // ---------------------------------------------------------------------------
@@ -558,6 +778,109 @@ __global__ void softmax_block_kernel(float* __restrict__ out, const float* __res
     }
 }
 
+// Rows that fit in registers: GROUP threads (a warp, or the whole block) own one row,
+// each thread keeps ITEMS units (float4 when VEC4, else scalars read through the axis
+// stride), so the row is read from memory exactly once and written once.
+template <bool LOG, int GROUP, int ITEMS, bool VEC4>
+__global__ void __launch_bounds__(GROUP == 32 ? 256 : GROUP)
+softmax_reg_kernel(float* __restrict__ out, const float* __restrict__ in, SoftGeo g, int64_t n_rows) {
+    constexpr int kBlock = GROUP == 32 ? 256 : GROUP;
+    constexpr int kRows = kBlock / GROUP;
+    constexpr int W = VEC4 ? 4 : 1;
+    __shared__ float red[32];
+    const int lane = threadIdx.x % GROUP;
+    const int64_t n_units = VEC4 ? g.n_axis / 4 : g.n_axis;
+    for (int64_t row0 = int64_t(blockIdx.x) * kRows; row0 < n_rows; row0 += int64_t(gridDim.x) * kRows) {
+        const int64_t row = row0 + threadIdx.x / GROUP;
+        const bool live = row < n_rows;
+        int64_t bi = 0, bo = 0;
+        if (live) {
+            soft_bases(g, row, bi, bo);
+        }
+        float v[ITEMS * W];
+        float peak = -INFINITY;
+#pragma unroll
+        for (int i = 0; i < ITEMS; ++i) {
+            const int64_t u = lane + int64_t(i) * GROUP;
+            if (live && u < n_units) {
+                if constexpr (VEC4) {
+                    const float4 t = reinterpret_cast<const float4*>(in + bi)[u];
+                    v[4 * i] = t.x;
+                    v[4 * i + 1] = t.y;
+                    v[4 * i + 2] = t.z;
+                    v[4 * i + 3] = t.w;
+                } else {
+                    v[i] = in[bi + u * g.axis_stride_in];
+                }
+            } else {
+#pragma unroll
+                for (int w = 0; w < W; ++w) {
+                    v[W * i + w] = -INFINITY;
+                }
+            }
+#pragma unroll
+            for (int w = 0; w < W; ++w) {
+                peak = fmaxf(peak, v[W * i + w]);
+            }
+        }
+        if constexpr (GROUP == 32) {
+#pragma unroll
+            for (int d = 16; d > 0; d >>= 1) {
+                peak = fmaxf(peak, __shfl_xor_sync(0xffffffffU, peak, d));
+            }
+        } else {
+            peak = block_all_max(peak, red);
+        }
+        // slots past the row hold -inf: exp(-inf - peak) = 0 adds nothing (a row of all
+        // -inf gives NaN everywhere, as on the CPU)
+        float denom = 0.0F;
+#pragma unroll
+        for (int i = 0; i < ITEMS * W; ++i) {
+            const float e = expf(v[i] - peak);
+            denom += e;
+            if (!LOG) {
+                v[i] = e;
+            }
+        }
+        if constexpr (GROUP == 32) {
+#pragma unroll
+            for (int d = 16; d > 0; d >>= 1) {
+                denom += __shfl_xor_sync(0xffffffffU, denom, d);
+            }
+        } else {
+            denom = block_all_sum(denom, red);
+        }
+        const float lg = logf(denom);
+#pragma unroll
+        for (int i = 0; i < ITEMS; ++i) {
+            const int64_t u = lane + int64_t(i) * GROUP;
+            if (live && u < n_units) {
+                float r[W];
+#pragma unroll
+                for (int w = 0; w < W; ++w) {
+                    r[w] = LOG ? (v[W * i + w] - peak) - lg : v[W * i + w] / denom;
+                }
+                if constexpr (VEC4) {
+                    reinterpret_cast<float4*>(out + bo)[u] = make_float4(r[0], r[1], r[2], r[3]);
+                } else {
+                    out[bo + u * g.axis_stride_out] = r[0];
+                }
+            }
+        }
+    }
+}
+
+template <bool LOG, int GROUP, int ITEMS, bool VEC4>
+void launch_softmax_reg(b200_ctx* ctx, float* dst, const float* src, const SoftGeo& g, int64_t n_rows) {
+    constexpr int kBlock = GROUP == 32 ? 256 : GROUP;
+    constexpr int kRows = kBlock / GROUP;
+    const int64_t blocks = ceil_div(n_rows, kRows);
+    const unsigned grid = static_cast<unsigned>(std::min<int64_t>(blocks, int64_t(kSmCount) * (2048 / kBlock) * 4));
+    softmax_reg_kernel<LOG, GROUP, ITEMS, VEC4><<<grid, kBlock, 0, ctx->stream>>>(dst, src, g, n_rows);
+    ctx->count_launch();
+    check_last_launch("softmax (registers)");
+}
+
 template <bool LOG>
 void run_softmax(b200_ctx* ctx, const View& out, const View& in, int axis4) {
     SoftGeo g{};
@@ -601,6 +924,29 @@ void run_softmax(b200_ctx* ctx, const View& out, const View& in, int axis4) {
         check_last_launch("softmax (thread)");
         return;
     }
+    {
+        bool v4 = g.axis_stride_in == 1 && g.axis_stride_out == 1 && g.n_axis % 4 == 0 &&
+                  reinterpret_cast<uintptr_t>(src) % 16 == 0 && reinterpret_cast<uintptr_t>(dst) % 16 == 0;
+        for (int a = 0; a < kMaxDims && v4; ++a) {
+            if (g.kdim[a] > 1 && (g.kstride_in[a] % 4 != 0 || g.kstride_out[a] % 4 != 0)) {
+                v4 = false;
+            }
+        }
+        const int64_t n = g.n_axis;
+        if (v4) {
+            const int64_t u = n / 4;
+            if (u <= 64) return launch_softmax_reg<LOG, 32, 2, true>(ctx, dst, src, g, n_rows);
+            if (u <= 256) return launch_softmax_reg<LOG, 32, 8, true>(ctx, dst, src, g, n_rows);
+            if (u <= 2048) return launch_softmax_reg<LOG, 256, 8, true>(ctx, dst, src, g, n_rows);
+            if (u <= 8192) return launch_softmax_reg<LOG, 1024, 8, true>(ctx, dst, src, g, n_rows);
+        } else {
+            if (n <= 256) return launch_softmax_reg<LOG, 32, 8, false>(ctx, dst, src, g, n_rows);
+            if (n <= 1024) return launch_softmax_reg<LOG, 32, 32, false>(ctx, dst, src, g, n_rows);
+            if (n <= 8192) return launch_softmax_reg<LOG, 256, 32, false>(ctx, dst, src, g, n_rows);
+            if (n <= 32768) return launch_softmax_reg<LOG, 1024, 32, false>(ctx, dst, src, g, n_rows);
+        }
+    }
+    // longer rows: staged in shared memory, or re-read when even that does not fit
     int threads = 128;
     if (g.n_axis > 512) threads = 256;
     if (g.n_axis > 4096) threads = 512;
