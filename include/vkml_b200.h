@@ -241,6 +241,29 @@ int b200_dist_wait(b200_ctx* ctx);
 int b200_dist_mark_grad(b200_ctx* ctx, void* data, size_t count);
 int b200_dist_clear_grads(b200_ctx* ctx);
 
+/* -- an entry point that allocates nothing (no counterpart in vkML: its backends
+ *    always own an allocator) --
+ *
+ * out[c] = sum over r of in[r * row_pitch + c], f32, for callers that are not allowed
+ * to allocate device memory: code inside a latency-critical loop or a host callback, a
+ * process whose device memory was budgeted once at start-up, a plug-in that was given a
+ * stream and buffers and nothing else.  It needs no b200_ctx.  The split reduction's
+ * partial sums live in a fixed array inside the library image (4 MiB + 16 KiB, held on
+ * every GPU the library is loaded on until the process exits), so:
+ *   - cols may not exceed B200_NOALLOC_MAX_COLUMNS; larger inputs are refused with
+ *     B200_INVALID_ARGUMENT and a message in `error` (use a sum node through b200_compute);
+ *   - the first call on each device looks the array's device address up; make that call
+ *     before any stream capture begins on that device;
+ *   - every call shares the one array: calls that overlap on the GPU (different streams)
+ *     race with each other and must be serialised by the caller.
+ * `in`, `out` are device pointers, `row_pitch` is in elements (>= cols), `stream` is a
+ * cudaStream_t (NULL = the default stream); the work is ordered on it, not finished, when
+ * the call returns.  `error` (may be NULL) receives a message when the status is not B200_OK.
+ * The summation order is fixed, so repeated calls give identical bytes. */
+#define B200_NOALLOC_MAX_COLUMNS 1048576
+int b200_sum_columns_f32_noalloc(const float* in, int64_t rows, int64_t cols, int64_t row_pitch,
+                                 float* out, void* stream, char* error, size_t error_len);
+
 #ifdef __cplusplus
 }
 #endif

@@ -106,6 +106,7 @@ SYMBOLS = {
     "b200_dist_wait": (C.c_int, [_P]),
     "b200_dist_mark_grad": (C.c_int, [_P, _P, C.c_size_t]),
     "b200_dist_clear_grads": (C.c_int, [_P]),
+    "b200_sum_columns_f32_noalloc": (C.c_int, [_P, C.c_int64, C.c_int64, C.c_int64, _P, _P, C.c_char_p, C.c_size_t]),
 }
 
 LIB_PATH = os.path.join(os.path.dirname(os.path.abspath(__file__)), "lib", "libvkml_b200.so")

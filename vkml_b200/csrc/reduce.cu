@@ -1032,3 +1032,157 @@ void launch_softmax(b200_ctx* ctx, const b200_node& node) {
 }
 
 }  // namespace b200
+
+// ---------------------------------------------------------------------------
+// Column sum that allocates nothing (b200_sum_columns_f32_noalloc).
+//
+// For callers that must not touch the device allocator at all: code running inside a
+// latency-critical loop or a host callback, a process whose memory budget was fixed at
+// start-up, a plug-in that was handed a stream and buffers but no permission to call
+// cudaMalloc.  It is the split column reduction used for bias gradients
+// (reduce_thread_kernel + last-block fold), with the partial sums and arrival counters
+// kept in a fixed array that is part of the library image instead of the context's
+// growable scratch buffer.
+//
+// The array costs its full size on every GPU the library is loaded on, until the process
+// exits.  Every call uses the same array and it keeps what the previous call left there:
+// the counters are cleared at the start of each call (stream-ordered), the partial planes
+// are fully written before they are read.  Two calls that run on the GPU at the same time
+// (different streams, or different host threads on different streams) would share it and
+// corrupt each other: callers serialise them.
+// ---------------------------------------------------------------------------
+
+namespace b200 {
+namespace {
+
+constexpr size_t kNoAllocCounterBytes = size_t(kMaxCounters) * sizeof(unsigned);  // 16 KiB
+constexpr size_t kNoAllocPartialBytes = size_t(B200_NOALLOC_MAX_COLUMNS) * sizeof(float);  // 4 MiB
+constexpr size_t kNoAllocScratchBytes = kNoAllocCounterBytes + kNoAllocPartialBytes;
+
+// Inside device code this name is the array; inside host code it is only a handle the
+// runtime can look up -- never an address a kernel may be given.
+static __device__ __align__(256) unsigned char g_noalloc_scratch[kNoAllocScratchBytes];
+
+constexpr int kMaxDevices = 64;
+std::mutex g_noalloc_mu;
+void* g_noalloc_ptr[kMaxDevices] = {};
+
+// Device address of the array on the CURRENT device, looked up once per device.
+int noalloc_scratch(void** out, std::string& why) {
+    int dev = -1;
+    cudaError_t err = cudaGetDevice(&dev);
+    if (err != cudaSuccess || dev < 0 || dev >= kMaxDevices) {
+        cudaGetLastError();
+        why = "cannot identify the current CUDA device";
+        return B200_DEVICE_ERROR;
+    }
+    std::lock_guard<std::mutex> lock(g_noalloc_mu);
+    if (g_noalloc_ptr[dev] == nullptr) {
+        void* p = nullptr;
+        err = cudaGetSymbolAddress(&p, g_noalloc_scratch);
+        if (err != cudaSuccess || p == nullptr) {
+            cudaGetLastError();
+            why = std::string("cudaGetSymbolAddress failed: ") + cudaGetErrorString(err);
+            return B200_DEVICE_ERROR;
+        }
+        g_noalloc_ptr[dev] = p;
+    }
+    *out = g_noalloc_ptr[dev];
+    return B200_OK;
+}
+
+void put_error(char* error, size_t error_len, const std::string& msg) {
+    if (error != nullptr && error_len > 0) {
+        std::snprintf(error, error_len, "%s", msg.c_str());
+    }
+}
+
+template <typename I>
+void launch_noalloc(const float* in, float* out, int64_t rows, int64_t cols, int64_t pitch, int64_t splits,
+                    float* partial, unsigned* counters, cudaStream_t stream) {
+    RedGeoT<I> g{};
+    for (int a = 0; a < kMaxDims; ++a) {
+        g.kdim[a] = g.rdim[a] = 1;
+        g.kstride[a] = g.rstride[a] = 0;
+    }
+    g.krank = g.rrank = 1;
+    g.kdim[kMaxDims - 1] = static_cast<I>(cols);
+    g.kstride[kMaxDims - 1] = 1;
+    g.rdim[kMaxDims - 1] = static_cast<I>(rows);
+    g.rstride[kMaxDims - 1] = static_cast<I>(pitch);
+    dim3 grid(static_cast<unsigned>(ceil_div(cols, 256)), static_cast<unsigned>(splits));
+    reduce_thread_kernel<SumP, I><<<grid, 256, 0, stream>>>(out, splits > 1 ? partial : nullptr,
+                                                             splits > 1 ? counters : nullptr, in, g, cols,
+                                                             static_cast<I>(rows), kPostNone);
+}
+
+}  // namespace
+}  // namespace b200
+
+extern "C" int b200_sum_columns_f32_noalloc(const float* in, int64_t rows, int64_t cols, int64_t row_pitch,
+                                            float* out, void* stream, char* error, size_t error_len) {
+    using namespace b200;
+    if (error != nullptr && error_len > 0) {
+        error[0] = '\0';
+    }
+    if (rows < 0 || cols < 0 || row_pitch < 0 || (cols > 0 && out == nullptr) ||
+        (rows > 0 && cols > 0 && in == nullptr)) {
+        put_error(error, error_len, "b200_sum_columns_f32_noalloc: null pointer or negative extent");
+        return B200_INVALID_ARGUMENT;
+    }
+    if (cols > B200_NOALLOC_MAX_COLUMNS) {
+        put_error(error, error_len,
+                  "b200_sum_columns_f32_noalloc: " + std::to_string(cols) + " columns exceed the fixed scratch array (" +
+                      std::to_string(B200_NOALLOC_MAX_COLUMNS) + " columns); use b200_compute with a sum node instead");
+        return B200_INVALID_ARGUMENT;
+    }
+    if (rows > 1 && row_pitch < cols) {
+        put_error(error, error_len, "b200_sum_columns_f32_noalloc: row_pitch is smaller than the row length");
+        return B200_INVALID_ARGUMENT;
+    }
+    if (cols == 0) {
+        return B200_OK;
+    }
+    void* scratch = nullptr;
+    std::string why;
+    const int rc = noalloc_scratch(&scratch, why);
+    if (rc != B200_OK) {
+        put_error(error, error_len, "b200_sum_columns_f32_noalloc: " + why);
+        return rc;
+    }
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    unsigned* counters = static_cast<unsigned*>(scratch);
+    float* partial = reinterpret_cast<float*>(static_cast<unsigned char*>(scratch) + kNoAllocCounterBytes);
+
+    // as many splits as fill the machine, as few as fit the partial planes
+    int64_t splits = 1;
+    if (rows >= 64) {
+        splits = ceil_div(int64_t(kSmCount) * 2048, cols);
+        splits = std::min<int64_t>(splits, rows / 16);
+        splits = std::min<int64_t>(splits, B200_NOALLOC_MAX_COLUMNS / cols);
+        splits = std::max<int64_t>(1, std::min<int64_t>(splits, 1024));
+    }
+    if (splits > 1) {
+        // the arrival counters must start at zero whatever an earlier call left behind
+        const cudaError_t err = cudaMemsetAsync(counters, 0, kNoAllocCounterBytes, s);
+        if (err != cudaSuccess) {
+            cudaGetLastError();
+            put_error(error, error_len, std::string("b200_sum_columns_f32_noalloc: ") + cudaGetErrorString(err));
+            return B200_DEVICE_ERROR;
+        }
+    }
+    const bool small = rows < (int64_t(1) << 31) && cols < (int64_t(1) << 31) &&
+                       (rows == 0 ? 0 : (rows - 1) * row_pitch + cols) < (int64_t(1) << 31);
+    if (small) {
+        launch_noalloc<uint32_t>(in, out, rows, cols, row_pitch, splits, partial, counters, s);
+    } else {
+        launch_noalloc<int64_t>(in, out, rows, cols, row_pitch, splits, partial, counters, s);
+    }
+    const cudaError_t err = cudaPeekAtLastError();
+    if (err != cudaSuccess) {
+        cudaGetLastError();
+        put_error(error, error_len, std::string("b200_sum_columns_f32_noalloc: launch failed: ") + cudaGetErrorString(err));
+        return B200_DEVICE_ERROR;
+    }
+    return B200_OK;
+}
