@@ -46,9 +46,14 @@ def parse():
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--size", type=int, default=8192, help="M = N = K")
     ap.add_argument("--precision", default="3xtf32", choices=["3xtf32", "tf32", "fp32"])
-    ap.add_argument("--workload", default="gemm", choices=["gemm", "ops"],
-                    help="gemm: the contract line; ops: per-kernel HBM table of the memory-bound family")
+    ap.add_argument("--workload", default="gemm", choices=["gemm", "ops", "gemm-sweep"],
+                    help="gemm: the contract line; ops: per-kernel HBM table of the memory-bound family; "
+                         "gemm-sweep: every GEMM shape of the BASELINE sweep")
     ap.add_argument("--filter", default="", help="ops workload: substring of the case names to run")
+    ap.add_argument("--train", default="mlp_wide_b2048",
+                    help="recorded training step replayed for the secondary `train` object "
+                         "(a file under tests/golden/programs/, or 'none')")
+    ap.add_argument("--train-steps", type=int, default=10)
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true")
     return ap.parse_args()
@@ -322,6 +327,10 @@ def run_b200(args, rank, local_rank, world):
     if rank == 0 and world == 1 and not args.no_cpu_baseline:
         cpu = cpu_baseline(a_host, b_host)
 
+    del a, b, c, packed
+    backend.trim()
+    train = train_section(args, backend, rank, world, dist, barrier, max_over_ranks)
+
     if rank == 0:
         line = {
             "metric": "fp32_gemm_tflops", "value": value, "unit": "TFLOP/s", "n_gpus": world, "steps": args.steps,
@@ -336,12 +345,119 @@ def run_b200(args, rank, local_rank, world):
                        "cache": "operands (268 MB each at 8192) exceed L2; no flush needed",
                        "parallelism": "independent replicas" if world > 1 else "single GPU"},
             "roofline": roofline, "cpu_baseline": cpu, "e2e": e2e, "gpu_launches": launches,
-            "kernels": kernel_share, "clocks": clocks,
+            "kernels": kernel_share, "clocks": clocks, "train": train,
         }
         print(json.dumps(line))
     if dist is not None:
         dist.barrier()
         dist.destroy_process_group()
+
+
+# ---------------------------------------------------------------------------
+# secondary object: a whole training step, replayed from the framework's recorded traffic
+# ---------------------------------------------------------------------------
+
+def train_section(args, backend, rank, world, dist, barrier, max_over_ranks):
+    """Samples/s of a recorded training step (forward, backward, SGD-momentum update, loss
+    read-back) replayed through the C ABI; at N > 1 every rank runs the step on its own
+    batch and the backward span's gradient sinks are all-reduced over NCCL while the span runs."""
+    from vkml_b200.replay import Replayer, load_program
+    path = os.path.join(ROOT, "tests", "golden", "programs", args.train + ".json.gz")
+    if args.train == "none" or not os.path.exists(path):
+        return None
+    program = load_program(path)
+    meta = program["meta"]
+    rng = np.random.default_rng(SEED_DATA + 1 + rank)
+    wrng = np.random.default_rng(SEED_DATA + 1)  # identical parameters on every rank
+    batch = meta["batch"]
+    if meta["model"] == "mlp":
+        widths = meta["widths"]
+        params = []
+        for fin, fout in zip(widths[:-1], widths[1:]):
+            bound = 1.0 / np.sqrt(fin)
+            params.append(wrng.uniform(-bound, bound, (fout, fin)).astype(np.float32))
+            params.append(wrng.uniform(-bound, bound, (fout,)).astype(np.float32))
+        x_shape, classes = (batch, widths[0]), widths[-1]
+        x = rng.standard_normal(x_shape, dtype=np.float32)
+        desc = "MLP " + "-".join(map(str, widths))
+    else:
+        cin, hw, classes = meta["cin"], meta["hw"], meta["classes"]
+        feat = meta["c3"] * (hw // 8) ** 2
+        params = []
+        for cout, ci in ((meta["c1"], cin), (meta["c2"], meta["c1"]), (meta["c3"], meta["c2"])):
+            bound = 1.0 / np.sqrt(ci * 9)
+            params.append(wrng.uniform(-bound, bound, (cout, ci, 3, 3)).astype(np.float32))
+            params.append(wrng.uniform(-bound, bound, (cout,)).astype(np.float32))
+        bound = 1.0 / np.sqrt(feat)
+        params.append(wrng.uniform(-bound, bound, (classes, feat)).astype(np.float32))
+        params.append(wrng.uniform(-bound, bound, (classes,)).astype(np.float32))
+        x_shape = (batch, cin, hw, hw)
+        x = rng.random(x_shape, dtype=np.float32)
+        desc = f"CNN conv3x3 {meta['c1']}-{meta['c2']}-{meta['c3']} + Linear {feat}->{classes}"
+    y = rng.integers(0, classes, batch).astype(np.int64)
+    pin_x, pin_y = backend.alloc_host(x.nbytes), backend.alloc_host(y.nbytes)
+    pin_x[:] = x.view(np.uint8).reshape(-1)
+    pin_y[:] = y.view(np.uint8).reshape(-1)
+    mode = {"upload": True}
+
+    def feed(tag, nbytes):
+        if tag[0] == "pro":
+            return params[tag[1]]
+        if not mode["upload"]:
+            return None
+        return pin_x if tag[1] == 0 else pin_y
+
+    if world > 1:
+        uid = [backend.dist_unique_id() if rank == 0 else None]
+        dist.broadcast_object_list(uid, src=0)
+        backend.dist_init(rank, world, uid[0])
+    r = Replayer(backend, program, feed, grad_sync=world > 1)
+    for _ in range(4):  # steps 0 and 1 differ from the steady state; then two warm steady steps
+        r.step()
+    barrier()
+    k = max(3, args.train_steps)
+    # end to end: x and labels uploaded from pinned host memory every step, loss read back
+    l0 = backend.stats()["kernel_launches"]
+    t0 = time.perf_counter()
+    for _ in range(k):
+        r.step()
+    backend.synchronize()
+    e2e_ms = max_over_ranks((time.perf_counter() - t0) * 1e3)
+    launches = (backend.stats()["kernel_launches"] - l0) / k
+    barrier()
+    # inputs resident: the recorded uploads are skipped (the buffers keep the last batch)
+    mode["upload"] = False
+    backend.timer_begin()
+    for _ in range(k):
+        r.step()
+    dev_ms = max_over_ranks(backend.timer_end())
+    barrier()
+    # a separate, profiled pass for the per-kernel breakdown (events around every launch)
+    backend.set_profiling(True)
+    for _ in range(k):
+        r.step()
+    records = backend.last_profile()
+    backend.set_profiling(False)
+    barrier()
+    losses = [float(d.view(np.float32)[0]) for _, d in r.downloads if d.nbytes == 4]
+    by_label = {}
+    for label, t in records:
+        by_label[label] = by_label.get(label, 0.0) + t / k
+    top = dict(sorted(by_label.items(), key=lambda kv: -kv[1])[:8])
+    out = {"workload": f"{desc}, per-GPU batch {batch}, fp32, cross-entropy, SGD momentum 0.9: the framework's "
+                       f"recorded step ({args.train}) replayed through Backend.compute",
+           "samples_per_s": batch * world * k / (dev_ms * 1e-3), "ms_per_step": dev_ms / k,
+           "e2e_samples_per_s": batch * world * k / (e2e_ms * 1e-3), "e2e_ms_per_step": e2e_ms / k,
+           "h2d_bytes_per_step": int(x.nbytes + y.nbytes), "d2h_bytes_per_step": 4,
+           "gpu_launches_per_step": launches, "steps": k, "n_gpus": world,
+           "parallelism": f"dp{world}: batch sharded, NCCL all-reduce of gradient sinks overlapped with backward"
+                          if world > 1 else "single GPU",
+           "comm_bytes_per_step": backend.stats()["comm_bytes"] / max(1, r.steps_run),
+           "loss_first_last": [losses[0], losses[-1]] if losses else None,
+           "device_ms_per_step_by_kernel": {a: round(b, 4) for a, b in top.items()}}
+    backend.free_host(pin_x)
+    backend.free_host(pin_y)
+    return out
 
 
 # ---------------------------------------------------------------------------
@@ -482,6 +598,68 @@ def run_ops(args, local_rank):
     return results
 
 
+def run_gemm_sweep(args, local_rank):
+    """One JSON line per GEMM shape of BASELINE config 2 (squares, skinny M=64, long-K split-K) and
+    of the wide-MLP / CNN training steps, per precision: device time of the whole matmul node."""
+    import vkml_b200
+    from vkml_b200 import DeviceTensor, NodeDesc, Op, graph
+    backend = vkml_b200.Backend(local_rank)
+    rng = np.random.default_rng(SEED_DATA)
+    shapes = [("square 256", 1, 256, 256, 256, "nn"), ("square 1024", 1, 1024, 1024, 1024, "nn"),
+              ("square 4096", 1, 4096, 4096, 4096, "nn"), ("square 8192", 1, 8192, 8192, 8192, "nn"),
+              ("skinny M=64, K=N=4096", 1, 64, 4096, 4096, "nn"), ("long K=65536, M=N=512", 1, 512, 65536, 512, "nn"),
+              ("wide MLP fwd 2048x4096 . W^T(8192)", 1, 2048, 4096, 8192, "nt"),
+              ("wide MLP fwd 2048x8192 . W^T(8192)", 1, 2048, 8192, 8192, "nt"),
+              ("wide MLP dX 2048x8192 . W(8192x8192)", 1, 2048, 8192, 8192, "nn"),
+              ("wide MLP dW x^T(8192x2048) . g(2048x8192)", 1, 8192, 2048, 8192, "tn"),
+              ("wide MLP head 2048x8192 . W^T(1000)", 1, 2048, 8192, 1000, "nt"),
+              ("conv2 fwd W[128x576] bcast . cols[256][576x256]", 256, 128, 576, 256, "bn"),
+              ("conv3 fwd W[256x1152] bcast . cols[256][1152x64]", 256, 256, 1152, 64, "bn"),
+              ("conv1 fwd W[64x27] bcast . cols[256][27x1024]", 256, 64, 27, 1024, "bn"),
+              ("MNIST MLP 64x784 . W^T(128)", 1, 64, 784, 128, "nt")]
+    for name, batch, m, k, n, kind in shapes:
+        if args.filter and args.filter not in name:
+            continue
+        if kind == "bn":   # A broadcast over the batch
+            a = DeviceTensor.from_host(backend, rng.standard_normal((m, k), dtype=np.float32)).reshape(
+                (1, 1, m, k)).broadcast_to((1, batch, m, k))
+            b = DeviceTensor.from_host(backend, rng.standard_normal((1, batch, k, n), dtype=np.float32))
+        else:
+            a = DeviceTensor.from_host(backend, rng.standard_normal((k, m) if kind[0] == "t" else (m, k),
+                                                                    dtype=np.float32))
+            b = DeviceTensor.from_host(backend, rng.standard_normal((n, k) if kind[1] == "t" else (k, n),
+                                                                    dtype=np.float32))
+            a = (a.transpose(0, 1) if kind[0] == "t" else a)
+            b = (b.transpose(0, 1) if kind[1] == "t" else b)
+            a = DeviceTensor(backend, a.storage, (1, 1) + a.dims, (0, 0) + a.strides, a.dtype)
+            b = DeviceTensor(backend, b.storage, (1, 1) + b.dims, (0, 0) + b.strides, b.dtype)
+        c = DeviceTensor.empty(backend, (1, batch, m, n))
+        packed = graph.pack_nodes([NodeDesc(int(Op.MATMUL), c.desc, [a.desc, b.desc])])
+        flops = 2.0 * batch * m * n * k
+        row = {"gemm": name, "batch": batch, "m": m, "k": k, "n": n, "layout": kind}
+        for prec, code in (("3xtf32", 0), ("tf32", 1), ("fp32", 2)):
+            if prec == "fp32" and flops > 3e11:
+                continue
+            backend.set_gemm_precision(code)
+            reps = 20 if flops < 1e11 else 5
+            for _ in range(3):
+                backend.compute_packed(packed, 1)
+            backend.synchronize()
+            backend.timer_begin()
+            for _ in range(reps):
+                backend.compute_packed(packed, 1)
+            ms = backend.timer_end() / reps
+            backend.set_profiling(True)
+            backend.compute_packed(packed, 1)
+            rec = backend.last_profile()
+            backend.set_profiling(False)
+            row[prec] = {"ms": round(ms, 4), "tflops": round(flops / (ms * 1e-3) / 1e12, 2),
+                         "kernel_ms": {l: round(t, 4) for l, t in rec}}
+        print(json.dumps(row), flush=True)
+        del a, b, c, packed
+        backend.trim()
+
+
 def main():
     args = parse()
     rank = int(os.environ.get("RANK", "0"))
@@ -489,6 +667,8 @@ def main():
     world = int(os.environ.get("WORLD_SIZE", "1"))
     if args.workload == "ops":
         run_ops(args, local_rank)
+    elif args.workload == "gemm-sweep":
+        run_gemm_sweep(args, local_rank)
     elif args.impl == "reference":
         run_reference(args, rank, world)
     else:

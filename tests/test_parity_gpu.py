@@ -250,3 +250,37 @@ def test_device_copies(backend):
         backend.copy_from_host(tc.storage, 1999, a)
     z = backend.allocate(0)
     assert z.data == 0 and z.nbytes == 0
+
+
+def test_profiling_stats_timer_and_pinned_memory(backend):
+    """The auxiliary ABI: per-launch device times, counters, the stream stopwatch, page-locked buffers."""
+    from vkml_b200 import DeviceTensor, NodeDesc
+    rng = np.random.default_rng(9)
+    a = DeviceTensor.from_host(backend, rng.standard_normal((1, 1, 512, 512)).astype(np.float32))
+    b = DeviceTensor.from_host(backend, rng.standard_normal((1, 1, 512, 512)).astype(np.float32))
+    c = DeviceTensor.empty(backend, (1, 1, 512, 512))
+    r = DeviceTensor.empty(backend, (1, 1, 512, 512))
+    before = backend.stats()
+    backend.set_profiling(True)
+    backend.timer_begin()
+    backend.compute([NodeDesc(Op.MATMUL, c.desc, [a.desc, b.desc]), NodeDesc(Op.RELU, r.desc, [c.desc])])
+    ms = backend.timer_end()
+    prof = backend.last_profile()
+    backend.set_profiling(False)
+    labels = [l for l, _ in prof]
+    assert labels[:3] == ["matmul.split_a", "matmul.split_b", "matmul.tcgen05_3xtf32"] and labels[-1] == "relu", labels
+    assert labels[3:-1] in ([], ["matmul.fold"])  # a split-K fold when the tiles alone cannot fill the machine
+    assert all(t > 0 for _, t in prof) and 0 < sum(t for _, t in prof) <= ms * 1.5
+    after = backend.stats()
+    assert after["kernel_launches"] - before["kernel_launches"] == len(labels)
+    assert after["nodes_computed"] - before["nodes_computed"] == 2
+    assert after["compute_calls"] - before["compute_calls"] == 1
+    assert backend.last_profile() == []  # reading clears, and nothing is recorded once disabled
+    pin = backend.alloc_host(512 * 512 * 4)
+    backend.copy_to_host(pin, r.storage, 0, pin.nbytes)
+    got = np.frombuffer(pin, dtype=np.float32).reshape(512, 512).copy()
+    backend.free_host(pin)
+    np.testing.assert_array_equal(got, r.numpy().reshape(512, 512))
+    assert (got >= 0).all() and got.max() > 0
+    caps = backend.capabilities()
+    assert caps["compute_capability"][0] == 10 and caps["shader_core_count"] >= 100 and caps["asynchronous"]

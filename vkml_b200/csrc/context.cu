@@ -23,9 +23,16 @@ ProfScope::ProfScope(b200_ctx* ctx, const char* label) : ctx_(ctx) {
     ProfEntry e{};
     std::snprintf(e.label, sizeof(e.label), "%s", label);
     e.op = ctx->current_op;
-    if (cudaEventCreate(&e.begin) != cudaSuccess || cudaEventCreate(&e.end) != cudaSuccess) {
-        cudaGetLastError();
-        return;
+    // events are recycled: creating a pair per launch would cost more than a small kernel
+    for (cudaEvent_t* ev : {&e.begin, &e.end}) {
+        if (!ctx->event_pool.empty()) {
+            *ev = ctx->event_pool.back();
+            ctx->event_pool.pop_back();
+        } else if (cudaEventCreate(ev) != cudaSuccess) {
+            cudaGetLastError();
+            if (ev == &e.end) ctx->event_pool.push_back(e.begin);
+            return;
+        }
     }
     cudaEventRecord(e.begin, ctx->stream);
     ctx->prof.push_back(e);
@@ -407,6 +414,11 @@ int b200_create(int cuda_ordinal, b200_ctx** out) {
         *ctx->h_status = 0;
         // VKML_B200_GEMM_PRECISION = 3xtf32 (default) | tf32 | fp32, read once per context:
         // the counterpart of the VKML_GEMM_* switches (vulkan_backend.cpp:2160-2178)
+        if (const char* e = std::getenv("VKML_B200_COMM_SMS")) {
+            const int v = std::atoi(e);
+            if (v < 0 || v > 64) fail(B200_INVALID_ARGUMENT, "VKML_B200_COMM_SMS must be 0..64");
+            ctx->comm_sms = v;
+        }
         if (const char* e = std::getenv("VKML_B200_GEMM_PRECISION")) {
             const std::string v(e);
             if (v == "tf32") ctx->gemm_precision = B200_GEMM_TF32;
@@ -433,6 +445,7 @@ void b200_destroy(b200_ctx* ctx) {
     if (ctx->d_counters != nullptr) cudaFree(ctx->d_counters);
     if (ctx->h_status != nullptr) cudaFreeHost(ctx->h_status);
     if (ctx->staging != nullptr) cudaFreeHost(ctx->staging);
+    for (cudaEvent_t ev : ctx->event_pool) cudaEventDestroy(ev);
     if (ctx->timer_begin != nullptr) cudaEventDestroy(ctx->timer_begin);
     if (ctx->timer_end != nullptr) cudaEventDestroy(ctx->timer_end);
     cudaGetLastError();
@@ -486,6 +499,11 @@ int b200_compute(b200_ctx* ctx, const b200_node* nodes, size_t n_nodes, uint32_t
         // With no buffers registered, the gradients are the span's SINKS: f32 outputs that
         // no later node of the span reads.  backward() realises exactly the leaf gradients
         // (src/autograd/autograd.cpp:627-666), so every other output is consumed in-span.
+        ctx->in_grad_sync_span = grad_sync && ctx->dist != nullptr;
+        struct SpanGuard {
+            b200_ctx* c;
+            ~SpanGuard() { c->in_grad_sync_span = false; }
+        } span_guard{ctx};
         std::vector<char> is_sink;
         if (grad_sync && ctx->grads.empty()) {
             is_sink.assign(n_nodes, 0);
@@ -657,8 +675,8 @@ int b200_profile_enable(b200_ctx* ctx, int on) {
     return guarded(ctx, [&] {
         B200_CUDA_CHECK(cudaStreamSynchronize(ctx->stream));
         for (ProfEntry& e : ctx->prof) {
-            cudaEventDestroy(e.begin);
-            cudaEventDestroy(e.end);
+            ctx->event_pool.push_back(e.begin);
+            ctx->event_pool.push_back(e.end);
         }
         ctx->prof.clear();
         ctx->profiling = on != 0;
@@ -682,8 +700,8 @@ int b200_profile_read(b200_ctx* ctx, b200_profile_record* out, size_t capacity, 
                 out[n].op = e.op;
                 ++n;
             }
-            cudaEventDestroy(e.begin);
-            cudaEventDestroy(e.end);
+            ctx->event_pool.push_back(e.begin);
+            ctx->event_pool.push_back(e.end);
         }
         ctx->prof.clear();
         *count = n;

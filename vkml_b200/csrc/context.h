@@ -73,6 +73,10 @@ struct b200_ctx {
     size_t staging_bytes = 0;
 
     int gemm_precision = B200_GEMM_3XTF32;
+    // SMs the persistent GEMM kernel leaves free while a span's gradients are being all-reduced,
+    // so the communication kernels always find room (VKML_B200_COMM_SMS, default 8).
+    int comm_sms = 8;
+    bool in_grad_sync_span = false;
 
     std::atomic<uint64_t> compute_calls{0}, kernel_launches{0}, nodes_computed{0}, comm_bytes{0};
 
@@ -83,6 +87,7 @@ struct b200_ctx {
     bool profiling = false;
     uint32_t current_op = 0;
     std::vector<b200::ProfEntry> prof;
+    std::vector<cudaEvent_t> event_pool;
 
     b200::DistState* dist = nullptr;
     std::vector<b200::GradBuffer> grads;

@@ -14,7 +14,10 @@
 //     A_hi, A_lo : [batches_a * M][Kp]     B_hi, B_lo : [batches_b * N][Kp]
 // with Kp = K rounded up to 32 and zero-filled, so every TMA tile is a legal,
 // 128-byte-aligned box regardless of the caller's pitches.  A broadcast batch
-// (both batch strides 0) is stored once.
+// (both batch strides 0) is stored once.  An operand whose M (or N) axis is the
+// contiguous one -- a transposed view as A, a row-major [K,N] matrix as B -- is
+// NOT transposed: its planes keep the [Kp][M or N] layout and the MMA reads them
+// through MN-major descriptors, so the split is a dense 128-bit pass.
 //
 // Main kernel: persistent, one CTA per SM, 6 warps:
 //     warp 0   TMA producer: per K-block of 32 floats, 4 boxes
@@ -163,23 +166,41 @@ __device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
     asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
 }
 
-// Shared-memory matrix descriptor for a K-major tile whose rows are exactly one
-// 128-byte swizzle row (32 floats): 8-row groups are 1024 bytes apart (the
-// stride-dimension offset); the leading-dimension offset is unused because the
-// K extent of one instruction (32 bytes) lies inside the swizzle row.
-__device__ __forceinline__ uint64_t smem_desc_sw128(uint32_t smem_addr) {
+// Shared-memory matrix descriptors, 128-byte swizzle, 32-bit elements.
+//
+// K-major tile ([rows][32 floats], one swizzle row per matrix row): 8-row groups are 1024
+// bytes apart (stride-dimension offset); the leading-dimension offset is unused because the
+// K extent of one instruction (8 floats = 32 bytes) lies inside the swizzle row.  One K step
+// advances the start address by 32 bytes.
+//
+// MN-major tile (the operand is stored with its M or N axis contiguous, as a row-major
+// [K][N] matrix is for B): the tile is a row of "atoms", each 32 K-rows of 128 bytes (32
+// floats along MN).  32-bit operands must use the 128-byte swizzle with 32-byte atomicity
+// here (layout type 1, TMA mode SWIZZLE_128B_ATOM_32B): the pattern repeats every 4 K-rows,
+// so the stride-dimension offset is 512 bytes; the next atom along MN starts kMnAtomBytes
+// later (leading-dimension offset).  One K step (8 K-rows) advances the start by 1024 bytes.
+constexpr uint32_t kMnAtomBytes = BK * 128;  // 32 K-rows x 128 bytes
+
+__device__ __forceinline__ uint64_t smem_desc(uint32_t smem_addr, uint32_t lbo_bytes, uint32_t sbo_bytes,
+                                              uint32_t layout_type) {
     uint64_t d = 0;
-    d |= static_cast<uint64_t>((smem_addr & 0x3FFFF) >> 4);  // start address, bits 0-13
-    d |= static_cast<uint64_t>(1024 >> 4) << 32;             // stride-dimension byte offset, bits 32-45
-    d |= static_cast<uint64_t>(1) << 46;                     // descriptor version for sm_100
-    d |= static_cast<uint64_t>(2) << 61;                     // layout: 128-byte swizzle
+    d |= static_cast<uint64_t>((smem_addr & 0x3FFFF) >> 4);   // start address, bits 0-13
+    d |= static_cast<uint64_t>(lbo_bytes >> 4) << 16;         // leading-dimension byte offset, bits 16-29
+    d |= static_cast<uint64_t>(sbo_bytes >> 4) << 32;         // stride-dimension byte offset, bits 32-45
+    d |= static_cast<uint64_t>(1) << 46;                      // descriptor version for sm_100
+    d |= static_cast<uint64_t>(layout_type) << 61;            // 2: 128-byte swizzle, 1: same with 32-byte atoms
     return d;
 }
 
-// Instruction descriptor: D = f32, A = B = tf32, both K-major, M x N tile.
-__host__ __device__ constexpr uint32_t make_idesc(int m, int n) {
-    return (1u << 4) | (2u << 7) | (2u << 10) | (static_cast<uint32_t>(n >> 3) << 17) |
-           (static_cast<uint32_t>(m >> 4) << 24);
+template <bool MN_MAJOR>
+__device__ __forceinline__ uint64_t operand_desc(uint32_t smem_addr) {
+    return MN_MAJOR ? smem_desc(smem_addr, kMnAtomBytes, 512, 1) : smem_desc(smem_addr, 0, 1024, 2);
+}
+
+// Instruction descriptor: D = f32, A = B = tf32, M x N tile, operand majors as given.
+__host__ __device__ constexpr uint32_t make_idesc(int m, int n, bool a_mn, bool b_mn) {
+    return (1u << 4) | (2u << 7) | (2u << 10) | (a_mn ? (1u << 15) : 0u) | (b_mn ? (1u << 16) : 0u) |
+           (static_cast<uint32_t>(n >> 3) << 17) | (static_cast<uint32_t>(m >> 4) << 24);
 }
 
 // ---------------------------------------------------------------------------
@@ -212,15 +233,56 @@ struct SplitArgs {
     int64_t rows, k, kp;
     int64_t s_b0, s_b1, s_r, s_k;  // element strides of src
     int64_t n_batches;
+    int64_t out_rows;    // plane rows per batch (>= rows; the extra rows are written as zero)
 };
 
-// One 32x32 (rows x k) tile per block iteration; reads follow whichever of the
-// two axes has unit stride, writes are always along k (dense planes).
+// Source rows dense along K and 16-byte aligned: one thread per four K-elements, 128-bit
+// loads and stores, no shared memory.
+__global__ void __launch_bounds__(256) split_rows_kernel(SplitArgs a) {
+    const int64_t kp4 = a.kp / 4;
+    const int64_t total = kp4 * a.out_rows * a.n_batches;
+    const int64_t step = int64_t(gridDim.x) * blockDim.x;
+    for (int64_t i = int64_t(blockIdx.x) * blockDim.x + threadIdx.x; i < total; i += step) {
+        const int64_t k4 = i % kp4;
+        const int64_t rb = i / kp4;
+        const int64_t r = rb % a.out_rows;
+        const int64_t b = rb / a.out_rows;
+        const int64_t k = k4 * 4;
+        float4 v = make_float4(0.0F, 0.0F, 0.0F, 0.0F);
+        if (r < a.rows) {
+            const float* src = a.src + (b / a.b1) * a.s_b0 + (b % a.b1) * a.s_b1 + r * a.s_r;
+            if (k + 3 < a.k) {
+                v = *reinterpret_cast<const float4*>(src + k);
+            } else {
+                if (k < a.k) v.x = src[k];
+                if (k + 1 < a.k) v.y = src[k + 1];
+                if (k + 2 < a.k) v.z = src[k + 2];
+            }
+        }
+        float4 h, l;
+        split_tf32(v.x, h.x, l.x);
+        split_tf32(v.y, h.y, l.y);
+        split_tf32(v.z, h.z, l.z);
+        split_tf32(v.w, h.w, l.w);
+        const int64_t o = rb * a.kp + k;
+        *reinterpret_cast<float4*>(a.hi + o) = h;
+        if (a.lo != nullptr) {
+            *reinterpret_cast<float4*>(a.lo + o) = l;
+        }
+    }
+}
+
+// General layouts, 64x64 (rows x k) tiles through shared memory: global reads follow
+// whichever of the two axes has unit stride (so a row-major [K,N] operand is read along N
+// and written K-major, i.e. transposed), writes are always dense along k.  16 elements per
+// thread in flight in each phase.
+constexpr int kSplitTile = 64;
+
 __global__ void __launch_bounds__(256) split_kernel(SplitArgs a) {
-    __shared__ float tile[32][33];
-    const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;
-    const int64_t tiles_k = a.kp / 32;
-    const int64_t tiles_r = (a.rows + 31) / 32;
+    __shared__ float tile[kSplitTile][kSplitTile + 1];  // [row][k]
+    const int fast = threadIdx.x & 63, slow = threadIdx.x >> 6;
+    const int64_t tiles_k = a.kp / kSplitTile + (a.kp % kSplitTile != 0);
+    const int64_t tiles_r = (a.rows + kSplitTile - 1) / kSplitTile;
     const int64_t n_tiles = tiles_k * tiles_r * a.n_batches;
     const bool k_fast = a.s_k == 1 || a.s_r != 1;
     for (int64_t t = blockIdx.x; t < n_tiles; t += gridDim.x) {
@@ -228,37 +290,58 @@ __global__ void __launch_bounds__(256) split_kernel(SplitArgs a) {
         const int64_t tr = (t / tiles_k) % tiles_r;
         const int64_t b = t / (tiles_k * tiles_r);
         const float* src = a.src + (b / a.b1) * a.s_b0 + (b % a.b1) * a.s_b1;
-        const int64_t r0 = tr * 32, k0 = tk * 32;
+        const int64_t r0 = tr * kSplitTile, k0 = tk * kSplitTile;
+        const bool full = r0 + kSplitTile <= a.rows && k0 + kSplitTile <= a.k;
+        if (k_fast) {
+            const float* p = src + (r0 + slow) * a.s_r + (k0 + fast) * a.s_k;
+            const int64_t step = 4 * a.s_r;
 #pragma unroll
-        for (int j = 0; j < 4; ++j) {
-            int rr, kk;
-            if (k_fast) {
-                kk = tx;
-                rr = ty + 8 * j;
-            } else {
-                rr = tx;
-                kk = ty + 8 * j;
+            for (int j = 0; j < kSplitTile / 4; ++j) {
+                const bool ok = full || (r0 + slow + 4 * j < a.rows && k0 + fast < a.k);
+                tile[slow + 4 * j][fast] = ok ? p[j * step] : 0.0F;
             }
-            const int64_t r = r0 + rr, k = k0 + kk;
-            tile[rr][kk] = (r < a.rows && k < a.k) ? src[r * a.s_r + k * a.s_k] : 0.0F;
+        } else {
+            const float* p = src + (r0 + fast) * a.s_r + (k0 + slow) * a.s_k;
+            const int64_t step = 4 * a.s_k;
+#pragma unroll
+            for (int j = 0; j < kSplitTile / 4; ++j) {
+                const bool ok = full || (r0 + fast < a.rows && k0 + slow + 4 * j < a.k);
+                tile[fast][slow + 4 * j] = ok ? p[j * step] : 0.0F;
+            }
         }
         __syncthreads();
+        if (k0 + fast < a.kp) {
+            float* hi = a.hi + (b * a.rows + r0 + slow) * a.kp + k0 + fast;
+            float* lo = a.lo != nullptr ? a.lo + (b * a.rows + r0 + slow) * a.kp + k0 + fast : nullptr;
+            const int64_t ostep = 4 * a.kp;
 #pragma unroll
-        for (int j = 0; j < 4; ++j) {
-            const int rr = ty + 8 * j;
-            const int64_t r = r0 + rr;
-            if (r < a.rows) {
-                float hi, lo;
-                split_tf32(tile[rr][tx], hi, lo);
-                const int64_t o = (b * a.rows + r) * a.kp + k0 + tx;
-                a.hi[o] = hi;
-                if (a.lo != nullptr) {
-                    a.lo[o] = lo;
+            for (int j = 0; j < kSplitTile / 4; ++j) {
+                if (full || r0 + slow + 4 * j < a.rows) {
+                    float h, l;
+                    split_tf32(tile[slow + 4 * j][fast], h, l);
+                    hi[j * ostep] = h;
+                    if (lo != nullptr) {
+                        lo[j * ostep] = l;
+                    }
                 }
             }
         }
         __syncthreads();
     }
+}
+
+void launch_split(b200_ctx* ctx, const SplitArgs& s, const char* label) {
+    ProfScope scope(ctx, label);
+    const bool rows_dense = s.s_k == 1 && s.s_r % 4 == 0 && s.s_b0 % 4 == 0 && s.s_b1 % 4 == 0 &&
+                            reinterpret_cast<uintptr_t>(s.src) % 16 == 0;
+    if (rows_dense) {
+        const int64_t total = (s.kp / 4) * s.out_rows * s.n_batches;
+        split_rows_kernel<<<grid_for(ceil_div(total, 2), 256), 256, 0, ctx->stream>>>(s);
+    } else {
+        const int64_t tiles = ceil_div(s.kp, kSplitTile) * ceil_div(s.rows, kSplitTile) * s.n_batches;
+        split_kernel<<<grid_for(tiles, 1, 8), 256, 0, ctx->stream>>>(s);
+    }
+    ctx->count_launch();
 }
 
 // ---------------------------------------------------------------------------
@@ -288,14 +371,14 @@ struct Smem {
     static constexpr int kTotal = STAGES * kStageBytes + kBarrierBytes + 1024;  // + alignment slack
 };
 
-template <int BN, int STAGES, bool THREE_PASS>
+template <int BN, int STAGES, bool THREE_PASS, bool A_MN, bool B_MN>
 __global__ void __launch_bounds__(kThreads, 1)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a_hi, const __grid_constant__ CUtensorMap map_a_lo,
                const __grid_constant__ CUtensorMap map_b_hi, const __grid_constant__ CUtensorMap map_b_lo,
                TcArgs g) {
     using S = Smem<BN, STAGES>;
     constexpr uint32_t kTmemCols = 2 * BN < 32 ? 32 : 2 * BN;
-    constexpr uint32_t kIdesc = make_idesc(BM, BN);
+    constexpr uint32_t kIdesc = make_idesc(BM, BN, A_MN, B_MN);
     constexpr uint32_t kStageTx = THREE_PASS ? S::kStageBytes : (S::kABytes + S::kBBytes);
 
     extern __shared__ uint8_t smem_raw[];
@@ -361,8 +444,10 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a_hi, const __grid_consta
                 int split;
                 int64_t batch, tm, tn;
                 decode(u, split, batch, tm, tn);
-                const int a_row = static_cast<int>(batch * g.a_batch_rows + tm * BM);
-                const int b_row = static_cast<int>(batch * g.b_batch_rows + tn * BN);
+                // K-major plane: coordinates (k, plane row); MN-major plane: (m or n, plane K-row)
+                const int a_base = static_cast<int>(batch * g.a_batch_rows);
+                const int b_base = static_cast<int>(batch * g.b_batch_rows);
+                const int m0 = static_cast<int>(tm * BM), n0 = static_cast<int>(tn * BN);
                 const int64_t kb0 = int64_t(split) * g.kb_per_split;
                 const int64_t kb1 = min(kb0 + g.kb_per_split, g.k_blocks);
                 for (int64_t kb = kb0; kb < kb1; ++kb, ++it) {
@@ -374,12 +459,33 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a_hi, const __grid_consta
                     }
                     const uint32_t stage = base + s * S::kStageBytes;
                     const int kc = static_cast<int>(kb * BK);
-                    mbar_arrive_expect_tx(full_bar(s), kStageTx);
-                    tma_load_2d(stage, &map_a_hi, full_bar(s), kc, a_row);
-                    tma_load_2d(stage + 2 * S::kABytes, &map_b_hi, full_bar(s), kc, b_row);
+                    const uint32_t bar = full_bar(s);
+                    mbar_arrive_expect_tx(bar, kStageTx);
+                    auto load_a = [&](uint32_t dst, const CUtensorMap* map) {
+                        if (A_MN) {
+#pragma unroll
+                            for (int atom = 0; atom < BM / 32; ++atom) {
+                                tma_load_2d(dst + atom * kMnAtomBytes, map, bar, m0 + 32 * atom, a_base + kc);
+                            }
+                        } else {
+                            tma_load_2d(dst, map, bar, kc, a_base + m0);
+                        }
+                    };
+                    auto load_b = [&](uint32_t dst, const CUtensorMap* map) {
+                        if (B_MN) {
+#pragma unroll
+                            for (int atom = 0; atom < BN / 32; ++atom) {
+                                tma_load_2d(dst + atom * kMnAtomBytes, map, bar, n0 + 32 * atom, b_base + kc);
+                            }
+                        } else {
+                            tma_load_2d(dst, map, bar, kc, b_base + n0);
+                        }
+                    };
+                    load_a(stage, &map_a_hi);
+                    load_b(stage + 2 * S::kABytes, &map_b_hi);
                     if (THREE_PASS) {
-                        tma_load_2d(stage + S::kABytes, &map_a_lo, full_bar(s), kc, a_row);
-                        tma_load_2d(stage + 2 * S::kABytes + S::kBBytes, &map_b_lo, full_bar(s), kc, b_row);
+                        load_a(stage + S::kABytes, &map_a_lo);
+                        load_b(stage + 2 * S::kABytes + S::kBBytes, &map_b_lo);
                     }
                 }
             }
@@ -412,20 +518,22 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a_hi, const __grid_consta
                     }
                     tc_fence_after();
                     const uint32_t stage = base + s * S::kStageBytes;
-                    const uint64_t a_hi = smem_desc_sw128(stage);
-                    const uint64_t a_lo = smem_desc_sw128(stage + S::kABytes);
-                    const uint64_t b_hi = smem_desc_sw128(stage + 2 * S::kABytes);
-                    const uint64_t b_lo = smem_desc_sw128(stage + 2 * S::kABytes + S::kBBytes);
+                    const uint64_t a_hi = operand_desc<A_MN>(stage);
+                    const uint64_t a_lo = operand_desc<A_MN>(stage + S::kABytes);
+                    const uint64_t b_hi = operand_desc<B_MN>(stage + 2 * S::kABytes);
+                    const uint64_t b_lo = operand_desc<B_MN>(stage + 2 * S::kABytes + S::kBBytes);
 #pragma unroll
                     for (int kk = 0; kk < BK / UMMA_K; ++kk) {
-                        const uint64_t adv = static_cast<uint64_t>((kk * UMMA_K * 4) >> 4);  // +32 bytes per step
+                        // one K step: +32 bytes inside the swizzle row (K-major), +8 K-rows (MN-major)
+                        const uint64_t adv_a = static_cast<uint64_t>((A_MN ? kk * 1024 : kk * UMMA_K * 4) >> 4);
+                        const uint64_t adv_b = static_cast<uint64_t>((B_MN ? kk * 1024 : kk * UMMA_K * 4) >> 4);
                         const uint32_t first = (kb == kb0 && kk == 0) ? 0u : 1u;
                         if (THREE_PASS) {
-                            umma_tf32(d_tmem, a_lo + adv, b_hi + adv, kIdesc, first);
-                            umma_tf32(d_tmem, a_hi + adv, b_lo + adv, kIdesc, 1u);
-                            umma_tf32(d_tmem, a_hi + adv, b_hi + adv, kIdesc, 1u);
+                            umma_tf32(d_tmem, a_lo + adv_a, b_hi + adv_b, kIdesc, first);
+                            umma_tf32(d_tmem, a_hi + adv_a, b_lo + adv_b, kIdesc, 1u);
+                            umma_tf32(d_tmem, a_hi + adv_a, b_hi + adv_b, kIdesc, 1u);
                         } else {
-                            umma_tf32(d_tmem, a_hi + adv, b_hi + adv, kIdesc, first);
+                            umma_tf32(d_tmem, a_hi + adv_a, b_hi + adv_b, kIdesc, first);
                         }
                     }
                     umma_commit(empty_bar(s));  // the stage is free once these MMAs have read it
@@ -543,15 +651,18 @@ EncodeTiledFn encode_tiled() {
     return fn;
 }
 
-// K-major plane [rows][kp] of f32, boxes of 32 floats x box_rows, 128-byte swizzle.
-CUtensorMap make_map(float* plane, int64_t rows, int64_t kp, int box_rows) {
+// Plane [rows][pitch] of f32 (pitch in floats, a multiple of 4), boxes of 32 floats x box_rows,
+// 128-byte swizzle.  K-major planes: pitch = Kp, rows = matrix rows, box_rows = tile rows.
+// MN-major planes: pitch = padded M or N, rows = batches * Kp, box_rows = 32 K-rows.
+CUtensorMap make_map(float* plane, int64_t rows, int64_t pitch, int box_rows, bool mn_major) {
     CUtensorMap m;
-    const cuuint64_t dims[2] = {static_cast<cuuint64_t>(kp), static_cast<cuuint64_t>(rows)};
-    const cuuint64_t strides[1] = {static_cast<cuuint64_t>(kp) * sizeof(float)};
+    const cuuint64_t dims[2] = {static_cast<cuuint64_t>(pitch), static_cast<cuuint64_t>(rows)};
+    const cuuint64_t strides[1] = {static_cast<cuuint64_t>(pitch) * sizeof(float)};
     const cuuint32_t box[2] = {BK, static_cast<cuuint32_t>(box_rows)};
     const cuuint32_t elem[2] = {1, 1};
     const CUresult rc = encode_tiled()(&m, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2, plane, dims, strides, box, elem,
-                                       CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                                       CU_TENSOR_MAP_INTERLEAVE_NONE,
+                                       mn_major ? CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B : CU_TENSOR_MAP_SWIZZLE_128B,
                                        CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     if (rc != CUDA_SUCCESS) {
         fail(B200_INTERNAL_ERROR, "cuTensorMapEncodeTiled failed with code " + std::to_string(rc));
@@ -561,19 +672,32 @@ CUtensorMap make_map(float* plane, int64_t rows, int64_t kp, int box_rows) {
 
 int64_t align_up(int64_t v, int64_t a) { return (v + a - 1) / a * a; }
 
-template <int BN, int STAGES>
-void launch_main(b200_ctx* ctx, bool three_pass, const CUtensorMap& ah, const CUtensorMap& al,
-                 const CUtensorMap& bh, const CUtensorMap& bl, const TcArgs& g, int grid) {
+template <int BN, int STAGES, bool THREE, bool A_MN, bool B_MN>
+void launch_one(b200_ctx* ctx, const CUtensorMap& ah, const CUtensorMap& al, const CUtensorMap& bh,
+                const CUtensorMap& bl, const TcArgs& g, int grid) {
     using S = Smem<BN, STAGES>;
-    if (three_pass) {
-        B200_CUDA_CHECK(cudaFuncSetAttribute(gemm_tc_kernel<BN, STAGES, true>,
-                                             cudaFuncAttributeMaxDynamicSharedMemorySize, S::kTotal));
-        gemm_tc_kernel<BN, STAGES, true><<<grid, kThreads, S::kTotal, ctx->stream>>>(ah, al, bh, bl, g);
-    } else {
-        B200_CUDA_CHECK(cudaFuncSetAttribute(gemm_tc_kernel<BN, STAGES, false>,
-                                             cudaFuncAttributeMaxDynamicSharedMemorySize, S::kTotal));
-        gemm_tc_kernel<BN, STAGES, false><<<grid, kThreads, S::kTotal, ctx->stream>>>(ah, al, bh, bl, g);
+    auto kernel = gemm_tc_kernel<BN, STAGES, THREE, A_MN, B_MN>;
+    B200_CUDA_CHECK(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, S::kTotal));
+    kernel<<<grid, kThreads, S::kTotal, ctx->stream>>>(ah, al, bh, bl, g);
+}
+
+template <int BN, int STAGES>
+void launch_main(b200_ctx* ctx, bool three_pass, bool a_mn, bool b_mn, const CUtensorMap& ah,
+                 const CUtensorMap& al, const CUtensorMap& bh, const CUtensorMap& bl, const TcArgs& g, int grid) {
+#define B200_TC_CASE(T, A, B)                                                     \
+    if (three_pass == T && a_mn == A && b_mn == B) {                              \
+        launch_one<BN, STAGES, T, A, B>(ctx, ah, al, bh, bl, g, grid);            \
+        return;                                                                   \
     }
+    B200_TC_CASE(true, false, false)
+    B200_TC_CASE(true, false, true)
+    B200_TC_CASE(true, true, false)
+    B200_TC_CASE(true, true, true)
+    B200_TC_CASE(false, false, false)
+    B200_TC_CASE(false, false, true)
+    B200_TC_CASE(false, true, false)
+    B200_TC_CASE(false, true, true)
+#undef B200_TC_CASE
 }
 
 }  // namespace
@@ -623,9 +747,20 @@ void gemm_tc(b200_ctx* ctx, const GemmProblem& p, bool three_pass) {
     int64_t kb_per_split = ceil_div(k_blocks, splits);
     splits = ceil_div(k_blocks, kb_per_split);
 
+    // An operand whose M (or N) axis is the contiguous one is consumed MN-major by the tensor
+    // core: its planes keep the source's [K][MN] layout (padded to [Kp][MN rounded up to 4]) and
+    // the split is a dense 128-bit pass.  Everything else becomes a K-major plane [MN][Kp].
+    auto dense16 = [](const float* ptr, int64_t s_other, int64_t sb0, int64_t sb1, bool bcast) {
+        return reinterpret_cast<uintptr_t>(ptr) % 16 == 0 && s_other % 4 == 0 &&
+               (bcast || (sb0 % 4 == 0 && sb1 % 4 == 0));
+    };
+    const bool a_mn = p.a_s[2] == 1 && p.a_s[3] != 1 && dense16(p.a, p.a_s[3], p.a_s[0], p.a_s[1], a_bcast);
+    const bool b_mn = p.b_s[3] == 1 && p.b_s[2] != 1 && dense16(p.b, p.b_s[2], p.b_s[0], p.b_s[1], b_bcast);
+    const int64_t mp = align_up(p.m, 4), np = align_up(p.n, 4);
+
     const int64_t planes = three_pass ? 2 : 1;
-    const int64_t a_plane = align_up(nb_a * p.m * kp * 4, 1024);
-    const int64_t b_plane = align_up(nb_b * p.n * kp * 4, 1024);
+    const int64_t a_plane = align_up(nb_a * (a_mn ? kp * mp : p.m * kp) * 4, 1024);
+    const int64_t b_plane = align_up(nb_b * (b_mn ? kp * np : p.n * kp) * 4, 1024);
     const int64_t out_elems = batches * p.m * p.n;
     const int64_t partial_bytes = splits > 1 ? align_up(out_elems * splits * 4, 1024) : 0;
     char* ws = static_cast<char*>(
@@ -639,55 +774,72 @@ void gemm_tc(b200_ctx* ctx, const GemmProblem& p, bool three_pass) {
 
     // ---- operand split ----
     {
+        // `rows` x `k` below are the plane's (outer, inner) axes: (M, K) for a K-major plane,
+        // (K, M) for an MN-major one
         SplitArgs s{};
         s.src = p.a;
         s.hi = a_hi;
         s.lo = a_lo;
         s.b1 = a_bcast ? 1 : p.b1;
-        s.rows = p.m;
-        s.k = p.k;
-        s.kp = kp;
         s.s_b0 = a_bcast ? 0 : p.a_s[0];
         s.s_b1 = a_bcast ? 0 : p.a_s[1];
-        s.s_r = p.a_s[2];
-        s.s_k = p.a_s[3];
         s.n_batches = nb_a;
-        const int64_t t = (kp / 32) * ceil_div(p.m, 32) * nb_a;
-        {
-            ProfScope scope(ctx, "matmul.split_a");
-            split_kernel<<<grid_for(t, 1, 16), 256, 0, ctx->stream>>>(s);
+        if (a_mn) {
+            s.rows = p.k;
+            s.out_rows = kp;
+            s.k = p.m;
+            s.kp = mp;
+            s.s_r = p.a_s[3];
+            s.s_k = 1;
+        } else {
+            s.rows = s.out_rows = p.m;
+            s.k = p.k;
+            s.kp = kp;
+            s.s_r = p.a_s[2];
+            s.s_k = p.a_s[3];
         }
-        ctx->count_launch();
+        launch_split(ctx, s, "matmul.split_a");
         s.src = p.b;
         s.hi = b_hi;
         s.lo = b_lo;
         s.b1 = b_bcast ? 1 : p.b1;
-        s.rows = p.n;
         s.s_b0 = b_bcast ? 0 : p.b_s[0];
         s.s_b1 = b_bcast ? 0 : p.b_s[1];
-        s.s_r = p.b_s[3];
-        s.s_k = p.b_s[2];
         s.n_batches = nb_b;
-        const int64_t t2 = (kp / 32) * ceil_div(p.n, 32) * nb_b;
-        ProfScope scope(ctx, "matmul.split_b");
-        split_kernel<<<grid_for(t2, 1, 16), 256, 0, ctx->stream>>>(s);
-        ctx->count_launch();
+        if (b_mn) {
+            s.rows = p.k;
+            s.out_rows = kp;
+            s.k = p.n;
+            s.kp = np;
+            s.s_r = p.b_s[2];
+            s.s_k = 1;
+        } else {
+            s.rows = s.out_rows = p.n;
+            s.k = p.k;
+            s.kp = kp;
+            s.s_r = p.b_s[3];
+            s.s_k = p.b_s[2];
+        }
+        launch_split(ctx, s, "matmul.split_b");
         check_last_launch("matmul (operand split)");
     }
 
     // ---- main kernel ----
-    const CUtensorMap ah = make_map(a_hi, nb_a * p.m, kp, BM);
-    const CUtensorMap al = three_pass ? make_map(a_lo, nb_a * p.m, kp, BM) : ah;
-    const CUtensorMap bh = make_map(b_hi, nb_b * p.n, kp, bn);
-    const CUtensorMap bl = three_pass ? make_map(b_lo, nb_b * p.n, kp, bn) : bh;
+    auto map_of = [&](float* plane, bool mn, int64_t nb, int64_t extent, int64_t extent_p, int tile) {
+        return mn ? make_map(plane, nb * kp, extent_p, BK, true) : make_map(plane, nb * extent, kp, tile, false);
+    };
+    const CUtensorMap ah = map_of(a_hi, a_mn, nb_a, p.m, mp, BM);
+    const CUtensorMap al = three_pass ? map_of(a_lo, a_mn, nb_a, p.m, mp, BM) : ah;
+    const CUtensorMap bh = map_of(b_hi, b_mn, nb_b, p.n, np, bn);
+    const CUtensorMap bl = three_pass ? map_of(b_lo, b_mn, nb_b, p.n, np, bn) : bh;
 
     TcArgs g{};
     g.out = splits > 1 ? partial : p.out;
     g.m = p.m;
     g.n = p.n;
     g.batches = batches;
-    g.a_batch_rows = a_bcast ? 0 : p.m;
-    g.b_batch_rows = b_bcast ? 0 : p.n;
+    g.a_batch_rows = a_bcast ? 0 : (a_mn ? kp : p.m);  // plane rows between consecutive batches
+    g.b_batch_rows = b_bcast ? 0 : (b_mn ? kp : p.n);
     g.k_blocks = k_blocks;
     g.kb_per_split = kb_per_split;
     g.splits = static_cast<int>(splits);
@@ -695,15 +847,19 @@ void gemm_tc(b200_ctx* ctx, const GemmProblem& p, bool three_pass) {
     g.tiles_m = tiles_m;
     g.tiles_n = tiles_n;
     g.status = ctx->d_status;
-    const int grid = static_cast<int>(std::min<int64_t>(tiles * splits, ctx->prop.multiProcessorCount));
+    int sms = ctx->prop.multiProcessorCount;
+    if (ctx->in_grad_sync_span) {
+        sms = std::max(sms - ctx->comm_sms, sms / 2);  // leave room for the all-reduce kernels
+    }
+    const int grid = static_cast<int>(std::min<int64_t>(tiles * splits, sms));
     {
         ProfScope scope(ctx, three_pass ? "matmul.tcgen05_3xtf32" : "matmul.tcgen05_tf32");
         if (bn == 256) {
-            launch_main<256, 2>(ctx, three_pass, ah, al, bh, bl, g, grid);
+            launch_main<256, 2>(ctx, three_pass, a_mn, b_mn, ah, al, bh, bl, g, grid);
         } else if (bn == 128) {
-            launch_main<128, 3>(ctx, three_pass, ah, al, bh, bl, g, grid);
+            launch_main<128, 3>(ctx, three_pass, a_mn, b_mn, ah, al, bh, bl, g, grid);
         } else {
-            launch_main<64, 4>(ctx, three_pass, ah, al, bh, bl, g, grid);
+            launch_main<64, 4>(ctx, three_pass, a_mn, b_mn, ah, al, bh, bl, g, grid);
         }
     }
     ctx->count_launch();

@@ -5,6 +5,7 @@ the op parameter PODs (op.h:226-318) and a strided tensor description equal to
 """
 from __future__ import annotations
 
+import ctypes
 import enum
 import struct
 from dataclasses import dataclass, field
@@ -162,9 +163,8 @@ class NodeDesc:
         n.out = self.out.to_c()
         for i, s in enumerate(self.src):
             n.src[i] = s.to_c()
-        raw = bytes(self.params) + b"\0" * (_abi.PARAM_BYTES - len(self.params))
-        for i in range(_abi.PARAM_BYTES):
-            n.params[i] = raw[i]
+        if self.params:
+            ctypes.memmove(n.params, bytes(self.params), min(len(self.params), _abi.PARAM_BYTES))
         return n
 
 
