@@ -35,7 +35,7 @@ sys.path.insert(0, ROOT)
 SEED_DATA = 20260728
 # dram__bytes_read.sum + dram__bytes_write.sum of one launch of the tensor-core kernel,
 # from profiles/ (None until a capture of this kernel has been taken).
-TRAFFIC_BYTES_PER_LAUNCH = None
+TRAFFIC_BYTES_PER_LAUNCH = 4820527104  # 4.565 GB read + 0.256 GB written at 8192^3 (profiles/gemm_tc_3xtf32.md)
 
 
 def parse():
@@ -281,7 +281,8 @@ def run_b200(args, rank, local_rank, world):
         peak = pk["bf16_tflops"] / 2.0
         roofline = {"bound": "tensor", "kernel": main_label, "achieved": achieved, "peak": peak,
                     "unit": "TFLOP/s", "frac": achieved / peak,
-                    "traffic": TRAFFIC_BYTES_PER_LAUNCH, "avg_launch_ms": avg_ms,
+                    "traffic": TRAFFIC_BYTES_PER_LAUNCH if (size == 8192 and args.precision == "3xtf32") else None,
+                    "avg_launch_ms": avg_ms,
                     "tensor_pipe_tflops": achieved * passes, "tensor_pipe_frac": achieved * passes / peak,
                     "peak_source": f"{pk['source']}: bf16_tflops/2 (TF32 runs at half the bf16 rate)",
                     "note": "achieved counts the algorithmic 2*M*N*K once; 3xTF32 issues it three times on "

@@ -414,6 +414,12 @@ int b200_create(int cuda_ordinal, b200_ctx** out) {
         *ctx->h_status = 0;
         // VKML_B200_GEMM_PRECISION = 3xtf32 (default) | tf32 | fp32, read once per context:
         // the counterpart of the VKML_GEMM_* switches (vulkan_backend.cpp:2160-2178)
+        if (const char* e = std::getenv("VKML_B200_GEMM_BN")) {
+            ctx->gemm_bn_override = std::atoi(e);
+        }
+        if (const char* e = std::getenv("VKML_B200_HOIST_GRADIENTS")) {
+            ctx->hoist_gradients = std::atoi(e) != 0;
+        }
         if (const char* e = std::getenv("VKML_B200_COMM_SMS")) {
             const int v = std::atoi(e);
             if (v < 0 || v > 64) fail(B200_INVALID_ARGUMENT, "VKML_B200_COMM_SMS must be 0..64");
@@ -530,7 +536,62 @@ int b200_compute(b200_ctx* ctx, const b200_node* nodes, size_t n_nodes, uint32_t
                 is_sink[i] = consumed ? 0 : 1;
             }
         }
-        for (size_t i = 0; i < n_nodes; ++i) {
+        // Execution order.  Only dependency order is contractual (backend.h:34-45), and the
+        // executor's depth-first order puts every parameter gradient at the tail of the span.
+        // When gradients are exchanged, each sink is hoisted to just after the last node it
+        // reads from, so its all-reduce runs under the remaining backward work instead of
+        // after it.  Every node still computes the same values from the same inputs.
+        std::vector<size_t> order;
+        order.reserve(n_nodes);
+        if (!is_sink.empty() && ctx->hoist_gradients) {
+            std::vector<std::vector<size_t>> deps(n_nodes);
+            std::vector<size_t> pending;
+            auto bytes_of = [](const b200_tensor& t) {
+                size_t n = dtype_size(t.dtype);
+                for (int d = 0; d < t.ndim; ++d) n *= static_cast<size_t>(t.dims[d]);
+                return n;
+            };
+            for (size_t j = 0; j < n_nodes; ++j) {
+                if (!is_sink[j]) continue;
+                pending.push_back(j);
+                for (uint32_t k = 0; k < nodes[j].n_src && k < B200_MAX_SRC; ++k) {
+                    const char* p = static_cast<const char*>(nodes[j].src[k].data);
+                    for (size_t i = j; i-- > 0;) {  // latest earlier writer of that address
+                        if (is_view_or_leaf(nodes[i].op) || nodes[i].out.data == nullptr) continue;
+                        const char* lo = static_cast<const char*>(nodes[i].out.data);
+                        if (p >= lo && p < lo + bytes_of(nodes[i].out)) {
+                            deps[j].push_back(i);
+                            break;
+                        }
+                    }
+                }
+            }
+            std::vector<char> emitted(n_nodes, 0);
+            auto flush = [&] {
+                for (size_t q = 0; q < pending.size();) {
+                    const size_t j = pending[q];
+                    bool ready = true;
+                    for (size_t d : deps[j]) ready = ready && emitted[d];
+                    if (ready) {
+                        order.push_back(j);
+                        emitted[j] = 1;
+                        pending.erase(pending.begin() + static_cast<std::ptrdiff_t>(q));
+                    } else {
+                        ++q;
+                    }
+                }
+            };
+            flush();
+            for (size_t i = 0; i < n_nodes; ++i) {
+                if (is_sink[i]) continue;
+                order.push_back(i);
+                emitted[i] = 1;
+                flush();
+            }
+        } else {
+            for (size_t i = 0; i < n_nodes; ++i) order.push_back(i);
+        }
+        for (const size_t i : order) {
             const b200_node& node = nodes[i];
             if (is_view_or_leaf(node.op)) {
                 continue;  // resolved by the executor through aliasing (backend.h:34-45)

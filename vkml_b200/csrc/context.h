@@ -73,10 +73,15 @@ struct b200_ctx {
     size_t staging_bytes = 0;
 
     int gemm_precision = B200_GEMM_3XTF32;
+    int gemm_bn_override = 0;  // VKML_B200_GEMM_BN: force the N extent of the tensor-core tile (tuning aid)
     // SMs the persistent GEMM kernel leaves free while a span's gradients are being all-reduced,
-    // so the communication kernels always find room (VKML_B200_COMM_SMS, default 8).
-    int comm_sms = 8;
+    // so the communication kernels always find room (VKML_B200_COMM_SMS, default 0: measured no gain at 2 GPUs).
+    int comm_sms = 0;
+    // Hoist each gradient-producing node of a grad-sync span to just after its last input
+    // is produced, so its all-reduce overlaps the rest of backward (VKML_B200_HOIST_GRADIENTS).
+    bool hoist_gradients = true;
     bool in_grad_sync_span = false;
+    bool comm_pending = false;  // an all-reduce was issued in this span and has not been joined yet
 
     std::atomic<uint64_t> compute_calls{0}, kernel_launches{0}, nodes_computed{0}, comm_bytes{0};
 

@@ -93,6 +93,7 @@ static void all_reduce_mean(b200_ctx* ctx, void* data, size_t count) {
     nccl_check(nccl().AllReduce(data, data, count, kNcclFloat32, kNcclAvg, d->comm, d->comm_stream),
                "ncclAllReduce");
     d->pending = true;
+    ctx->comm_pending = true;
     ctx->comm_bytes.fetch_add(count * sizeof(float), std::memory_order_relaxed);
 }
 
@@ -142,6 +143,7 @@ void dist_join(b200_ctx* ctx) {
         B200_CUDA_CHECK(cudaStreamWaitEvent(ctx->stream, d->reduced, 0));
         d->pending = false;
     }
+    ctx->comm_pending = false;
 }
 
 void dist_destroy(b200_ctx* ctx) {
@@ -213,7 +215,11 @@ int b200_dist_init(b200_ctx* ctx, int rank, int world_size, const void* id) {
         ctx->dist = d;
         d->rank = rank;
         d->world = world_size;
-        B200_CUDA_CHECK(cudaStreamCreateWithFlags(&d->comm_stream, cudaStreamNonBlocking));
+        // highest priority: when SMs free up, the all-reduce's blocks are placed before the next
+        // compute blocks, so communication is never starved by a queue of GEMM tiles
+        int least = 0, greatest = 0;
+        B200_CUDA_CHECK(cudaDeviceGetStreamPriorityRange(&least, &greatest));
+        B200_CUDA_CHECK(cudaStreamCreateWithPriority(&d->comm_stream, cudaStreamNonBlocking, greatest));
         B200_CUDA_CHECK(cudaEventCreateWithFlags(&d->produced, cudaEventDisableTiming));
         B200_CUDA_CHECK(cudaEventCreateWithFlags(&d->reduced, cudaEventDisableTiming));
         NcclUniqueId uid;

@@ -730,9 +730,21 @@ void gemm_tc(b200_ctx* ctx, const GemmProblem& p, bool three_pass) {
     const int64_t nb_a = a_bcast ? 1 : batches;
     const int64_t nb_b = b_bcast ? 1 : batches;
 
+    // Tile width: 128x256 tiles are the most efficient per tile (measured 5.5 % better than two
+    // 128x128 tiles), but the persistent grid runs whole waves of 148 tiles, so the narrower
+    // tile wins whenever it wastes less of the last wave (M=2048, N=8192: 4 waves of 256-wide
+    // tiles against 7 half-cost waves of 128-wide ones).
     int bn = 64;
     if (p.n > 64) bn = 128;
-    if (p.n > 128 && p.m * p.n * batches >= int64_t(128) * 256 * kSmCount) bn = 256;
+    if (p.n > 128 && p.m * p.n * batches >= int64_t(128) * 256 * kSmCount) {
+        const int64_t tm = ceil_div(p.m, BM);
+        const double cost256 = double(ceil_div(tm * ceil_div(p.n, 256) * batches, kSmCount));
+        const double cost128 = double(ceil_div(tm * ceil_div(p.n, 128) * batches, kSmCount)) * 0.5275;
+        bn = cost128 < cost256 ? 128 : 256;
+    }
+    if (ctx->gemm_bn_override == 64 || ctx->gemm_bn_override == 128 || ctx->gemm_bn_override == 256) {
+        bn = ctx->gemm_bn_override;
+    }
     const int64_t tiles_m = ceil_div(p.m, BM);
     const int64_t tiles_n = ceil_div(p.n, bn);
     const int64_t tiles = tiles_m * tiles_n * batches;
@@ -848,7 +860,7 @@ void gemm_tc(b200_ctx* ctx, const GemmProblem& p, bool three_pass) {
     g.tiles_n = tiles_n;
     g.status = ctx->d_status;
     int sms = ctx->prop.multiProcessorCount;
-    if (ctx->in_grad_sync_span) {
+    if (ctx->in_grad_sync_span && ctx->comm_pending) {
         sms = std::max(sms - ctx->comm_sms, sms / 2);  // leave room for the all-reduce kernels
     }
     const int grid = static_cast<int>(std::min<int64_t>(tiles * splits, sms));
