@@ -440,6 +440,23 @@ def train_section(args, backend, rank, world, dist, barrier, max_over_ranks):
     records = backend.last_profile()
     backend.set_profiling(False)
     barrier()
+    comm_bytes = int(backend.stats()["comm_bytes"] / max(1, r.steps_run))
+    alone_ms = None
+    if world > 1 and comm_bytes:
+        # the same bytes all-reduced with nothing else on the GPU: the part of it that the
+        # step does not hide is ms_per_step(N) - ms_per_step(1)
+        buf = backend.allocate(comm_bytes)
+        for _ in range(2):
+            backend.dist_all_reduce_mean(buf.data, comm_bytes // 4)
+            backend.dist_wait()
+        barrier()
+        backend.timer_begin()
+        for _ in range(k):
+            backend.dist_all_reduce_mean(buf.data, comm_bytes // 4)
+            backend.dist_wait()
+        alone_ms = max_over_ranks(backend.timer_end()) / k
+        del buf
+        barrier()
     losses = [float(d.view(np.float32)[0]) for _, d in r.downloads if d.nbytes == 4]
     by_label = {}
     for label, t in records:
@@ -453,7 +470,7 @@ def train_section(args, backend, rank, world, dist, barrier, max_over_ranks):
            "gpu_launches_per_step": launches, "steps": k, "n_gpus": world,
            "parallelism": f"dp{world}: batch sharded, NCCL all-reduce of gradient sinks overlapped with backward"
                           if world > 1 else "single GPU",
-           "comm_bytes_per_step": backend.stats()["comm_bytes"] / max(1, r.steps_run),
+           "comm_bytes_per_step": comm_bytes, "all_reduce_alone_ms": alone_ms,
            "loss_first_last": [losses[0], losses[-1]] if losses else None,
            "device_ms_per_step_by_kernel": {a: round(b, 4) for a, b in top.items()}}
     backend.free_host(pin_x)

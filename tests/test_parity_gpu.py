@@ -234,6 +234,54 @@ def test_a_span_is_ordered(backend):
     assert st["kernel_launches"] > 0 and st["compute_calls"] > 0
 
 
+def test_operand_planes_are_shared_inside_a_span_only(backend):
+    """A matrix that feeds several tensor-core matmuls of one span (a layer's forward, its
+    input gradient and its weight gradient) is split into TF32 planes once: the results are
+    bit-identical to running each product in a span of its own, the split launches drop,
+    and nothing survives the span (the operand is overwritten between two spans)."""
+    from vkml_b200 import DeviceTensor, NodeDesc
+    rng = np.random.default_rng(31)
+    b, k, n = 256, 1000, 384          # 1000: not a multiple of the 32-wide padding
+    x = DeviceTensor.from_host(backend, rng.standard_normal((1, 1, b, k)).astype(np.float32))
+    w = DeviceTensor.from_host(backend, rng.standard_normal((1, 1, n, k)).astype(np.float32))
+    g = DeviceTensor.from_host(backend, rng.standard_normal((1, 1, b, n)).astype(np.float32))
+
+    def products():
+        y = DeviceTensor.empty(backend, (1, 1, b, n))
+        dx = DeviceTensor.empty(backend, (1, 1, b, k))
+        dw2 = DeviceTensor.empty(backend, (1, 1, k, n))
+        nodes = [NodeDesc(Op.MATMUL, y.desc, [x.desc, w.transpose(2, 3).desc]),    # forward: x W^T
+                 NodeDesc(Op.MATMUL, dx.desc, [g.desc, w.desc]),                    # input gradient: g W
+                 NodeDesc(Op.MATMUL, dw2.desc, [x.transpose(2, 3).desc, g.desc])]   # weight gradient: x^T g
+        return nodes, (y, dx, dw2)
+
+    nodes, outs = products()
+    before = backend.stats()["kernel_launches"]
+    backend.compute(nodes)
+    shared = [t.numpy() for t in outs]
+    launches_shared = backend.stats()["kernel_launches"] - before
+
+    nodes, outs = products()
+    before = backend.stats()["kernel_launches"]
+    for node in nodes:
+        backend.compute([node])
+    alone = [t.numpy() for t in outs]
+    launches_alone = backend.stats()["kernel_launches"] - before
+    for a, c in zip(shared, alone):
+        assert np.array_equal(a.view(np.uint32), c.view(np.uint32))
+    assert launches_alone - launches_shared == 3      # x, W and g are each split once instead of twice
+
+    # the same span again after W changed: a stale plane would reproduce the old product
+    w2 = rng.standard_normal((1, 1, n, k)).astype(np.float32)
+    backend.copy_from_host(w.storage, 0, w2)
+    nodes, outs = products()
+    backend.compute(nodes)
+    xh, gh = x.numpy()[0, 0].astype(np.float64), g.numpy()[0, 0].astype(np.float64)
+    np.testing.assert_allclose(outs[0].numpy()[0, 0], xh @ w2[0, 0].astype(np.float64).T, rtol=0, atol=2e-3)
+    np.testing.assert_allclose(outs[1].numpy()[0, 0], gh @ w2[0, 0].astype(np.float64), rtol=0, atol=2e-3)
+    np.testing.assert_allclose(outs[2].numpy()[0, 0], xh.T @ gh, rtol=0, atol=2e-3)
+
+
 def test_device_copies(backend):
     from vkml_b200 import DeviceTensor
     rng = np.random.default_rng(4)

@@ -190,7 +190,7 @@ bool cast_pair_ok(int from, int to) {
     }
 }
 
-void dispatch_matmul(b200_ctx* ctx, const b200_node& node) {
+GemmProblem matmul_problem(const b200_node& node) {
     const View out = make_view(node.out);
     const View a = make_view(node.src[0]);
     const View b = make_view(node.src[1]);
@@ -220,10 +220,40 @@ void dispatch_matmul(b200_ctx* ctx, const b200_node& node) {
         p.a_s[i] = a.stride[i];
         p.b_s[i] = b.stride[i];
     }
+    return p;
+}
+
+void dispatch_matmul(b200_ctx* ctx, const b200_node& node) {
+    const GemmProblem p = matmul_problem(node);
     if (ctx->gemm_precision != B200_GEMM_FP32 && gemm_tc_eligible(ctx, p)) {
         gemm_tc(ctx, p, ctx->gemm_precision == B200_GEMM_3XTF32);
     } else {
         gemm_simt(ctx, p);
+    }
+}
+
+// Counts, before a span runs, how often each operand matrix feeds a tensor-core matmul, so
+// that a matrix used twice (a weight in forward and backward, an activation in forward and in
+// the weight gradient) is split into its TF32 planes only once.
+void count_matmul_operands(b200_ctx* ctx, const b200_node* nodes, size_t n_nodes) {
+    if (ctx->gemm_precision == B200_GEMM_FP32 || !ctx->share_planes) return;
+    size_t matmuls = 0;
+    for (size_t i = 0; i < n_nodes; ++i) matmuls += nodes[i].op == B200_OP_MATMUL ? 1 : 0;
+    if (matmuls < 2) return;
+    for (size_t i = 0; i < n_nodes; ++i) {
+        const b200_node& node = nodes[i];
+        if (node.op != B200_OP_MATMUL || node.out.data == nullptr || node.n_src < 2 ||
+            node.src[0].data == nullptr || node.src[1].data == nullptr) {
+            continue;
+        }
+        try {
+            const GemmProblem p = matmul_problem(node);
+            if (p.b0 * p.b1 * p.m * p.n * p.k != 0 && gemm_tc_eligible(ctx, p)) {
+                gemm_tc_note_uses(ctx, p);
+            }
+        } catch (const Error&) {
+            // reported when the node is dispatched
+        }
     }
 }
 
@@ -408,14 +438,24 @@ int b200_create(int cuda_ordinal, b200_ctx** out) {
         B200_CUDA_CHECK(cudaStreamCreateWithFlags(&ctx->stream, cudaStreamNonBlocking));
         B200_CUDA_CHECK(cudaMalloc(&ctx->d_status, sizeof(uint32_t)));
         B200_CUDA_CHECK(cudaMemset(ctx->d_status, 0, sizeof(uint32_t)));
-        B200_CUDA_CHECK(cudaMalloc(&ctx->d_counters, sizeof(unsigned) * 4096));
-        B200_CUDA_CHECK(cudaMemset(ctx->d_counters, 0, sizeof(unsigned) * 4096));
+        B200_CUDA_CHECK(cudaMalloc(&ctx->d_counters, sizeof(unsigned) * (4096 + 64)));
+        B200_CUDA_CHECK(cudaMemset(ctx->d_counters, 0, sizeof(unsigned) * (4096 + 64)));
         B200_CUDA_CHECK(cudaMallocHost(&ctx->h_status, sizeof(uint32_t)));
         *ctx->h_status = 0;
         // VKML_B200_GEMM_PRECISION = 3xtf32 (default) | tf32 | fp32, read once per context:
         // the counterpart of the VKML_GEMM_* switches (vulkan_backend.cpp:2160-2178)
         if (const char* e = std::getenv("VKML_B200_GEMM_BN")) {
             ctx->gemm_bn_override = std::atoi(e);
+        }
+        if (const char* e = std::getenv("VKML_B200_GEMM_SCHEDULE")) {
+            const std::string v(e);
+            if (v == "static") ctx->gemm_schedule = 0;
+            else if (v == "dynamic") ctx->gemm_schedule = 1;
+            else if (v == "auto") ctx->gemm_schedule = -1;
+            else fail(B200_INVALID_ARGUMENT, "VKML_B200_GEMM_SCHEDULE must be auto, static or dynamic");
+        }
+        if (const char* e = std::getenv("VKML_B200_SHARE_PLANES")) {
+            ctx->share_planes = std::atoi(e) != 0;
         }
         if (const char* e = std::getenv("VKML_B200_HOIST_GRADIENTS")) {
             ctx->hoist_gradients = std::atoi(e) != 0;
@@ -508,8 +548,12 @@ int b200_compute(b200_ctx* ctx, const b200_node* nodes, size_t n_nodes, uint32_t
         ctx->in_grad_sync_span = grad_sync && ctx->dist != nullptr;
         struct SpanGuard {
             b200_ctx* c;
-            ~SpanGuard() { c->in_grad_sync_span = false; }
+            ~SpanGuard() {
+                c->in_grad_sync_span = false;
+                gemm_tc_end_span(c);
+            }
         } span_guard{ctx};
+        count_matmul_operands(ctx, nodes, n_nodes);
         std::vector<char> is_sink;
         if (grad_sync && ctx->grads.empty()) {
             is_sink.assign(n_nodes, 0);
@@ -614,6 +658,12 @@ int b200_compute(b200_ctx* ctx, const b200_node* nodes, size_t n_nodes, uint32_t
                 if (sn != 0 && node.src[s].data == nullptr) {
                     fail(B200_INVALID_ARGUMENT, "source " + std::to_string(s) + " has no storage");
                 }
+            }
+            if (!ctx->plane_cache.empty()) {
+                // cannot happen under the caller's contract (outputs are fresh buffers), but a
+                // plane must never outlive the data it was split from
+                gemm_tc_invalidate(ctx, node.out.data,
+                                   static_cast<const char*>(node.out.data) + numel * dtype_size(node.out.dtype));
             }
             dispatch_node(ctx, node);
             ctx->nodes_computed.fetch_add(1, std::memory_order_relaxed);

@@ -51,6 +51,31 @@ struct GradBuffer {
     size_t count;
 };
 
+// A matmul operand as it lies in memory: `rows` lines of `cols` elements, batched.  Two uses of
+// the same memory (a weight in forward and in the input-gradient product; an activation in
+// forward and, transposed, in the weight-gradient product) give the same key.
+struct PlaneKey {
+    const void* src;
+    int64_t v[8];  // rows, cols, row stride, column stride, inner batch extent, batch strides, batches
+    bool operator<(const PlaneKey& o) const {
+        if (src != o.src) return src < o.src;
+        for (int i = 0; i < 8; ++i) {
+            if (v[i] != o.v[i]) return v[i] < o.v[i];
+        }
+        return false;
+    }
+};
+
+// The TF32 hi / lo planes of one operand, kept for the rest of the compute span.
+struct PlaneEntry {
+    float* hi;
+    float* lo;
+    size_t bytes;
+    int uses_left;
+    const char* src_begin;
+    const char* src_end;
+};
+
 }  // namespace b200
 
 struct b200_ctx {
@@ -73,13 +98,18 @@ struct b200_ctx {
     size_t staging_bytes = 0;
 
     int gemm_precision = B200_GEMM_3XTF32;
+    // VKML_B200_GEMM_SCHEDULE: how the persistent GEMM's CTAs get their tiles. -1 (auto): a fixed
+    // round-robin walk, except in a gradient-synchronising span, where tiles are drawn from a
+    // counter so that CTAs sharing their SM with an all-reduce do not stretch the kernel; 0 / 1
+    // force the fixed / drawn order.
+    int gemm_schedule = -1;
     int gemm_bn_override = 0;  // VKML_B200_GEMM_BN: force the N extent of the tensor-core tile (tuning aid)
     // SMs the persistent GEMM kernel leaves free while a span's gradients are being all-reduced,
     // so the communication kernels always find room (VKML_B200_COMM_SMS, default 0: measured no gain at 2 GPUs).
     int comm_sms = 0;
     // Hoist each gradient-producing node of a grad-sync span to just after its last input
     // is produced, so its all-reduce overlaps the rest of backward (VKML_B200_HOIST_GRADIENTS).
-    bool hoist_gradients = true;
+    bool hoist_gradients = false;  // measured at 2 GPUs: 13.5 ms/step hoisted, 13.1 ms in the recorded order
     bool in_grad_sync_span = false;
     bool comm_pending = false;  // an all-reduce was issued in this span and has not been joined yet
 
@@ -96,6 +126,15 @@ struct b200_ctx {
 
     b200::DistState* dist = nullptr;
     std::vector<b200::GradBuffer> grads;
+
+    // Operand planes shared between the matmuls of ONE compute span (gemm_tc.cu).  A span's
+    // outputs are distinct live buffers, each written once by its producer before any reader
+    // (include/vkml/backend/api/backend.h:34-45), so a plane stays valid until the span ends.
+    std::map<b200::PlaneKey, int> plane_uses;               // counted before the span runs
+    std::map<b200::PlaneKey, b200::PlaneEntry> plane_cache;
+    size_t plane_cache_bytes = 0;
+    bool share_planes = true;  // VKML_B200_SHARE_PLANES=0 splits every operand afresh (A/B aid)
+    uint64_t plane_hits = 0;
 
     void* ensure_workspace(size_t nbytes);
     void count_launch(uint64_t n = 1) { kernel_launches.fetch_add(n, std::memory_order_relaxed); }

@@ -25,4 +25,11 @@ void gemm_simt(b200_ctx* ctx, const GemmProblem& p);
 bool gemm_tc_eligible(const b200_ctx* ctx, const GemmProblem& p);
 void gemm_tc(b200_ctx* ctx, const GemmProblem& p, bool three_pass);
 
+// Reuse of split operand planes inside one compute span: count the operands of every
+// tensor-core matmul before the span runs, drop planes whose source a node overwrites, and
+// release what is left when the span ends.
+void gemm_tc_note_uses(b200_ctx* ctx, const GemmProblem& p);
+void gemm_tc_invalidate(b200_ctx* ctx, const void* begin, const void* end);
+void gemm_tc_end_span(b200_ctx* ctx);
+
 }  // namespace b200

@@ -50,6 +50,7 @@ constexpr int BK = 32;          // floats per K-block = one 128-byte swizzle row
 constexpr int UMMA_K = 8;       // tf32
 constexpr int kThreads = 192;
 constexpr int kGroupM = 16;
+constexpr int kSchedRing = 4;  // published-but-unconsumed tile numbers per CTA
 constexpr uint64_t kWaitLimitNs = 4000000000ULL;  // 4 s
 
 // ---------------------------------------------------------------------------
@@ -360,6 +361,10 @@ struct TcArgs {
     int64_t split_stride;  // elements between partial planes
     int64_t tiles_m, tiles_n;
     uint32_t* status;
+    // Dynamic tile order: null = every CTA walks units blockIdx.x, +gridDim.x, ... ; otherwise a
+    // zeroed counter from which CTAs draw their units after the first, so a CTA that starts late
+    // or shares its SM with another kernel (an all-reduce) simply takes fewer tiles.
+    unsigned int* sched;
 };
 
 template <int BN, int STAGES>
@@ -389,6 +394,10 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a_hi, const __grid_consta
     auto empty_bar = [&](int s) { return bars + 8u * (STAGES + s); };
     auto acc_full = [&](int a) { return bars + 8u * (2 * STAGES + a); };
     auto acc_empty = [&](int a) { return bars + 8u * (2 * STAGES + 2 + a); };
+    // dynamic tile order: the producer publishes each next unit through a small ring
+    auto sched_full = [&](int r) { return bars + 8u * (2 * STAGES + 4 + r); };
+    auto sched_empty = [&](int r) { return bars + 8u * (2 * STAGES + 4 + kSchedRing + r); };
+    __shared__ int sched_ring[kSchedRing];
     __shared__ uint32_t tmem_base_slot;
     __shared__ int abort_flag;
 
@@ -404,6 +413,10 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a_hi, const __grid_consta
         for (int a = 0; a < 2; ++a) {
             mbar_init(acc_full(a), 1);
             mbar_init(acc_empty(a), 4);
+        }
+        for (int r = 0; r < kSchedRing; ++r) {
+            mbar_init(sched_full(r), 1);
+            mbar_init(sched_empty(r), 5);  // the MMA thread and the four epilogue warps
         }
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
@@ -435,12 +448,39 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a_hi, const __grid_consta
         tn = in_group / rows_in_group;
     };
 
+    const bool dynamic = g.sched != nullptr;
+    // unit after the t-th one of this CTA, for the MMA thread and the epilogue warps (-1: none)
+    auto next_unit = [&](int64_t u, uint32_t t, bool single_thread) -> int64_t {
+        if (!dynamic) {
+            u += gridDim.x;
+            return u < n_units ? u : -1;
+        }
+        const int r = t % kSchedRing;
+        if (!mbar_wait(sched_full(r), (t / kSchedRing) & 1, abort_p, g.status)) {
+            return -1;
+        }
+        const int v = *reinterpret_cast<volatile int*>(&sched_ring[r]);
+        if (!single_thread) {
+            __syncwarp();
+        }
+        if (single_thread || lane == 0) {
+            mbar_arrive(sched_empty(r));
+        }
+        return v;
+    };
+
     if (warp == 0) {
         // ---------------- TMA producer ----------------
         if (lane == 0) {
             uint32_t it = 0;
+            uint32_t t = 0;
             bool ok = true;
-            for (int64_t u = blockIdx.x; u < n_units && ok; u += gridDim.x) {
+            for (int64_t u = blockIdx.x; u >= 0 && u < n_units && ok; ++t) {
+                // draw the next unit now; its value is needed only after this tile's loads
+                int64_t nxt = u + gridDim.x;
+                if (dynamic) {
+                    nxt = int64_t(gridDim.x) + atomicAdd(g.sched, 1u);
+                }
                 int split;
                 int64_t batch, tm, tn;
                 decode(u, split, batch, tm, tn);
@@ -488,6 +528,15 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a_hi, const __grid_consta
                         load_b(stage + 2 * S::kABytes + S::kBBytes, &map_b_lo);
                     }
                 }
+                if (dynamic && ok) {
+                    const int r = t % kSchedRing;
+                    if (!mbar_wait(sched_empty(r), ((t / kSchedRing) & 1) ^ 1, abort_p, g.status)) {
+                        break;
+                    }
+                    *reinterpret_cast<volatile int*>(&sched_ring[r]) = nxt < n_units ? static_cast<int>(nxt) : -1;
+                    mbar_arrive(sched_full(r));
+                }
+                u = nxt;
             }
         }
     } else if (warp == 1) {
@@ -496,7 +545,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a_hi, const __grid_consta
             uint32_t it = 0;
             uint32_t tile_it = 0;
             bool ok = true;
-            for (int64_t u = blockIdx.x; u < n_units && ok; u += gridDim.x, ++tile_it) {
+            for (int64_t u = blockIdx.x; u >= 0 && u < n_units && ok; u = next_unit(u, tile_it, true), ++tile_it) {
                 int split;
                 int64_t batch, tm, tn;
                 decode(u, split, batch, tm, tn);
@@ -548,7 +597,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a_hi, const __grid_consta
         const int quarter = warp & 3;  // TMEM lanes 32*quarter .. +31 belong to this warp
         uint32_t tile_it = 0;
         bool ok = true;
-        for (int64_t u = blockIdx.x; u < n_units && ok; u += gridDim.x, ++tile_it) {
+        for (int64_t u = blockIdx.x; u >= 0 && u < n_units && ok; u = next_unit(u, tile_it, false), ++tile_it) {
             int split;
             int64_t batch, tm, tn;
             decode(u, split, batch, tm, tn);
@@ -700,6 +749,87 @@ void launch_main(b200_ctx* ctx, bool three_pass, bool a_mn, bool b_mn, const CUt
 #undef B200_TC_CASE
 }
 
+
+// One matmul operand, described by the matrix it is in memory.
+struct Operand {
+    PlaneKey key{};
+    bool mn = false;     // consumed MN-major (the M or N axis is the contiguous one)
+    bool cached = false;
+    int64_t nb = 1, rows = 0, cols = 0, rows_pad = 0, cols_pad = 0;
+    size_t plane_bytes = 0;
+    const char* src_begin = nullptr;
+    const char* src_end = nullptr;
+    float* hi = nullptr;
+    float* lo = nullptr;
+    SplitArgs split{};
+};
+
+// `s_mn` / `s_k` are the element strides along the operand's M (or N) axis and along K.
+// An operand whose M (or N) axis is contiguous keeps its [K][MN] layout and is consumed
+// MN-major; everything else becomes a K-major plane [MN][Kp].  Planes of densely readable
+// sources are padded to 32 rows and 32 columns of zeros, so the same plane serves a later use
+// of the same memory in the other orientation.
+Operand plan_operand(const float* ptr, int64_t s_b0, int64_t s_b1, int64_t s_mn, int64_t s_k, int64_t mn_extent,
+                     int64_t k_extent, bool bcast, const GemmProblem& p) {
+    Operand o;
+    const int64_t sb0 = bcast ? 0 : s_b0, sb1 = bcast ? 0 : s_b1;
+    const bool aligned = reinterpret_cast<uintptr_t>(ptr) % 16 == 0 && sb0 % 4 == 0 && sb1 % 4 == 0;
+    o.mn = s_mn == 1 && s_k != 1 && aligned && s_k % 4 == 0;
+    o.nb = bcast ? 1 : p.b0 * p.b1;
+    int64_t s_r, s_c;
+    if (o.mn) {
+        o.rows = k_extent;
+        o.cols = mn_extent;
+        s_r = s_k;
+        s_c = 1;
+    } else {
+        o.rows = mn_extent;
+        o.cols = k_extent;
+        s_r = s_mn;
+        s_c = s_k;
+    }
+    const bool dense = s_c == 1 && s_r % 4 == 0 && aligned;  // the 128-bit split kernel's condition
+    o.rows_pad = dense ? align_up(o.rows, 32) : o.rows;
+    o.cols_pad = align_up(o.cols, 32);
+    o.plane_bytes = static_cast<size_t>(align_up(o.nb * o.rows_pad * o.cols_pad * 4, 1024));
+    const int64_t b1 = bcast ? 1 : p.b1;
+    o.key.src = ptr;
+    const int64_t kv[8] = {o.rows, o.cols, s_r, s_c, b1, sb0, sb1, o.nb};
+    for (int i = 0; i < 8; ++i) o.key.v[i] = kv[i];
+    auto mag = [](int64_t v) { return v < 0 ? -v : v; };
+    const int64_t b0 = bcast ? 1 : p.b0;
+    const int64_t span = (b0 - 1) * mag(sb0) + (b1 - 1) * mag(sb1) + (o.rows - 1) * mag(s_r) + (o.cols - 1) * mag(s_c) + 1;
+    o.src_begin = reinterpret_cast<const char*>(ptr);
+    o.src_end = o.src_begin + span * 4;
+    o.split.src = ptr;
+    o.split.b1 = b1;
+    o.split.s_b0 = sb0;
+    o.split.s_b1 = sb1;
+    o.split.n_batches = o.nb;
+    o.split.rows = o.rows;
+    o.split.out_rows = o.rows_pad;
+    o.split.k = o.cols;
+    o.split.kp = o.cols_pad;
+    o.split.s_r = s_r;
+    o.split.s_k = s_c;
+    return o;
+}
+
+size_t plane_cache_limit(const b200_ctx* ctx) {
+    return std::min<size_t>(size_t(16) << 30, ctx->prop.totalGlobalMem / 8);
+}
+
+void release_use(b200_ctx* ctx, const Operand& o) {
+    if (!o.cached) return;
+    auto it = ctx->plane_cache.find(o.key);
+    if (it == ctx->plane_cache.end()) return;
+    if (--it->second.uses_left <= 0) {
+        ctx->alloc.release(it->second.hi);
+        ctx->plane_cache_bytes -= it->second.bytes;
+        ctx->plane_cache.erase(it);
+    }
+}
+
 }  // namespace
 
 bool gemm_tc_eligible(const b200_ctx* ctx, const GemmProblem& p) {
@@ -727,8 +857,6 @@ void gemm_tc(b200_ctx* ctx, const GemmProblem& p, bool three_pass) {
     const int64_t kp = align_up(p.k, BK);
     const bool a_bcast = (p.a_s[0] == 0 || p.b0 == 1) && (p.a_s[1] == 0 || p.b1 == 1);
     const bool b_bcast = (p.b_s[0] == 0 || p.b0 == 1) && (p.b_s[1] == 0 || p.b1 == 1);
-    const int64_t nb_a = a_bcast ? 1 : batches;
-    const int64_t nb_b = b_bcast ? 1 : batches;
 
     // Tile width: 128x256 tiles are the most efficient per tile (measured 5.5 % better than two
     // 128x128 tiles), but the persistent grid runs whole waves of 148 tiles, so the narrower
@@ -759,99 +887,90 @@ void gemm_tc(b200_ctx* ctx, const GemmProblem& p, bool three_pass) {
     int64_t kb_per_split = ceil_div(k_blocks, splits);
     splits = ceil_div(k_blocks, kb_per_split);
 
-    // An operand whose M (or N) axis is the contiguous one is consumed MN-major by the tensor
-    // core: its planes keep the source's [K][MN] layout (padded to [Kp][MN rounded up to 4]) and
-    // the split is a dense 128-bit pass.  Everything else becomes a K-major plane [MN][Kp].
-    auto dense16 = [](const float* ptr, int64_t s_other, int64_t sb0, int64_t sb1, bool bcast) {
-        return reinterpret_cast<uintptr_t>(ptr) % 16 == 0 && s_other % 4 == 0 &&
-               (bcast || (sb0 % 4 == 0 && sb1 % 4 == 0));
-    };
-    const bool a_mn = p.a_s[2] == 1 && p.a_s[3] != 1 && dense16(p.a, p.a_s[3], p.a_s[0], p.a_s[1], a_bcast);
-    const bool b_mn = p.b_s[3] == 1 && p.b_s[2] != 1 && dense16(p.b, p.b_s[2], p.b_s[0], p.b_s[1], b_bcast);
-    const int64_t mp = align_up(p.m, 4), np = align_up(p.n, 4);
-
-    const int64_t planes = three_pass ? 2 : 1;
-    const int64_t a_plane = align_up(nb_a * (a_mn ? kp * mp : p.m * kp) * 4, 1024);
-    const int64_t b_plane = align_up(nb_b * (b_mn ? kp * np : p.n * kp) * 4, 1024);
     const int64_t out_elems = batches * p.m * p.n;
-    const int64_t partial_bytes = splits > 1 ? align_up(out_elems * splits * 4, 1024) : 0;
-    char* ws = static_cast<char*>(
-        ctx->ensure_workspace(static_cast<size_t>(planes * (a_plane + b_plane) + partial_bytes + 1024)));
-    ws = reinterpret_cast<char*>(align_up(reinterpret_cast<int64_t>(ws), 1024));
-    float* a_hi = reinterpret_cast<float*>(ws);
-    float* a_lo = three_pass ? reinterpret_cast<float*>(ws + a_plane) : nullptr;
-    float* b_hi = reinterpret_cast<float*>(ws + planes * a_plane);
-    float* b_lo = three_pass ? reinterpret_cast<float*>(ws + planes * a_plane + b_plane) : nullptr;
-    float* partial = splits > 1 ? reinterpret_cast<float*>(ws + planes * (a_plane + b_plane)) : nullptr;
+    const size_t partial_bytes = splits > 1 ? static_cast<size_t>(align_up(out_elems * splits * 4, 1024)) : 0;
+    Operand oa = plan_operand(p.a, p.a_s[0], p.a_s[1], p.a_s[2], p.a_s[3], p.m, p.k, a_bcast, p);
+    Operand ob = plan_operand(p.b, p.b_s[0], p.b_s[1], p.b_s[3], p.b_s[2], p.n, p.k, b_bcast, p);
+    const bool a_mn = oa.mn, b_mn = ob.mn;
 
-    // ---- operand split ----
-    {
-        // `rows` x `k` below are the plane's (outer, inner) axes: (M, K) for a K-major plane,
-        // (K, M) for an MN-major one
-        SplitArgs s{};
-        s.src = p.a;
-        s.hi = a_hi;
-        s.lo = a_lo;
-        s.b1 = a_bcast ? 1 : p.b1;
-        s.s_b0 = a_bcast ? 0 : p.a_s[0];
-        s.s_b1 = a_bcast ? 0 : p.a_s[1];
-        s.n_batches = nb_a;
-        if (a_mn) {
-            s.rows = p.k;
-            s.out_rows = kp;
-            s.k = p.m;
-            s.kp = mp;
-            s.s_r = p.a_s[3];
-            s.s_k = 1;
-        } else {
-            s.rows = s.out_rows = p.m;
-            s.k = p.k;
-            s.kp = kp;
-            s.s_r = p.a_s[2];
-            s.s_k = p.a_s[3];
+    // ---- operand planes: from this span's cache, into it, or into the workspace ----
+    const size_t planes = three_pass ? 2 : 1;
+    auto from_cache = [&](Operand& o) {
+        auto it = ctx->plane_cache.find(o.key);
+        if (it == ctx->plane_cache.end()) return false;
+        o.hi = it->second.hi;
+        o.lo = it->second.lo;
+        o.cached = true;
+        ++ctx->plane_hits;
+        return true;
+    };
+    auto into_cache = [&](Operand& o) {
+        auto uses = ctx->plane_uses.find(o.key);
+        const size_t bytes = planes * o.plane_bytes;
+        if (uses == ctx->plane_uses.end() || uses->second < 2 ||
+            ctx->plane_cache_bytes + bytes > plane_cache_limit(ctx)) {
+            return false;
         }
-        launch_split(ctx, s, "matmul.split_a");
-        s.src = p.b;
-        s.hi = b_hi;
-        s.lo = b_lo;
-        s.b1 = b_bcast ? 1 : p.b1;
-        s.s_b0 = b_bcast ? 0 : p.b_s[0];
-        s.s_b1 = b_bcast ? 0 : p.b_s[1];
-        s.n_batches = nb_b;
-        if (b_mn) {
-            s.rows = p.k;
-            s.out_rows = kp;
-            s.k = p.n;
-            s.kp = np;
-            s.s_r = p.b_s[2];
-            s.s_k = 1;
-        } else {
-            s.rows = s.out_rows = p.n;
-            s.k = p.k;
-            s.kp = kp;
-            s.s_r = p.b_s[3];
-            s.s_k = p.b_s[2];
-        }
-        launch_split(ctx, s, "matmul.split_b");
+        char* block = static_cast<char*>(ctx->alloc.allocate(bytes));
+        o.hi = reinterpret_cast<float*>(block);
+        o.lo = three_pass ? reinterpret_cast<float*>(block + o.plane_bytes) : nullptr;
+        ctx->plane_cache[o.key] = PlaneEntry{o.hi, o.lo, bytes, uses->second, o.src_begin, o.src_end};
+        ctx->plane_cache_bytes += bytes;
+        o.cached = true;
+        return true;
+    };
+    const bool a_hit = from_cache(oa);
+    if (!a_hit) into_cache(oa);
+    // (B may be the very plane A just put there: x times its own transpose)
+    const bool b_hit = from_cache(ob);
+    if (!b_hit) into_cache(ob);
+    size_t ws_bytes = partial_bytes + 2048;
+    if (!oa.cached) ws_bytes += planes * oa.plane_bytes;
+    if (!ob.cached) ws_bytes += planes * ob.plane_bytes;
+    char* ws = static_cast<char*>(ctx->ensure_workspace(ws_bytes));
+    ws = reinterpret_cast<char*>(align_up(reinterpret_cast<int64_t>(ws), 1024));
+    auto from_workspace = [&](Operand& o) {
+        if (o.cached) return;
+        o.hi = reinterpret_cast<float*>(ws);
+        o.lo = three_pass ? reinterpret_cast<float*>(ws + o.plane_bytes) : nullptr;
+        ws += planes * o.plane_bytes;
+    };
+    from_workspace(oa);
+    from_workspace(ob);
+    float* partial = splits > 1 ? reinterpret_cast<float*>(ws) : nullptr;
+
+    if (!a_hit) {
+        oa.split.hi = oa.hi;
+        oa.split.lo = oa.lo;
+        launch_split(ctx, oa.split, "matmul.split_a");
+    }
+    if (!b_hit) {
+        ob.split.hi = ob.hi;
+        ob.split.lo = ob.lo;
+        launch_split(ctx, ob.split, "matmul.split_b");
+    }
+    if (!a_hit || !b_hit) {
         check_last_launch("matmul (operand split)");
     }
 
     // ---- main kernel ----
-    auto map_of = [&](float* plane, bool mn, int64_t nb, int64_t extent, int64_t extent_p, int tile) {
-        return mn ? make_map(plane, nb * kp, extent_p, BK, true) : make_map(plane, nb * extent, kp, tile, false);
+    // K-major plane: [batch][MN rows (padded)][Kp]; MN-major plane: [batch][Kp rows][MN padded]
+    auto map_of = [&](float* plane, const Operand& o, int tile) {
+        return o.mn ? make_map(plane, o.nb * o.rows_pad, o.cols_pad, BK, true)
+                    : make_map(plane, o.nb * o.rows_pad, o.cols_pad, tile, false);
     };
-    const CUtensorMap ah = map_of(a_hi, a_mn, nb_a, p.m, mp, BM);
-    const CUtensorMap al = three_pass ? map_of(a_lo, a_mn, nb_a, p.m, mp, BM) : ah;
-    const CUtensorMap bh = map_of(b_hi, b_mn, nb_b, p.n, np, bn);
-    const CUtensorMap bl = three_pass ? map_of(b_lo, b_mn, nb_b, p.n, np, bn) : bh;
+    const CUtensorMap ah = map_of(oa.hi, oa, BM);
+    const CUtensorMap al = three_pass ? map_of(oa.lo, oa, BM) : ah;
+    const CUtensorMap bh = map_of(ob.hi, ob, bn);
+    const CUtensorMap bl = three_pass ? map_of(ob.lo, ob, bn) : bh;
 
     TcArgs g{};
     g.out = splits > 1 ? partial : p.out;
     g.m = p.m;
     g.n = p.n;
     g.batches = batches;
-    g.a_batch_rows = a_bcast ? 0 : (a_mn ? kp : p.m);  // plane rows between consecutive batches
-    g.b_batch_rows = b_bcast ? 0 : (b_mn ? kp : p.n);
+    g.a_batch_rows = a_bcast ? 0 : oa.rows_pad;  // plane rows between consecutive batches
+    g.b_batch_rows = b_bcast ? 0 : ob.rows_pad;
     g.k_blocks = k_blocks;
     g.kb_per_split = kb_per_split;
     g.splits = static_cast<int>(splits);
@@ -864,6 +983,12 @@ void gemm_tc(b200_ctx* ctx, const GemmProblem& p, bool three_pass) {
         sms = std::max(sms - ctx->comm_sms, sms / 2);  // leave room for the all-reduce kernels
     }
     const int grid = static_cast<int>(std::min<int64_t>(tiles * splits, sms));
+    const bool dynamic = (ctx->gemm_schedule == 1 || (ctx->gemm_schedule < 0 && ctx->in_grad_sync_span)) &&
+                         tiles * splits > grid && tiles * splits < (int64_t(1) << 30);
+    if (dynamic) {
+        g.sched = ctx->d_counters + 4096;  // past the reductions' arrival counters
+        B200_CUDA_CHECK(cudaMemsetAsync(g.sched, 0, sizeof(unsigned int), ctx->stream));
+    }
     {
         ProfScope scope(ctx, three_pass ? "matmul.tcgen05_3xtf32" : "matmul.tcgen05_tf32");
         if (bn == 256) {
@@ -884,6 +1009,42 @@ void gemm_tc(b200_ctx* ctx, const GemmProblem& p, bool three_pass) {
         ctx->count_launch();
         check_last_launch("matmul (fold)");
     }
+    // the stream is in order: a plane released here is only reused by later work
+    release_use(ctx, oa);
+    release_use(ctx, ob);
+}
+
+void gemm_tc_note_uses(b200_ctx* ctx, const GemmProblem& p) {
+    const int64_t batches = p.b0 * p.b1;
+    (void)batches;
+    const bool a_bcast = (p.a_s[0] == 0 || p.b0 == 1) && (p.a_s[1] == 0 || p.b1 == 1);
+    const bool b_bcast = (p.b_s[0] == 0 || p.b0 == 1) && (p.b_s[1] == 0 || p.b1 == 1);
+    ++ctx->plane_uses[plan_operand(p.a, p.a_s[0], p.a_s[1], p.a_s[2], p.a_s[3], p.m, p.k, a_bcast, p).key];
+    ++ctx->plane_uses[plan_operand(p.b, p.b_s[0], p.b_s[1], p.b_s[3], p.b_s[2], p.n, p.k, b_bcast, p).key];
+}
+
+void gemm_tc_invalidate(b200_ctx* ctx, const void* begin, const void* end) {
+    if (ctx->plane_cache.empty()) return;
+    const char* lo = static_cast<const char*>(begin);
+    const char* hi = static_cast<const char*>(end);
+    for (auto it = ctx->plane_cache.begin(); it != ctx->plane_cache.end();) {
+        if (lo < it->second.src_end && it->second.src_begin < hi) {
+            ctx->alloc.release(it->second.hi);
+            ctx->plane_cache_bytes -= it->second.bytes;
+            it = ctx->plane_cache.erase(it);
+        } else {
+            ++it;
+        }
+    }
+}
+
+void gemm_tc_end_span(b200_ctx* ctx) {
+    for (auto& kv : ctx->plane_cache) {
+        ctx->alloc.release(kv.second.hi);
+    }
+    ctx->plane_cache.clear();
+    ctx->plane_uses.clear();
+    ctx->plane_cache_bytes = 0;
 }
 
 }  // namespace b200
