@@ -241,6 +241,31 @@ int b200_dist_wait(b200_ctx* ctx);
 int b200_dist_mark_grad(b200_ctx* ctx, void* data, size_t count);
 int b200_dist_clear_grads(b200_ctx* ctx);
 
+/* -- step tape (no counterpart in vkML today; its plan is to "re-submit the cached command
+ *    buffer" of an unchanged step, docs/ARCHITECTURE.md:565-569) --
+ *
+ * A tape replays the backend calls of whole training steps -- the allocations, frees,
+ * uploads, compute spans, batched device copies and downloads the framework's executor,
+ * Tensor::from_host/to_host and assign() make (src/dispatch/executor.cpp:105-144,
+ * src/core/tensor.cpp:101-111,178-201,397-425) -- from flat arrays of 64-bit words in which
+ * buffers are named by position (prologue allocation j, or allocation j of the step d steps
+ * back) instead of by address.  Each event becomes exactly one call of this ABI, in the
+ * recorded order, so a replayed step does the same device work as the framework's step at
+ * the host cost of native code.  The word format is documented in vkml_b200/csrc/tape.cu and
+ * produced by vkml_b200/tape.py from a recorded program.
+ *
+ * `lookback` is how many steps back a template may refer.  A prologue template allocates the
+ * buffers that live for the whole run (parameters, optimiser state); every other template is
+ * one step.  `uploads[i]` / `downloads[i]` are the host buffers of the template's i-th upload /
+ * download (a NULL upload leaves the device buffer as it is).  Spans recorded as gradient
+ * spans are computed with `grad_sync_flags` (0 or B200_COMPUTE_GRAD_SYNC). */
+typedef struct b200_tape b200_tape;
+int b200_tape_create(b200_ctx* ctx, int lookback, b200_tape** out);
+int b200_tape_add_template(b200_tape* tape, const int64_t* words, size_t n_words, int is_prologue, int* index);
+int b200_tape_run(b200_tape* tape, int index, const void* const* uploads, size_t n_uploads,
+                  void* const* downloads, size_t n_downloads, uint32_t grad_sync_flags);
+void b200_tape_destroy(b200_tape* tape);
+
 /* -- an entry point that allocates nothing (no counterpart in vkML: its backends
  *    always own an allocator) --
  *

@@ -169,7 +169,8 @@ def elementwise_cases(seed=1234, sizes=ELEMENT_SIZES, quick=False):
     for name in ("maximum", "minimum", "add", "mul", "sub"):
         yield Case(f"{name}/special", Op[name.upper()], [x, y], x.shape, DType.F32)
     # layouts: every stride pattern, rank 2 and rank 4
-    for shape in [(33, 65), (3, 5, 17, 9), (64, 128), (255, 257)]:
+    # (200, 132) and (3, 64, 68) mix whole 64x64 tiles (128-bit path) with ragged edge tiles
+    for shape in [(33, 65), (3, 5, 17, 9), (64, 128), (255, 257), (200, 132), (3, 64, 68)]:
         for tag_a, a in layouts(rng, shape):
             yield Case(f"relu/{shape}/{tag_a}", Op.RELU, [a], shape, DType.F32)
             yield Case(f"contiguous/{shape}/{tag_a}", Op.CONTIGUOUS, [a], shape, DType.F32)
@@ -183,6 +184,9 @@ def elementwise_cases(seed=1234, sizes=ELEMENT_SIZES, quick=False):
     col = np.broadcast_to(rng.standard_normal((64, 1)).astype(np.float32), (64, 128))
     scalar = np.broadcast_to(np.float32(0.25).reshape(()), (64, 128))
     yield Case("add/row-broadcast", Op.ADD, [a, row], a.shape, DType.F32)
+    a_t = np.ascontiguousarray(a.T).T
+    yield Case("add/transposed+row-broadcast", Op.ADD, [a_t, row], a.shape, DType.F32)
+    yield Case("mul/col-broadcast*transposed", Op.MUL, [col, a_t], a.shape, DType.F32)
     yield Case("mul/col-broadcast", Op.MUL, [a, col], a.shape, DType.F32)
     yield Case("div/scalar-broadcast", Op.DIV, [a, scalar], a.shape, DType.F32)
     yield Case("equal/both-broadcast", Op.EQUAL,
@@ -423,7 +427,12 @@ def movement_cases(seed=21, quick=False):
 
     geos = [(2, 3, 8, 8, (3, 3), (1, 1), (1, 1), (1, 1)), (2, 4, 9, 7, (3, 2), (2, 1), (1, 0), (1, 1)),
             (1, 2, 10, 10, (3, 3), (1, 1), (2, 2), (2, 2)), (3, 1, 5, 5, (1, 1), (1, 1), (0, 0), (1, 1)),
-            (2, 3, 6, 6, (2, 2), (2, 2), (0, 0), (1, 1)), (4, 3, 32, 32, (3, 3), (1, 1), (1, 1), (1, 1))]
+            (2, 3, 6, 6, (2, 2), (2, 2), (0, 0), (1, 1)), (4, 3, 32, 32, (3, 3), (1, 1), (1, 1), (1, 1)),
+            # dense, unit-stride geometries (planes grouped per block, 128-bit rows): odd plane counts,
+            # a 5x5 window with padding 2, no padding, a non-square window, an 8x8 plane
+            (5, 7, 16, 16, (3, 3), (1, 1), (1, 1), (1, 1)), (3, 5, 12, 20, (5, 5), (1, 1), (2, 2), (1, 1)),
+            (2, 3, 10, 12, (3, 5), (1, 1), (0, 0), (1, 1)), (9, 13, 8, 8, (3, 3), (1, 1), (1, 1), (1, 1)),
+            (1, 2, 64, 64, (3, 3), (1, 1), (1, 1), (1, 1))]
     if quick:
         geos = geos[:3]
     for n, c, h, w, k, s, p, d in geos:
@@ -435,7 +444,11 @@ def movement_cases(seed=21, quick=False):
             yield Case(f"col2im/{(n, c, h, w)}/k={k}s={s}p={p}d={d}/{tag}", Op.COL2IM, [cols], (n, c, h, w),
                        DType.F32, params)
     pools = [(2, 3, 8, 8, (2, 2), (2, 2), (0, 0), (1, 1)), (2, 2, 9, 9, (3, 3), (2, 2), (1, 1), (1, 1)),
-             (1, 4, 7, 6, (3, 2), (1, 1), (1, 1), (1, 1)), (4, 8, 32, 32, (2, 2), (2, 2), (0, 0), (1, 1))]
+             (1, 4, 7, 6, (3, 2), (1, 1), (1, 1), (1, 1)), (4, 8, 32, 32, (2, 2), (2, 2), (0, 0), (1, 1)),
+             # 128-bit 2x2 paths: width a multiple of 8; an odd height (a leftover row) keeps the forward
+             # vector path but sends the adjoint to the per-window kernel
+             (3, 5, 16, 24, (2, 2), (2, 2), (0, 0), (1, 1)), (2, 3, 9, 8, (2, 2), (2, 2), (0, 0), (1, 1)),
+             (1, 1, 2, 8, (2, 2), (2, 2), (0, 0), (1, 1))]
     for n, c, h, w, k, s, p, d in pools:
         oh, ow, params = unfold(n, c, h, w, k, s, p, d)
         x = rng.integers(0, 5, (n, c, h, w)).astype(np.float32)  # many ties: first-max rule matters

@@ -117,3 +117,90 @@ def test_param_packing_matches_the_cxx_structs():
     assert graph.clamp_params(None, 1.0)[8:10] == b"\x00\x01"
     assert np.frombuffer(graph.scaled_add_params(0.9, -0.1), dtype=np.float32).tolist() == [
         np.float32(0.9), np.float32(-0.1)]
+
+
+def test_tape_encoding_round_trips():
+    """vkml_b200.tape.encode against an independent decoder of the documented word format:
+    every recorded program decodes back to its own events."""
+    import glob
+    import os
+    import struct
+    from vkml_b200.replay import load_program
+    from vkml_b200.tape import encode
+
+    def ref(w, i):
+        where, j = int(w[i]), int(w[i + 1])
+        return (None if where == -2 else ["pro" if where == -1 else where, j]), i + 2
+
+    def tensor(w, i):
+        buf, i = ref(w, i)
+        off, dtype, nd = int(w[i]), int(w[i + 1]), int(w[i + 2])
+        dims = [int(v) for v in w[i + 3:i + 3 + nd]]
+        strides = [int(v) for v in w[i + 7:i + 7 + nd]]
+        return {"buf": buf, "off": off, "dtype": dtype, "dims": dims, "strides": strides}, i + 11
+
+    def decode(w):
+        out, i = [], 0
+        while i < len(w):
+            ev = int(w[i]); i += 1
+            if ev == 1:
+                out.append({"ev": "alloc", "bytes": int(w[i])}); i += 1
+            elif ev == 2:
+                buf, i = ref(w, i); out.append({"ev": "free", "buf": buf})
+            elif ev in (3, 6):
+                buf, i = ref(w, i)
+                out.append({"ev": "h2d" if ev == 3 else "d2h", "buf": buf, "off": int(w[i]), "bytes": int(w[i + 1])})
+                i += 3
+            elif ev == 4:
+                n, gs = int(w[i]), int(w[i + 1]); i += 2
+                nodes = []
+                for _ in range(n):
+                    op, n_src = int(w[i]), int(w[i + 1])
+                    params = struct.pack("<8q", *[int(v) for v in w[i + 2:i + 10]])
+                    i += 10
+                    o, i = tensor(w, i)
+                    srcs = []
+                    for _ in range(n_src):
+                        t, i = tensor(w, i); srcs.append(t)
+                    nodes.append({"op": op, "params": params, "out": o, "src": srcs})
+                out.append({"ev": "compute", "grad_sync": bool(gs), "nodes": nodes})
+            elif ev == 5:
+                n = int(w[i]); i += 1
+                copies = []
+                for _ in range(n):
+                    d, i = ref(w, i); doff = int(w[i]); i += 1
+                    s, i = ref(w, i); soff, nb = int(w[i]), int(w[i + 1]); i += 2
+                    copies.append([d, doff, s, soff, nb])
+                out.append({"ev": "d2d", "copies": copies})
+            elif ev == 7:
+                out.append({"ev": "sync"})
+            else:
+                raise AssertionError(ev)
+        return out
+
+    here = os.path.dirname(os.path.abspath(__file__))
+    paths = sorted(glob.glob(os.path.join(here, "golden", "programs", "*.json.gz")))
+    assert paths
+    for path in paths:
+        program = load_program(path)
+        for events in [program["prologue"]] + program["steps"]:
+            words, n_up, downs = encode(events)
+            got = decode(words)
+            assert len(got) == len(events)
+            assert n_up == sum(e["ev"] == "h2d" for e in events)
+            assert downs == [e["bytes"] for e in events if e["ev"] == "d2h"]
+            for g, e in zip(got, events):
+                assert g["ev"] == e["ev"]
+                if e["ev"] == "compute":
+                    assert g["grad_sync"] == bool(e.get("grad_sync")) and len(g["nodes"]) == len(e["nodes"])
+                    for gn, en in zip(g["nodes"], e["nodes"]):
+                        assert gn["op"] == en["op"] and gn["out"] == {k: en["out"][k] for k in gn["out"]}
+                        assert gn["params"] == bytes.fromhex(en["params"]).ljust(64, b"\0")
+                        assert gn["src"] == [{k: s[k] for k in ("buf", "off", "dtype", "dims", "strides")}
+                                             for s in en["src"]]
+                elif e["ev"] == "d2d":
+                    assert g["copies"] == [list(c) for c in e["copies"]]
+                else:
+                    for k in ("bytes", "buf", "off"):
+                        if k in e:
+                            assert g[k] == e[k], (k, g, e)

@@ -304,4 +304,28 @@ inline unsigned grid_for(int64_t work, int threads, int blocks_per_sm = 8) {
     return static_cast<unsigned>(g);
 }
 
+// Division of a 31-bit unsigned number by a divisor known at launch time: one multiply-high
+// and a shift instead of the ~20-instruction hardware sequence.  With p = 31 + ceil(log2 d)
+// and m = ceil(2^p / d), floor(n / d) == (n * m) >> p for every n < 2^31.
+struct FastDiv {
+    uint32_t d = 1, mul = 0, shr = 0;
+    FastDiv() = default;
+    explicit FastDiv(uint32_t divisor) : d(divisor) {
+        if (divisor > 1) {
+            uint32_t lg = 0;
+            while ((uint64_t(1) << lg) < divisor) ++lg;
+            const uint32_t p = 31 + lg;
+            mul = static_cast<uint32_t>(((uint64_t(1) << p) + divisor - 1) / divisor);
+            shr = p - 32;
+        }
+    }
+#ifdef __CUDACC__
+    __device__ __forceinline__ uint32_t div(uint32_t n) const { return d == 1 ? n : __umulhi(n, mul) >> shr; }
+    __device__ __forceinline__ void divmod(uint32_t n, uint32_t& q, uint32_t& r) const {
+        q = div(n);
+        r = n - q * d;
+    }
+#endif
+};
+
 }  // namespace b200

@@ -152,6 +152,230 @@ col2im_kernel(float* __restrict__ out, const float* __restrict__ cols, Strides4 
     out[int64_t(plane) * (w.image_h * w.image_w) + hw] = acc;
 }
 
+// ---------------------------------------------------------------------------
+// Dense fast paths of the convolution pipeline: contiguous [N,C,H,W] images and
+// [N, C*kh*kw, L] columns, unit stride and dilation, output rows a multiple of four wide.
+// A block owns `group` consecutive (n, c) planes, stages them in shared memory with
+// 128-bit loads and writes 128-bit vectors; all index arithmetic is 32-bit with
+// multiply-high divisions.  Same values in the same order as the generic kernels.
+// ---------------------------------------------------------------------------
+struct DenseGeo {
+    int h, w, ph, pw, oh, ow, kh, kw;
+    int padded_w, padded_plane;  // im2col: (w + 2 pw), (h + 2 ph) * padded_w
+    int group, planes;
+    int vec_in;                  // the staged source can be read as 128-bit vectors
+};
+
+template <int KH, int KW>
+__global__ void __launch_bounds__(kThreads)
+im2col_dense_kernel(float* __restrict__ out, const float* __restrict__ in, DenseGeo g, FastDiv div_w4,
+                    FastDiv div_w, FastDiv div_h, FastDiv div_l4, FastDiv div_ow) {
+    extern __shared__ __align__(16) float tile[];  // group x (h + 2 ph) x (w + 2 pw), zero border
+    const int kh = KH > 0 ? KH : g.kh, kw = KW > 0 ? KW : g.kw;
+    const int first = blockIdx.x * g.group;
+    const int count = min(g.group, g.planes - first);
+    const int plane = g.h * g.w;
+    for (int i = threadIdx.x; i < count * g.padded_plane; i += kThreads) {
+        tile[i] = 0.0F;
+    }
+    __syncthreads();
+    const float* src = in + int64_t(first) * plane;
+    if (g.vec_in) {
+        const int n4 = count * plane / 4;
+        for (int i = threadIdx.x; i < n4; i += kThreads) {
+            const float4 v = reinterpret_cast<const float4*>(src)[i];
+            uint32_t row, x4, pl, h;
+            div_w4.divmod(static_cast<uint32_t>(i), row, x4);  // row counts across the group's planes
+            div_h.divmod(row, pl, h);
+            float* d = tile + pl * g.padded_plane + (h + g.ph) * g.padded_w + g.pw + 4 * x4;
+            d[0] = v.x;
+            d[1] = v.y;
+            d[2] = v.z;
+            d[3] = v.w;
+        }
+    } else {
+        for (int i = threadIdx.x; i < count * plane; i += kThreads) {
+            uint32_t row, x, pl, h;
+            div_w.divmod(static_cast<uint32_t>(i), row, x);
+            div_h.divmod(row, pl, h);
+            tile[pl * g.padded_plane + (h + g.ph) * g.padded_w + g.pw + x] = src[i];
+        }
+    }
+    __syncthreads();
+    const int l = g.oh * g.ow;
+    const int l4 = l / 4;
+    float* dst = out + int64_t(first) * (kh * kw) * l;
+    for (int i = threadIdx.x; i < count * l4; i += kThreads) {
+        uint32_t pl, p4, oh, ow;
+        div_l4.divmod(static_cast<uint32_t>(i), pl, p4);
+        div_ow.divmod(4 * p4, oh, ow);
+        // tap (ki, kj) of output position (oh, ow) is padded-plane element (oh + ki, ow + kj)
+        const float* sp = tile + pl * g.padded_plane + oh * g.padded_w + ow;
+        float* o = dst + pl * (kh * kw) * l + 4 * p4;
+#pragma unroll
+        for (int ki = 0; ki < kh; ++ki) {
+#pragma unroll
+            for (int kj = 0; kj < kw; ++kj) {
+                const float* t = sp + ki * g.padded_w + kj;
+                *reinterpret_cast<float4*>(o + (ki * kw + kj) * l) = make_float4(t[0], t[1], t[2], t[3]);
+            }
+        }
+    }
+}
+
+template <int KH, int KW>
+__global__ void __launch_bounds__(kThreads)
+col2im_dense_kernel(float* __restrict__ out, const float* __restrict__ cols, DenseGeo g, FastDiv div_hw4,
+                    FastDiv div_w) {
+    extern __shared__ __align__(16) float tile[];  // group x (kh kw) x L: this block's slice of the columns
+    const int kh = KH > 0 ? KH : g.kh, kw = KW > 0 ? KW : g.kw;
+    const int kk = kh * kw;
+    const int l = g.oh * g.ow;
+    const int first = blockIdx.x * g.group;
+    const int count = min(g.group, g.planes - first);
+    const float4* src = reinterpret_cast<const float4*>(cols + int64_t(first) * kk * l);
+    const int n4 = count * kk * l / 4;
+    for (int i = threadIdx.x; i < n4; i += kThreads) {
+        reinterpret_cast<float4*>(tile)[i] = src[i];
+    }
+    __syncthreads();
+    const int hw = g.h * g.w;
+    const int hw4 = hw / 4;
+    float* dst = out + int64_t(first) * hw;
+    for (int i = threadIdx.x; i < count * hw4; i += kThreads) {
+        uint32_t pl, p4, h, x;
+        div_hw4.divmod(static_cast<uint32_t>(i), pl, p4);
+        div_w.divmod(4 * p4, h, x);
+        const float* t = tile + pl * kk * l;
+        float acc[4] = {0.0F, 0.0F, 0.0F, 0.0F};
+        // (ki, kj) order, as the pull loop of the CPU backend.  A tap outside the column
+        // image adds +0.0, which leaves a sum that started at +0.0 unchanged bit for bit.
+#pragma unroll
+        for (int ki = 0; ki < kh; ++ki) {
+            const int oh = static_cast<int>(h) + g.ph - ki;
+            const bool ok_h = oh >= 0 && oh < g.oh;
+#pragma unroll
+            for (int kj = 0; kj < kw; ++kj) {
+                const int ow0 = static_cast<int>(x) + g.pw - kj;
+                const float* r = t + (ki * kw + kj) * l + oh * g.ow + ow0;
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                    const bool ok = ok_h && ow0 + e >= 0 && ow0 + e < g.ow;
+                    float v = 0.0F;
+                    if (ok) {
+                        v = r[e];
+                    }
+                    acc[e] += v;
+                }
+            }
+        }
+        *reinterpret_cast<float4*>(dst + pl * hw + 4 * p4) = make_float4(acc[0], acc[1], acc[2], acc[3]);
+    }
+}
+
+// 2x2 pooling with stride 2 over dense planes whose width is a multiple of eight: one thread
+// per four windows, rows read as two 128-bit vectors, first strict maximum in (ki, kj) order.
+__global__ void __launch_bounds__(kThreads)
+max_pool2d_dense2_kernel(float* __restrict__ out, const float* __restrict__ in, int h, int w, int out_h,
+                         uint32_t items, FastDiv div_ow4, FastDiv div_oh, uint32_t* status) {
+    const uint32_t step = gridDim.x * kThreads;
+    const int out_w = w / 2;
+    for (uint32_t i = blockIdx.x * kThreads + threadIdx.x; i < items; i += step) {
+        uint32_t prow, ow4, plane, oh;
+        div_ow4.divmod(i, prow, ow4);   // prow = plane * out_h + oh
+        div_oh.divmod(prow, plane, oh);
+        const float* top = in + (int64_t(plane) * h + 2 * oh) * w + 8 * ow4;
+        float v[2][8];
+#pragma unroll
+        for (int ki = 0; ki < 2; ++ki) {
+            const float4 lo = *reinterpret_cast<const float4*>(top + ki * w);
+            const float4 hi = *reinterpret_cast<const float4*>(top + ki * w + 4);
+            v[ki][0] = lo.x; v[ki][1] = lo.y; v[ki][2] = lo.z; v[ki][3] = lo.w;
+            v[ki][4] = hi.x; v[ki][5] = hi.y; v[ki][6] = hi.z; v[ki][7] = hi.w;
+        }
+        float best[4];
+        bool missing = false;
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            float m = -INFINITY;
+            bool any = false;
+#pragma unroll
+            for (int ki = 0; ki < 2; ++ki) {
+#pragma unroll
+                for (int kj = 0; kj < 2; ++kj) {
+                    if (v[ki][2 * j + kj] > m) {
+                        m = v[ki][2 * j + kj];
+                        any = true;
+                    }
+                }
+            }
+            if (!any) {
+                missing = true;  // the CPU backend asserts here: no element above -inf
+                m = __int_as_float(0x7fc00000);
+            }
+            best[j] = m;
+        }
+        if (missing) {
+            atomicOr(status, kStatusInternal);
+        }
+        *reinterpret_cast<float4*>(out + int64_t(prow) * out_w + 4 * ow4) =
+            make_float4(best[0], best[1], best[2], best[3]);
+    }
+}
+
+// Its adjoint under the same conditions (image exactly 2 out_h x 2 out_w): the thread that
+// owns four windows writes their 2 x 8 patch, the gradient (as 0 + g) at each window's first
+// maximum and zero elsewhere.
+__global__ void __launch_bounds__(kThreads)
+max_pool2d_backward_dense2_kernel(float* __restrict__ out, const float* __restrict__ grad,
+                                  const float* __restrict__ in, int w, uint32_t items, FastDiv div_ow4) {
+    const uint32_t step = gridDim.x * kThreads;
+    const int out_w = w / 2;
+    for (uint32_t i = blockIdx.x * kThreads + threadIdx.x; i < items; i += step) {
+        uint32_t prow, ow4;
+        div_ow4.divmod(i, prow, ow4);   // prow = plane * out_h + oh; image row 2 * prow (h == 2 out_h)
+        const int64_t base = int64_t(prow) * 2 * w + 8 * ow4;
+        float v[2][8];
+#pragma unroll
+        for (int ki = 0; ki < 2; ++ki) {
+            const float4 lo = *reinterpret_cast<const float4*>(in + base + ki * w);
+            const float4 hi = *reinterpret_cast<const float4*>(in + base + ki * w + 4);
+            v[ki][0] = lo.x; v[ki][1] = lo.y; v[ki][2] = lo.z; v[ki][3] = lo.w;
+            v[ki][4] = hi.x; v[ki][5] = hi.y; v[ki][6] = hi.z; v[ki][7] = hi.w;
+        }
+        const float4 g4 = *reinterpret_cast<const float4*>(grad + int64_t(prow) * out_w + 4 * ow4);
+        const float g[4] = {0.0F + g4.x, 0.0F + g4.y, 0.0F + g4.z, 0.0F + g4.w};
+        float r[2][8];
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            float m = -INFINITY;
+            int best = -1;
+#pragma unroll
+            for (int ki = 0; ki < 2; ++ki) {
+#pragma unroll
+                for (int kj = 0; kj < 2; ++kj) {
+                    if (v[ki][2 * j + kj] > m) {
+                        m = v[ki][2 * j + kj];
+                        best = ki * 2 + kj;
+                    }
+                }
+            }
+#pragma unroll
+            for (int ki = 0; ki < 2; ++ki) {
+#pragma unroll
+                for (int kj = 0; kj < 2; ++kj) {
+                    r[ki][2 * j + kj] = (ki * 2 + kj == best) ? g[j] : 0.0F;
+                }
+            }
+        }
+#pragma unroll
+        for (int ki = 0; ki < 2; ++ki) {
+            *reinterpret_cast<float4*>(out + base + ki * w) = make_float4(r[ki][0], r[ki][1], r[ki][2], r[ki][3]);
+            *reinterpret_cast<float4*>(out + base + ki * w + 4) = make_float4(r[ki][4], r[ki][5], r[ki][6], r[ki][7]);
+        }
+    }
+}
+
 // First strict maximum of one window; -1 if nothing beat -inf.
 __device__ __forceinline__ int argmax_in_window(const float* plane, int64_t sh_, int64_t sw_, const Win& w,
                                                 int oh, int ow, float& best) {
@@ -482,6 +706,24 @@ int64_t index_stride(const View& idx) {
 
 }  // namespace
 
+bool aligned16(const void* p) { return reinterpret_cast<uintptr_t>(p) % 16 == 0; }
+
+// Planes per block of the dense convolution kernels: enough for two vector items per thread,
+// within the shared-memory allowance, and never so many that the grid cannot fill the machine.
+int planes_per_block(int64_t items_per_plane, int64_t bytes_per_plane, int64_t byte_limit, int64_t planes) {
+    int64_t group = ceil_div(int64_t(2) * kThreads, std::max<int64_t>(items_per_plane, 1));
+    group = std::min(group, std::max<int64_t>(byte_limit / std::max<int64_t>(bytes_per_plane, 1), 1));
+    group = std::min(group, std::max<int64_t>(planes / (int64_t(kSmCount) * 8), 1));
+    return static_cast<int>(std::max<int64_t>(group, 1));
+}
+
+constexpr int kDenseSmemLimit = 96 * 1024;
+
+template <typename K>
+void allow_large_smem(K kernel) {
+    B200_CUDA_CHECK(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kDenseSmemLimit));
+}
+
 void launch_movement(b200_ctx* ctx, const b200_node& node) {
     const View out = make_view(node.out);
     const int64_t total = out.numel;
@@ -505,6 +747,38 @@ void launch_movement(b200_ctx* ctx, const b200_node& node) {
                 fail(B200_SHAPE_ERROR, "im2col: geometry does not match the tensors");
             }
             if (positions >= kMax32 || rows >= kMax32) fail(B200_NOT_IMPLEMENTED, "im2col: extent too large");
+            {
+                const bool unit = w.sh == 1 && w.sw == 1 && w.dh == 1 && w.dw == 1;
+                const int64_t planes = n * w.channels;
+                const int64_t padded_w = w.image_w + 2 * int64_t(w.pw);
+                const int64_t padded_plane = (w.image_h + 2 * int64_t(w.ph)) * padded_w;
+                const int64_t taps = int64_t(w.kh) * w.kw;
+                if (unit && in.contiguous && w.out_w % 4 == 0 && aligned16(o) && w.ph >= 0 && w.pw >= 0 &&
+                    padded_plane * 4 <= 48 * 1024 && planes < kMax32 && taps * positions < (kMax32 >> 8)) {
+                    DenseGeo g{};
+                    g.h = w.image_h; g.w = w.image_w; g.ph = w.ph; g.pw = w.pw;
+                    g.oh = w.out_h; g.ow = w.out_w; g.kh = w.kh; g.kw = w.kw;
+                    g.padded_w = static_cast<int>(padded_w);
+                    g.padded_plane = static_cast<int>(padded_plane);
+                    g.planes = static_cast<int>(planes);
+                    g.group = planes_per_block(positions / 4, padded_plane * 4, 48 * 1024, planes);
+                    g.group = static_cast<int>(std::min<int64_t>(g.group, (kMax32 >> 2) / (taps * positions)));
+                    g.vec_in = w.image_w % 4 == 0 && aligned16(in.data);
+                    const unsigned grid = static_cast<unsigned>(ceil_div(planes, g.group));
+                    const size_t smem = size_t(g.group) * padded_plane * 4;
+                    const FastDiv div_w4(g.vec_in ? w.image_w / 4 : 1), div_w(w.image_w), div_h(w.image_h),
+                        div_l4(static_cast<uint32_t>(positions / 4)), div_ow(w.out_w);
+                    const float* src = reinterpret_cast<const float*>(in.data);
+                    if (w.kh == 3 && w.kw == 3) {
+                        im2col_dense_kernel<3, 3><<<grid, kThreads, smem, ctx->stream>>>(o, src, g, div_w4, div_w, div_h,
+                                                                                         div_l4, div_ow);
+                    } else {
+                        im2col_dense_kernel<0, 0><<<grid, kThreads, smem, ctx->stream>>>(o, src, g, div_w4, div_w, div_h,
+                                                                                         div_l4, div_ow);
+                    }
+                    break;
+                }
+            }
             const int block = block_for(positions);
             const int64_t chunks = ceil_div(positions, block);
             check_grid(n * w.channels * chunks, "im2col");
@@ -528,12 +802,41 @@ void launch_movement(b200_ctx* ctx, const b200_node& node) {
                 fail(B200_SHAPE_ERROR, "col2im: geometry does not match the tensors");
             }
             if (plane >= kMax32 || w.channels >= kMax32) fail(B200_NOT_IMPLEMENTED, "col2im: extent too large");
+            const float* src = reinterpret_cast<const float*>(cols.data);
+            const bool unit = w.sh == 1 && w.sw == 1 && w.dh == 1 && w.dw == 1;
+            {
+                const int64_t planes = n * w.channels;
+                const int64_t l = int64_t(w.out_h) * w.out_w;
+                const int64_t taps = int64_t(w.kh) * w.kw;
+                const int64_t plane_bytes = taps * l * 4;
+                if (unit && cols.contiguous && (taps * l) % 4 == 0 && w.image_w % 4 == 0 && aligned16(o) &&
+                    aligned16(src) && plane_bytes <= kDenseSmemLimit && planes < kMax32 && l > 0) {
+                    DenseGeo g{};
+                    g.h = w.image_h; g.w = w.image_w; g.ph = w.ph; g.pw = w.pw;
+                    g.oh = w.out_h; g.ow = w.out_w; g.kh = w.kh; g.kw = w.kw;
+                    g.planes = static_cast<int>(planes);
+                    g.group = planes_per_block(plane / 4, plane_bytes, 36 * 1024, planes);
+                    const unsigned grid = static_cast<unsigned>(ceil_div(planes, g.group));
+                    const size_t smem = size_t(g.group) * plane_bytes;
+                    const FastDiv div_hw4(static_cast<uint32_t>(plane / 4)), div_w(w.image_w);
+                    static const bool once = [] {
+                        allow_large_smem(col2im_dense_kernel<3, 3>);
+                        allow_large_smem(col2im_dense_kernel<0, 0>);
+                        return true;
+                    }();
+                    (void)once;
+                    if (w.kh == 3 && w.kw == 3) {
+                        col2im_dense_kernel<3, 3><<<grid, kThreads, smem, ctx->stream>>>(o, src, g, div_hw4, div_w);
+                    } else {
+                        col2im_dense_kernel<0, 0><<<grid, kThreads, smem, ctx->stream>>>(o, src, g, div_hw4, div_w);
+                    }
+                    break;
+                }
+            }
             const int block = block_for(plane);
             const int64_t chunks = ceil_div(plane, block);
             check_grid(n * w.channels * chunks, "col2im");
             const unsigned grid = static_cast<unsigned>(n * w.channels * chunks);
-            const float* src = reinterpret_cast<const float*>(cols.data);
-            const bool unit = w.sh == 1 && w.sw == 1 && w.dh == 1 && w.dw == 1;
             if (unit && w.kh == 3 && w.kw == 3) {
                 col2im_kernel<true, 3, 3><<<grid, block, 0, ctx->stream>>>(o, src, strides_of(cols), w,
                                                                            static_cast<int>(chunks));
@@ -567,6 +870,15 @@ void launch_movement(b200_ctx* ctx, const b200_node& node) {
             check_grid(out.dim[0] * out.dim[1] * chunks, "max_pool2d");
             const bool tiled = w.sh == w.kh && w.sw == w.kw && w.ph == 0 && w.pw == 0 && w.dh == 1 && w.dw == 1 &&
                                ((w.kh == 2 && w.kw == 2) || (w.kh == 3 && w.kw == 3));
+            if (tiled && w.kh == 2 && in.contiguous && w.image_w % 8 == 0 && aligned16(in.data) && aligned16(o) &&
+                total / 4 < kMax32 && out.dim[0] * out.dim[1] * w.image_h < kMax32) {
+                const uint32_t items = static_cast<uint32_t>(total / 4);
+                const FastDiv div_ow4(static_cast<uint32_t>(out.dim[3] / 4)), div_oh(static_cast<uint32_t>(out.dim[2]));
+                max_pool2d_dense2_kernel<<<grid_for(items, kThreads), kThreads, 0, ctx->stream>>>(
+                    o, reinterpret_cast<const float*>(in.data), w.image_h, w.image_w, static_cast<int>(out.dim[2]), items,
+                    div_ow4, div_oh, ctx->d_status);
+                break;
+            }
             if (tiled) {
                 const unsigned grid = static_cast<unsigned>(out.dim[0] * out.dim[1] * chunks);
                 const float* src = reinterpret_cast<const float*>(in.data);
@@ -613,6 +925,15 @@ void launch_movement(b200_ctx* ctx, const b200_node& node) {
                                ((w.kh == 2 && w.kw == 2) || (w.kh == 3 && w.kw == 3));
             if (out.dim[1] >= kMax32 || int64_t(w.image_h) * w.image_w >= kMax32) {
                 fail(B200_NOT_IMPLEMENTED, "max_pool2d_backward: extent too large");
+            }
+            if (tiled && w.kh == 2 && in.contiguous && grad.contiguous && w.image_w % 8 == 0 && w.image_h % 2 == 0 &&
+                out_h * 2 == w.image_h && out_w * 2 == w.image_w && aligned16(src) && aligned16(g) && aligned16(o) &&
+                total / 16 < kMax32) {
+                const uint32_t items = static_cast<uint32_t>(planes * out_h * (out_w / 4));
+                const FastDiv div_ow4(static_cast<uint32_t>(out_w / 4));
+                max_pool2d_backward_dense2_kernel<<<grid_for(items, kThreads), kThreads, 0, ctx->stream>>>(
+                    o, g, src, w.image_w, items, div_ow4);
+                break;
             }
             if (tiled) {
                 const int cover_h = static_cast<int>(ceil_div(w.image_h, w.kh));
