@@ -463,7 +463,10 @@ def train_section(args, backend, rank, world, dist, barrier, max_over_ranks):
     by_label = {}
     for label, t in records:
         by_label[label] = by_label.get(label, 0.0) + t / k
-    top = dict(sorted(by_label.items(), key=lambda kv: -kv[1])[:8])
+    top = dict(sorted(by_label.items(), key=lambda kv: -kv[1]))
+    counts = {}
+    for label, _ in records:
+        counts[label] = counts.get(label, 0) + 1.0 / k
     out = {"workload": f"{desc}, per-GPU batch {batch}, fp32, cross-entropy, SGD momentum 0.9: the framework's "
                        f"recorded step ({args.train}) replayed by the library's step tape",
            "samples_per_s": batch * world * k / (dev_ms * 1e-3), "ms_per_step": dev_ms / k,
@@ -474,7 +477,8 @@ def train_section(args, backend, rank, world, dist, barrier, max_over_ranks):
                           if world > 1 else "single GPU",
            "comm_bytes_per_step": comm_bytes, "all_reduce_alone_ms": alone_ms,
            "loss_last": loss_last,
-           "device_ms_per_step_by_kernel": {a: round(b, 4) for a, b in top.items()}}
+           "device_ms_per_step_by_kernel": {a: round(b, 4) for a, b in top.items()},
+           "launches_per_step_by_kernel": {a: round(counts[a], 2) for a in top}}
     tape.close()
     backend.free_host(pin_x)
     backend.free_host(pin_y)
