@@ -49,6 +49,7 @@ def parse():
     ap.add_argument("--workload", default="gemm", choices=["gemm", "ops", "gemm-sweep"],
                     help="gemm: the contract line; ops: per-kernel HBM table of the memory-bound family; "
                          "gemm-sweep: every GEMM shape of the BASELINE sweep")
+    ap.add_argument("--no-graphs", action="store_true", help="train object: replay every step eagerly")
     ap.add_argument("--filter", default="", help="ops workload: substring of the case names to run")
     ap.add_argument("--train", default="mlp_wide_b2048",
                     help="recorded training step replayed for the secondary `train` object "
@@ -407,6 +408,9 @@ def train_section(args, backend, rank, world, dist, barrier, max_over_ranks):
     # The library's native step tape issues the recorded calls (one foreign call per step), so
     # the host side costs what the framework's C++ executor would, not a Python loop per node.
     tape = Tape(backend, program, grad_sync=world > 1)
+    # steady-state steps as captured CUDA graphs (single GPU; gradient-synchronising steps replay eagerly)
+    use_graphs = world == 1 and not args.no_graphs
+    tape.enable_graphs(use_graphs)
     tape.run_prologue(params)
     first = [pin_x.ctypes.data, pin_y.ctypes.data]
     for _ in range(len(program["steps"]) - 1):   # the recorded first steps differ from the steady state
@@ -414,8 +418,13 @@ def train_section(args, backend, rank, world, dist, barrier, max_over_ranks):
     steady = tape.template_for_step(tape.steps_run)
     with_uploads = tape.upload_ptrs(steady, first)
     resident = tape.upload_ptrs(steady, [None, None])
-    for _ in range(3):
+    # a graph is captured the second time a step's addresses come up, and the allocator cycles
+    # through at most six address sets for these programs: fourteen steps see every set twice
+    warm = 14 if use_graphs else 3
+    for _ in range(warm):
         tape.step_fast(with_uploads)
+    for _ in range(warm):
+        tape.step_fast(resident)
     backend.synchronize()
     barrier()
     k = max(3, args.train_steps)
@@ -476,7 +485,8 @@ def train_section(args, backend, rank, world, dist, barrier, max_over_ranks):
            "parallelism": f"dp{world}: batch sharded, NCCL all-reduce of gradient sinks overlapped with backward"
                           if world > 1 else "single GPU",
            "comm_bytes_per_step": comm_bytes, "all_reduce_alone_ms": alone_ms,
-           "loss_last": loss_last,
+           "loss_last": loss_last, "host_side": "library step tape" + (", CUDA graphs" if use_graphs else ""),
+           "tape": tape.stats(),
            "device_ms_per_step_by_kernel": {a: round(b, 4) for a, b in top.items()},
            "launches_per_step_by_kernel": {a: round(counts[a], 2) for a in top}}
     tape.close()

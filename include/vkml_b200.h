@@ -264,6 +264,14 @@ int b200_tape_create(b200_ctx* ctx, int lookback, b200_tape** out);
 int b200_tape_add_template(b200_tape* tape, const int64_t* words, size_t n_words, int is_prologue, int* index);
 int b200_tape_run(b200_tape* tape, int index, const void* const* uploads, size_t n_uploads,
                   void* const* downloads, size_t n_downloads, uint32_t grad_sync_flags);
+/* Graph mode: once the allocator hands a step the same device addresses as an earlier step
+ * (the steady state of training), the step's device work is captured from the stream into a
+ * CUDA graph and later steps with those addresses are one cudaGraphLaunch.  Same kernels, same
+ * order, same arguments as the eager replay.  Needs page-locked upload buffers at unchanged
+ * addresses (b200_alloc_host); anything else, profiling, and gradient-synchronising steps fall
+ * back to the eager replay by themselves.  A step then returns after its one synchronisation. */
+int b200_tape_enable_graphs(b200_tape* tape, int on);
+int b200_tape_stats(b200_tape* tape, uint64_t* steps, uint64_t* graph_launches, uint64_t* graph_captures);
 void b200_tape_destroy(b200_tape* tape);
 
 /* -- an entry point that allocates nothing (no counterpart in vkML: its backends

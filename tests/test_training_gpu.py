@@ -144,3 +144,64 @@ def test_the_native_tape_replays_what_the_python_replay_does(lib, backend):
     assert backend.stats()["driver_allocations"] == before
     assert np.isfinite(tape.downloads[0].view(np.float32)[0])
     tape.close()
+
+
+@pytest.mark.parametrize("name", ["mlp_784_128_10_b64", "cnn_reduced_b16", "mlp_wide_reduced_b128"])
+def test_graph_replay_is_bit_identical_to_eager_replay(backend, name):
+    """Steady-state steps launched as captured CUDA graphs give the same loss bits as the same
+    tape run eagerly, with fresh data in the page-locked upload buffers every step."""
+    import os
+    from vkml_b200.replay import load_program
+    from vkml_b200.tape import Tape
+    program = load_program(os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden", "programs",
+                                        name + ".json.gz"))
+    meta = program["meta"]
+    batch, steps = meta["batch"], 24
+    rng = np.random.default_rng(77)
+    if meta["model"] == "mlp":
+        widths = meta["widths"]
+        params = []
+        for fin, fout in zip(widths[:-1], widths[1:]):
+            bound = 1.0 / np.sqrt(fin)
+            params.append(rng.uniform(-bound, bound, (fout, fin)).astype(np.float32))
+            params.append(rng.uniform(-bound, bound, (fout,)).astype(np.float32))
+        x = rng.standard_normal((steps, batch, widths[0])).astype(np.float32)
+        classes = widths[-1]
+    else:
+        cin, hw, classes = meta["cin"], meta["hw"], meta["classes"]
+        feat = meta["c3"] * (hw // 8) ** 2
+        params = []
+        for cout, ci in ((meta["c1"], cin), (meta["c2"], meta["c1"]), (meta["c3"], meta["c2"])):
+            bound = 1.0 / np.sqrt(ci * 9)
+            params.append(rng.uniform(-bound, bound, (cout, ci, 3, 3)).astype(np.float32))
+            params.append(rng.uniform(-bound, bound, (cout,)).astype(np.float32))
+        bound = 1.0 / np.sqrt(feat)
+        params.append(rng.uniform(-bound, bound, (classes, feat)).astype(np.float32))
+        params.append(rng.uniform(-bound, bound, (classes,)).astype(np.float32))
+        x = rng.random((steps, batch, cin, hw, hw)).astype(np.float32)
+    y = rng.integers(0, classes, (steps, batch)).astype(np.int64)
+    pin_x, pin_y = backend.alloc_host(x[0].nbytes), backend.alloc_host(y[0].nbytes)
+
+    def run(graphs):
+        tape = Tape(backend, program)
+        tape.enable_graphs(graphs)
+        tape.run_prologue(params)
+        losses = []
+        for s in range(steps):
+            pin_x[:] = x[s].view(np.uint8).reshape(-1)
+            pin_y[:] = y[s].view(np.uint8).reshape(-1)
+            tape.step([pin_x.ctypes.data, pin_y.ctypes.data])
+            losses.append(tape.downloads[0].view(np.float32)[0].copy())
+        backend.synchronize()
+        stats = tape.stats()
+        tape.close()
+        return np.array(losses, dtype=np.float32), stats
+
+    eager, st_e = run(False)
+    graph, st_g = run(True)
+    assert st_e["graph_launches"] == 0
+    assert st_g["graph_launches"] >= steps // 2 and 1 <= st_g["graph_captures"] <= 8, st_g
+    assert np.all(np.isfinite(eager))
+    assert np.array_equal(eager.view(np.uint32), graph.view(np.uint32)), (eager, graph)
+    backend.free_host(pin_x)
+    backend.free_host(pin_y)

@@ -109,6 +109,8 @@ SYMBOLS = {
     "b200_tape_create": (C.c_int, [_P, C.c_int, C.POINTER(_P)]),
     "b200_tape_add_template": (C.c_int, [_P, C.POINTER(C.c_int64), C.c_size_t, C.c_int, C.POINTER(C.c_int)]),
     "b200_tape_run": (C.c_int, [_P, C.c_int, C.POINTER(_P), C.c_size_t, C.POINTER(_P), C.c_size_t, C.c_uint32]),
+    "b200_tape_enable_graphs": (C.c_int, [_P, C.c_int]),
+    "b200_tape_stats": (C.c_int, [_P, C.POINTER(C.c_uint64), C.POINTER(C.c_uint64), C.POINTER(C.c_uint64)]),
     "b200_tape_destroy": (None, [_P]),
     "b200_sum_columns_f32_noalloc": (C.c_int, [_P, C.c_int64, C.c_int64, C.c_int64, _P, _P, C.c_char_p, C.c_size_t]),
 }

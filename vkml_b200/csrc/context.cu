@@ -17,7 +17,7 @@ void check_last_launch(const char* what) {
 }
 
 ProfScope::ProfScope(b200_ctx* ctx, const char* label) : ctx_(ctx) {
-    if (!ctx->profiling) {
+    if (!ctx->profiling || ctx->capturing) {
         return;
     }
     ProfEntry e{};
@@ -80,19 +80,26 @@ void* CachingAllocator::allocate(size_t nbytes) {
     std::lock_guard<std::mutex> lock(mu_);
     void* ptr = nullptr;
     auto it = free_.lower_bound(size);
-    // accept a cached block up to 25 % larger than needed
+    // accept a cached block up to 25 % larger than needed; within a class the lowest address goes
+    // out first.  The allocator's state is then the SET of free blocks, with no memory of the
+    // order they were freed in, so a loop that allocates and frees the same shapes every
+    // iteration is handed the same addresses again after a few iterations (2 to 6 for the
+    // recorded training steps) -- which is what lets a step be replayed as a CUDA graph.
     if (it != free_.end() && it->first <= size + size / 4) {
-        ptr = it->second;
-        free_.erase(it);
+        ptr = *it->second.begin();
+        it->second.erase(it->second.begin());
+        if (it->second.empty()) free_.erase(it);
     } else {
         cudaError_t err = cudaMalloc(&ptr, size);
         if (err != cudaSuccess) {
             // give the cache back to the driver and try once more
             cudaGetLastError();
             for (auto& kv : free_) {
-                cudaFree(kv.second);
-                reserved -= kv.first;
-                sizes_.erase(kv.second);
+                for (void* block : kv.second) {
+                    cudaFree(block);
+                    reserved -= kv.first;
+                    sizes_.erase(block);
+                }
             }
             free_.clear();
             err = cudaMalloc(&ptr, size);
@@ -126,16 +133,18 @@ void CachingAllocator::release(void* ptr) {
     }
     in_use -= it->second;
     --live;
-    free_.emplace(it->second, ptr);
+    free_[it->second].insert(ptr);
     live_.erase(it);
 }
 
 void CachingAllocator::trim() {
     std::lock_guard<std::mutex> lock(mu_);
     for (auto& kv : free_) {
-        cudaFree(kv.second);
-        reserved -= kv.first;
-        sizes_.erase(kv.second);
+        for (void* block : kv.second) {
+            cudaFree(block);
+            reserved -= kv.first;
+            sizes_.erase(block);
+        }
     }
     free_.clear();
 }
@@ -373,12 +382,12 @@ void* b200_ctx::ensure_workspace(size_t nbytes) {
     // Work already queued may still be using the old buffer; the stream is
     // in-order, so freeing it through the stream-ordered cache is safe.
     if (workspace != nullptr) {
-        alloc.release(workspace);
+        scratch.release(workspace);
         workspace = nullptr;
         workspace_bytes = 0;
     }
     const size_t want = std::max(nbytes, size_t(8) << 20);
-    workspace = alloc.allocate(want);
+    workspace = scratch.allocate(want);
     workspace_bytes = want;
     return workspace;
 }
@@ -529,6 +538,7 @@ int b200_trim(b200_ctx* ctx) {
     return guarded(ctx, [&] {
         B200_CUDA_CHECK(cudaStreamSynchronize(ctx->stream));
         ctx->alloc.trim();
+        ctx->scratch.trim();
     });
 }
 
@@ -680,7 +690,7 @@ int b200_compute(b200_ctx* ctx, const b200_node* nodes, size_t n_nodes, uint32_t
         if (grad_sync) {
             dist_join(ctx);
         }
-        if (flags & B200_COMPUTE_SYNC) {
+        if ((flags & B200_COMPUTE_SYNC) && !ctx->capturing) {
             B200_CUDA_CHECK(cudaStreamSynchronize(ctx->stream));
         }
     });
@@ -768,12 +778,12 @@ const char* b200_last_error(b200_ctx* ctx) {
 
 int b200_get_stats(b200_ctx* ctx, b200_stats* out) {
     if (ctx == nullptr || out == nullptr) return B200_INVALID_ARGUMENT;
-    out->reserved_bytes = ctx->alloc.reserved;
+    out->reserved_bytes = ctx->alloc.reserved + ctx->scratch.reserved;  // both pools
     out->in_use_bytes = ctx->alloc.in_use;
     out->peak_in_use_bytes = ctx->alloc.peak;
     out->live_allocations = ctx->alloc.live;
     out->total_allocations = ctx->alloc.total;
-    out->driver_allocations = ctx->alloc.driver_allocs;
+    out->driver_allocations = ctx->alloc.driver_allocs + ctx->scratch.driver_allocs;
     out->compute_calls = ctx->compute_calls.load();
     out->kernel_launches = ctx->kernel_launches.load();
     out->nodes_computed = ctx->nodes_computed.load();

@@ -7,6 +7,7 @@
 #include <atomic>
 #include <map>
 #include <mutex>
+#include <set>
 #include <unordered_map>
 #include <vector>
 
@@ -20,7 +21,7 @@ namespace b200 {
 // context runs on ONE in-order stream, so a block that is freed and handed out
 // again is only ever touched by later work on the same stream: recycling needs
 // no events.  Blocks come from cudaMalloc in size classes and return to
-// per-size free lists; nothing goes back to the driver until trim().
+// per-size free lists (lowest address first); nothing goes back to the driver until trim().
 class CachingAllocator {
 public:
     void* allocate(size_t nbytes);
@@ -33,7 +34,7 @@ public:
 private:
     static size_t round_size(size_t n);
     std::mutex mu_;
-    std::multimap<size_t, void*> free_;           // size -> block
+    std::map<size_t, std::set<void*>> free_;      // size -> free blocks, lowest address handed out first
     std::unordered_map<void*, size_t> sizes_;     // every block ever handed out
     std::unordered_map<void*, size_t> live_;      // blocks currently out (ptr -> size)
 };
@@ -82,7 +83,11 @@ struct b200_ctx {
     int device = 0;
     cudaStream_t stream = nullptr;
     cudaDeviceProp prop{};
-    b200::CachingAllocator alloc;
+    b200::CachingAllocator alloc;    // the caller's buffers (b200_alloc / b200_free)
+    // The library's own scratch (workspace, shared operand planes) comes from a second pool, so it
+    // can never land on a block the caller has already freed on the host but whose last reader
+    // is not queued yet (a replay that books a step's frees before issuing its work does that).
+    b200::CachingAllocator scratch;
 
     uint32_t* d_status = nullptr;  // device status word (DeviceStatusBits)
     uint32_t* h_status = nullptr;  // pinned mirror
@@ -120,6 +125,7 @@ struct b200_ctx {
 
     cudaEvent_t timer_begin = nullptr, timer_end = nullptr;
     bool profiling = false;
+    bool capturing = false;  // the stream is being captured into a CUDA graph (tape.cu): no events, no waits
     uint32_t current_op = 0;
     std::vector<b200::ProfEntry> prof;
     std::vector<cudaEvent_t> event_pool;

@@ -824,7 +824,7 @@ void release_use(b200_ctx* ctx, const Operand& o) {
     auto it = ctx->plane_cache.find(o.key);
     if (it == ctx->plane_cache.end()) return;
     if (--it->second.uses_left <= 0) {
-        ctx->alloc.release(it->second.hi);
+        ctx->scratch.release(it->second.hi);
         ctx->plane_cache_bytes -= it->second.bytes;
         ctx->plane_cache.erase(it);
     }
@@ -911,7 +911,7 @@ void gemm_tc(b200_ctx* ctx, const GemmProblem& p, bool three_pass) {
             ctx->plane_cache_bytes + bytes > plane_cache_limit(ctx)) {
             return false;
         }
-        char* block = static_cast<char*>(ctx->alloc.allocate(bytes));
+        char* block = static_cast<char*>(ctx->scratch.allocate(bytes));
         o.hi = reinterpret_cast<float*>(block);
         o.lo = three_pass ? reinterpret_cast<float*>(block + o.plane_bytes) : nullptr;
         ctx->plane_cache[o.key] = PlaneEntry{o.hi, o.lo, bytes, uses->second, o.src_begin, o.src_end};
@@ -1029,7 +1029,7 @@ void gemm_tc_invalidate(b200_ctx* ctx, const void* begin, const void* end) {
     const char* hi = static_cast<const char*>(end);
     for (auto it = ctx->plane_cache.begin(); it != ctx->plane_cache.end();) {
         if (lo < it->second.src_end && it->second.src_begin < hi) {
-            ctx->alloc.release(it->second.hi);
+            ctx->scratch.release(it->second.hi);
             ctx->plane_cache_bytes -= it->second.bytes;
             it = ctx->plane_cache.erase(it);
         } else {
@@ -1040,7 +1040,7 @@ void gemm_tc_invalidate(b200_ctx* ctx, const void* begin, const void* end) {
 
 void gemm_tc_end_span(b200_ctx* ctx) {
     for (auto& kv : ctx->plane_cache) {
-        ctx->alloc.release(kv.second.hi);
+        ctx->scratch.release(kv.second.hi);
     }
     ctx->plane_cache.clear();
     ctx->plane_uses.clear();

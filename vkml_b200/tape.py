@@ -147,6 +147,16 @@ class Tape:
         self.downloads = bufs
         self.steps_run += 1
 
+    def enable_graphs(self, on: bool = True) -> None:
+        """Replay steady-state steps as captured CUDA graphs (see b200_tape_enable_graphs)."""
+        self.b._check(self._lib.b200_tape_enable_graphs(self._tape, 1 if on else 0), "tape_enable_graphs")
+
+    def stats(self) -> dict:
+        steps, launches, captures = C.c_uint64(), C.c_uint64(), C.c_uint64()
+        self.b._check(self._lib.b200_tape_stats(self._tape, C.byref(steps), C.byref(launches), C.byref(captures)),
+                      "tape_stats")
+        return {"steps": steps.value, "graph_launches": launches.value, "graph_captures": captures.value}
+
     def close(self) -> None:
         if self._tape:
             self._lib.b200_tape_destroy(self._tape)
