@@ -44,36 +44,35 @@ gemm_simt_kernel(GemmProblem p, float* __restrict__ dst, int64_t k_chunk, int64_
 
     float acc[4][4] = {};
 
+    // The next K-block travels from global memory to registers while the current one is
+    // multiplied out of shared memory, so the load latency is paid once per tile, not per block.
+    float ra[4], rb[4];
+    auto fetch = [&](int64_t k0) {
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            const int e = tid + 256 * j;
+            const int mm = a_k_fast ? (e >> 4) : (e & 63);
+            const int ka = a_k_fast ? (e & 15) : (e >> 6);
+            const int64_t gm = m0 + mm, gka = k0 + ka;
+            ra[j] = (gm < p.m && gka < k_end) ? A[gm * p.a_s[2] + gka * p.a_s[3]] : 0.0F;
+            const int nn = b_n_fast ? (e & 63) : (e >> 4);
+            const int kb = b_n_fast ? (e >> 6) : (e & 15);
+            const int64_t gn = n0 + nn, gkb = k0 + kb;
+            rb[j] = (gn < p.n && gkb < k_end) ? B[gkb * p.b_s[2] + gn * p.b_s[3]] : 0.0F;
+        }
+    };
+    fetch(k_begin);
     for (int64_t k0 = k_begin; k0 < k_end; k0 += BK) {
 #pragma unroll
         for (int j = 0; j < 4; ++j) {
             const int e = tid + 256 * j;
-            int mm, kk;
-            if (a_k_fast) {
-                kk = e & 15;
-                mm = e >> 4;
-            } else {
-                mm = e & 63;
-                kk = e >> 6;
-            }
-            const int64_t gm = m0 + mm, gk = k0 + kk;
-            As[kk][mm] = (gm < p.m && gk < k_end) ? A[gm * p.a_s[2] + gk * p.a_s[3]] : 0.0F;
-        }
-#pragma unroll
-        for (int j = 0; j < 4; ++j) {
-            const int e = tid + 256 * j;
-            int nn, kk;
-            if (b_n_fast) {
-                nn = e & 63;
-                kk = e >> 6;
-            } else {
-                kk = e & 15;
-                nn = e >> 4;
-            }
-            const int64_t gn = n0 + nn, gk = k0 + kk;
-            Bs[kk][nn] = (gn < p.n && gk < k_end) ? B[gk * p.b_s[2] + gn * p.b_s[3]] : 0.0F;
+            As[a_k_fast ? (e & 15) : (e >> 6)][a_k_fast ? (e >> 4) : (e & 63)] = ra[j];
+            Bs[b_n_fast ? (e >> 6) : (e & 15)][b_n_fast ? (e & 63) : (e >> 4)] = rb[j];
         }
         __syncthreads();
+        if (k0 + BK < k_end) {
+            fetch(k0 + BK);
+        }
 #pragma unroll
         for (int kk = 0; kk < BK; ++kk) {
             const float4 av = *reinterpret_cast<const float4*>(&As[kk][ty * 4]);
@@ -137,8 +136,10 @@ void gemm_simt(b200_ctx* ctx, const GemmProblem& p) {
         fail(B200_NOT_IMPLEMENTED, "matmul: too many output tiles for one launch");
     }
     int64_t splits = 1;
-    if (tiles < kSmCount && p.k >= 512) {
-        splits = std::min<int64_t>(ceil_div(2 * kSmCount, tiles), p.k / 128);
+    // few tiles and a long K: spread K over the idle SMs in chunks of at least 48 (three
+    // K-blocks, enough for the register prefetch to overlap anything)
+    if (tiles < kSmCount && p.k >= 192) {
+        splits = std::min<int64_t>(ceil_div(2 * kSmCount, tiles), p.k / 48);
         splits = std::max<int64_t>(1, std::min<int64_t>(splits, 64));
     }
     int64_t k_chunk = ceil_div(ceil_div(p.k, splits), BK) * BK;
