@@ -402,8 +402,8 @@ def matmul_tc_cases(seed=12):
     yield mk("nt", rnd(1, 1, m, k), t(rnd(1, 1, k, n)))
     yield mk("tn", t(rnd(1, 1, m, k)), rnd(1, 1, k, n))
     yield mk("tt", t(rnd(1, 1, m, k)), t(rnd(1, 1, k, n)))
-    yield mk("bn64", rnd(1, 1, 257, 777), rnd(1, 1, 777, 50))
-    yield mk("bn128", rnd(1, 1, 129, 513), rnd(1, 1, 513, 100))
+    yield mk("bn64", rnd(1, 1, 1025, 777), rnd(1, 1, 777, 50))
+    yield mk("bn128", rnd(1, 1, 513, 513), rnd(1, 1, 513, 100))
     yield mk("bn256", rnd(1, 1, 2100, 96), rnd(1, 1, 96, 2500))
     yield mk("k33", rnd(1, 1, 1024, 33), rnd(1, 1, 33, 1024))
     yield mk("split-k", rnd(1, 1, 128, 8192), rnd(1, 1, 8192, 128))

@@ -82,8 +82,8 @@ def test_matmul_default_precision(cuda, oracle, backend):
 def test_matmul_tensor_core_3xtf32(cuda, oracle, backend):
     """tcgen05 path with the 3xTF32 split: inside the fp32 backward-error bound AND
     inside the relative Frobenius bound 1e-5*sqrt(K) the path is specified to."""
-    before = backend.stats()["kernel_launches"]
     n = 0
+    backend.set_profiling(True)
     for case in cases.matmul_tc_cases():
         want = oracle.run(case.op, case.srcs, case.out_shape, case.out_dtype, case.params)
         got = cuda.run(case.op, case.srcs, case.out_shape, case.out_dtype, case.params)
@@ -92,8 +92,43 @@ def test_matmul_tensor_core_3xtf32(cuda, oracle, backend):
         assert rel < 1e-5 * np.sqrt(case.reduction_n), f"{case.name}: relative Frobenius error {rel:.3g}"
         assert rel < 1e-5, f"{case.name}: 3xTF32 should be near fp32-grade, got {rel:.3g}"
         n += 1
-    # every case took split + split + GEMM (+ fold): the tensor-core path really ran
-    assert backend.stats()["kernel_launches"] - before >= 3 * n
+    labels = [l for l, _ in backend.last_profile()]
+    backend.set_profiling(False)
+    # every case really ran on the tensor cores (operand planes or direct operands)
+    assert sum(l.startswith("matmul.tcgen05_3xtf32") for l in labels) == n, labels
+    assert not any(l == "matmul.fp32_simt" for l in labels)
+
+
+def test_matmul_tensor_core_both_operand_schemes(oracle, monkeypatch):
+    """The two ways operands reach the tensor cores -- TF32 planes written to HBM first, or fp32
+    tiles split inside the kernel -- each forced for every eligible shape: both inside the bounds
+    against the oracle, and bit-identical to each other (same split, same accumulation order)."""
+    import vkml_b200
+    from helpers import CudaImpl
+    results = {}
+    for operands in ("planes", "direct"):
+        monkeypatch.setenv("VKML_B200_GEMM_OPERANDS", operands)
+        b = vkml_b200.Backend(0)
+        impl = CudaImpl(b)
+        b.set_profiling(True)
+        outs = []
+        for case in cases.matmul_tc_cases():
+            want = oracle.run(case.op, case.srcs, case.out_shape, case.out_dtype, case.params)
+            got = impl.run(case.op, case.srcs, case.out_shape, case.out_dtype, case.params)
+            cases.check(case, got, want)
+            rel = np.linalg.norm((got.astype(np.float64) - want).ravel()) / np.linalg.norm(want.astype(np.float64).ravel())
+            assert rel < 1e-5, f"{case.name}: {rel:.3g}"
+            outs.append((case.name, got))
+        labels = [l for l, _ in b.last_profile() if l.startswith("matmul.tcgen05")]
+        b.set_profiling(False)
+        assert len(labels) == len(outs)
+        results[operands] = (outs, labels)
+    assert all(l == "matmul.tcgen05_3xtf32" for l in results["planes"][1])
+    # operands with a pitch that is not a multiple of 16 bytes cannot be read by TMA directly
+    direct_labels = results["direct"][1]
+    assert sum(l == "matmul.tcgen05_3xtf32_direct" for l in direct_labels) >= 10, direct_labels
+    for (name, a), (_, d) in zip(results["planes"][0], results["direct"][0]):
+        assert np.array_equal(a.view(np.uint32), d.view(np.uint32)), name
 
 
 def test_matmul_tensor_core_tf32_opt_in(cuda, oracle, backend):
@@ -234,12 +269,15 @@ def test_a_span_is_ordered(backend):
     assert st["kernel_launches"] > 0 and st["compute_calls"] > 0
 
 
-def test_operand_planes_are_shared_inside_a_span_only(backend):
-    """A matrix that feeds several tensor-core matmuls of one span (a layer's forward, its
-    input gradient and its weight gradient) is split into TF32 planes once: the results are
-    bit-identical to running each product in a span of its own, the split launches drop,
-    and nothing survives the span (the operand is overwritten between two spans)."""
+def test_operand_planes_are_shared_inside_a_span_only(monkeypatch):
+    """With the plane scheme: a matrix that feeds several tensor-core matmuls of one span (a
+    layer's forward, its input gradient and its weight gradient) is split into TF32 planes once:
+    the results are bit-identical to running each product in a span of its own, the split
+    launches drop, and nothing survives the span (the operand is overwritten between two spans)."""
+    import vkml_b200
     from vkml_b200 import DeviceTensor, NodeDesc
+    monkeypatch.setenv("VKML_B200_GEMM_OPERANDS", "planes")
+    backend = vkml_b200.Backend(0)
     rng = np.random.default_rng(31)
     b, k, n = 256, 1000, 384          # 1000: not a multiple of the 32-wide padding
     x = DeviceTensor.from_host(backend, rng.standard_normal((1, 1, b, k)).astype(np.float32))

@@ -456,6 +456,13 @@ int b200_create(int cuda_ordinal, b200_ctx** out) {
         if (const char* e = std::getenv("VKML_B200_GEMM_BN")) {
             ctx->gemm_bn_override = std::atoi(e);
         }
+        if (const char* e = std::getenv("VKML_B200_GEMM_OPERANDS")) {
+            const std::string v(e);
+            if (v == "planes") ctx->gemm_operands = 0;
+            else if (v == "direct") ctx->gemm_operands = 1;
+            else if (v == "auto") ctx->gemm_operands = -1;
+            else fail(B200_INVALID_ARGUMENT, "VKML_B200_GEMM_OPERANDS must be auto, planes or direct");
+        }
         if (const char* e = std::getenv("VKML_B200_GEMM_SCHEDULE")) {
             const std::string v(e);
             if (v == "static") ctx->gemm_schedule = 0;

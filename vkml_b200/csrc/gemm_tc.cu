@@ -49,6 +49,8 @@ constexpr int BM = 128;
 constexpr int BK = 32;          // floats per K-block = one 128-byte swizzle row
 constexpr int UMMA_K = 8;       // tf32
 constexpr int kThreads = 192;
+constexpr int kProducerThreads = 256;  // direct-operand variant: two groups of four warps
+constexpr int kThreadsDirect = kThreads + kProducerThreads;
 constexpr int kGroupM = 16;
 constexpr int kSchedRing = 4;  // published-but-unconsumed tile numbers per CTA
 constexpr uint64_t kWaitLimitNs = 4000000000ULL;  // 4 s
@@ -96,17 +98,20 @@ __device__ __forceinline__ uint64_t global_ns() {
 // or another role already aborted.
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag,
                                           uint32_t* status) {
-    if (mbar_try_wait(bar, parity)) {
-        return true;
-    }
-    const uint64_t start = global_ns();
+    // The clock is only consulted every 1024 polls (reading %globaltimer costs far more than a
+    // poll, and the converter warps wait here once per K-block), so the limit is the stated time
+    // plus at most 1024 polls.
+    uint64_t start = 0;
     uint32_t spins = 0;
     while (!mbar_try_wait(bar, parity)) {
         if ((++spins & 0x3ff) == 0) {
             if (*abort_flag != 0) {
                 return false;
             }
-            if (global_ns() - start > kWaitLimitNs) {
+            const uint64_t now = global_ns();
+            if (start == 0) {
+                start = now;
+            } else if (now - start > kWaitLimitNs) {
                 *abort_flag = 1;
                 atomicOr(status, kStatusWaitTimedOut);
                 return false;
@@ -121,6 +126,14 @@ __device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map
     asm volatile(
         "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
         ::"r"(dst), "l"(reinterpret_cast<uint64_t>(map)), "r"(bar), "r"(c0), "r"(c1)
+        : "memory");
+}
+
+__device__ __forceinline__ void tma_load_4d(uint32_t dst, const CUtensorMap* map, uint32_t bar, int c0, int c1,
+                                            int c2, int c3) {
+    asm volatile(
+        "cp.async.bulk.tensor.4d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5, %6}], [%2];"
+        ::"r"(dst), "l"(reinterpret_cast<uint64_t>(map)), "r"(bar), "r"(c0), "r"(c1), "r"(c2), "r"(c3)
         : "memory");
 }
 
@@ -224,6 +237,24 @@ __device__ __forceinline__ void split_tf32(float x, float& hi, float& lo) {
     }
     hi = fh;
     lo = fl;
+}
+
+// The same split on the integer pipe.  Conversion instructions issue at a quarter of the rate of
+// integer adds, and a K-block of a 128x256 tile needs 24576 of them; adding half a TF32 ulp to
+// the magnitude and clearing the 13 low bits is the same round-to-nearest, ties-away rounding
+// (a mantissa carry runs into the exponent as it should).  Infinity, NaN and a rounding that
+// overflows take the reference routine.
+__device__ __forceinline__ void split_tf32_fast(float x, float& hi, float& lo) {
+    const uint32_t b = __float_as_uint(x);
+    const uint32_t h = (b + 0x1000u) & 0xFFFFE000u;
+    if ((h << 1) >= 0xFF000000u) {  // x is infinite or NaN, or hi overflowed
+        split_tf32(x, hi, lo);
+        return;
+    }
+    const float fh = __uint_as_float(h);
+    const uint32_t r = __float_as_uint(x - fh);  // exact
+    hi = fh;
+    lo = __uint_as_float((r + 0x1000u) & 0xFFFFE000u);
 }
 
 struct SplitArgs {
@@ -367,6 +398,18 @@ struct TcArgs {
     unsigned int* sched;
 };
 
+// Direct-operand variant: TMA brings the fp32 operand tiles themselves into the `hi` slots of a
+// stage (through tensor maps over the caller's matrices: same swizzles, zero fill past the
+// edges), eight converter warps split them in place into hi and lo, and only then is the stage
+// handed to the MMA warp.  No plane ever exists in HBM: the kernel reads 4 bytes per operand
+// element instead of 8, and the split pre-pass (4 read + 8 written) disappears.  It costs
+// shared-memory bandwidth (one more read and write of every tile), so it is for products the
+// plane scheme would leave waiting on HBM, not for the large compute-bound ones.
+struct DirectArgs {
+    int64_t b1;          // inner batch extent
+    int a_bcast, b_bcast;
+};
+
 template <int BN, int STAGES>
 struct Smem {
     static constexpr int kABytes = BM * BK * 4;  // one A plane tile
@@ -376,11 +419,11 @@ struct Smem {
     static constexpr int kTotal = STAGES * kStageBytes + kBarrierBytes + 1024;  // + alignment slack
 };
 
-template <int BN, int STAGES, bool THREE_PASS, bool A_MN, bool B_MN>
-__global__ void __launch_bounds__(kThreads, 1)
+template <int BN, int STAGES, bool THREE_PASS, bool A_MN, bool B_MN, bool DIRECT>
+__global__ void __launch_bounds__(DIRECT ? kThreadsDirect : kThreads, 1)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a_hi, const __grid_constant__ CUtensorMap map_a_lo,
                const __grid_constant__ CUtensorMap map_b_hi, const __grid_constant__ CUtensorMap map_b_lo,
-               TcArgs g) {
+               TcArgs g, DirectArgs da) {
     using S = Smem<BN, STAGES>;
     constexpr uint32_t kTmemCols = 2 * BN < 32 ? 32 : 2 * BN;
     constexpr uint32_t kIdesc = make_idesc(BM, BN, A_MN, B_MN);
@@ -397,6 +440,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a_hi, const __grid_consta
     // dynamic tile order: the producer publishes each next unit through a small ring
     auto sched_full = [&](int r) { return bars + 8u * (2 * STAGES + 4 + r); };
     auto sched_empty = [&](int r) { return bars + 8u * (2 * STAGES + 4 + kSchedRing + r); };
+    auto raw_bar = [&](int s) { return bars + 8u * (2 * STAGES + 4 + 2 * kSchedRing + s); };  // direct: fp32 tile landed
     __shared__ int sched_ring[kSchedRing];
     __shared__ uint32_t tmem_base_slot;
     __shared__ int abort_flag;
@@ -407,8 +451,10 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a_hi, const __grid_consta
     if (threadIdx.x == 0) {
         abort_flag = 0;
         for (int s = 0; s < STAGES; ++s) {
-            mbar_init(full_bar(s), 1);
+            // TMA: one arrival with the byte count; direct: every thread of a producer group
+            mbar_init(full_bar(s), DIRECT ? kProducerThreads : 1);
             mbar_init(empty_bar(s), 1);
+            mbar_init(raw_bar(s), 1);
         }
         for (int a = 0; a < 2; ++a) {
             mbar_init(acc_full(a), 1);
@@ -469,7 +515,61 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a_hi, const __grid_consta
         return v;
     };
 
-    if (warp == 0) {
+    if (DIRECT && warp >= 6) {
+        // ---------------- converters: split the fp32 tiles of each stage in place ----------------
+        const int tc = static_cast<int>(threadIdx.x) - kThreads;  // 0 .. kProducerThreads-1
+        uint32_t it = 0;
+        bool ok = true;
+        for (int64_t u = blockIdx.x; u < n_units && ok; u += gridDim.x) {
+            int split;
+            int64_t batch, tm, tn;
+            decode(u, split, batch, tm, tn);
+            const int64_t kb0 = int64_t(split) * g.kb_per_split;
+            const int64_t kb1 = min(kb0 + g.kb_per_split, g.k_blocks);
+            for (int64_t kb = kb0; kb < kb1; ++kb, ++it) {
+                const int s = it % STAGES;
+                const uint32_t ph = (it / STAGES) & 1;
+                if (!mbar_wait(raw_bar(s), ph, abort_p, g.status)) {
+                    ok = false;
+                    break;
+                }
+                // The split is elementwise, so the tile's swizzle is irrelevant here: every float
+                // of a hi slot becomes hi in place and lo at the same offset of the lo slot.  All
+                // of a thread's vectors are loaded before any is stored, so the shared-memory
+                // latency is paid once per stage.
+                uint8_t* stage_ptr = smem_raw + (base - smem_u32(smem_raw)) + s * S::kStageBytes;
+                constexpr int NA = S::kABytes / 16 / kProducerThreads;
+                constexpr int NB = S::kBBytes / 16 / kProducerThreads;
+                static_assert(NA >= 1 && NB >= 1, "tile smaller than the converter group");
+                float4 v[NA + NB];
+                float4* a_hi = reinterpret_cast<float4*>(stage_ptr) + tc;
+                float4* a_lo = reinterpret_cast<float4*>(stage_ptr + S::kABytes) + tc;
+                float4* b_hi = reinterpret_cast<float4*>(stage_ptr + 2 * S::kABytes) + tc;
+                float4* b_lo = reinterpret_cast<float4*>(stage_ptr + 2 * S::kABytes + S::kBBytes) + tc;
+#pragma unroll
+                for (int j = 0; j < NA; ++j) v[j] = a_hi[j * kProducerThreads];
+#pragma unroll
+                for (int j = 0; j < NB; ++j) v[NA + j] = b_hi[j * kProducerThreads];
+#pragma unroll
+                for (int j = 0; j < NA + NB; ++j) {
+                    float4 h, l;
+                    split_tf32_fast(v[j].x, h.x, l.x);
+                    split_tf32_fast(v[j].y, h.y, l.y);
+                    split_tf32_fast(v[j].z, h.z, l.z);
+                    split_tf32_fast(v[j].w, h.w, l.w);
+                    float4* hi = j < NA ? a_hi + j * kProducerThreads : b_hi + (j - NA) * kProducerThreads;
+                    float4* lo = j < NA ? a_lo + j * kProducerThreads : b_lo + (j - NA) * kProducerThreads;
+                    *hi = h;
+                    if (THREE_PASS) {
+                        *lo = l;
+                    }
+                }
+                // generic-proxy stores must be visible to the tensor core's async-proxy reads
+                asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+                mbar_arrive(full_bar(s));
+            }
+        }
+    } else if (warp == 0) {
         // ---------------- TMA producer ----------------
         if (lane == 0) {
             uint32_t it = 0;
@@ -499,6 +599,33 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a_hi, const __grid_consta
                     }
                     const uint32_t stage = base + s * S::kStageBytes;
                     const int kc = static_cast<int>(kb * BK);
+                    if (DIRECT) {
+                        // fp32 tiles of the caller's matrices into the hi slots; coordinates are
+                        // (unit-stride axis, other axis, inner batch, outer batch)
+                        const uint32_t rbar = raw_bar(s);
+                        mbar_arrive_expect_tx(rbar, S::kABytes + S::kBBytes);
+                        const int64_t bo = batch / da.b1, bi = batch - bo * da.b1;
+                        const int a1 = da.a_bcast ? 0 : static_cast<int>(bi), a0 = da.a_bcast ? 0 : static_cast<int>(bo);
+                        const int b1c = da.b_bcast ? 0 : static_cast<int>(bi), b0c = da.b_bcast ? 0 : static_cast<int>(bo);
+                        if (A_MN) {
+#pragma unroll
+                            for (int atom = 0; atom < BM / 32; ++atom) {
+                                tma_load_4d(stage + atom * kMnAtomBytes, &map_a_hi, rbar, m0 + 32 * atom, kc, a1, a0);
+                            }
+                        } else {
+                            tma_load_4d(stage, &map_a_hi, rbar, kc, m0, a1, a0);
+                        }
+                        const uint32_t bdst = stage + 2 * S::kABytes;
+                        if (B_MN) {
+#pragma unroll
+                            for (int atom = 0; atom < BN / 32; ++atom) {
+                                tma_load_4d(bdst + atom * kMnAtomBytes, &map_b_hi, rbar, n0 + 32 * atom, kc, b1c, b0c);
+                            }
+                        } else {
+                            tma_load_4d(bdst, &map_b_hi, rbar, kc, n0, b1c, b0c);
+                        }
+                        continue;
+                    }
                     const uint32_t bar = full_bar(s);
                     mbar_arrive_expect_tx(bar, kStageTx);
                     auto load_a = [&](uint32_t dst, const CUtensorMap* map) {
@@ -721,21 +848,60 @@ CUtensorMap make_map(float* plane, int64_t rows, int64_t pitch, int box_rows, bo
 
 int64_t align_up(int64_t v, int64_t a) { return (v + a - 1) / a * a; }
 
+// The caller's own matrix as a 4-D tensor: (unit-stride axis, the other matrix axis, inner
+// batch, outer batch), f32, boxes of 32 floats x box_rows, zero fill outside.  A broadcast
+// batch axis is given extent 1 and always addressed at coordinate 0.
+CUtensorMap make_raw_map(const float* base, int64_t cols, int64_t rows, int64_t pitch, int64_t b1, int64_t s_b1,
+                         int64_t b0, int64_t s_b0, int box_rows, bool mn_major) {
+    CUtensorMap m;
+    const int64_t plane = std::max<int64_t>(rows * pitch, 4);
+    if (b1 <= 1 || s_b1 == 0) {
+        b1 = 1;
+        s_b1 = plane;
+    }
+    if (b0 <= 1 || s_b0 == 0) {
+        b0 = 1;
+        s_b0 = std::max(plane, s_b1 * b1);
+    }
+    const cuuint64_t dims[4] = {static_cast<cuuint64_t>(cols), static_cast<cuuint64_t>(rows),
+                                static_cast<cuuint64_t>(b1), static_cast<cuuint64_t>(b0)};
+    const cuuint64_t strides[3] = {static_cast<cuuint64_t>(pitch) * sizeof(float),
+                                   static_cast<cuuint64_t>(s_b1) * sizeof(float),
+                                   static_cast<cuuint64_t>(s_b0) * sizeof(float)};
+    const cuuint32_t box[4] = {BK, static_cast<cuuint32_t>(box_rows), 1, 1};
+    const cuuint32_t elem[4] = {1, 1, 1, 1};
+    const CUresult rc = encode_tiled()(&m, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, const_cast<float*>(base), dims, strides,
+                                       box, elem, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                                       mn_major ? CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B : CU_TENSOR_MAP_SWIZZLE_128B,
+                                       CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (rc != CUDA_SUCCESS) {
+        fail(B200_INTERNAL_ERROR, "cuTensorMapEncodeTiled (operand map) failed with code " + std::to_string(rc));
+    }
+    return m;
+}
+
 template <int BN, int STAGES, bool THREE, bool A_MN, bool B_MN>
 void launch_one(b200_ctx* ctx, const CUtensorMap& ah, const CUtensorMap& al, const CUtensorMap& bh,
-                const CUtensorMap& bl, const TcArgs& g, int grid) {
+                const CUtensorMap& bl, const TcArgs& g, int grid, const DirectArgs* direct) {
     using S = Smem<BN, STAGES>;
-    auto kernel = gemm_tc_kernel<BN, STAGES, THREE, A_MN, B_MN>;
+    if (direct != nullptr) {
+        auto kernel = gemm_tc_kernel<BN, STAGES, THREE, A_MN, B_MN, true>;
+        B200_CUDA_CHECK(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, S::kTotal));
+        kernel<<<grid, kThreadsDirect, S::kTotal, ctx->stream>>>(ah, al, bh, bl, g, *direct);
+        return;
+    }
+    auto kernel = gemm_tc_kernel<BN, STAGES, THREE, A_MN, B_MN, false>;
     B200_CUDA_CHECK(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, S::kTotal));
-    kernel<<<grid, kThreads, S::kTotal, ctx->stream>>>(ah, al, bh, bl, g);
+    kernel<<<grid, kThreads, S::kTotal, ctx->stream>>>(ah, al, bh, bl, g, DirectArgs{});
 }
 
 template <int BN, int STAGES>
 void launch_main(b200_ctx* ctx, bool three_pass, bool a_mn, bool b_mn, const CUtensorMap& ah,
-                 const CUtensorMap& al, const CUtensorMap& bh, const CUtensorMap& bl, const TcArgs& g, int grid) {
+                 const CUtensorMap& al, const CUtensorMap& bh, const CUtensorMap& bl, const TcArgs& g, int grid,
+                 const DirectArgs* direct = nullptr) {
 #define B200_TC_CASE(T, A, B)                                                     \
     if (three_pass == T && a_mn == A && b_mn == B) {                              \
-        launch_one<BN, STAGES, T, A, B>(ctx, ah, al, bh, bl, g, grid);            \
+        launch_one<BN, STAGES, T, A, B>(ctx, ah, al, bh, bl, g, grid, direct);    \
         return;                                                                   \
     }
     B200_TC_CASE(true, false, false)
@@ -754,6 +920,7 @@ void launch_main(b200_ctx* ctx, bool three_pass, bool a_mn, bool b_mn, const CUt
 struct Operand {
     PlaneKey key{};
     bool mn = false;     // consumed MN-major (the M or N axis is the contiguous one)
+    bool dense = false;  // unit stride along one axis, everything else 16-byte aligned
     bool cached = false;
     int64_t nb = 1, rows = 0, cols = 0, rows_pad = 0, cols_pad = 0;
     size_t plane_bytes = 0;
@@ -789,6 +956,7 @@ Operand plan_operand(const float* ptr, int64_t s_b0, int64_t s_b1, int64_t s_mn,
         s_c = s_k;
     }
     const bool dense = s_c == 1 && s_r % 4 == 0 && aligned;  // the 128-bit split kernel's condition
+    o.dense = dense;
     o.rows_pad = dense ? align_up(o.rows, 32) : o.rows;
     o.cols_pad = align_up(o.cols, 32);
     o.plane_bytes = static_cast<size_t>(align_up(o.nb * o.rows_pad * o.cols_pad * 4, 1024));
@@ -814,6 +982,14 @@ Operand plan_operand(const float* ptr, int64_t s_b0, int64_t s_b1, int64_t s_mn,
     o.split.s_k = s_c;
     return o;
 }
+
+// Whether reading the operands directly beats splitting them into planes first.  Measured: the
+// in-kernel split is bound by shared-memory traffic (the converter's loads and stores contend
+// with the tensor core's operand reads), 7.5 ms against 4.5 ms at 8192^3 and 1.09 ms against
+// 0.97 ms over the GEMMs of the CNN step; it wins only on isolated HBM-bound products whose
+// planes nobody else uses (conv2 forward alone: 0.100 ms against 0.164 ms).  So the automatic
+// choice is always planes, and the direct variant is an opt-in (VKML_B200_GEMM_OPERANDS=direct).
+bool direct_pays(const GemmProblem&, int64_t, int) { return false; }
 
 size_t plane_cache_limit(const b200_ctx* ctx) {
     return std::min<size_t>(size_t(16) << 30, ctx->prop.totalGlobalMem / 8);
@@ -881,7 +1057,9 @@ void gemm_tc(b200_ctx* ctx, const GemmProblem& p, bool three_pass) {
     // split K when the tiles alone cannot fill the machine
     int64_t splits = 1;
     if (tiles < kSmCount && k_blocks >= 16) {
-        splits = std::min<int64_t>(ceil_div(kSmCount, tiles), k_blocks / 8);
+        // as many K-slices as keep every unit in ONE wave of the persistent grid: rounding up
+        // instead (32 tiles x 5 slices = 160 units on 148 SMs) runs a second, nearly empty wave
+        splits = std::min<int64_t>(kSmCount / tiles, k_blocks / 8);
         splits = std::max<int64_t>(1, std::min<int64_t>(splits, 64));
     }
     int64_t kb_per_split = ceil_div(k_blocks, splits);
@@ -892,6 +1070,61 @@ void gemm_tc(b200_ctx* ctx, const GemmProblem& p, bool three_pass) {
     Operand oa = plan_operand(p.a, p.a_s[0], p.a_s[1], p.a_s[2], p.a_s[3], p.m, p.k, a_bcast, p);
     Operand ob = plan_operand(p.b, p.b_s[0], p.b_s[1], p.b_s[3], p.b_s[2], p.n, p.k, b_bcast, p);
     const bool a_mn = oa.mn, b_mn = ob.mn;
+
+    // ---- direct operands: no planes at all ----
+    const bool want_dynamic = ctx->gemm_schedule == 1 || (ctx->gemm_schedule < 0 && ctx->in_grad_sync_span);
+    if (ctx->gemm_operands != 0 && oa.dense && ob.dense && !want_dynamic &&
+        (ctx->gemm_operands == 1 || direct_pays(p, batches, bn))) {
+        float* partial = nullptr;
+        if (splits > 1) {
+            char* ws = static_cast<char*>(ctx->ensure_workspace(partial_bytes + 2048));
+            partial = reinterpret_cast<float*>(align_up(reinterpret_cast<int64_t>(ws), 1024));
+        }
+        DirectArgs da{};
+        da.b1 = p.b1;
+        da.a_bcast = a_bcast ? 1 : 0;
+        da.b_bcast = b_bcast ? 1 : 0;
+        // A: K-major = rows M with pitch a_s[2]; MN-major = rows K with pitch a_s[3]
+        const CUtensorMap raw_a =
+            a_mn ? make_raw_map(p.a, p.m, p.k, p.a_s[3], a_bcast ? 1 : p.b1, p.a_s[1], a_bcast ? 1 : p.b0, p.a_s[0], BK, true)
+                 : make_raw_map(p.a, p.k, p.m, p.a_s[2], a_bcast ? 1 : p.b1, p.a_s[1], a_bcast ? 1 : p.b0, p.a_s[0], BM, false);
+        const CUtensorMap raw_b =
+            b_mn ? make_raw_map(p.b, p.n, p.k, p.b_s[2], b_bcast ? 1 : p.b1, p.b_s[1], b_bcast ? 1 : p.b0, p.b_s[0], BK, true)
+                 : make_raw_map(p.b, p.k, p.n, p.b_s[3], b_bcast ? 1 : p.b1, p.b_s[1], b_bcast ? 1 : p.b0, p.b_s[0], bn, false);
+        TcArgs g{};
+        g.out = splits > 1 ? partial : p.out;
+        g.m = p.m;
+        g.n = p.n;
+        g.batches = batches;
+        g.k_blocks = k_blocks;
+        g.kb_per_split = kb_per_split;
+        g.splits = static_cast<int>(splits);
+        g.split_stride = out_elems;
+        g.tiles_m = tiles_m;
+        g.tiles_n = tiles_n;
+        g.status = ctx->d_status;
+        const int grid = static_cast<int>(std::min<int64_t>(tiles * splits, ctx->prop.multiProcessorCount));
+        {
+            ProfScope scope(ctx, three_pass ? "matmul.tcgen05_3xtf32_direct" : "matmul.tcgen05_tf32_direct");
+            if (bn == 256) {
+                launch_main<256, 2>(ctx, three_pass, a_mn, b_mn, raw_a, raw_a, raw_b, raw_b, g, grid, &da);
+            } else if (bn == 128) {
+                launch_main<128, 3>(ctx, three_pass, a_mn, b_mn, raw_a, raw_a, raw_b, raw_b, g, grid, &da);
+            } else {
+                launch_main<64, 4>(ctx, three_pass, a_mn, b_mn, raw_a, raw_a, raw_b, raw_b, g, grid, &da);
+            }
+        }
+        ctx->count_launch();
+        check_last_launch("matmul (tcgen05, direct operands)");
+        if (splits > 1) {
+            ProfScope scope(ctx, "matmul.fold");
+            fold_partials_kernel<<<grid_for(out_elems, 256), 256, 0, ctx->stream>>>(p.out, partial, out_elems,
+                                                                                  static_cast<int>(splits));
+            ctx->count_launch();
+            check_last_launch("matmul (fold)");
+        }
+        return;
+    }
 
     // ---- operand planes: from this span's cache, into it, or into the workspace ----
     const size_t planes = three_pass ? 2 : 1;
