@@ -773,11 +773,71 @@ static int compute_one(const b200_node* n) {
     }
 }
 
+/* F16 is storage, never arithmetic (kernels_elementwise.cpp:89-99): every kernel of the CPU
+ * backend widens Half to float on load, computes in float and narrows once, round-to-nearest-even,
+ * on store (reduce_generic<Half, ...> kernels_reduce.cpp:45-92, softmax_impl<Log, Half> :206-251,
+ * matmul_impl<Half> kernels_matmul.cpp:35-92, the movement kernels kernels_movement.cpp:685-709).
+ * So a node that touches F16 is the same node on widened copies with the result narrowed. */
+static void dense_like(const b200_tensor* t, int dtype, void* data, b200_tensor* out) {
+    *out = *t;
+    out->dtype = dtype;
+    out->data = data;
+    int64_t stride = (int64_t)esize(dtype);
+    for (int d = t->ndim - 1; d >= 0; --d) {
+        out->strides[d] = stride;
+        stride *= t->dims[d];
+    }
+}
+
+static int compute_f16(const b200_node* n) {
+    b200_node w = *n;
+    void* temps[B200_MAX_SRC + 1] = {0};
+    int rc = B200_OK;
+    for (uint32_t s = 0; s < n->n_src && rc == B200_OK; ++s) {
+        if (n->src[s].dtype != B200_F16) continue;
+        const int64_t cnt = numel(&n->src[s]);
+        temps[s] = malloc((size_t)(cnt > 0 ? cnt : 1) * 4);
+        b200_node c;
+        memset(&c, 0, sizeof c);
+        c.op = B200_OP_CAST;
+        c.n_src = 1;
+        c.src[0] = n->src[s];
+        dense_like(&n->src[s], B200_F32, temps[s], &c.out);
+        rc = k_cast(&c);
+        w.src[s] = c.out;
+    }
+    if (rc == B200_OK && n->out.dtype == B200_F16) {
+        const int64_t cnt = numel(&n->out);
+        temps[B200_MAX_SRC] = malloc((size_t)(cnt > 0 ? cnt : 1) * 4);
+        dense_like(&n->out, B200_F32, temps[B200_MAX_SRC], &w.out);
+    }
+    if (rc == B200_OK) rc = compute_one(&w);
+    if (rc == B200_OK && n->out.dtype == B200_F16) {
+        b200_node c;
+        memset(&c, 0, sizeof c);
+        c.op = B200_OP_CAST;
+        c.n_src = 1;
+        c.src[0] = w.out;
+        c.out = n->out;
+        rc = k_cast(&c);
+    }
+    for (int i = 0; i <= B200_MAX_SRC; ++i) free(temps[i]);
+    return rc;
+}
+
+static int touches_f16(const b200_node* n) {
+    if (n->op == B200_OP_CAST || n->op == B200_OP_FULL) return 0; /* handle F16 themselves */
+    if (n->out.dtype == B200_F16) return 1;
+    for (uint32_t s = 0; s < n->n_src; ++s)
+        if (n->src[s].dtype == B200_F16) return 1;
+    return 0;
+}
+
 /* Evaluate `n_nodes` descriptors in order on host memory. Returns a b200_status. */
 int vkml_oracle_compute(const b200_node* nodes, size_t n_nodes) {
     for (size_t i = 0; i < n_nodes; ++i) {
         if (is_view_or_leaf(nodes[i].op)) continue;
-        const int rc = compute_one(&nodes[i]);
+        const int rc = touches_f16(&nodes[i]) ? compute_f16(&nodes[i]) : compute_one(&nodes[i]);
         if (rc != B200_OK) return rc;
     }
     return B200_OK;

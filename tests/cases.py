@@ -87,6 +87,22 @@ def check(case: Case, got: np.ndarray, want: np.ndarray, exact_override: bool = 
         return
     kind, ulp, rtol, atol = POLICY["exact"] if exact_override else policy_for(case.op_name)
     floating = np.issubdtype(got.dtype, np.floating)
+    if got.dtype == np.float16 and kind != "exact":
+        # F16 is storage: both sides compute in f32 and narrow once, so an f32 difference inside the
+        # op's own policy can move the narrowed value by at most one f16 ulp (tests/python/test_f16.py
+        # in vkML holds f16 results to 1e-3)
+        nan_g, nan_w = np.isnan(got), np.isnan(want)
+        assert np.array_equal(nan_g, nan_w), f"{case.name}: NaN pattern differs"
+        gi = got.view(np.int16).astype(np.int64)
+        wi = want.view(np.int16).astype(np.int64)
+        gi = np.where(gi < 0, np.int64(0x8000) - gi, gi)
+        wi = np.where(wi < 0, np.int64(0x8000) - wi, wi)
+        bad = (np.abs(gi - wi) > 1) & ~nan_g
+        if np.any(bad):
+            idx = np.argwhere(bad)[0]
+            raise AssertionError(f"{case.name} [f16 ulp]: {int(bad.sum())}/{bad.size} differ; first at {tuple(idx)}: "
+                                 f"got {got[tuple(idx)]!r} want {want[tuple(idx)]!r}")
+        return
     nan_g = np.zeros(got.shape, dtype=bool)
     if floating:
         nan_g, nan_w = np.isnan(got), np.isnan(want)
@@ -332,6 +348,17 @@ def softmax_cases(seed=5, quick=False):
     big = np.full((2, 2000), 1000.0, dtype=np.float32)
     big[:, ::7] = 1002.0
     yield Case("softmax/large-logits-wide", Op.SOFTMAX, [big], big.shape, DType.F32, graph.axis_params(1))
+    if not quick:
+        # many long dense rows: the persistent kernel that prefetches the next row while one is processed
+        # (row lengths at both ends of its range, more rows than two per SM, a row of NaN and of -inf)
+        rng2 = np.random.default_rng(seed + 100)
+        for shape in ((300, 8200), (297, 32768)):
+            x = (rng2.standard_normal(shape) * 2.0).astype(np.float32)
+            x[5, 17] = np.nan
+            x[7, :] = -np.inf
+            x[9, 100] = np.inf
+            for name in ("softmax", "log_softmax"):
+                yield Case(f"{name}/{shape}/long-rows", Op[name.upper()], [x], shape, DType.F32, graph.axis_params(1))
 
 
 def matmul_cases(seed=11, quick=False):
@@ -500,6 +527,63 @@ def movement_cases(seed=21, quick=False):
     yield Case("slice_backward/axis0", Op.SLICE_BACKWARD, [g], (5, 4, 5), DType.F32, graph.slice_params(0, 1, 4, 1))
     yield Case("slice_backward/axis2-strided-g", Op.SLICE_BACKWARD, [np.ascontiguousarray(g.transpose(0, 2, 1)).transpose(0, 2, 1)],
                (3, 4, 15), DType.F32, graph.slice_params(2, 0, 15, 3))
+
+
+def f16_cases(seed=77):
+    """F16 storage through every kernel family: operands and results are half, arithmetic is f32."""
+    rng = np.random.default_rng(seed)
+
+    def h(*shape, scale=1.0):
+        return (rng.standard_normal(shape) * scale).astype(np.float16)
+
+    H = DType.F16
+    a, b = h(33, 65), h(33, 65)
+    for name in ("add", "sub", "mul", "maximum", "minimum", "div"):
+        bb = np.where(np.abs(b) < 0.05, np.float16(0.5), b).astype(np.float16) if name == "div" else b
+        yield Case(f"f16/{name}", Op[name.upper()], [a, bb], a.shape, H)
+    yield Case("f16/add/transposed+row-broadcast", Op.ADD,
+               [np.ascontiguousarray(a.T).T, np.broadcast_to(h(65), (33, 65))], a.shape, H)
+    yield Case("f16/scaled_add", Op.SCALED_ADD, [a, b], a.shape, H, graph.scaled_add_params(0.9, -0.1))
+    for name in ("relu", "neg", "abs", "square", "exp", "tanh", "sigmoid", "sqrt"):
+        x = np.abs(a) + np.float16(0.1) if name == "sqrt" else a
+        yield Case(f"f16/{name}", Op[name.upper()], [x], x.shape, H)
+    special = np.array([np.nan, -0.0, 0.0, 1.0, -1.0, np.inf, -np.inf, 6e-8, -6e-8, 65504.0], dtype=np.float16)
+    yield Case("f16/relu/special", Op.RELU, [special], special.shape, H)
+    yield Case("f16/add/overflow", Op.ADD, [special, special[::-1].copy()], special.shape, H)
+    yield Case("f16/less", Op.LESS, [a, b], a.shape, DType.BOOL)
+    yield Case("f16/where", Op.WHERE, [(rng.random((33, 65)) < 0.5).astype(np.uint8), a, b], a.shape, H)
+    yield Case("f16/contiguous/transposed", Op.CONTIGUOUS, [np.ascontiguousarray(a.T).T], a.shape, H)
+    yield Case("f16/cat", Op.CAT, [a, h(7, 65)], (40, 65), H, graph.axis_params(0))
+    yield Case("f16/tril", Op.TRIL, [a], a.shape, H, graph.tri_params(0))
+    # reductions: f32 accumulation, one narrowing
+    x = h(40, 300)
+    tas = np.abs(x.astype(np.float64))
+    yield Case("f16/sum/rows", Op.SUM, [x], (40,), H, graph.reduce_params([1], 2), terms_abs_sum=tas.sum(1), reduction_n=300)
+    yield Case("f16/mean/cols", Op.MEAN, [x], (1, 300), H, graph.reduce_params([0], 2, True),
+               terms_abs_sum=tas.sum(0, keepdims=True) / 40, reduction_n=40)
+    yield Case("f16/max/rows", Op.MAX, [x], (40,), H, graph.reduce_params([1], 2))
+    yield Case("f16/argmax/rows", Op.ARGMAX, [x], (40,), DType.I64, graph.reduce_params([1], 2))
+    yield Case("f16/softmax", Op.SOFTMAX, [h(17, 100, scale=2.0)], (17, 100), H, graph.axis_params(1))
+    yield Case("f16/log_softmax", Op.LOG_SOFTMAX, [h(17, 100, scale=2.0)], (17, 100), H, graph.axis_params(1))
+    # matmul: CUDA-core size and tensor-core size
+    for m, k, n in ((48, 96, 40), (256, 512, 384)):
+        a4, b4 = h(1, 1, m, k), h(1, 1, k, n)
+        tas4 = np.abs(a4.astype(np.float64)) @ np.abs(b4.astype(np.float64))
+        yield Case(f"f16/matmul/{m}x{k}x{n}", Op.MATMUL, [a4, b4], (1, 1, m, n), H, terms_abs_sum=tas4, reduction_n=k)
+    # window and index movement
+    img = h(2, 3, 8, 8)
+    up = graph.unfold_params((3, 3), (1, 1), (1, 1), (1, 1), (8, 8))
+    yield Case("f16/im2col", Op.IM2COL, [img], (2, 27, 64), H, up)
+    yield Case("f16/col2im", Op.COL2IM, [h(2, 27, 64)], (2, 3, 8, 8), H, up)
+    pool = graph.unfold_params((2, 2), (2, 2), (0, 0), (1, 1), (8, 8))
+    ties = rng.integers(0, 5, (2, 3, 8, 8)).astype(np.float16)
+    yield Case("f16/max_pool2d", Op.MAX_POOL2D, [ties], (2, 3, 4, 4), H, pool)
+    yield Case("f16/max_pool2d_backward", Op.MAX_POOL2D_BACKWARD, [h(2, 3, 4, 4), ties], (2, 3, 8, 8), H, pool)
+    table = h(50, 16)
+    idx = rng.integers(0, 50, 200).astype(np.int64)
+    yield Case("f16/index_select", Op.INDEX_SELECT, [table, idx], (200, 16), H, graph.axis_params(0))
+    yield Case("f16/scatter_add", Op.SCATTER_ADD, [h(200, 16), idx], (50, 16), H, graph.axis_params(0))
+    yield Case("f16/slice_backward", Op.SLICE_BACKWARD, [h(3, 4, 5)], (3, 11, 5), H, graph.slice_params(1, 2, 10, 2))
 
 
 def all_cases(quick=False):

@@ -62,7 +62,16 @@ def test_supports_is_honest():
     assert sup(_node(Op.ADD, DType.F32, [DType.F32, DType.F32]))
     assert sup(_node(Op.RESHAPE, DType.F32, [DType.F32]))            # views and leaves always
     assert sup(_node(Op.INPUT, DType.F16, []))
-    assert not sup(_node(Op.ADD, DType.F16, [DType.F16, DType.F16]))  # f16 arithmetic is not implemented
+    # F16 is a storage dtype: floating operands and result of one dtype (vulkan_backend.cpp:1055-1184)
+    assert sup(_node(Op.ADD, DType.F16, [DType.F16, DType.F16]))
+    assert not sup(_node(Op.ADD, DType.F16, [DType.F16, DType.F32]))
+    assert not sup(_node(Op.ADD, DType.F32, [DType.F16, DType.F16]))
+    assert sup(_node(Op.LESS, DType.BOOL, [DType.F16, DType.F16]))
+    assert sup(_node(Op.ARGMAX, DType.I64, [DType.F16]))
+    assert sup(_node(Op.SOFTMAX, DType.F16, [DType.F16]))
+    assert sup(_node(Op.MATMUL, DType.F16, [DType.F16, DType.F16], shape=(1, 1, 4, 4)))
+    assert not sup(_node(Op.PROD, DType.F16, [DType.F16]))
+    assert not sup(_node(Op.RAND, DType.F16, []))
     assert not sup(_node(Op.PROD, DType.F32, [DType.F32]))            # declined by vkML's GPU backend too
     assert sup(_node(Op.EQUAL, DType.BOOL, [DType.F32, DType.F32]))
     assert not sup(_node(Op.EQUAL, DType.F32, [DType.F32, DType.F32]))

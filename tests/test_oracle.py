@@ -131,6 +131,23 @@ def test_oracle_matches_reference_bit_for_bit(oracle, ref):
     assert n > 800
 
 
+def test_f16_storage_matches_reference_bit_for_bit(oracle, ref):
+    """F16 operands and results: the restatement's widen / compute in f32 / narrow once composition
+    against the compiled reference's Half kernels, every family, bit for bit."""
+    n = 0
+    for case in cases.f16_cases():
+        rc_r, want = ref.run_status(case.op, case.srcs, case.out_shape, case.out_dtype, case.params)
+        rc_o, got = oracle.run_status(case.op, case.srcs, case.out_shape, case.out_dtype, case.params)
+        assert rc_r == 0 and rc_o == 0, f"{case.name}: status oracle {rc_o}, reference {rc_r}"
+        assert got.dtype == want.dtype and got.shape == want.shape, case.name
+        if not np.array_equal(bits(got), bits(want)):
+            bad = np.argwhere(bits(got) != bits(want))
+            raise AssertionError(f"{case.name}: oracle differs from the reference at {bad[:3].tolist()}: "
+                                 f"{got[tuple(bad[0])]!r} vs {want[tuple(bad[0])]!r}")
+        n += 1
+    assert n >= 38
+
+
 def test_index_errors_match_the_reference(oracle, ref):
     table = np.arange(12, dtype=np.float32).reshape(4, 3)
     for bad_index in (-1, 4):

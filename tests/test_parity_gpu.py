@@ -49,6 +49,12 @@ def test_elementwise(cuda, oracle, backend):
     assert _run_family(cases.elementwise_cases(), cuda, oracle, backend) >= 390
 
 
+def test_f16_storage(cuda, oracle, backend):
+    """F16 operands and results through every kernel family (widened, computed in f32, narrowed
+    once): exact ops bit-identical to the CPU backend's Half kernels, the rest within one f16 ulp."""
+    assert _run_family(cases.f16_cases(), cuda, oracle, backend) >= 38
+
+
 def test_creation(cuda, oracle, backend):
     assert _run_family(cases.creation_cases(), cuda, oracle, backend) >= 25
 

@@ -266,9 +266,92 @@ void count_matmul_operands(b200_ctx* ctx, const b200_node* nodes, size_t n_nodes
     }
 }
 
+bool touches_f16(const b200_node& n) {
+    if (n.op == B200_OP_CAST || n.op == B200_OP_FULL) return false;  // these handle F16 themselves
+    if (n.out.dtype == B200_F16) return true;
+    for (uint32_t s = 0; s < n.n_src && s < B200_MAX_SRC; ++s) {
+        if (n.src[s].dtype == B200_F16) return true;
+    }
+    return false;
+}
+
+b200_tensor dense_f32_like(const b200_tensor& like, void* data) {
+    b200_tensor t = like;
+    t.dtype = B200_F32;
+    t.data = data;
+    int64_t stride = 4;
+    for (int d = like.ndim - 1; d >= 0; --d) {
+        t.strides[d] = stride;
+        stride *= like.dims[d];
+    }
+    return t;
+}
+
+void dispatch_node(b200_ctx* ctx, const b200_node& node);
+
+// F16 is storage, never arithmetic, in vkML (src/backend/cpu/kernels_elementwise.cpp:89-99; fp32
+// accumulation everywhere, docs/ARCHITECTURE.md 7.3): every kernel widens Half on load, computes in
+// float and narrows once, round-to-nearest-even, on store.  A node that touches F16 therefore runs
+// here as the same node on widened copies with the result narrowed -- bit-identical to the CPU
+// backend's Half kernels for every family (pinned on the CPU by the oracle tests) -- at the price
+// of the temporaries' traffic.  It is the coverage path; the fp32 kernels are the tuned ones.
+void dispatch_f16(b200_ctx* ctx, const b200_node& node) {
+    b200_node w = node;
+    void* temps[B200_MAX_SRC + 1] = {};
+    struct Release {
+        b200_ctx* c;
+        void** t;
+        ~Release() {
+            for (int i = 0; i <= B200_MAX_SRC; ++i) {
+                if (t[i] != nullptr) c->scratch.release(t[i]);  // stream-ordered: safe with work queued
+            }
+        }
+    } release{ctx, temps};
+    auto numel_of = [](const b200_tensor& t) {
+        int64_t n = 1;
+        for (int d = 0; d < t.ndim; ++d) n *= t.dims[d];
+        return n;
+    };
+    for (uint32_t s = 0; s < node.n_src && s < B200_MAX_SRC; ++s) {
+        if (node.src[s].dtype != B200_F16) continue;
+        const int64_t n = numel_of(node.src[s]);
+        temps[s] = ctx->scratch.allocate(static_cast<size_t>(std::max<int64_t>(n, 1)) * 4);
+        b200_node c{};
+        c.op = B200_OP_CAST;
+        c.n_src = 1;
+        c.src[0] = node.src[s];
+        c.out = dense_f32_like(node.src[s], temps[s]);
+        if (n > 0) {
+            ProfScope scope(ctx, "f16.widen");
+            launch_elementwise(ctx, c);
+        }
+        w.src[s] = c.out;
+    }
+    if (node.out.dtype == B200_F16) {
+        const int64_t n = numel_of(node.out);
+        temps[B200_MAX_SRC] = ctx->scratch.allocate(static_cast<size_t>(std::max<int64_t>(n, 1)) * 4);
+        w.out = dense_f32_like(node.out, temps[B200_MAX_SRC]);
+    }
+    dispatch_node(ctx, w);
+    if (node.out.dtype == B200_F16) {
+        b200_node c{};
+        c.op = B200_OP_CAST;
+        c.n_src = 1;
+        c.src[0] = w.out;
+        c.out = node.out;
+        ctx->current_op = B200_OP_CAST;
+        ProfScope scope(ctx, "f16.narrow");
+        launch_elementwise(ctx, c);
+    }
+}
+
 void dispatch_node(b200_ctx* ctx, const b200_node& node) {
     const uint32_t op = node.op;
     ctx->current_op = op;
+    if (touches_f16(node)) {
+        dispatch_f16(ctx, node);
+        return;
+    }
     if (op == B200_OP_MATMUL) {
         dispatch_matmul(ctx, node);  // times its kernels one by one
         return;
@@ -323,8 +406,8 @@ int guarded(b200_ctx* ctx, Fn&& fn) {
 
 }  // namespace
 
-// Mirrors VulkanBackend::supports (src/backend/vulkan/vulkan_backend.cpp:1012-1187)
-// for f32; f16 appears only as a cast endpoint.  Honest rather than optimistic:
+// Mirrors VulkanBackend::supports (src/backend/vulkan/vulkan_backend.cpp:1012-1187):
+// f32 natively, f16 storage through widened copies (dispatch_f16).  Honest rather than optimistic:
 // a false here becomes NotImplementedError at realize, there is no fallback.
 bool supports_node(const b200_node& n) {
     const uint32_t op = n.op;
@@ -332,6 +415,23 @@ bool supports_node(const b200_node& n) {
     if (op >= B200_OP_COUNT) return false;
     if (n.n_src > B200_MAX_SRC) return false;
     if (!dense(n.out)) return false;
+    if (touches_f16(n)) {
+        // vkML's rule for its GPU backend: the floating operands and the result share one dtype
+        // (vulkan_backend.cpp:1055-1184); the node then runs as its f32 self on widened copies
+        b200_node w = n;
+        auto widen = [](b200_tensor& t) {
+            t.dtype = B200_F32;
+            for (int d = 0; d < t.ndim; ++d) t.strides[d] *= 2;
+        };
+        bool f32_seen = n.out.dtype == B200_F32;
+        if (n.out.dtype == B200_F16) widen(w.out);
+        for (uint32_t s = 0; s < n.n_src; ++s) {
+            f32_seen = f32_seen || n.src[s].dtype == B200_F32;
+            if (n.src[s].dtype == B200_F16) widen(w.src[s]);
+        }
+        if (op == B200_OP_RAND) return false;  // F32 only in vkML as well (vulkan_backend.cpp:1037)
+        return !f32_seen && supports_node(w);
+    }
     const int dt = n.out.dtype;
     switch (op) {
         case B200_OP_FULL: return dt == B200_F32 || dt == B200_F16 || dt == B200_I64 || dt == B200_I32 || dt == B200_BOOL;

@@ -870,6 +870,144 @@ softmax_reg_kernel(float* __restrict__ out, const float* __restrict__ in, SoftGe
     }
 }
 
+// Long dense rows (2049 .. 8192 float4 units), one 1024-thread block per SM, persistent over rows.
+// The row in flight lives in registers, as in softmax_reg_kernel, but it arrives through shared
+// memory: while a row is reduced, normalised and stored, the bulk-copy engine already fetches the
+// block's next row (cp.async.bulk + mbarrier), so the SM's loads and stores overlap instead of
+// alternating.  The wait is bounded: on expiry the kernel records kStatusWaitTimedOut and returns.
+__device__ __forceinline__ uint32_t sm_u32(const void* p) { return static_cast<uint32_t>(__cvta_generic_to_shared(p)); }
+
+template <bool LOG>
+__global__ void __launch_bounds__(1024, 1)
+softmax_bulk_kernel(float* __restrict__ out, const float* __restrict__ in, SoftGeo g, int64_t n_rows,
+                    uint32_t* status) {
+    constexpr int ITEMS = 8;
+    extern __shared__ __align__(128) unsigned char row_buf[];
+    __shared__ float red[32];
+    __shared__ __align__(8) unsigned long long bar;
+    const int tid = threadIdx.x;
+    const int64_t n_units = g.n_axis / 4;
+    const uint32_t row_bytes = static_cast<uint32_t>(g.n_axis) * 4u;
+    const uint32_t sbar = sm_u32(&bar), sdst = sm_u32(row_buf);
+    auto fetch = [&](int64_t row) {  // thread 0 only
+        int64_t bi, bo;
+        soft_bases(g, row, bi, bo);
+        asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(sbar), "r"(row_bytes) : "memory");
+        asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+                     ::"r"(sdst), "l"(reinterpret_cast<uint64_t>(in + bi)), "r"(row_bytes), "r"(sbar)
+                     : "memory");
+    };
+    if (tid == 0) {
+        asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(sbar));
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+    }
+    __syncthreads();
+    int64_t row = blockIdx.x;
+    if (tid == 0 && row < n_rows) {
+        fetch(row);
+    }
+    uint32_t phase = 0;
+    for (; row < n_rows; row += gridDim.x) {
+        // bounded wait for the row (4 s on the global timer, consulted every 1024 polls)
+        int ok = 1;
+        {
+            unsigned long long start = 0;
+            uint32_t spins = 0;
+            for (;;) {
+                uint32_t done;
+                asm volatile(
+                    "{ .reg .pred p; mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2; selp.u32 %0, 1, 0, p; }"
+                    : "=r"(done)
+                    : "r"(sbar), "r"(phase)
+                    : "memory");
+                if (done) break;
+                if ((++spins & 0x3ff) == 0) {
+                    unsigned long long now;
+                    asm volatile("mov.u64 %0, %globaltimer;" : "=l"(now));
+                    if (start == 0) {
+                        start = now;
+                    } else if (now - start > 4000000000ULL) {
+                        ok = 0;
+                        break;
+                    }
+                }
+            }
+        }
+        phase ^= 1u;
+        float v[ITEMS * 4];
+        float peak = -INFINITY;
+#pragma unroll
+        for (int i = 0; i < ITEMS; ++i) {
+            const int64_t u = tid + int64_t(i) * 1024;
+            if (ok && u < n_units) {
+                const float4 t = reinterpret_cast<const float4*>(row_buf)[u];
+                v[4 * i] = t.x;
+                v[4 * i + 1] = t.y;
+                v[4 * i + 2] = t.z;
+                v[4 * i + 3] = t.w;
+            } else {
+#pragma unroll
+                for (int w = 0; w < 4; ++w) v[4 * i + w] = -INFINITY;
+            }
+#pragma unroll
+            for (int w = 0; w < 4; ++w) peak = fmaxf(peak, v[4 * i + w]);
+        }
+        // every thread holds its part of the row: the buffer may take the next one
+        if (!__syncthreads_and(ok)) {
+            if (tid == 0) atomicOr(status, kStatusWaitTimedOut);
+            return;
+        }
+        const int64_t next = row + gridDim.x;
+        if (tid == 0 && next < n_rows) {
+            // order the threads' generic-proxy reads of the buffer before the async-proxy refill
+            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+            fetch(next);
+        }
+        peak = block_all_max(peak, red);
+        float denom = 0.0F;
+#pragma unroll
+        for (int i = 0; i < ITEMS * 4; ++i) {
+            const float e = expf(v[i] - peak);
+            denom += e;
+            if (!LOG) {
+                v[i] = e;
+            }
+        }
+        denom = block_all_sum(denom, red);
+        const float lg = logf(denom);
+        int64_t bi, bo;
+        soft_bases(g, row, bi, bo);
+#pragma unroll
+        for (int i = 0; i < ITEMS; ++i) {
+            const int64_t u = tid + int64_t(i) * 1024;
+            if (u < n_units) {
+                float r[4];
+#pragma unroll
+                for (int w = 0; w < 4; ++w) {
+                    r[w] = LOG ? (v[4 * i + w] - peak) - lg : v[4 * i + w] / denom;
+                }
+                reinterpret_cast<float4*>(out + bo)[u] = make_float4(r[0], r[1], r[2], r[3]);
+            }
+        }
+    }
+}
+
+template <bool LOG>
+void launch_softmax_bulk(b200_ctx* ctx, float* dst, const float* src, const SoftGeo& g, int64_t n_rows) {
+    const size_t smem = static_cast<size_t>(g.n_axis) * sizeof(float);
+    static bool raised[2] = {false, false};
+    if (!raised[LOG ? 1 : 0]) {
+        B200_CUDA_CHECK(cudaFuncSetAttribute(softmax_bulk_kernel<LOG>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                             160 * 1024));
+        raised[LOG ? 1 : 0] = true;
+    }
+    const unsigned grid = static_cast<unsigned>(std::min<int64_t>(n_rows, kSmCount));
+    softmax_bulk_kernel<LOG><<<grid, 1024, smem, ctx->stream>>>(dst, src, g, n_rows, ctx->d_status);
+    ctx->count_launch();
+    check_last_launch("softmax (bulk prefetch)");
+}
+
 template <bool LOG, int GROUP, int ITEMS, bool VEC4>
 void launch_softmax_reg(b200_ctx* ctx, float* dst, const float* src, const SoftGeo& g, int64_t n_rows) {
     constexpr int kBlock = GROUP == 32 ? 256 : GROUP;
@@ -938,6 +1076,9 @@ void run_softmax(b200_ctx* ctx, const View& out, const View& in, int axis4) {
             if (u <= 64) return launch_softmax_reg<LOG, 32, 2, true>(ctx, dst, src, g, n_rows);
             if (u <= 256) return launch_softmax_reg<LOG, 32, 8, true>(ctx, dst, src, g, n_rows);
             if (u <= 2048) return launch_softmax_reg<LOG, 256, 8, true>(ctx, dst, src, g, n_rows);
+            // enough rows to keep every SM busy with more than one: prefetch the next row while
+            // the current one is processed
+            if (u <= 8192 && n_rows >= 2 * int64_t(kSmCount)) return launch_softmax_bulk<LOG>(ctx, dst, src, g, n_rows);
             if (u <= 8192) return launch_softmax_reg<LOG, 1024, 8, true>(ctx, dst, src, g, n_rows);
         } else {
             if (n <= 256) return launch_softmax_reg<LOG, 32, 8, false>(ctx, dst, src, g, n_rows);
