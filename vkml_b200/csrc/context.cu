@@ -573,6 +573,9 @@ int b200_create(int cuda_ordinal, b200_ctx** out) {
         if (const char* e = std::getenv("VKML_B200_SHARE_PLANES")) {
             ctx->share_planes = std::atoi(e) != 0;
         }
+        if (const char* e = std::getenv("VKML_B200_LAZY_JOIN")) {
+            ctx->lazy_join = std::atoi(e) != 0;
+        }
         if (const char* e = std::getenv("VKML_B200_HOIST_GRADIENTS")) {
             ctx->hoist_gradients = std::atoi(e) != 0;
         }
@@ -637,7 +640,13 @@ int b200_alloc(b200_ctx* ctx, size_t nbytes, void** out) {
 
 int b200_free(b200_ctx* ctx, void* ptr) {
     if (ctx == nullptr) return B200_INVALID_ARGUMENT;
-    return guarded(ctx, [&] { ctx->alloc.release(ptr); });
+    return guarded(ctx, [&] {
+        if (ptr != nullptr && dist_has_pending(ctx)) {
+            // a buffer still being all-reduced: later work that reuses the block must come after it
+            dist_wait_range(ctx, ptr, static_cast<const char*>(ptr) + 1);
+        }
+        ctx->alloc.release(ptr);
+    });
 }
 
 int b200_trim(b200_ctx* ctx) {
@@ -752,6 +761,42 @@ int b200_compute(b200_ctx* ctx, const b200_node* nodes, size_t n_nodes, uint32_t
         } else {
             for (size_t i = 0; i < n_nodes; ++i) order.push_back(i);
         }
+        auto tensor_bytes = [](const b200_tensor& t) {
+            size_t n = dtype_size(t.dtype);
+            for (int d = 0; d < t.ndim; ++d) n *= static_cast<size_t>(t.dims[d]);
+            return n;
+        };
+        // All-reduces of an earlier gradient span may still be running.  Nodes are taken in the
+        // order their inputs become available: key = the latest pending all-reduce a node depends
+        // on, directly or through producers inside this span; a stable sort by that key keeps
+        // every producer before its consumers and leaves a span that touches no gradient as it is.
+        if (dist_has_pending(ctx) && n_nodes > 1) {
+            std::vector<int> key(n_nodes, -1);
+            for (size_t j = 0; j < n_nodes; ++j) {
+                const b200_node& node = nodes[j];
+                if (is_view_or_leaf(node.op)) continue;
+                int k = -1;
+                if (node.out.data != nullptr) {
+                    k = std::max(k, dist_pending_index(ctx, node.out.data,
+                                                       static_cast<const char*>(node.out.data) + tensor_bytes(node.out)));
+                }
+                for (uint32_t s = 0; s < node.n_src && s < B200_MAX_SRC; ++s) {
+                    const char* p = static_cast<const char*>(node.src[s].data);
+                    if (p == nullptr) continue;
+                    k = std::max(k, dist_pending_index(ctx, p, p + 1));
+                    for (size_t i = j; i-- > 0;) {  // latest earlier writer of that address
+                        if (is_view_or_leaf(nodes[i].op) || nodes[i].out.data == nullptr) continue;
+                        const char* lo = static_cast<const char*>(nodes[i].out.data);
+                        if (p >= lo && p < lo + tensor_bytes(nodes[i].out)) {
+                            k = std::max(k, key[i]);
+                            break;
+                        }
+                    }
+                }
+                key[j] = k;
+            }
+            std::stable_sort(order.begin(), order.end(), [&](size_t a, size_t b) { return key[a] < key[b]; });
+        }
         for (const size_t i : order) {
             const b200_node& node = nodes[i];
             if (is_view_or_leaf(node.op)) {
@@ -774,6 +819,13 @@ int b200_compute(b200_ctx* ctx, const b200_node* nodes, size_t n_nodes, uint32_t
                 for (int d = 0; d < node.src[s].ndim; ++d) sn *= node.src[s].dims[d];
                 if (sn != 0 && node.src[s].data == nullptr) {
                     fail(B200_INVALID_ARGUMENT, "source " + std::to_string(s) + " has no storage");
+                }
+            }
+            if (dist_has_pending(ctx)) {
+                dist_wait_range(ctx, node.out.data, static_cast<const char*>(node.out.data) + tensor_bytes(node.out));
+                for (uint32_t s = 0; s < node.n_src && s < B200_MAX_SRC; ++s) {
+                    const char* p = static_cast<const char*>(node.src[s].data);
+                    if (p != nullptr) dist_wait_range(ctx, p, p + 1);
                 }
             }
             if (!ctx->plane_cache.empty()) {
@@ -811,6 +863,7 @@ int b200_copy_from_host(b200_ctx* ctx, void* dst_device, const void* src_host, s
         // For pageable memory the runtime stages the bytes before returning, so
         // the caller may reuse `src_host` immediately; pinned memory is read
         // asynchronously, in stream order.
+        dist_wait_range(ctx, dst_device, static_cast<const char*>(dst_device) + nbytes);
         B200_CUDA_CHECK(cudaMemcpyAsync(dst_device, src_host, nbytes, cudaMemcpyHostToDevice, ctx->stream));
         cudaPointerAttributes attr{};
         const cudaError_t e = cudaPointerGetAttributes(&attr, src_host);
@@ -845,6 +898,7 @@ int b200_copy_to_host(b200_ctx* ctx, void* dst_host, const void* src_device, siz
     if (nbytes == 0) return B200_OK;
     if (dst_host == nullptr || src_device == nullptr) return B200_INVALID_ARGUMENT;
     return guarded(ctx, [&] {
+        dist_wait_range(ctx, src_device, static_cast<const char*>(src_device) + nbytes);
         B200_CUDA_CHECK(cudaMemcpyAsync(dst_host, src_device, nbytes, cudaMemcpyDeviceToHost, ctx->stream));
         B200_CUDA_CHECK(cudaStreamSynchronize(ctx->stream));
     });
@@ -858,6 +912,8 @@ int b200_copy_device_to_device(b200_ctx* ctx, const b200_copy* copies, size_t n)
             if (copies[i].dst == nullptr || copies[i].src == nullptr) {
                 fail(B200_INVALID_ARGUMENT, "null pointer in copy_device_to_device");
             }
+            dist_wait_range(ctx, copies[i].dst, static_cast<const char*>(copies[i].dst) + copies[i].nbytes);
+            dist_wait_range(ctx, copies[i].src, static_cast<const char*>(copies[i].src) + copies[i].nbytes);
             B200_CUDA_CHECK(cudaMemcpyAsync(copies[i].dst, copies[i].src, copies[i].nbytes,
                                             cudaMemcpyDeviceToDevice, ctx->stream));
         }
@@ -868,6 +924,7 @@ int b200_synchronize(b200_ctx* ctx) {
     if (ctx == nullptr) return B200_INVALID_ARGUMENT;
     int device_rc = B200_OK;
     const int rc = guarded(ctx, [&] {
+        dist_wait_range(ctx, nullptr, nullptr);  // "everything submitted" includes the all-reduces
         B200_CUDA_CHECK(cudaMemcpyAsync(ctx->h_status, ctx->d_status, sizeof(uint32_t),
                                         cudaMemcpyDeviceToHost, ctx->stream));
         B200_CUDA_CHECK(cudaStreamSynchronize(ctx->stream));
@@ -951,6 +1008,7 @@ int b200_timer_end(b200_ctx* ctx, float* milliseconds) {
     if (ctx == nullptr || milliseconds == nullptr) return B200_INVALID_ARGUMENT;
     return guarded(ctx, [&] {
         if (ctx->timer_begin == nullptr) fail(B200_INVALID_ARGUMENT, "b200_timer_end without b200_timer_begin");
+        dist_wait_range(ctx, nullptr, nullptr);
         B200_CUDA_CHECK(cudaEventRecord(ctx->timer_end, ctx->stream));
         B200_CUDA_CHECK(cudaEventSynchronize(ctx->timer_end));
         B200_CUDA_CHECK(cudaEventElapsedTime(milliseconds, ctx->timer_begin, ctx->timer_end));

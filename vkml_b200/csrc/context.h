@@ -118,6 +118,11 @@ struct b200_ctx {
     // Hoist each gradient-producing node of a grad-sync span to just after its last input
     // is produced, so its all-reduce overlaps the rest of backward (VKML_B200_HOIST_GRADIENTS).
     bool hoist_gradients = false;  // measured at 2 GPUs: 13.5 ms/step hoisted, 13.1 ms in the recorded order
+    // Lazy joining (VKML_B200_LAZY_JOIN, default on): a gradient span returns without waiting for its
+    // all-reduces; the compute stream waits for each one where its buffer is next touched, and the
+    // nodes of a later span are taken in the order their gradients arrive, so the optimiser's
+    // updates of the early-reduced parameters run under the tail of the communication.
+    bool lazy_join = true;
     bool in_grad_sync_span = false;
     bool comm_pending = false;  // an all-reduce was issued in this span and has not been joined yet
 
@@ -166,6 +171,9 @@ void dist_destroy(b200_ctx* ctx);
 void dist_after_node(b200_ctx* ctx, const b200_node& node);  // all-reduce a registered gradient once its producer is queued
 void dist_all_reduce_now(b200_ctx* ctx, void* data, size_t count);  // average across ranks on the comm stream
 void dist_join(b200_ctx* ctx);                                // make the compute stream wait for outstanding all-reduces
+void dist_wait_range(b200_ctx* ctx, const void* lo, const void* hi);  // ... for those touching [lo, hi) (nullptr: all)
+int dist_pending_index(const b200_ctx* ctx, const void* lo, const void* hi);
+bool dist_has_pending(const b200_ctx* ctx);
 
 void check_last_launch(const char* what);
 

@@ -84,6 +84,14 @@ struct DistState {
     cudaEvent_t reduced = nullptr;   // comm -> compute
     bool pending = false;
     std::vector<char> done;          // per registered gradient, within one span
+    // all-reduces that the compute stream has not been made to wait for yet, in issue order
+    struct Lazy {
+        const char* lo;
+        const char* hi;
+        cudaEvent_t done;
+    };
+    std::vector<Lazy> lazy;
+    std::vector<cudaEvent_t> event_pool;
 };
 
 static void all_reduce_mean(b200_ctx* ctx, void* data, size_t count) {
@@ -95,7 +103,52 @@ static void all_reduce_mean(b200_ctx* ctx, void* data, size_t count) {
     d->pending = true;
     ctx->comm_pending = true;
     ctx->comm_bytes.fetch_add(count * sizeof(float), std::memory_order_relaxed);
+    if (ctx->lazy_join) {
+        cudaEvent_t ev = nullptr;
+        if (!d->event_pool.empty()) {
+            ev = d->event_pool.back();
+            d->event_pool.pop_back();
+        } else {
+            B200_CUDA_CHECK(cudaEventCreateWithFlags(&ev, cudaEventDisableTiming));
+        }
+        B200_CUDA_CHECK(cudaEventRecord(ev, d->comm_stream));
+        d->lazy.push_back(DistState::Lazy{static_cast<const char*>(data),
+                                          static_cast<const char*>(data) + count * sizeof(float), ev});
+    }
 }
+
+// Makes the compute stream wait for the pending all-reduces that overlap [lo, hi) and for every
+// one issued before them (the communication stream is in order); nullptr: for all of them.
+void dist_wait_range(b200_ctx* ctx, const void* lo, const void* hi) {
+    DistState* d = ctx->dist;
+    if (d == nullptr || d->lazy.empty()) return;
+    const char* a = static_cast<const char*>(lo);
+    const char* b = static_cast<const char*>(hi);
+    int last = -1;
+    for (size_t i = 0; i < d->lazy.size(); ++i) {
+        if (lo == nullptr || (a < d->lazy[i].hi && d->lazy[i].lo < b)) last = static_cast<int>(i);
+    }
+    if (last < 0) return;
+    B200_CUDA_CHECK(cudaStreamWaitEvent(ctx->stream, d->lazy[static_cast<size_t>(last)].done, 0));
+    for (int i = 0; i <= last; ++i) d->event_pool.push_back(d->lazy[static_cast<size_t>(i)].done);
+    d->lazy.erase(d->lazy.begin(), d->lazy.begin() + last + 1);
+    if (d->lazy.empty()) d->pending = false;
+}
+
+// Position (in issue order) of the last pending all-reduce overlapping [lo, hi), or -1.
+int dist_pending_index(const b200_ctx* ctx, const void* lo, const void* hi) {
+    const DistState* d = ctx->dist;
+    if (d == nullptr) return -1;
+    const char* a = static_cast<const char*>(lo);
+    const char* b = static_cast<const char*>(hi);
+    int last = -1;
+    for (size_t i = 0; i < d->lazy.size(); ++i) {
+        if (a < d->lazy[i].hi && d->lazy[i].lo < b) last = static_cast<int>(i);
+    }
+    return last;
+}
+
+bool dist_has_pending(const b200_ctx* ctx) { return ctx->dist != nullptr && !ctx->dist->lazy.empty(); }
 
 void dist_all_reduce_now(b200_ctx* ctx, void* data, size_t count) {
     if (ctx->dist != nullptr && count != 0) {
@@ -138,11 +191,12 @@ void dist_join(b200_ctx* ctx) {
         }
     }
     d->done.clear();
-    if (d->pending) {
+    if (d->pending && !ctx->lazy_join) {
         B200_CUDA_CHECK(cudaEventRecord(d->reduced, d->comm_stream));
         B200_CUDA_CHECK(cudaStreamWaitEvent(ctx->stream, d->reduced, 0));
         d->pending = false;
     }
+    // with lazy joining the compute stream waits where a reduced buffer is next touched
     ctx->comm_pending = false;
 }
 
@@ -153,6 +207,8 @@ void dist_destroy(b200_ctx* ctx) {
     }
     if (d->comm_stream != nullptr) cudaStreamSynchronize(d->comm_stream);
     if (d->comm != nullptr && nccl().CommDestroy != nullptr) nccl().CommDestroy(d->comm);
+    for (auto& l : d->lazy) cudaEventDestroy(l.done);
+    for (cudaEvent_t e : d->event_pool) cudaEventDestroy(e);
     if (d->produced != nullptr) cudaEventDestroy(d->produced);
     if (d->reduced != nullptr) cudaEventDestroy(d->reduced);
     if (d->comm_stream != nullptr) cudaStreamDestroy(d->comm_stream);
@@ -247,6 +303,7 @@ int b200_dist_wait(b200_ctx* ctx) {
     return guarded_dist(ctx, [&] {
         if (ctx->dist == nullptr) return;
         DistState* d = ctx->dist;
+        dist_wait_range(ctx, nullptr, nullptr);
         if (d->pending) {
             B200_CUDA_CHECK(cudaEventRecord(d->reduced, d->comm_stream));
             B200_CUDA_CHECK(cudaStreamWaitEvent(ctx->stream, d->reduced, 0));
