@@ -304,6 +304,19 @@ inline unsigned grid_for(int64_t work, int threads, int blocks_per_sm = 8) {
     return static_cast<unsigned>(g);
 }
 
+// Programmatic dependent launch.  Every kernel of the library starts with this pair: the first
+// instruction lets the NEXT kernel of the stream be scheduled as soon as all blocks of this one
+// are running (instead of after its last block has retired), the second holds this kernel until
+// the PREVIOUS one has completed and its writes are visible.  Since the wait precedes every
+// memory access, the stream keeps its in-order semantics; what overlaps is launch latency, block
+// scheduling and the kernels' own set-up.  Without the launch attribute both are no-ops.
+#ifdef __CUDACC__
+__device__ __forceinline__ void pdl_prologue() {
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+}
+#endif
+
 // Division of a 31-bit unsigned number by a divisor known at launch time: one multiply-high
 // and a shift instead of the ~20-instruction hardware sequence.  With p = 31 + ceil(log2 d)
 // and m = ceil(2^p / d), floor(n / d) == (n * m) >> p for every n < 2^31.

@@ -573,6 +573,9 @@ int b200_create(int cuda_ordinal, b200_ctx** out) {
         if (const char* e = std::getenv("VKML_B200_SHARE_PLANES")) {
             ctx->share_planes = std::atoi(e) != 0;
         }
+        if (const char* e = std::getenv("VKML_B200_PDL")) {
+            ctx->pdl = std::atoi(e) != 0;
+        }
         if (const char* e = std::getenv("VKML_B200_LAZY_JOIN")) {
             ctx->lazy_join = std::atoi(e) != 0;
         }

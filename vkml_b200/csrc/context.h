@@ -9,6 +9,7 @@
 #include <mutex>
 #include <set>
 #include <unordered_map>
+#include <utility>
 #include <vector>
 
 namespace b200 {
@@ -123,6 +124,7 @@ struct b200_ctx {
     // nodes of a later span are taken in the order their gradients arrive, so the optimiser's
     // updates of the early-reduced parameters run under the tail of the communication.
     bool lazy_join = true;
+    bool pdl = true;  // programmatic dependent launch between consecutive kernels (VKML_B200_PDL)
     bool in_grad_sync_span = false;
     bool comm_pending = false;  // an all-reduce was issued in this span and has not been joined yet
 
@@ -155,6 +157,26 @@ struct b200_ctx {
 };
 
 namespace b200 {
+
+// The one place kernels are launched from.  With programmatic dependent launch enabled
+// (VKML_B200_PDL, default on) the launch carries the stream-serialization attribute that
+// pdl_prologue() in the kernels relies on.
+template <typename... Params, typename... Args>
+inline void launch_kernel(b200_ctx* ctx, void (*kernel)(Params...), dim3 grid, dim3 block, size_t smem,
+                          Args&&... args) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = ctx->stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = ctx->pdl ? 1 : 0;
+    // a failed launch is picked up by check_last_launch() at the call site
+    (void)cudaLaunchKernelEx(&cfg, kernel, std::forward<Args>(args)...);
+}
 
 // Per-family launchers (one translation unit each). Each reads the node, picks a
 // kernel from the operand layouts, and launches on ctx->stream.

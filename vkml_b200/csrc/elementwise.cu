@@ -278,6 +278,7 @@ __global__ void __launch_bounds__(kThreads)
 flat_kernel(typename F::Out* __restrict__ out, const typename F::In0* __restrict__ a,
             const typename F::In1* __restrict__ b, const typename F::In2* __restrict__ c,
             int64_t n, typename F::P p) {
+    pdl_prologue();
     using VA = Vec<typename F::In0, VEC>;
     using VB = Vec<typename F::In1, VEC>;
     using VC = Vec<typename F::In2, VEC>;
@@ -381,6 +382,7 @@ __global__ void __launch_bounds__(kThreads)
 strided_kernel(typename F::Out* __restrict__ out, const typename F::In0* __restrict__ a,
                const typename F::In1* __restrict__ b, const typename F::In2* __restrict__ c,
                I nvec, LayoutT<I> L, typename F::P p) {
+    pdl_prologue();
     constexpr int kUnroll = unroll_for<VEC>();
     const int inner = kMaxDims - 1;
     const int64_t step = int64_t(gridDim.x) * kThreads * kUnroll;
@@ -435,6 +437,7 @@ __global__ void __launch_bounds__(256)
 tiled_kernel(typename F::Out* __restrict__ out, const typename F::In0* __restrict__ a,
              const typename F::In1* __restrict__ b, const typename F::In2* __restrict__ c,
              TileArgs t, typename F::P p) {
+    pdl_prologue();
     __shared__ typename F::In0 ta[kTile][kTile + 1];
     __shared__ typename F::In1 tb[kTile][kTile + 1];
     const int64_t tiles_c = (t.cols + kTile - 1) / kTile;
@@ -695,10 +698,9 @@ void launch_strided(b200_ctx* ctx, typename F::Out* o, const typename F::In0* a,
                     const typename F::P& p) {
     const unsigned grid = grid_for(ceil_div(nvec, unroll_for<VEC>()), kThreads);
     if (small_index) {
-        strided_kernel<F, VEC, uint32_t><<<grid, kThreads, 0, ctx->stream>>>(
-            o, a, b, c, static_cast<uint32_t>(nvec), narrow<uint32_t>(L), p);
+        launch_kernel(ctx, strided_kernel<F, VEC, uint32_t>, grid, kThreads, 0, o, a, b, c, static_cast<uint32_t>(nvec), narrow<uint32_t>(L), p);
     } else {
-        strided_kernel<F, VEC, int64_t><<<grid, kThreads, 0, ctx->stream>>>(o, a, b, c, nvec,
+        launch_kernel(ctx, strided_kernel<F, VEC, int64_t>, grid, kThreads, 0, o, a, b, c, nvec,
                                                                             narrow<int64_t>(L), p);
     }
 }
@@ -751,10 +753,9 @@ void run(b200_ctx* ctx, const b200_node& node, const typename F::P& p) {
             al = al && aligned_for<typename F::In2>(c, kVec);
         }
         if (al) {
-            flat_kernel<F, kVec><<<grid_for(ceil_div(n / kVec + 1, unroll_for<kVec>()), kThreads), kThreads, 0, ctx->stream>>>(
-                o, a, b, c, n, p);
+            launch_kernel(ctx, flat_kernel<F, kVec>, grid_for(ceil_div(n / kVec + 1, unroll_for<kVec>()), kThreads), kThreads, 0, o, a, b, c, n, p);
         } else {
-            flat_kernel<F, 1><<<grid_for(ceil_div(n, unroll_for<1>()), kThreads), kThreads, 0, ctx->stream>>>(o, a, b, c, n,
+            launch_kernel(ctx, flat_kernel<F, 1>, grid_for(ceil_div(n, unroll_for<1>()), kThreads), kThreads, 0, o, a, b, c, n,
                                                                                                    p);
         }
         ctx->count_launch();
@@ -803,7 +804,7 @@ void run(b200_ctx* ctx, const b200_node& node, const typename F::P& p) {
             if (ok && any_t && t.rows >= 8 && t.cols >= 8) {
                 const int64_t tiles = ceil_div(ceil_div(t.rows, kTile), 4) * ceil_div(ceil_div(t.cols, kTile), 4) * 16 *
                                       t.batch;
-                tiled_kernel<F><<<grid_for(tiles, 1, 8), 256, 0, ctx->stream>>>(o, a, b, c, t, p);
+                launch_kernel(ctx, tiled_kernel<F>, grid_for(tiles, 1, 8), 256, 0, o, a, b, c, t, p);
                 ctx->count_launch();
                 check_last_launch("elementwise tiled");
                 return;
@@ -851,6 +852,7 @@ void run(b200_ctx* ctx, const b200_node& node, const typename F::P& p) {
 // 16-byte stores; the pointer comes from the allocator, so it is 512-byte aligned.
 template <typename T>
 __global__ void __launch_bounds__(kThreads) fill_kernel(T* __restrict__ out, int64_t n, T value) {
+    pdl_prologue();
     constexpr int V = 16 / sizeof(T);
     Vec<T, V> v;
 #pragma unroll
@@ -873,6 +875,7 @@ __global__ void __launch_bounds__(kThreads) fill_kernel(T* __restrict__ out, int
 template <typename T>
 __global__ void __launch_bounds__(kThreads)
 arange_kernel(T* __restrict__ out, int64_t n, double start, double step) {
+    pdl_prologue();
     const int64_t stride = int64_t(gridDim.x) * blockDim.x;
     for (int64_t i = int64_t(blockIdx.x) * blockDim.x + threadIdx.x; i < n; i += stride) {
         out[i] = static_cast<T>(__dadd_rn(start, __dmul_rn(static_cast<double>(i), step)));
@@ -883,6 +886,7 @@ arange_kernel(T* __restrict__ out, int64_t n, double start, double step) {
 // word's top 24 bits scaled by 2^-24 (src/backend/cpu/philox.h:47-89).
 __global__ void __launch_bounds__(kThreads)
 rand_kernel(float* __restrict__ out, int64_t n, uint64_t seed, uint64_t offset) {
+    pdl_prologue();
     const int64_t stride = int64_t(gridDim.x) * blockDim.x;
     for (int64_t i = int64_t(blockIdx.x) * blockDim.x + threadIdx.x; i < n; i += stride) {
         uint32_t c0 = static_cast<uint32_t>(i), c1 = static_cast<uint32_t>(uint64_t(i) >> 32);
@@ -907,6 +911,7 @@ rand_kernel(float* __restrict__ out, int64_t n, uint64_t seed, uint64_t offset) 
 __global__ void __launch_bounds__(kThreads)
 tri_kernel(float* __restrict__ out, const float* __restrict__ in, Geo gin, int64_t n, int64_t width,
            int64_t height, int diagonal, int upper) {
+    pdl_prologue();
     const int64_t stride = int64_t(gridDim.x) * blockDim.x;
     for (int64_t i = int64_t(blockIdx.x) * blockDim.x + threadIdx.x; i < n; i += stride) {
         const int64_t col = i % width;
@@ -922,6 +927,7 @@ template <typename T>
 __global__ void __launch_bounds__(kThreads)
 cat_kernel(T* __restrict__ out, const T* __restrict__ a, const T* __restrict__ b, Geo ga, Geo gb,
            int64_t n, int64_t inner, int64_t out_extent, int64_t a_extent, int64_t b_extent) {
+    pdl_prologue();
     const int64_t stride = int64_t(gridDim.x) * blockDim.x;
     for (int64_t i = int64_t(blockIdx.x) * blockDim.x + threadIdx.x; i < n; i += stride) {
         const int64_t rest = i % inner;
@@ -940,6 +946,7 @@ cat_kernel(T* __restrict__ out, const T* __restrict__ a, const T* __restrict__ b
 __global__ void __launch_bounds__(kThreads)
 slice_backward_kernel(float* __restrict__ out, const float* __restrict__ g, Geo gout, Geo gg,
                       int64_t n, int axis, int64_t start, int64_t step) {
+    pdl_prologue();
     const int64_t stride = int64_t(gridDim.x) * blockDim.x;
     for (int64_t i = int64_t(blockIdx.x) * blockDim.x + threadIdx.x; i < n; i += stride) {
         int64_t rem = i;
@@ -974,7 +981,7 @@ void run_full(b200_ctx* ctx, const b200_node& node) {
     const unsigned g = grid_for(ceil_div(n, 4), kThreads);
     switch (out.dtype) {
         case B200_F32:
-            fill_kernel<float><<<g, kThreads, 0, ctx->stream>>>(reinterpret_cast<float*>(out.data), n,
+            launch_kernel(ctx, fill_kernel<float>, g, kThreads, 0, reinterpret_cast<float*>(out.data), n,
                                                                static_cast<float>(p.value));
             break;
         case B200_F16: {
@@ -989,21 +996,17 @@ void run_full(b200_ctx* ctx, const b200_node& node) {
                 const __half h = __float2half_rn(f);
                 std::memcpy(&bits, &h, 2);
             }
-            fill_kernel<uint16_t><<<g, kThreads, 0, ctx->stream>>>(
-                reinterpret_cast<uint16_t*>(out.data), n, bits);
+            launch_kernel(ctx, fill_kernel<uint16_t>, g, kThreads, 0, reinterpret_cast<uint16_t*>(out.data), n, bits);
             break;
         }
         case B200_I64:
-            fill_kernel<int64_t><<<g, kThreads, 0, ctx->stream>>>(
-                reinterpret_cast<int64_t*>(out.data), n, static_cast<int64_t>(p.value));
+            launch_kernel(ctx, fill_kernel<int64_t>, g, kThreads, 0, reinterpret_cast<int64_t*>(out.data), n, static_cast<int64_t>(p.value));
             break;
         case B200_I32:
-            fill_kernel<int32_t><<<g, kThreads, 0, ctx->stream>>>(
-                reinterpret_cast<int32_t*>(out.data), n, static_cast<int32_t>(p.value));
+            launch_kernel(ctx, fill_kernel<int32_t>, g, kThreads, 0, reinterpret_cast<int32_t*>(out.data), n, static_cast<int32_t>(p.value));
             break;
         case B200_BOOL:
-            fill_kernel<uint8_t><<<g, kThreads, 0, ctx->stream>>>(
-                reinterpret_cast<uint8_t*>(out.data), n, static_cast<uint8_t>(p.value != 0.0 ? 1 : 0));
+            launch_kernel(ctx, fill_kernel<uint8_t>, g, kThreads, 0, reinterpret_cast<uint8_t*>(out.data), n, static_cast<uint8_t>(p.value != 0.0 ? 1 : 0));
             break;
         default: fail(B200_DTYPE_ERROR, "full: unsupported dtype");
     }
@@ -1053,11 +1056,9 @@ void launch_elementwise(b200_ctx* ctx, const b200_node& node) {
             const auto p = get_params<ArangeParams>(node);
             if (out.numel == 0) return;
             if (out.dtype == B200_F32) {
-                arange_kernel<float><<<grid_for(out.numel, kThreads), kThreads, 0, ctx->stream>>>(
-                    reinterpret_cast<float*>(out.data), out.numel, p.start, p.step);
+                launch_kernel(ctx, arange_kernel<float>, grid_for(out.numel, kThreads), kThreads, 0, reinterpret_cast<float*>(out.data), out.numel, p.start, p.step);
             } else if (out.dtype == B200_I64) {
-                arange_kernel<int64_t><<<grid_for(out.numel, kThreads), kThreads, 0, ctx->stream>>>(
-                    reinterpret_cast<int64_t*>(out.data), out.numel, p.start, p.step);
+                launch_kernel(ctx, arange_kernel<int64_t>, grid_for(out.numel, kThreads), kThreads, 0, reinterpret_cast<int64_t*>(out.data), out.numel, p.start, p.step);
             } else {
                 fail(B200_DTYPE_ERROR, "arange: unsupported dtype");
             }
@@ -1070,8 +1071,7 @@ void launch_elementwise(b200_ctx* ctx, const b200_node& node) {
             const View out = make_view(node.out);
             const auto p = get_params<RandParams>(node);
             if (out.numel == 0) return;
-            rand_kernel<<<grid_for(out.numel, kThreads), kThreads, 0, ctx->stream>>>(
-                reinterpret_cast<float*>(out.data), out.numel, p.seed, p.offset);
+            launch_kernel(ctx, rand_kernel, grid_for(out.numel, kThreads), kThreads, 0, reinterpret_cast<float*>(out.data), out.numel, p.seed, p.offset);
             ctx->count_launch();
             check_last_launch("rand");
             return;
@@ -1095,8 +1095,7 @@ void launch_elementwise(b200_ctx* ctx, const b200_node& node) {
             const View in = make_view(node.src[0]);
             if (out.numel == 0) return;
             const auto p = get_params<TriParams>(node);
-            tri_kernel<<<grid_for(out.numel, kThreads), kThreads, 0, ctx->stream>>>(
-                reinterpret_cast<float*>(out.data), reinterpret_cast<const float*>(in.data),
+            launch_kernel(ctx, tri_kernel, grid_for(out.numel, kThreads), kThreads, 0, reinterpret_cast<float*>(out.data), reinterpret_cast<const float*>(in.data),
                 geo_of(in), out.numel, out.dim[3], out.dim[2], p.diagonal,
                 node.op == B200_OP_TRIU ? 1 : 0);
             ctx->count_launch();
@@ -1113,8 +1112,7 @@ void launch_elementwise(b200_ctx* ctx, const b200_node& node) {
             for (int i = axis + 1; i < kMaxDims; ++i) inner *= out.dim[i];
             const unsigned g = grid_for(out.numel, kThreads);
             if (dtype_size(out.dtype) == 4) {
-                cat_kernel<uint32_t><<<g, kThreads, 0, ctx->stream>>>(
-                    reinterpret_cast<uint32_t*>(out.data), reinterpret_cast<const uint32_t*>(a.data),
+                launch_kernel(ctx, cat_kernel<uint32_t>, g, kThreads, 0, reinterpret_cast<uint32_t*>(out.data), reinterpret_cast<const uint32_t*>(a.data),
                     reinterpret_cast<const uint32_t*>(b.data), geo_of(a), geo_of(b), out.numel, inner,
                     out.dim[axis], a.dim[axis], b.dim[axis]);
             } else {
@@ -1130,8 +1128,7 @@ void launch_elementwise(b200_ctx* ctx, const b200_node& node) {
             const View g = make_view(node.src[0]);
             if (out.numel == 0) return;
             const auto p = get_params<SliceParams>(node);
-            slice_backward_kernel<<<grid_for(out.numel, kThreads), kThreads, 0, ctx->stream>>>(
-                reinterpret_cast<float*>(out.data), reinterpret_cast<const float*>(g.data),
+            launch_kernel(ctx, slice_backward_kernel, grid_for(out.numel, kThreads), kThreads, 0, reinterpret_cast<float*>(out.data), reinterpret_cast<const float*>(g.data),
                 geo_of(out), geo_of(g), out.numel, p.axis + (kMaxDims - node.out.ndim), p.start,
                 p.step);
             ctx->count_launch();

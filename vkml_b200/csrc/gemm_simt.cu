@@ -18,6 +18,7 @@ constexpr int BM = 64, BN = 64, BK = 16;
 
 __global__ void __launch_bounds__(256)
 gemm_simt_kernel(GemmProblem p, float* __restrict__ dst, int64_t k_chunk, int64_t split_stride) {
+    pdl_prologue();
     __shared__ float As[BK][BM + 4];
     __shared__ float Bs[BK][BN + 4];
 
@@ -109,6 +110,7 @@ gemm_simt_kernel(GemmProblem p, float* __restrict__ dst, int64_t k_chunk, int64_
 
 __global__ void __launch_bounds__(256)
 split_fold_kernel(float* __restrict__ out, const float* __restrict__ partial, int64_t n, int splits) {
+    pdl_prologue();
     const int64_t stride = int64_t(gridDim.x) * blockDim.x;
     for (int64_t i = int64_t(blockIdx.x) * blockDim.x + threadIdx.x; i < n; i += stride) {
         float acc = partial[i];
@@ -150,10 +152,10 @@ void gemm_simt(b200_ctx* ctx, const GemmProblem& p) {
     }
     dim3 grid(static_cast<unsigned>(tiles), 1, static_cast<unsigned>(splits));
     ProfScope scope(ctx, "matmul.fp32_simt");
-    gemm_simt_kernel<<<grid, 256, 0, ctx->stream>>>(p, dst, k_chunk, out_elems);
+    launch_kernel(ctx, gemm_simt_kernel, grid, 256, 0, p, dst, k_chunk, out_elems);
     ctx->count_launch();
     if (splits > 1) {
-        split_fold_kernel<<<grid_for(out_elems, 256), 256, 0, ctx->stream>>>(p.out, dst, out_elems,
+        launch_kernel(ctx, split_fold_kernel, grid_for(out_elems, 256), 256, 0, p.out, dst, out_elems,
                                                                            static_cast<int>(splits));
         ctx->count_launch();
     }

@@ -271,6 +271,7 @@ struct SplitArgs {
 // Source rows dense along K and 16-byte aligned: one thread per four K-elements, 128-bit
 // loads and stores, no shared memory.
 __global__ void __launch_bounds__(256) split_rows_kernel(SplitArgs a) {
+    pdl_prologue();
     const int64_t kp4 = a.kp / 4;
     const int64_t total = kp4 * a.out_rows * a.n_batches;
     const int64_t step = int64_t(gridDim.x) * blockDim.x;
@@ -311,6 +312,7 @@ __global__ void __launch_bounds__(256) split_rows_kernel(SplitArgs a) {
 constexpr int kSplitTile = 64;
 
 __global__ void __launch_bounds__(256) split_kernel(SplitArgs a) {
+    pdl_prologue();
     __shared__ float tile[kSplitTile][kSplitTile + 1];  // [row][k]
     const int fast = threadIdx.x & 63, slow = threadIdx.x >> 6;
     const int64_t tiles_k = a.kp / kSplitTile + (a.kp % kSplitTile != 0);
@@ -368,10 +370,10 @@ void launch_split(b200_ctx* ctx, const SplitArgs& s, const char* label) {
                             reinterpret_cast<uintptr_t>(s.src) % 16 == 0;
     if (rows_dense) {
         const int64_t total = (s.kp / 4) * s.out_rows * s.n_batches;
-        split_rows_kernel<<<grid_for(ceil_div(total, 2), 256), 256, 0, ctx->stream>>>(s);
+        launch_kernel(ctx, split_rows_kernel, grid_for(ceil_div(total, 2), 256), 256, 0, s);
     } else {
         const int64_t tiles = ceil_div(s.kp, kSplitTile) * ceil_div(s.rows, kSplitTile) * s.n_batches;
-        split_kernel<<<grid_for(tiles, 1, 8), 256, 0, ctx->stream>>>(s);
+        launch_kernel(ctx, split_kernel, grid_for(tiles, 1, 8), 256, 0, s);
     }
     ctx->count_launch();
 }
@@ -475,6 +477,9 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a_hi, const __grid_consta
     tc_fence_after();
     const uint32_t tmem_base = tmem_base_slot;
     volatile int* abort_p = &abort_flag;
+    // barriers and tensor memory are set up: only now wait for the previous kernel (the operand
+    // split, usually), so this kernel's set-up runs under that kernel's tail
+    pdl_prologue();
 
     const int64_t tiles_per_batch = g.tiles_m * g.tiles_n;
     const int64_t n_units = tiles_per_batch * g.batches * g.splits;
@@ -794,6 +799,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a_hi, const __grid_consta
 
 __global__ void __launch_bounds__(256)
 fold_partials_kernel(float* __restrict__ out, const float* __restrict__ partial, int64_t n, int splits) {
+    pdl_prologue();
     const int64_t stride = int64_t(gridDim.x) * blockDim.x;
     for (int64_t i = int64_t(blockIdx.x) * blockDim.x + threadIdx.x; i < n; i += stride) {
         float acc = partial[i];
@@ -887,12 +893,12 @@ void launch_one(b200_ctx* ctx, const CUtensorMap& ah, const CUtensorMap& al, con
     if (direct != nullptr) {
         auto kernel = gemm_tc_kernel<BN, STAGES, THREE, A_MN, B_MN, true>;
         B200_CUDA_CHECK(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, S::kTotal));
-        kernel<<<grid, kThreadsDirect, S::kTotal, ctx->stream>>>(ah, al, bh, bl, g, *direct);
+        launch_kernel(ctx, kernel, grid, kThreadsDirect, S::kTotal, ah, al, bh, bl, g, *direct);
         return;
     }
     auto kernel = gemm_tc_kernel<BN, STAGES, THREE, A_MN, B_MN, false>;
     B200_CUDA_CHECK(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, S::kTotal));
-    kernel<<<grid, kThreads, S::kTotal, ctx->stream>>>(ah, al, bh, bl, g, DirectArgs{});
+    launch_kernel(ctx, kernel, grid, kThreads, S::kTotal, ah, al, bh, bl, g, DirectArgs{});
 }
 
 template <int BN, int STAGES>
@@ -1118,7 +1124,7 @@ void gemm_tc(b200_ctx* ctx, const GemmProblem& p, bool three_pass) {
         check_last_launch("matmul (tcgen05, direct operands)");
         if (splits > 1) {
             ProfScope scope(ctx, "matmul.fold");
-            fold_partials_kernel<<<grid_for(out_elems, 256), 256, 0, ctx->stream>>>(p.out, partial, out_elems,
+            launch_kernel(ctx, fold_partials_kernel, grid_for(out_elems, 256), 256, 0, p.out, partial, out_elems,
                                                                                   static_cast<int>(splits));
             ctx->count_launch();
             check_last_launch("matmul (fold)");
@@ -1237,7 +1243,7 @@ void gemm_tc(b200_ctx* ctx, const GemmProblem& p, bool three_pass) {
 
     if (splits > 1) {
         ProfScope scope(ctx, "matmul.fold");
-        fold_partials_kernel<<<grid_for(out_elems, 256), 256, 0, ctx->stream>>>(p.out, partial, out_elems,
+        launch_kernel(ctx, fold_partials_kernel, grid_for(out_elems, 256), 256, 0, p.out, partial, out_elems,
                                                                               static_cast<int>(splits));
         ctx->count_launch();
         check_last_launch("matmul (fold)");

@@ -72,6 +72,7 @@ Strides4 strides_of(const View& v) {
 __global__ void __launch_bounds__(kThreads)
 im2col_kernel(float* __restrict__ out, const float* __restrict__ in, Strides4 is, Win w, int positions,
               int chunks) {
+    pdl_prologue();
     const unsigned b = blockIdx.x;
     const unsigned chunk = b % chunks;
     const unsigned nc = b / chunks;  // n * channels + c
@@ -109,6 +110,7 @@ im2col_kernel(float* __restrict__ out, const float* __restrict__ in, Strides4 is
 template <bool UNIT, int KH, int KW>
 __global__ void __launch_bounds__(kThreads)
 col2im_kernel(float* __restrict__ out, const float* __restrict__ cols, Strides4 cs, Win w, int chunks) {
+    pdl_prologue();
     const unsigned b = blockIdx.x;
     const unsigned chunk = b % chunks;
     const unsigned plane = b / chunks;  // n * channels + c
@@ -170,6 +172,7 @@ template <int KH, int KW>
 __global__ void __launch_bounds__(kThreads)
 im2col_dense_kernel(float* __restrict__ out, const float* __restrict__ in, DenseGeo g, FastDiv div_w4,
                     FastDiv div_w, FastDiv div_h, FastDiv div_l4, FastDiv div_ow) {
+    pdl_prologue();
     extern __shared__ __align__(16) float tile[];  // group x (h + 2 ph) x (w + 2 pw), zero border
     const int kh = KH > 0 ? KH : g.kh, kw = KW > 0 ? KW : g.kw;
     const int first = blockIdx.x * g.group;
@@ -227,6 +230,7 @@ template <int KH, int KW>
 __global__ void __launch_bounds__(kThreads)
 col2im_dense_kernel(float* __restrict__ out, const float* __restrict__ cols, DenseGeo g, FastDiv div_hw4,
                     FastDiv div_w) {
+    pdl_prologue();
     extern __shared__ __align__(16) float tile[];  // group x (kh kw) x L: this block's slice of the columns
     const int kh = KH > 0 ? KH : g.kh, kw = KW > 0 ? KW : g.kw;
     const int kk = kh * kw;
@@ -278,6 +282,7 @@ col2im_dense_kernel(float* __restrict__ out, const float* __restrict__ cols, Den
 __global__ void __launch_bounds__(kThreads)
 max_pool2d_dense2_kernel(float* __restrict__ out, const float* __restrict__ in, int h, int w, int out_h,
                          uint32_t items, FastDiv div_ow4, FastDiv div_oh, uint32_t* status) {
+    pdl_prologue();
     const uint32_t step = gridDim.x * kThreads;
     const int out_w = w / 2;
     for (uint32_t i = blockIdx.x * kThreads + threadIdx.x; i < items; i += step) {
@@ -329,6 +334,7 @@ max_pool2d_dense2_kernel(float* __restrict__ out, const float* __restrict__ in, 
 __global__ void __launch_bounds__(kThreads)
 max_pool2d_backward_dense2_kernel(float* __restrict__ out, const float* __restrict__ grad,
                                   const float* __restrict__ in, int w, uint32_t items, FastDiv div_ow4) {
+    pdl_prologue();
     const uint32_t step = gridDim.x * kThreads;
     const int out_w = w / 2;
     for (uint32_t i = blockIdx.x * kThreads + threadIdx.x; i < items; i += step) {
@@ -405,6 +411,7 @@ __device__ __forceinline__ int argmax_in_window(const float* plane, int64_t sh_,
 __global__ void __launch_bounds__(kThreads)
 max_pool2d_kernel(float* __restrict__ out, const float* __restrict__ in, Strides4 is, Win w, int out_h,
                   int out_w, int channels, int chunks, uint32_t* status) {
+    pdl_prologue();
     const unsigned b = blockIdx.x;
     const unsigned chunk = b % chunks;
     const unsigned plane = b / chunks;
@@ -433,6 +440,7 @@ template <int KH, int KW>
 __global__ void __launch_bounds__(kThreads)
 max_pool2d_tiled_kernel(float* __restrict__ out, const float* __restrict__ in, Strides4 is, int out_h, int out_w,
                         int channels, int chunks, int vec_ok, uint32_t* status) {
+    pdl_prologue();
     const unsigned b = blockIdx.x;
     const unsigned chunk = b % chunks;
     const unsigned plane = b / chunks;
@@ -481,6 +489,7 @@ max_pool2d_tiled_kernel(float* __restrict__ out, const float* __restrict__ in, S
 __global__ void __launch_bounds__(kThreads)
 max_pool2d_backward_kernel(float* __restrict__ out, const float* __restrict__ grad, const float* __restrict__ in,
                            Strides4 gs, Strides4 is, Win w, int out_h, int out_w, int channels, int chunks) {
+    pdl_prologue();
     const unsigned b = blockIdx.x;
     const unsigned chunk = b % chunks;
     const unsigned plane = b / chunks;
@@ -533,6 +542,7 @@ __global__ void __launch_bounds__(kThreads)
 max_pool2d_backward_tiled_kernel(float* __restrict__ out, const float* __restrict__ grad,
                                  const float* __restrict__ in, Strides4 gs, Strides4 is, Win w, int out_h,
                                  int out_w, int cover_h, int cover_w, int channels, int chunks) {
+    pdl_prologue();
     const unsigned b = blockIdx.x;
     const unsigned chunk = b % chunks;
     const unsigned plane = b / chunks;
@@ -591,6 +601,7 @@ template <typename T, typename I>
 __global__ void __launch_bounds__(kThreads)
 index_select_kernel(T* __restrict__ out, const T* __restrict__ a, const int64_t* __restrict__ idx, GeoT<I> ga,
                     I idx_stride, I inner, I extent, I a_extent, I total, uint32_t* status) {
+    pdl_prologue();
     const int64_t stride = int64_t(gridDim.x) * blockDim.x;
     for (int64_t li = int64_t(blockIdx.x) * blockDim.x + threadIdx.x; li < int64_t(total); li += stride) {
         const I i = static_cast<I>(li);
@@ -612,6 +623,7 @@ __global__ void __launch_bounds__(kThreads)
 index_select_rows_kernel(uint4* __restrict__ out, const uint4* __restrict__ a, const int64_t* __restrict__ idx,
                          int64_t idx_stride, unsigned inner16, unsigned extent, unsigned a_extent,
                          unsigned total16, uint32_t* status) {
+    pdl_prologue();
     const int64_t stride = int64_t(gridDim.x) * blockDim.x;
     for (int64_t li = int64_t(blockIdx.x) * blockDim.x + threadIdx.x; li < int64_t(total16); li += stride) {
         const unsigned i = static_cast<unsigned>(li);
@@ -633,6 +645,7 @@ template <typename I>
 __global__ void __launch_bounds__(kThreads)
 scatter_add_kernel(float* __restrict__ out, const float* __restrict__ src, const int64_t* __restrict__ idx,
                    GeoT<I> gsrc, I idx_stride, I inner, I src_extent, I out_extent, I total) {
+    pdl_prologue();
     const int64_t stride = int64_t(gridDim.x) * blockDim.x;
     for (int64_t li = int64_t(blockIdx.x) * blockDim.x + threadIdx.x; li < int64_t(total); li += stride) {
         const I i = static_cast<I>(li);
@@ -655,6 +668,7 @@ scatter_add_kernel(float* __restrict__ out, const float* __restrict__ src, const
 __global__ void __launch_bounds__(kThreads)
 index_range_kernel(const int64_t* __restrict__ idx, int64_t idx_stride, int64_t n, int64_t extent,
                    uint32_t* status) {
+    pdl_prologue();
     const int64_t k = int64_t(blockIdx.x) * blockDim.x + threadIdx.x;
     if (k < n) {
         const int64_t t = idx[k * idx_stride];
@@ -770,10 +784,10 @@ void launch_movement(b200_ctx* ctx, const b200_node& node) {
                         div_l4(static_cast<uint32_t>(positions / 4)), div_ow(w.out_w);
                     const float* src = reinterpret_cast<const float*>(in.data);
                     if (w.kh == 3 && w.kw == 3) {
-                        im2col_dense_kernel<3, 3><<<grid, kThreads, smem, ctx->stream>>>(o, src, g, div_w4, div_w, div_h,
+                        launch_kernel(ctx, im2col_dense_kernel<3, 3>, grid, kThreads, smem, o, src, g, div_w4, div_w, div_h,
                                                                                          div_l4, div_ow);
                     } else {
-                        im2col_dense_kernel<0, 0><<<grid, kThreads, smem, ctx->stream>>>(o, src, g, div_w4, div_w, div_h,
+                        launch_kernel(ctx, im2col_dense_kernel<0, 0>, grid, kThreads, smem, o, src, g, div_w4, div_w, div_h,
                                                                                          div_l4, div_ow);
                     }
                     break;
@@ -782,8 +796,7 @@ void launch_movement(b200_ctx* ctx, const b200_node& node) {
             const int block = block_for(positions);
             const int64_t chunks = ceil_div(positions, block);
             check_grid(n * w.channels * chunks, "im2col");
-            im2col_kernel<<<static_cast<unsigned>(n * w.channels * chunks), block, 0, ctx->stream>>>(
-                o, reinterpret_cast<const float*>(in.data), strides_of(in), w, static_cast<int>(positions),
+            launch_kernel(ctx, im2col_kernel, static_cast<unsigned>(n * w.channels * chunks), block, 0, o, reinterpret_cast<const float*>(in.data), strides_of(in), w, static_cast<int>(positions),
                 static_cast<int>(chunks));
             break;
         }
@@ -826,9 +839,9 @@ void launch_movement(b200_ctx* ctx, const b200_node& node) {
                     }();
                     (void)once;
                     if (w.kh == 3 && w.kw == 3) {
-                        col2im_dense_kernel<3, 3><<<grid, kThreads, smem, ctx->stream>>>(o, src, g, div_hw4, div_w);
+                        launch_kernel(ctx, col2im_dense_kernel<3, 3>, grid, kThreads, smem, o, src, g, div_hw4, div_w);
                     } else {
-                        col2im_dense_kernel<0, 0><<<grid, kThreads, smem, ctx->stream>>>(o, src, g, div_hw4, div_w);
+                        launch_kernel(ctx, col2im_dense_kernel<0, 0>, grid, kThreads, smem, o, src, g, div_hw4, div_w);
                     }
                     break;
                 }
@@ -838,13 +851,13 @@ void launch_movement(b200_ctx* ctx, const b200_node& node) {
             check_grid(n * w.channels * chunks, "col2im");
             const unsigned grid = static_cast<unsigned>(n * w.channels * chunks);
             if (unit && w.kh == 3 && w.kw == 3) {
-                col2im_kernel<true, 3, 3><<<grid, block, 0, ctx->stream>>>(o, src, strides_of(cols), w,
+                launch_kernel(ctx, col2im_kernel<true, 3, 3>, grid, block, 0, o, src, strides_of(cols), w,
                                                                            static_cast<int>(chunks));
             } else if (unit) {
-                col2im_kernel<true, 0, 0><<<grid, block, 0, ctx->stream>>>(o, src, strides_of(cols), w,
+                launch_kernel(ctx, col2im_kernel<true, 0, 0>, grid, block, 0, o, src, strides_of(cols), w,
                                                                            static_cast<int>(chunks));
             } else {
-                col2im_kernel<false, 0, 0><<<grid, block, 0, ctx->stream>>>(o, src, strides_of(cols), w,
+                launch_kernel(ctx, col2im_kernel<false, 0, 0>, grid, block, 0, o, src, strides_of(cols), w,
                                                                             static_cast<int>(chunks));
             }
             break;
@@ -874,8 +887,7 @@ void launch_movement(b200_ctx* ctx, const b200_node& node) {
                 total / 4 < kMax32 && out.dim[0] * out.dim[1] * w.image_h < kMax32) {
                 const uint32_t items = static_cast<uint32_t>(total / 4);
                 const FastDiv div_ow4(static_cast<uint32_t>(out.dim[3] / 4)), div_oh(static_cast<uint32_t>(out.dim[2]));
-                max_pool2d_dense2_kernel<<<grid_for(items, kThreads), kThreads, 0, ctx->stream>>>(
-                    o, reinterpret_cast<const float*>(in.data), w.image_h, w.image_w, static_cast<int>(out.dim[2]), items,
+                launch_kernel(ctx, max_pool2d_dense2_kernel, grid_for(items, kThreads), kThreads, 0, o, reinterpret_cast<const float*>(in.data), w.image_h, w.image_w, static_cast<int>(out.dim[2]), items,
                     div_ow4, div_oh, ctx->d_status);
                 break;
             }
@@ -885,18 +897,15 @@ void launch_movement(b200_ctx* ctx, const b200_node& node) {
                 const int vec_ok = in.stride[3] == 1 && in.stride[2] % 2 == 0 && in.stride[1] % 2 == 0 &&
                                    in.stride[0] % 2 == 0 && reinterpret_cast<uintptr_t>(src) % 8 == 0;
                 if (w.kh == 2) {
-                    max_pool2d_tiled_kernel<2, 2><<<grid, block, 0, ctx->stream>>>(
-                        o, src, strides_of(in), static_cast<int>(out.dim[2]), static_cast<int>(out.dim[3]),
+                    launch_kernel(ctx, max_pool2d_tiled_kernel<2, 2>, grid, block, 0, o, src, strides_of(in), static_cast<int>(out.dim[2]), static_cast<int>(out.dim[3]),
                         static_cast<int>(out.dim[1]), static_cast<int>(chunks), vec_ok, ctx->d_status);
                 } else {
-                    max_pool2d_tiled_kernel<3, 3><<<grid, block, 0, ctx->stream>>>(
-                        o, src, strides_of(in), static_cast<int>(out.dim[2]), static_cast<int>(out.dim[3]),
+                    launch_kernel(ctx, max_pool2d_tiled_kernel<3, 3>, grid, block, 0, o, src, strides_of(in), static_cast<int>(out.dim[2]), static_cast<int>(out.dim[3]),
                         static_cast<int>(out.dim[1]), static_cast<int>(chunks), 0, ctx->d_status);
                 }
                 break;
             }
-            max_pool2d_kernel<<<static_cast<unsigned>(out.dim[0] * out.dim[1] * chunks), block, 0, ctx->stream>>>(
-                o, reinterpret_cast<const float*>(in.data), strides_of(in), w, static_cast<int>(out.dim[2]),
+            launch_kernel(ctx, max_pool2d_kernel, static_cast<unsigned>(out.dim[0] * out.dim[1] * chunks), block, 0, o, reinterpret_cast<const float*>(in.data), strides_of(in), w, static_cast<int>(out.dim[2]),
                 static_cast<int>(out.dim[3]), static_cast<int>(out.dim[1]), static_cast<int>(chunks), ctx->d_status);
             break;
         }
@@ -931,8 +940,7 @@ void launch_movement(b200_ctx* ctx, const b200_node& node) {
                 total / 16 < kMax32) {
                 const uint32_t items = static_cast<uint32_t>(planes * out_h * (out_w / 4));
                 const FastDiv div_ow4(static_cast<uint32_t>(out_w / 4));
-                max_pool2d_backward_dense2_kernel<<<grid_for(items, kThreads), kThreads, 0, ctx->stream>>>(
-                    o, g, src, w.image_w, items, div_ow4);
+                launch_kernel(ctx, max_pool2d_backward_dense2_kernel, grid_for(items, kThreads), kThreads, 0, o, g, src, w.image_w, items, div_ow4);
                 break;
             }
             if (tiled) {
@@ -944,12 +952,10 @@ void launch_movement(b200_ctx* ctx, const b200_node& node) {
                 check_grid(planes * chunks, "max_pool2d_backward");
                 const unsigned grid = static_cast<unsigned>(planes * chunks);
                 if (w.kh == 2) {
-                    max_pool2d_backward_tiled_kernel<2, 2><<<grid, block, 0, ctx->stream>>>(
-                        o, g, src, strides_of(grad), strides_of(in), w, out_h, out_w, cover_h, cover_w,
+                    launch_kernel(ctx, max_pool2d_backward_tiled_kernel<2, 2>, grid, block, 0, o, g, src, strides_of(grad), strides_of(in), w, out_h, out_w, cover_h, cover_w,
                         static_cast<int>(out.dim[1]), static_cast<int>(chunks));
                 } else {
-                    max_pool2d_backward_tiled_kernel<3, 3><<<grid, block, 0, ctx->stream>>>(
-                        o, g, src, strides_of(grad), strides_of(in), w, out_h, out_w, cover_h, cover_w,
+                    launch_kernel(ctx, max_pool2d_backward_tiled_kernel<3, 3>, grid, block, 0, o, g, src, strides_of(grad), strides_of(in), w, out_h, out_w, cover_h, cover_w,
                         static_cast<int>(out.dim[1]), static_cast<int>(chunks));
                 }
             } else {
@@ -957,8 +963,7 @@ void launch_movement(b200_ctx* ctx, const b200_node& node) {
                 const int block = block_for(per_plane);
                 const int64_t chunks = ceil_div(per_plane, block);
                 check_grid(planes * chunks, "max_pool2d_backward");
-                max_pool2d_backward_kernel<<<static_cast<unsigned>(planes * chunks), block, 0, ctx->stream>>>(
-                    o, g, src, strides_of(grad), strides_of(in), w, out_h, out_w, static_cast<int>(out.dim[1]),
+                launch_kernel(ctx, max_pool2d_backward_kernel, static_cast<unsigned>(planes * chunks), block, 0, o, g, src, strides_of(grad), strides_of(in), w, out_h, out_w, static_cast<int>(out.dim[1]),
                     static_cast<int>(chunks));
             }
             break;
@@ -983,15 +988,14 @@ void launch_movement(b200_ctx* ctx, const b200_node& node) {
             if (a.contiguous && row_bytes % 16 == 0 && small && reinterpret_cast<uintptr_t>(a.data) % 16 == 0 &&
                 reinterpret_cast<uintptr_t>(out.data) % 16 == 0) {
                 const int64_t total16 = total * static_cast<int64_t>(esz) / 16;
-                index_select_rows_kernel<<<grid_for(total16, kThreads), kThreads, 0, ctx->stream>>>(
-                    reinterpret_cast<uint4*>(out.data), reinterpret_cast<const uint4*>(a.data), ip, istride,
+                launch_kernel(ctx, index_select_rows_kernel, grid_for(total16, kThreads), kThreads, 0, reinterpret_cast<uint4*>(out.data), reinterpret_cast<const uint4*>(a.data), ip, istride,
                     static_cast<unsigned>(row_bytes / 16), static_cast<unsigned>(out.dim[axis]),
                     static_cast<unsigned>(a.dim[axis]), static_cast<unsigned>(total16), ctx->d_status);
                 break;
             }
             const unsigned grid = grid_for(total, kThreads);
 #define B200_INDEX_SELECT(T, I)                                                                              \
-    index_select_kernel<T, I><<<grid, kThreads, 0, ctx->stream>>>(                                           \
+    launch_kernel(ctx, index_select_kernel<T, I>, grid, kThreads, 0, \
         reinterpret_cast<T*>(out.data), reinterpret_cast<const T*>(a.data), ip, geo_t<I>(a),                 \
         static_cast<I>(istride), static_cast<I>(inner), static_cast<I>(out.dim[axis]),                       \
         static_cast<I>(a.dim[axis]), static_cast<I>(total), ctx->d_status)
@@ -1023,20 +1027,17 @@ void launch_movement(b200_ctx* ctx, const b200_node& node) {
             const int64_t istride = index_stride(idx);
             const int64_t n_idx = src.numel == 0 ? 0 : src.dim[axis];
             if (n_idx > 0) {
-                index_range_kernel<<<static_cast<unsigned>(ceil_div(n_idx, kThreads)), kThreads, 0, ctx->stream>>>(
-                    ip, istride, n_idx, out.dim[axis], ctx->d_status);
+                launch_kernel(ctx, index_range_kernel, static_cast<unsigned>(ceil_div(n_idx, kThreads)), kThreads, 0, ip, istride, n_idx, out.dim[axis], ctx->d_status);
                 ctx->count_launch();
             }
             const unsigned grid = grid_for(total, kThreads);
             const float* sp = reinterpret_cast<const float*>(src.data);
             const bool small = total < kMax32 && fits32(src) && istride >= 0 && istride * std::max<int64_t>(n_idx, 1) < kMax32;
             if (small) {
-                scatter_add_kernel<uint32_t><<<grid, kThreads, 0, ctx->stream>>>(
-                    o, sp, ip, geo_t<uint32_t>(src), static_cast<uint32_t>(istride), static_cast<uint32_t>(inner),
+                launch_kernel(ctx, scatter_add_kernel<uint32_t>, grid, kThreads, 0, o, sp, ip, geo_t<uint32_t>(src), static_cast<uint32_t>(istride), static_cast<uint32_t>(inner),
                     static_cast<uint32_t>(n_idx), static_cast<uint32_t>(out.dim[axis]), static_cast<uint32_t>(total));
             } else {
-                scatter_add_kernel<int64_t><<<grid, kThreads, 0, ctx->stream>>>(
-                    o, sp, ip, geo_t<int64_t>(src), istride, inner, n_idx, out.dim[axis], total);
+                launch_kernel(ctx, scatter_add_kernel<int64_t>, grid, kThreads, 0, o, sp, ip, geo_t<int64_t>(src), istride, inner, n_idx, out.dim[axis], total);
             }
             break;
         }

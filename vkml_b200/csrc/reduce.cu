@@ -190,6 +190,7 @@ template <typename P, int GROUP, bool VEC4, typename I>
 __global__ void __launch_bounds__(256)
 reduce_group_kernel(void* out, typename P::Acc* partial, unsigned* counters, const float* __restrict__ in,
                     RedGeoT<I> g, int64_t n_out, I n_units, int post, int64_t n_red) {
+    pdl_prologue();
     __shared__ typename P::Acc smem[8];
     __shared__ int last_flag;
     constexpr int kGroups = 256 / GROUP;
@@ -276,6 +277,7 @@ template <typename P, typename I>
 __global__ void __launch_bounds__(256)
 reduce_thread_kernel(void* out, typename P::Acc* partial, unsigned* counters, const float* __restrict__ in,
                      RedGeoT<I> g, int64_t n_out, I n_red, int post) {
+    pdl_prologue();
     __shared__ int last_flag;
     constexpr int U = 4;
     const int64_t o = int64_t(blockIdx.x) * blockDim.x + threadIdx.x;
@@ -329,6 +331,7 @@ template <typename P, typename I>
 __global__ void __launch_bounds__(256)
 reduce_thread4_kernel(float* out, float4* partial, unsigned* counters, const float* __restrict__ in,
                       RedGeoT<I> g, int64_t n_out4, I n_red, int post) {
+    pdl_prologue();
     __shared__ int last_flag;
     constexpr int U = 4;
     const int64_t o4 = int64_t(blockIdx.x) * blockDim.x + threadIdx.x;
@@ -394,6 +397,7 @@ template <typename P>
 __global__ void __launch_bounds__(256)
 reduce_finalize_kernel(void* out, const typename P::Acc* __restrict__ partial, int64_t n_out,
                        int splits, int post, int64_t n_red) {
+    pdl_prologue();
     const int64_t o = int64_t(blockIdx.x) * blockDim.x + threadIdx.x;
     if (o >= n_out) {
         return;
@@ -494,8 +498,7 @@ void launch_reduce_kernels(b200_ctx* ctx, const View& out, const float* src, con
                     part = static_cast<float4*>(ctx->ensure_workspace(sizeof(float4) * n_out4 * sp));
                 }
                 dim3 grid4(static_cast<unsigned>(bx), static_cast<unsigned>(sp));
-                reduce_thread4_kernel<P, I><<<grid4, 256, 0, ctx->stream>>>(
-                    reinterpret_cast<float*>(out.data), part, ctx->d_counters, src, g4, n_out4, static_cast<I>(n_red),
+                launch_kernel(ctx, reduce_thread4_kernel<P, I>, grid4, 256, 0, reinterpret_cast<float*>(out.data), part, ctx->d_counters, src, g4, n_out4, static_cast<I>(n_red),
                     post);
                 ctx->count_launch();
                 check_last_launch("reduce (thread x4)");
@@ -510,12 +513,11 @@ void launch_reduce_kernels(b200_ctx* ctx, const View& out, const float* src, con
             counters = blocks_x <= kMaxCounters ? ctx->d_counters : nullptr;
         }
         dim3 grid(static_cast<unsigned>(blocks_x), static_cast<unsigned>(splits));
-        reduce_thread_kernel<P, I><<<grid, 256, 0, ctx->stream>>>(out.data, partial, counters, src, g, n_out,
+        launch_kernel(ctx, reduce_thread_kernel<P, I>, grid, 256, 0, out.data, partial, counters, src, g, n_out,
                                                                   static_cast<I>(n_red), post);
         ctx->count_launch();
         if (splits > 1 && counters == nullptr) {
-            reduce_finalize_kernel<P><<<static_cast<unsigned>(blocks_x), 256, 0, ctx->stream>>>(
-                out.data, partial, n_out, static_cast<int>(splits), post, n_red);
+            launch_kernel(ctx, reduce_finalize_kernel<P>, static_cast<unsigned>(blocks_x), 256, 0, out.data, partial, n_out, static_cast<int>(splits), post, n_red);
             ctx->count_launch();
         }
         check_last_launch("reduce (thread)");
@@ -554,25 +556,24 @@ void launch_reduce_kernels(b200_ctx* ctx, const View& out, const float* src, con
     const I nu = static_cast<I>(n_units);
     if (warp) {
         if (vec4) {
-            reduce_group_kernel<P, 32, true, I><<<grid, 256, 0, ctx->stream>>>(out.data, partial, counters, src, g,
+            launch_kernel(ctx, reduce_group_kernel<P, 32, true, I>, grid, 256, 0, out.data, partial, counters, src, g,
                                                                                n_out, nu, post, n_red);
         } else {
-            reduce_group_kernel<P, 32, false, I><<<grid, 256, 0, ctx->stream>>>(out.data, partial, counters, src, g,
+            launch_kernel(ctx, reduce_group_kernel<P, 32, false, I>, grid, 256, 0, out.data, partial, counters, src, g,
                                                                                 n_out, nu, post, n_red);
         }
     } else {
         if (vec4) {
-            reduce_group_kernel<P, 256, true, I><<<grid, 256, 0, ctx->stream>>>(out.data, partial, counters, src, g,
+            launch_kernel(ctx, reduce_group_kernel<P, 256, true, I>, grid, 256, 0, out.data, partial, counters, src, g,
                                                                                 n_out, nu, post, n_red);
         } else {
-            reduce_group_kernel<P, 256, false, I><<<grid, 256, 0, ctx->stream>>>(out.data, partial, counters, src,
+            launch_kernel(ctx, reduce_group_kernel<P, 256, false, I>, grid, 256, 0, out.data, partial, counters, src,
                                                                                  g, n_out, nu, post, n_red);
         }
     }
     ctx->count_launch();
     if (splits > 1 && counters == nullptr) {
-        reduce_finalize_kernel<P><<<static_cast<unsigned>(ceil_div(n_out, 256)), 256, 0, ctx->stream>>>(
-            out.data, partial, n_out, static_cast<int>(splits), post, n_red);
+        launch_kernel(ctx, reduce_finalize_kernel<P>, static_cast<unsigned>(ceil_div(n_out, 256)), 256, 0, out.data, partial, n_out, static_cast<int>(splits), post, n_red);
         ctx->count_launch();
     }
     check_last_launch("reduce (group)");
@@ -645,6 +646,7 @@ template <bool LOG>
 __global__ void __launch_bounds__(256)
 softmax_thread_kernel(float* __restrict__ out, const float* __restrict__ in, SoftGeo g,
                       int64_t n_rows) {
+    pdl_prologue();
     const int64_t row = int64_t(blockIdx.x) * blockDim.x + threadIdx.x;
     if (row >= n_rows) {
         return;
@@ -716,6 +718,7 @@ __device__ __forceinline__ float block_all_sum(float v, float* smem) {
 template <bool LOG>
 __global__ void softmax_block_kernel(float* __restrict__ out, const float* __restrict__ in, SoftGeo g,
                                      int64_t n_rows, int staged, int vec4) {
+    pdl_prologue();
     extern __shared__ float row_cache[];
     __shared__ float red[32];
     for (int64_t row = blockIdx.x; row < n_rows; row += gridDim.x) {
@@ -784,6 +787,7 @@ __global__ void softmax_block_kernel(float* __restrict__ out, const float* __res
 template <bool LOG, int GROUP, int ITEMS, bool VEC4>
 __global__ void __launch_bounds__(GROUP == 32 ? 256 : GROUP)
 softmax_reg_kernel(float* __restrict__ out, const float* __restrict__ in, SoftGeo g, int64_t n_rows) {
+    pdl_prologue();
     constexpr int kBlock = GROUP == 32 ? 256 : GROUP;
     constexpr int kRows = kBlock / GROUP;
     constexpr int W = VEC4 ? 4 : 1;
@@ -881,6 +885,7 @@ template <bool LOG>
 __global__ void __launch_bounds__(1024, 1)
 softmax_bulk_kernel(float* __restrict__ out, const float* __restrict__ in, SoftGeo g, int64_t n_rows,
                     uint32_t* status) {
+    pdl_prologue();
     constexpr int ITEMS = 8;
     extern __shared__ __align__(128) unsigned char row_buf[];
     __shared__ float red[32];
@@ -1003,7 +1008,7 @@ void launch_softmax_bulk(b200_ctx* ctx, float* dst, const float* src, const Soft
         raised[LOG ? 1 : 0] = true;
     }
     const unsigned grid = static_cast<unsigned>(std::min<int64_t>(n_rows, kSmCount));
-    softmax_bulk_kernel<LOG><<<grid, 1024, smem, ctx->stream>>>(dst, src, g, n_rows, ctx->d_status);
+    launch_kernel(ctx, softmax_bulk_kernel<LOG>, grid, 1024, smem, dst, src, g, n_rows, ctx->d_status);
     ctx->count_launch();
     check_last_launch("softmax (bulk prefetch)");
 }
@@ -1014,7 +1019,7 @@ void launch_softmax_reg(b200_ctx* ctx, float* dst, const float* src, const SoftG
     constexpr int kRows = kBlock / GROUP;
     const int64_t blocks = ceil_div(n_rows, kRows);
     const unsigned grid = static_cast<unsigned>(std::min<int64_t>(blocks, int64_t(kSmCount) * (2048 / kBlock) * 4));
-    softmax_reg_kernel<LOG, GROUP, ITEMS, VEC4><<<grid, kBlock, 0, ctx->stream>>>(dst, src, g, n_rows);
+    launch_kernel(ctx, softmax_reg_kernel<LOG, GROUP, ITEMS, VEC4>, grid, kBlock, 0, dst, src, g, n_rows);
     ctx->count_launch();
     check_last_launch("softmax (registers)");
 }
@@ -1056,8 +1061,7 @@ void run_softmax(b200_ctx* ctx, const View& out, const View& in, int axis4) {
     float* dst = reinterpret_cast<float*>(out.data);
 
     if (g.n_axis <= 32) {
-        softmax_thread_kernel<LOG><<<static_cast<unsigned>(ceil_div(n_rows, 256)), 256, 0,
-                                     ctx->stream>>>(dst, src, g, n_rows);
+        launch_kernel(ctx, softmax_thread_kernel<LOG>, static_cast<unsigned>(ceil_div(n_rows, 256)), 256, 0, dst, src, g, n_rows);
         ctx->count_launch();
         check_last_launch("softmax (thread)");
         return;
@@ -1118,7 +1122,7 @@ void run_softmax(b200_ctx* ctx, const View& out, const View& in, int axis4) {
     }
     per_sm = std::max(per_sm, 1);
     const unsigned grid = static_cast<unsigned>(std::min<int64_t>(n_rows, int64_t(kSmCount) * per_sm));
-    softmax_block_kernel<LOG><<<grid, threads, smem, ctx->stream>>>(dst, src, g, n_rows, staged,
+    launch_kernel(ctx, softmax_block_kernel<LOG>, grid, threads, smem, dst, src, g, n_rows, staged,
                                                                    vec4 ? 1 : 0);
     ctx->count_launch();
     check_last_launch("softmax (block)");
