@@ -317,18 +317,9 @@ reduce_thread_kernel(void* out, typename P::Acc* partial, unsigned* counters, co
         return;
     }
     if (live) {
-        // eight partials in flight at a time, merged in split order
         typename P::Acc total = P::init();
-        for (I s0 = 0; s0 < splits; s0 += 8) {
-            typename P::Acc q[8];
-#pragma unroll
-            for (int j = 0; j < 8; ++j) {
-                if (s0 + j < splits) q[j] = partial[int64_t(s0 + j) * n_out + o];
-            }
-#pragma unroll
-            for (int j = 0; j < 8; ++j) {
-                if (s0 + j < splits) total = P::merge(total, q[j]);
-            }
+        for (I s = 0; s < splits; ++s) {
+            total = P::merge(total, partial[int64_t(s) * n_out + o]);
         }
         write_result<P>(out, o, total, post, int64_t(n_red));
     }
@@ -390,21 +381,12 @@ reduce_thread4_kernel(float* out, float4* partial, unsigned* counters, const flo
     }
     if (live) {
         float t[4] = {P::init(), P::init(), P::init(), P::init()};
-        for (I s0 = 0; s0 < splits; s0 += 8) {  // eight partials in flight, merged in split order
-            float4 q[8];
-#pragma unroll
-            for (int j = 0; j < 8; ++j) {
-                if (s0 + j < splits) q[j] = partial[int64_t(s0 + j) * n_out4 + o4];
-            }
-#pragma unroll
-            for (int j = 0; j < 8; ++j) {
-                if (s0 + j < splits) {
-                    t[0] = P::merge(t[0], q[j].x);
-                    t[1] = P::merge(t[1], q[j].y);
-                    t[2] = P::merge(t[2], q[j].z);
-                    t[3] = P::merge(t[3], q[j].w);
-                }
-            }
+        for (I s = 0; s < splits; ++s) {
+            const float4 q = partial[int64_t(s) * n_out4 + o4];
+            t[0] = P::merge(t[0], q.x);
+            t[1] = P::merge(t[1], q.y);
+            t[2] = P::merge(t[2], q.z);
+            t[3] = P::merge(t[3], q.w);
         }
         reinterpret_cast<float4*>(out)[o4] = make_float4(finish(t[0]), finish(t[1]), finish(t[2]), finish(t[3]));
     }
