@@ -48,7 +48,7 @@ def parse():
     ap.add_argument("--precision", default="3xtf32", choices=["3xtf32", "tf32", "fp32"])
     ap.add_argument("--workload", default="gemm", choices=["gemm", "ops", "gemm-sweep"],
                     help="gemm: the contract line; ops: per-kernel HBM table of the memory-bound family; "
-                         "gemm-sweep: every GEMM shape of the BASELINE sweep")
+                         "gemm-sweep: every GEMM shape of the benchmark's sweep")
     ap.add_argument("--no-graphs", action="store_true", help="train object: replay every step eagerly")
     ap.add_argument("--filter", default="", help="ops workload: substring of the case names to run")
     ap.add_argument("--train", default="mlp_wide_b2048",
@@ -496,7 +496,7 @@ def train_section(args, backend, rank, world, dist, barrier, max_over_ranks):
 
 
 # ---------------------------------------------------------------------------
-# memory-bound family: achieved HBM GB/s per kernel at the BASELINE shapes
+# memory-bound family: achieved HBM GB/s per kernel at the benchmark's shapes
 # ---------------------------------------------------------------------------
 
 def run_ops(args, local_rank):
@@ -634,7 +634,7 @@ def run_ops(args, local_rank):
 
 
 def run_gemm_sweep(args, local_rank):
-    """One JSON line per GEMM shape of BASELINE config 2 (squares, skinny M=64, long-K split-K) and
+    """One JSON line per GEMM shape of the benchmark's GEMM sweep (squares, skinny M=64, long-K split-K) and
     of the wide-MLP / CNN training steps, per precision: device time of the whole matmul node."""
     import vkml_b200
     from vkml_b200 import DeviceTensor, NodeDesc, Op, graph

@@ -125,10 +125,10 @@ def main():
                            "classes": classes, "lr": lr, "momentum": 0.9},
                lambda: training.train_cnn(lib, 2, cin, hw, c1, c2, c3, classes, params, x, y, batch, STEPS, lr=lr))
 
-    mlp("mlp_784_128_10_b64", [784, 128, 10], 64)                       # BASELINE config 1
-    mlp("mlp_wide_b2048", [4096, 8192, 8192, 8192, 1000], 2048)          # BASELINE config 5 (per-GPU batch)
+    mlp("mlp_784_128_10_b64", [784, 128, 10], 64)                       # benchmark configuration 1 (MNIST MLP)
+    mlp("mlp_wide_b2048", [4096, 8192, 8192, 8192, 1000], 2048)          # benchmark configuration 5 (wide MLP, per-GPU batch)
     mlp("mlp_wide_reduced_b128", [256, 512, 512, 512, 100], 128, lr=0.02)
-    cnn("cnn_cifar_b256", 256, 64, 128, 256)                            # BASELINE config 4 (per-GPU batch)
+    cnn("cnn_cifar_b256", 256, 64, 128, 256)                            # benchmark configuration 4 (CNN, per-GPU batch)
     cnn("cnn_reduced_b16", 16, 16, 32, 64)
 
 
