@@ -1,6 +1,6 @@
 """Regenerates tests/golden/reference_outputs.npz.
 
-Runs the `quick` subset of the seeded cases in tests/cases.py through the
+Runs the `quick` subset of the seeded cases in tests/cases.py, and the F16 storage cases, through the
 reference CPU backend compiled from its own sources (oracle/_ref/libvkml_ref.so,
 built by `make -C oracle ref` where the reference tree is present) and stores
 the OUTPUT bytes.  Inputs are not stored: they are regenerated from the same
@@ -26,15 +26,17 @@ def main():
     ref = RefImpl()
     names, arrays = [], {}
     seen = set()
-    for case in cases.all_cases(quick=True):
+    import itertools
+    for case in itertools.chain(cases.all_cases(quick=True), cases.f16_cases()):
         if case.name in seen:
             continue
         seen.add(case.name)
         rc, out = ref.run_status(case.op, case.srcs, case.out_shape, case.out_dtype, case.params)
         if rc != 0 or out.nbytes > LIMIT_BYTES:
             continue
-        # keep a spread: every op family, not every layout
-        if len([n for n in names if n.split("/")[0] == case.name.split("/")[0]]) >= 6:
+        # keep a spread: every op family, not every layout (all of the F16 storage cases)
+        family = case.name.split("/")[0]
+        if family != "f16" and len([n for n in names if n.split("/")[0] == family]) >= 6:
             continue
         arrays[f"out_{len(names)}"] = out
         names.append(case.name)

@@ -166,6 +166,7 @@ def test_golden_fixtures(oracle):
     names = json.loads(str(data["__index__"]))
     assert len(names) >= 60
     by_name = {c.name: c for c in cases.all_cases(quick=True)}
+    by_name.update({c.name: c for c in cases.f16_cases()})
     for i, name in enumerate(names):
         case = by_name[name]
         want = data[f"out_{i}"]

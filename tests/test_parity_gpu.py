@@ -160,6 +160,7 @@ def test_golden_fixtures(cuda, backend):
     data = np.load(os.path.join(GOLDEN, "reference_outputs.npz"))
     names = json.loads(str(data["__index__"]))
     by_name = {c.name: c for c in cases.all_cases(quick=True)}
+    by_name.update({c.name: c for c in cases.f16_cases()})
     for i, name in enumerate(names):
         case = by_name[name]
         if case.op == Op.PROD:

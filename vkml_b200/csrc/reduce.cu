@@ -31,21 +31,40 @@ struct RedGeoT {
     I kdim[kMaxDims], kstride[kMaxDims];  // kept axes (input strides), padded in front
     I rdim[kMaxDims], rstride[kMaxDims];  // reduced axes
     int krank, rrank;
+    // multiply-high reciprocals of kdim / rdim, used by the 32-bit kernels (set_divisors)
+    FastDiv kdiv[kMaxDims], rdiv[kMaxDims];
 };
-using RedGeo = RedGeoT<int64_t>;
 
 template <typename I>
-__device__ __forceinline__ I walk(const I* dim, const I* stride, int rank, I linear) {
+void set_divisors(RedGeoT<I>& g) {
+    for (int a = 0; a < kMaxDims; ++a) {
+        g.kdiv[a] = FastDiv(static_cast<uint32_t>(g.kdim[a] > 0 ? g.kdim[a] : 1));
+        g.rdiv[a] = FastDiv(static_cast<uint32_t>(g.rdim[a] > 0 ? g.rdim[a] : 1));
+    }
+}
+using RedGeo = RedGeoT<int64_t>;
+
+// Offset of the `linear`-th element of a row-major index space.  The outermost axis needs no
+// division (what is left of `linear` is its index); 32-bit walks divide by multiply-high.
+template <typename I>
+__device__ __forceinline__ I walk(const I* dim, const I* stride, const FastDiv* div, int rank, I linear) {
     if (rank == 1) {
         return linear * stride[kMaxDims - 1];
     }
     I off = 0;
 #pragma unroll
     for (int a = kMaxDims - 1; a >= 0; --a) {
-        if (a >= kMaxDims - rank) {
-            const I q = linear / dim[a];
+        if (a > kMaxDims - rank) {
+            I q;
+            if constexpr (sizeof(I) == 4) {
+                q = static_cast<I>(div[a].div(static_cast<uint32_t>(linear)));
+            } else {
+                q = linear / dim[a];
+            }
             off += (linear - q * dim[a]) * stride[a];
             linear = q;
+        } else if (a == kMaxDims - rank) {
+            off += linear * stride[a];
         }
     }
     return off;
@@ -203,7 +222,7 @@ reduce_group_kernel(void* out, typename P::Acc* partial, unsigned* counters, con
     typename P::Acc acc = P::init();
     const bool live = o < n_out;
     if (live) {
-        const I base = walk<I>(g.kdim, g.kstride, g.krank, static_cast<I>(o));
+        const I base = walk<I>(g.kdim, g.kstride, g.kdiv, g.krank, static_cast<I>(o));
         for (int64_t kb64 = int64_t(split) * (GROUP * U) + lane; kb64 < int64_t(n_units);
              kb64 += int64_t(splits) * (GROUP * U)) {
             const I kb = static_cast<I>(kb64);
@@ -213,7 +232,7 @@ reduce_group_kernel(void* out, typename P::Acc* partial, unsigned* counters, con
                 for (int u = 0; u < U; ++u) {
                     const I k = kb + u * GROUP;
                     if (k < n_units) {
-                        v[u] = *reinterpret_cast<const float4*>(in + base + walk<I>(g.rdim, g.rstride, g.rrank, k));
+                        v[u] = *reinterpret_cast<const float4*>(in + base + walk<I>(g.rdim, g.rstride, g.rdiv, g.rrank, k));
                     }
                 }
 #pragma unroll
@@ -234,7 +253,7 @@ reduce_group_kernel(void* out, typename P::Acc* partial, unsigned* counters, con
                 for (int u = 0; u < U; ++u) {
                     const I k = kb + u * GROUP;
                     if (k < n_units) {
-                        v[u] = in[base + walk<I>(g.rdim, g.rstride, g.rrank, k)];
+                        v[u] = in[base + walk<I>(g.rdim, g.rstride, g.rdiv, g.rrank, k)];
                     }
                 }
 #pragma unroll
@@ -286,14 +305,14 @@ reduce_thread_kernel(void* out, typename P::Acc* partial, unsigned* counters, co
     const bool live = o < n_out;
     typename P::Acc acc = P::init();
     if (live) {
-        const I base = walk<I>(g.kdim, g.kstride, g.krank, static_cast<I>(o));
+        const I base = walk<I>(g.kdim, g.kstride, g.kdiv, g.krank, static_cast<I>(o));
         for (int64_t kb64 = int64_t(split) * U; kb64 < int64_t(n_red); kb64 += int64_t(splits) * U) {
             const I kb = static_cast<I>(kb64);
             float v[U];
 #pragma unroll
             for (int u = 0; u < U; ++u) {
                 if (kb + u < n_red) {
-                    v[u] = in[base + walk<I>(g.rdim, g.rstride, g.rrank, kb + u)];
+                    v[u] = in[base + walk<I>(g.rdim, g.rstride, g.rdiv, g.rrank, kb + u)];
                 }
             }
 #pragma unroll
@@ -340,14 +359,14 @@ reduce_thread4_kernel(float* out, float4* partial, unsigned* counters, const flo
     const bool live = o4 < n_out4;
     float acc[4] = {P::init(), P::init(), P::init(), P::init()};
     if (live) {
-        const I base = walk<I>(g.kdim, g.kstride, g.krank, static_cast<I>(o4));
+        const I base = walk<I>(g.kdim, g.kstride, g.kdiv, g.krank, static_cast<I>(o4));
         for (int64_t kb64 = int64_t(split) * U; kb64 < int64_t(n_red); kb64 += int64_t(splits) * U) {
             const I kb = static_cast<I>(kb64);
             float4 v[U];
 #pragma unroll
             for (int u = 0; u < U; ++u) {
                 if (kb + u < n_red) {
-                    v[u] = *reinterpret_cast<const float4*>(in + base + walk<I>(g.rdim, g.rstride, g.rrank, kb + u));
+                    v[u] = *reinterpret_cast<const float4*>(in + base + walk<I>(g.rdim, g.rstride, g.rdiv, g.rrank, kb + u));
                 }
             }
 #pragma unroll
@@ -454,6 +473,7 @@ RedGeoT<I> narrow_geo(const RedGeo& g) {
         r.rdim[a] = static_cast<I>(g.rdim[a]);
         r.rstride[a] = static_cast<I>(g.rstride[a]);
     }
+    set_divisors(r);
     return r;
 }
 
@@ -492,6 +512,7 @@ void launch_reduce_kernels(b200_ctx* ctx, const View& out, const float* src, con
                 }
                 RedGeoT<I> g4 = g;
                 g4.kdim[kMaxDims - 1] = static_cast<I>(k_run / 4);
+                set_divisors(g4);
                 g4.kstride[kMaxDims - 1] = 4;
                 float4* part = nullptr;
                 if (sp > 1) {
@@ -534,6 +555,7 @@ void launch_reduce_kernels(b200_ctx* ctx, const View& out, const float* src, con
     int64_t n_units = n_red;
     if (vec4) {
         g.rdim[kMaxDims - 1] = static_cast<I>(inner_run / 4);
+        set_divisors(g);
         g.rstride[kMaxDims - 1] = 4;
         n_units = n_red / 4;
     }
@@ -1255,6 +1277,7 @@ void launch_noalloc(const float* in, float* out, int64_t rows, int64_t cols, int
     g.kstride[kMaxDims - 1] = 1;
     g.rdim[kMaxDims - 1] = static_cast<I>(rows);
     g.rstride[kMaxDims - 1] = static_cast<I>(pitch);
+    set_divisors(g);
     dim3 grid(static_cast<unsigned>(ceil_div(cols, 256)), static_cast<unsigned>(splits));
     reduce_thread_kernel<SumP, I><<<grid, 256, 0, stream>>>(out, splits > 1 ? partial : nullptr,
                                                              splits > 1 ? counters : nullptr, in, g, cols,
