@@ -494,38 +494,55 @@ tiled_kernel(typename F::Out* __restrict__ out, const typename F::In0* __restric
                     }
                 }
             }
+            // operands that are not transposed are read straight along C, in the phase-2 mapping;
+            // their loads are issued here, before the barrier, so they travel together with the
+            // transposed operand's instead of after it
+            Vec<typename F::In0, 4> xd[4];
+            Vec<typename F::In1, 4> yd[4];
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                const int wt = j * 8 + warp;
+                const int cc = ((wt & 1) * 8 + q) * 4;
+                const int rr = (wt >> 1) * 4 + l4;
+                xd[j] = Vec<typename F::In0, 4>{};
+                yd[j] = Vec<typename F::In1, 4>{};
+                if (!t.transposed[0]) {
+                    const typename F::In0* src = a + bi * t.sb[0] + (r0 + rr) * t.sr[0];
+                    if (t.sc[0] == 1) {
+                        xd[j] = *reinterpret_cast<const Vec<typename F::In0, 4>*>(src + c0 + cc);
+                    } else {
+#pragma unroll
+                        for (int e = 0; e < 4; ++e) xd[j].v[e] = src[0];
+                    }
+                }
+                if constexpr (F::NIN >= 2) {
+                    if (!t.transposed[1]) {
+                        const typename F::In1* src = b + bi * t.sb[1] + (r0 + rr) * t.sr[1];
+                        if (t.sc[1] == 1) {
+                            yd[j] = *reinterpret_cast<const Vec<typename F::In1, 4>*>(src + c0 + cc);
+                        } else {
+#pragma unroll
+                            for (int e = 0; e < 4; ++e) yd[j].v[e] = src[0];
+                        }
+                    }
+                }
+            }
             __syncthreads();
 #pragma unroll
             for (int j = 0; j < 4; ++j) {
                 const int wt = j * 8 + warp;
                 const int cc = ((wt & 1) * 8 + q) * 4;
                 const int rr = (wt >> 1) * 4 + l4;
-                Vec<typename F::In0, 4> x;
-                Vec<typename F::In1, 4> y{};
+                Vec<typename F::In0, 4> x = xd[j];
+                Vec<typename F::In1, 4> y = yd[j];
                 if (t.transposed[0]) {
 #pragma unroll
                     for (int e = 0; e < 4; ++e) x.v[e] = ta[rr][cc + e];
-                } else {
-                    const typename F::In0* src = a + bi * t.sb[0] + (r0 + rr) * t.sr[0];
-                    if (t.sc[0] == 1) {
-                        x = *reinterpret_cast<const Vec<typename F::In0, 4>*>(src + c0 + cc);
-                    } else {
-#pragma unroll
-                        for (int e = 0; e < 4; ++e) x.v[e] = src[0];
-                    }
                 }
                 if constexpr (F::NIN >= 2) {
                     if (t.transposed[1]) {
 #pragma unroll
                         for (int e = 0; e < 4; ++e) y.v[e] = tb[rr][cc + e];
-                    } else {
-                        const typename F::In1* src = b + bi * t.sb[1] + (r0 + rr) * t.sr[1];
-                        if (t.sc[1] == 1) {
-                            y = *reinterpret_cast<const Vec<typename F::In1, 4>*>(src + c0 + cc);
-                        } else {
-#pragma unroll
-                            for (int e = 0; e < 4; ++e) y.v[e] = src[0];
-                        }
                     }
                 }
                 Vec<typename F::Out, 4> o;
