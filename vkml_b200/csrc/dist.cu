@@ -92,6 +92,7 @@ struct DistState {
     };
     std::vector<Lazy> lazy;
     std::vector<cudaEvent_t> event_pool;
+    std::mutex lazy_mu;  // b200_free may arrive from any thread (a Storage deleter) and looks at `lazy`
 };
 
 static void all_reduce_mean(b200_ctx* ctx, void* data, size_t count) {
@@ -104,6 +105,7 @@ static void all_reduce_mean(b200_ctx* ctx, void* data, size_t count) {
     ctx->comm_pending = true;
     ctx->comm_bytes.fetch_add(count * sizeof(float), std::memory_order_relaxed);
     if (ctx->lazy_join) {
+        std::lock_guard<std::mutex> lock(d->lazy_mu);
         cudaEvent_t ev = nullptr;
         if (!d->event_pool.empty()) {
             ev = d->event_pool.back();
@@ -121,7 +123,9 @@ static void all_reduce_mean(b200_ctx* ctx, void* data, size_t count) {
 // one issued before them (the communication stream is in order); nullptr: for all of them.
 void dist_wait_range(b200_ctx* ctx, const void* lo, const void* hi) {
     DistState* d = ctx->dist;
-    if (d == nullptr || d->lazy.empty()) return;
+    if (d == nullptr) return;
+    std::lock_guard<std::mutex> lock(d->lazy_mu);
+    if (d->lazy.empty()) return;
     const char* a = static_cast<const char*>(lo);
     const char* b = static_cast<const char*>(hi);
     int last = -1;
@@ -137,8 +141,9 @@ void dist_wait_range(b200_ctx* ctx, const void* lo, const void* hi) {
 
 // Position (in issue order) of the last pending all-reduce overlapping [lo, hi), or -1.
 int dist_pending_index(const b200_ctx* ctx, const void* lo, const void* hi) {
-    const DistState* d = ctx->dist;
+    DistState* d = ctx->dist;
     if (d == nullptr) return -1;
+    std::lock_guard<std::mutex> lock(d->lazy_mu);
     const char* a = static_cast<const char*>(lo);
     const char* b = static_cast<const char*>(hi);
     int last = -1;
@@ -148,7 +153,12 @@ int dist_pending_index(const b200_ctx* ctx, const void* lo, const void* hi) {
     return last;
 }
 
-bool dist_has_pending(const b200_ctx* ctx) { return ctx->dist != nullptr && !ctx->dist->lazy.empty(); }
+bool dist_has_pending(const b200_ctx* ctx) {
+    DistState* d = ctx->dist;
+    if (d == nullptr) return false;
+    std::lock_guard<std::mutex> lock(d->lazy_mu);
+    return !d->lazy.empty();
+}
 
 void dist_all_reduce_now(b200_ctx* ctx, void* data, size_t count) {
     if (ctx->dist != nullptr && count != 0) {

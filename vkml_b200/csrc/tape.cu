@@ -252,70 +252,61 @@ void run_template(b200_tape* t, const std::vector<int64_t>& words, std::vector<S
     }
 }
 
-// After a graph step's one synchronisation: hand the staged downloads to the caller.
-void deliver_downloads(b200_tape* t, const std::vector<int64_t>& words, const HostBuffers& host) {
+// Consumes the words of one event whose kind has just been read (everything but a download).
+void skip_event(Reader& r, int64_t ev) {
+    if (ev == kAlloc) {
+        r.skip(1);
+    } else if (ev == kFree) {
+        r.skip(2);
+    } else if (ev == kH2D) {
+        r.skip(5);
+    } else if (ev == kCompute) {
+        const int64_t n_nodes = r.next();
+        r.skip(1);
+        for (int64_t i = 0; i < n_nodes; ++i) {
+            r.next();
+            const int64_t n_src = r.next();
+            r.skip(static_cast<size_t>(B200_PARAM_BYTES / 8 + kTensorWords * (1 + n_src)));
+        }
+    } else if (ev == kD2D) {
+        const int64_t n = r.next();
+        r.skip(static_cast<size_t>(7 * n));
+    } else if (ev != kSync) {
+        fail(B200_INVALID_ARGUMENT, "tape: unknown event " + std::to_string(ev));
+    }
+}
+
+// Visits the downloads of a template in order: fn(bytes, download index, offset in the stage).
+template <typename Fn>
+void for_each_download(const std::vector<int64_t>& words, Fn&& fn) {
     size_t stage_offset = 0;
     Reader r{words.data(), words.size()};
     while (!r.done()) {
         const int64_t ev = r.next();
-        if (ev == kAlloc) {
-            r.skip(1);
-        } else if (ev == kFree) {
-            r.skip(2);
-        } else if (ev == kH2D) {
-            r.skip(5);
-        } else if (ev == kCompute) {
-            const int64_t n_nodes = r.next();
-            r.skip(1);
-            for (int64_t i = 0; i < n_nodes; ++i) {
-                r.next();
-                const int64_t n_src = r.next();
-                r.skip(static_cast<size_t>(B200_PARAM_BYTES / 8 + kTensorWords * (1 + n_src)));
-            }
-        } else if (ev == kD2D) {
-            const int64_t n = r.next();
-            r.skip(static_cast<size_t>(7 * n));
-        } else if (ev == kD2H) {
-            r.skip(3);
-            const int64_t bytes = r.next(), index = r.next();
-            void* dst = host.download(index);
-            if (dst == nullptr) fail(B200_INVALID_ARGUMENT, "tape: a download has no host buffer");
-            std::memcpy(dst, t->stage + stage_offset, static_cast<size_t>(bytes));
-            stage_offset += static_cast<size_t>((bytes + 15) / 16 * 16);
+        if (ev != kD2H) {
+            skip_event(r, ev);
+            continue;
         }
+        r.skip(3);
+        const int64_t bytes = r.next(), index = r.next();
+        fn(bytes, index, stage_offset);
+        stage_offset += static_cast<size_t>((bytes + 15) / 16 * 16);
     }
 }
 
+// After a graph step's one synchronisation: hand the staged downloads to the caller.
+void deliver_downloads(b200_tape* t, const std::vector<int64_t>& words, const HostBuffers& host) {
+    for_each_download(words, [&](int64_t bytes, int64_t index, size_t stage_offset) {
+        void* dst = host.download(index);
+        if (dst == nullptr) fail(B200_INVALID_ARGUMENT, "tape: a download has no host buffer");
+        std::memcpy(dst, t->stage + stage_offset, static_cast<size_t>(bytes));
+    });
+}
+
+// Size of the pinned stage a template's downloads need; walking it also validates the event stream.
 size_t staged_download_bytes(const std::vector<int64_t>& words) {
     size_t total = 0;
-    Reader r{words.data(), words.size()};
-    while (!r.done()) {
-        const int64_t ev = r.next();
-        if (ev == kAlloc) {
-            r.skip(1);
-        } else if (ev == kFree) {
-            r.skip(2);
-        } else if (ev == kH2D) {
-            r.skip(5);
-        } else if (ev == kCompute) {
-            const int64_t n_nodes = r.next();
-            r.skip(1);
-            for (int64_t i = 0; i < n_nodes; ++i) {
-                r.next();
-                const int64_t n_src = r.next();
-                r.skip(static_cast<size_t>(B200_PARAM_BYTES / 8 + kTensorWords * (1 + n_src)));
-            }
-        } else if (ev == kD2D) {
-            const int64_t n = r.next();
-            r.skip(static_cast<size_t>(7 * n));
-        } else if (ev == kD2H) {
-            r.skip(3);
-            total += static_cast<size_t>((r.next() + 15) / 16 * 16);
-            r.skip(1);
-        } else if (ev != kSync) {
-            fail(B200_INVALID_ARGUMENT, "tape: unknown event " + std::to_string(ev));
-        }
-    }
+    for_each_download(words, [&](int64_t bytes, int64_t, size_t) { total += static_cast<size_t>((bytes + 15) / 16 * 16); });
     return total;
 }
 
