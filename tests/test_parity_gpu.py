@@ -327,6 +327,42 @@ def test_operand_planes_are_shared_inside_a_span_only(monkeypatch):
     np.testing.assert_allclose(outs[2].numpy()[0, 0], xh.T @ gh, rtol=0, atol=2e-3)
 
 
+def test_errors_leave_the_backend_usable(backend):
+    """A node the backend declines, a geometry that contradicts its tensors, a span that fails
+    half way and an allocation nobody can satisfy all come back as status codes (the exception
+    types vkML maps them to), and the context keeps working afterwards -- the contract behind
+    vkML's RecordingGuard (vulkan_backend.cpp:1216-1222) and OutOfMemoryError (allocator.h:41-44)."""
+    import vkml_b200 as V
+    from vkml_b200 import DeviceTensor, NodeDesc
+    from vkml_b200.backend import OutOfMemoryError, ShapeError
+    x = DeviceTensor.from_host(backend, np.arange(12, dtype=np.float32).reshape(3, 4))
+    y = DeviceTensor.empty(backend, (3, 4))
+    z = DeviceTensor.empty(backend, (3, 4))
+    # prod is declined (as by vkML's own GPU backend): NotImplementedError, nothing launched
+    with pytest.raises(NotImplementedError):
+        backend.compute([NodeDesc(Op.PROD, DeviceTensor.empty(backend, (3,)).desc, [x.desc], graph.reduce_params([1], 2))])
+    # operand extents that contradict the output's
+    a = DeviceTensor.empty(backend, (1, 1, 4, 5))
+    b = DeviceTensor.empty(backend, (1, 1, 6, 7))
+    with pytest.raises(ShapeError):
+        backend.compute([NodeDesc(Op.MATMUL, DeviceTensor.empty(backend, (1, 1, 4, 7)).desc, [a.desc, b.desc])])
+    # a span whose second node is invalid: the first node's work is ordered and valid, the error is
+    # reported, and the next span runs normally
+    bad = NodeDesc(Op.IM2COL, DeviceTensor.empty(backend, (1, 9, 4)).desc, [x.desc],
+                   graph.unfold_params((3, 3), (1, 1), (1, 1), (1, 1), (2, 2)))
+    with pytest.raises((ShapeError, ValueError)):
+        backend.compute([NodeDesc(Op.NEG, y.desc, [x.desc]), bad, NodeDesc(Op.RELU, z.desc, [x.desc])])
+    np.testing.assert_array_equal(y.numpy(), -x.numpy())
+    backend.compute([NodeDesc(Op.RELU, z.desc, [y.desc])])
+    np.testing.assert_array_equal(z.numpy(), np.zeros((3, 4), np.float32))
+    # an allocation larger than the device: OutOfMemoryError, and the allocator still serves
+    with pytest.raises(OutOfMemoryError):
+        backend.allocate(1 << 42)
+    w = DeviceTensor.from_host(backend, np.ones(1000, dtype=np.float32))
+    np.testing.assert_array_equal(w.numpy(), np.ones(1000, np.float32))
+    backend.synchronize()
+
+
 def test_device_copies(backend):
     from vkml_b200 import DeviceTensor
     rng = np.random.default_rng(4)
