@@ -449,6 +449,7 @@ def matmul_tc_cases(seed=12):
     yield mk("conv-dw", rnd(1, 8, 128, 256), t(rnd(1, 8, 256, 576)))
     yield mk("conv-dcols-bcast-a", t(rnd(1, 1, 576, 128)), rnd(1, 8, 128, 256))
     yield mk("bcast-b", rnd(4, 1, 100, 300), rnd(1, 1, 300, 200))
+    yield mk("conv1-k27-bcast-a", rnd(1, 1, 64, 27), rnd(1, 16, 27, 1024))     # K below one K-block
     big = rnd(1, 1, 700, 1200)
     yield mk("sliced", big[:, :, 5:605, 16:1016], rnd(1, 1, 1000, 300))
 

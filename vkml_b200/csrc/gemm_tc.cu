@@ -1019,7 +1019,7 @@ bool gemm_tc_eligible(const b200_ctx* ctx, const GemmProblem& p) {
         return false;
     }
     const int64_t batches = p.b0 * p.b1;
-    if (p.m < 32 || p.n < 16 || p.k < 32 || batches < 1) {
+    if (p.m < 32 || p.n < 16 || p.k < 16 || batches < 1) {  // K is zero-padded to the 32-wide K-block
         return false;
     }
     const double flops = 2.0 * double(p.m) * double(p.n) * double(p.k) * double(batches);
