@@ -277,6 +277,70 @@ col2im_dense_kernel(float* __restrict__ out, const float* __restrict__ cols, Den
     }
 }
 
+// The 3x3, padding 1 case (every convolution of the CNN benchmark): same staging, but the four
+// outputs of a thread read each tap plane as one aligned 128-bit vector plus, for the two shifted
+// taps, one neighbouring word, and the image-edge tests collapse to three conditions per thread
+// (first column, last column, row in range).  Same sum order: (ki, kj) ascending, +0.0 for taps
+// outside the column image.
+__global__ void __launch_bounds__(kThreads)
+col2im_dense_3x3p1_kernel(float* __restrict__ out, const float* __restrict__ cols, DenseGeo g, FastDiv div_hw4,
+                          FastDiv div_w) {
+    pdl_prologue();
+    extern __shared__ __align__(16) float tile[];  // group x 9 x L
+    const int l = g.oh * g.ow;                     // == h * w here
+    const int first = blockIdx.x * g.group;
+    const int count = min(g.group, g.planes - first);
+    const float4* src = reinterpret_cast<const float4*>(cols + int64_t(first) * 9 * l);
+    const int n4 = count * 9 * l / 4;
+    for (int i = threadIdx.x; i < n4; i += kThreads) {
+        reinterpret_cast<float4*>(tile)[i] = src[i];
+    }
+    __syncthreads();
+    const int hw = g.h * g.w;
+    const int hw4 = hw / 4;
+    float* dst = out + int64_t(first) * hw;
+    for (int i = threadIdx.x; i < count * hw4; i += kThreads) {
+        uint32_t pl, p4, h, x;
+        div_hw4.divmod(static_cast<uint32_t>(i), pl, p4);
+        div_w.divmod(4 * p4, h, x);
+        const float* t = tile + pl * 9 * l;
+        const bool has_left = x > 0;                                   // column x - 1 exists
+        const bool has_right = static_cast<int>(x) + 4 < g.ow;         // column x + 4 exists
+        float acc[4] = {0.0F, 0.0F, 0.0F, 0.0F};
+#pragma unroll
+        for (int ki = 0; ki < 3; ++ki) {
+            const int oh = static_cast<int>(h) + 1 - ki;
+            const bool ok_h = oh >= 0 && oh < g.oh;
+            const float* row = t + (ki * 3) * l + oh * g.ow + static_cast<int>(x);  // tap (ki, 0), column x
+            float4 a = make_float4(0.0F, 0.0F, 0.0F, 0.0F), b = a, c = a;
+            float a_next = 0.0F, c_prev = 0.0F;
+            if (ok_h) {
+                a = *reinterpret_cast<const float4*>(row);           // kj = 0 reads columns x+1 .. x+4
+                b = *reinterpret_cast<const float4*>(row + l);       // kj = 1 reads columns x   .. x+3
+                c = *reinterpret_cast<const float4*>(row + 2 * l);   // kj = 2 reads columns x-1 .. x+2
+                if (has_right) a_next = row[4];
+                if (has_left) c_prev = row[2 * l - 1];
+            }
+            // kj = 0
+            acc[0] += a.y;
+            acc[1] += a.z;
+            acc[2] += a.w;
+            acc[3] += a_next;
+            // kj = 1
+            acc[0] += b.x;
+            acc[1] += b.y;
+            acc[2] += b.z;
+            acc[3] += b.w;
+            // kj = 2
+            acc[0] += c_prev;
+            acc[1] += c.x;
+            acc[2] += c.y;
+            acc[3] += c.z;
+        }
+        *reinterpret_cast<float4*>(dst + pl * hw + 4 * p4) = make_float4(acc[0], acc[1], acc[2], acc[3]);
+    }
+}
+
 // 2x2 pooling with stride 2 over dense planes whose width is a multiple of eight: one thread
 // per four windows, rows read as two 128-bit vectors, first strict maximum in (ki, kj) order.
 __global__ void __launch_bounds__(kThreads)
@@ -838,7 +902,15 @@ void launch_movement(b200_ctx* ctx, const b200_node& node) {
                         return true;
                     }();
                     (void)once;
-                    if (w.kh == 3 && w.kw == 3) {
+                    if (w.kh == 3 && w.kw == 3 && w.ph == 1 && w.pw == 1 && l % 4 == 0 && w.out_w % 4 == 0 &&
+                        w.out_h == w.image_h && w.out_w == w.image_w) {
+                        static const bool once3 = [] {
+                            allow_large_smem(col2im_dense_3x3p1_kernel);
+                            return true;
+                        }();
+                        (void)once3;
+                        launch_kernel(ctx, col2im_dense_3x3p1_kernel, grid, kThreads, smem, o, src, g, div_hw4, div_w);
+                    } else if (w.kh == 3 && w.kw == 3) {
                         launch_kernel(ctx, col2im_dense_kernel<3, 3>, grid, kThreads, smem, o, src, g, div_hw4, div_w);
                     } else {
                         launch_kernel(ctx, col2im_dense_kernel<0, 0>, grid, kThreads, smem, o, src, g, div_hw4, div_w);
