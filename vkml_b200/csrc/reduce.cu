@@ -352,7 +352,7 @@ reduce_thread4_kernel(float* out, float4* partial, unsigned* counters, const flo
                       RedGeoT<I> g, int64_t n_out4, I n_red, int post) {
     pdl_prologue();
     __shared__ int last_flag;
-    constexpr int U = 4;
+    constexpr int U = 8;
     const int64_t o4 = int64_t(blockIdx.x) * blockDim.x + threadIdx.x;
     const I split = blockIdx.y;
     const I splits = gridDim.y;
@@ -507,7 +507,9 @@ void launch_reduce_kernels(b200_ctx* ctx, const View& out, const float* src, con
             if (v4 && bx <= kMaxCounters) {
                 int64_t sp = 1;
                 if (n_red >= 64) {
-                    sp = ceil_div(int64_t(kSmCount) * 1024, n_out4);
+                    // eight vectors per thread in flight, so half as many K-slices (and half the
+                    // partial rows the last block has to fold) keep the memory system as busy
+                    sp = ceil_div(int64_t(kSmCount) * 512, n_out4);
                     sp = std::max<int64_t>(1, std::min<int64_t>(std::min<int64_t>(sp, n_red / 16), 1024));
                 }
                 RedGeoT<I> g4 = g;
