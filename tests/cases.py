@@ -39,7 +39,7 @@ EXACT_OPS = {"full", "rand", "contiguous", "cast", "cat", "index_select", "im2co
              "max_pool2d_backward", "col2im", "scatter_add", "relu", "neg", "abs", "sign", "clamp",
              "maximum", "minimum", "where", "triu", "tril", "equal", "less", "greater", "less_equal",
              "greater_equal", "not_equal", "argmax", "argmin", "max", "min", "add", "sub", "mul",
-             "square", "scaled_add", "slice_backward"}
+             "square", "scaled_add", "slice_backward", "prod"}
 
 
 def policy_for(op_name: str):
@@ -322,6 +322,17 @@ def reduce_cases(seed=99, quick=False):
                   [np.nan, np.nan, np.nan, np.nan], [np.inf, 1, np.inf, 0]], dtype=np.float32)
     for name in ("max", "min", "argmax", "argmin", "sum"):
         yield mk(name, t, [1], tag="ties-nan")
+    # prod: multiplied in index order on both sides, so exact -- including the case a tree would get
+    # wrong (1e20 and 1e-20 alternating: 1 in order, inf or 0 once regrouped)
+    rngp = np.random.default_rng(seed + 7)
+    xp = rngp.uniform(0.5, 1.5, (33, 17)).astype(np.float32)
+    for axes in ([1], [0], []):
+        yield mk("prod", xp, axes, tag="dense")
+    yield mk("prod", np.ascontiguousarray(xp.T).T, [1], tag="transposed")
+    yield mk("prod", xp, [0], keepdim=True, tag="keepdim")
+    alt = np.tile(np.array([1e20, 1e-20], dtype=np.float32), 3000).reshape(3, 2000)
+    yield mk("prod", alt, [1], tag="order-sensitive")
+    yield mk("prod", rngp.uniform(0.9, 1.1, (4, 8, 6, 6)).astype(np.float32), [0, 2, 3], tag="multi-axis")
     wide = rng.integers(0, 4, (5, 5000)).astype(np.float32)  # many ties across lanes
     for name in ("argmax", "argmin", "max", "min"):
         yield mk(name, wide, [1], tag="many-ties")

@@ -70,9 +70,9 @@ def test_supports_is_honest():
     assert sup(_node(Op.ARGMAX, DType.I64, [DType.F16]))
     assert sup(_node(Op.SOFTMAX, DType.F16, [DType.F16]))
     assert sup(_node(Op.MATMUL, DType.F16, [DType.F16, DType.F16], shape=(1, 1, 4, 4)))
-    assert not sup(_node(Op.PROD, DType.F16, [DType.F16]))
+    assert sup(_node(Op.PROD, DType.F16, [DType.F16]))
     assert not sup(_node(Op.RAND, DType.F16, []))
-    assert not sup(_node(Op.PROD, DType.F32, [DType.F32]))            # declined by vkML's GPU backend too
+    assert sup(_node(Op.PROD, DType.F32, [DType.F32]))                # in index order, as on the CPU
     assert sup(_node(Op.EQUAL, DType.BOOL, [DType.F32, DType.F32]))
     assert not sup(_node(Op.EQUAL, DType.F32, [DType.F32, DType.F32]))
     assert sup(_node(Op.ARGMAX, DType.I64, [DType.F32]))

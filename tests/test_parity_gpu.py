@@ -163,8 +163,6 @@ def test_golden_fixtures(cuda, backend):
     by_name.update({c.name: c for c in cases.f16_cases()})
     for i, name in enumerate(names):
         case = by_name[name]
-        if case.op == Op.PROD:
-            continue
         got = cuda.run(case.op, case.srcs, case.out_shape, case.out_dtype, case.params, sync_check=False)
         cases.check(case, got, data[f"out_{i}"])
     backend.synchronize()
@@ -175,8 +173,6 @@ def test_known_answers(cuda, backend):
     with open(os.path.join(GOLDEN, "known_answers.json")) as f:
         table = json.load(f)
     for spec in table:
-        if spec["op"] == "prod":
-            continue
         srcs = []
         for s in spec["srcs"]:
             if s.get("values") is None:
@@ -328,7 +324,7 @@ def test_operand_planes_are_shared_inside_a_span_only(monkeypatch):
 
 
 def test_errors_leave_the_backend_usable(backend):
-    """A node the backend declines, a geometry that contradicts its tensors, a span that fails
+    """A node the backend does not know, a geometry that contradicts its tensors, a span that fails
     half way and an allocation nobody can satisfy all come back as status codes (the exception
     types vkML maps them to), and the context keeps working afterwards -- the contract behind
     vkML's RecordingGuard (vulkan_backend.cpp:1216-1222) and OutOfMemoryError (allocator.h:41-44)."""
@@ -338,9 +334,9 @@ def test_errors_leave_the_backend_usable(backend):
     x = DeviceTensor.from_host(backend, np.arange(12, dtype=np.float32).reshape(3, 4))
     y = DeviceTensor.empty(backend, (3, 4))
     z = DeviceTensor.empty(backend, (3, 4))
-    # prod is declined (as by vkML's own GPU backend): NotImplementedError, nothing launched
+    # an op the backend does not know: NotImplementedError, nothing launched
     with pytest.raises(NotImplementedError):
-        backend.compute([NodeDesc(Op.PROD, DeviceTensor.empty(backend, (3,)).desc, [x.desc], graph.reduce_params([1], 2))])
+        backend.compute([NodeDesc(999, DeviceTensor.empty(backend, (3,)).desc, [x.desc], graph.reduce_params([1], 2))])
     # operand extents that contradict the output's
     a = DeviceTensor.empty(backend, (1, 1, 4, 5))
     b = DeviceTensor.empty(backend, (1, 1, 6, 7))

@@ -360,9 +360,6 @@ void dispatch_node(b200_ctx* ctx, const b200_node& node) {
     if (op == B200_OP_SOFTMAX || op == B200_OP_LOG_SOFTMAX) {
         launch_softmax(ctx, node);
     } else if (op >= B200_OP_SUM && op <= B200_OP_ARGMIN) {
-        if (op == B200_OP_PROD) {
-            fail(B200_NOT_IMPLEMENTED, "prod is not implemented on this backend");
-        }
         launch_reduce(ctx, node);
     } else if (op == B200_OP_IM2COL || op == B200_OP_COL2IM || op == B200_OP_MAX_POOL2D ||
                op == B200_OP_MAX_POOL2D_BACKWARD || op == B200_OP_INDEX_SELECT ||
@@ -452,8 +449,8 @@ bool supports_node(const b200_node& n) {
                    n.src[1].dtype == B200_F32 && n.src[2].dtype == B200_F32;
         case B200_OP_TRIU: case B200_OP_TRIL: return dt == B200_F32 && srcs_f32(n, 1) && n.out.ndim >= 2;
         case B200_OP_SUM: case B200_OP_MEAN: case B200_OP_MAX: case B200_OP_MIN:
+        case B200_OP_PROD:  // in index order, as on the CPU (vkML's own GPU backend declines it)
             return dt == B200_F32 && srcs_f32(n, 1);
-        case B200_OP_PROD: return false;  // declined by vkML's GPU backend as well (vulkan_backend.cpp:1137-1154)
         case B200_OP_ARGMAX: case B200_OP_ARGMIN: return dt == B200_I64 && srcs_f32(n, 1);
         case B200_OP_MATMUL: return dt == B200_F32 && srcs_f32(n, 2) && n.out.ndim == 4;
         case B200_OP_SOFTMAX: case B200_OP_LOG_SOFTMAX: return dt == B200_F32 && srcs_f32(n, 1);

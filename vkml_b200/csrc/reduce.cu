@@ -20,6 +20,8 @@
 //   order inside the same launch.
 #include "context.h"
 
+#include <type_traits>
+
 #include <cfloat>
 #include <cmath>
 
@@ -75,6 +77,18 @@ struct ArgAcc {
     int64_t i;
 };
 
+// Product: the CPU backend multiplies in index order (kernels_reduce.cpp:118-126), and a product
+// regrouped by a tree is a different answer, not a rounding difference (1e20 and 1e-20 alternating
+// give 1 in order and inf once the large values are grouped) -- which is why vkML's own GPU
+// backend declines it (vulkan_backend.cpp:1137-1154).  Here one thread per output walks the
+// reduced axes in row-major order: sequential, bit-identical to the CPU, slow for long axes.
+struct ProdP {
+    using Acc = float;
+    static constexpr bool kSequential = true;
+    __device__ static Acc init() { return 1.0F; }
+    __device__ static Acc step(Acc a, float v, int64_t) { return a * v; }
+    __device__ static Acc merge(Acc a, Acc b) { return a * b; }
+};
 struct SumP {
     using Acc = float;
     __device__ static Acc init() { return 0.0F; }
@@ -477,11 +491,25 @@ RedGeoT<I> narrow_geo(const RedGeo& g) {
     return r;
 }
 
+template <typename P, typename = void>
+struct is_sequential : std::false_type {};
+template <typename P>
+struct is_sequential<P, std::void_t<decltype(P::kSequential)>> : std::bool_constant<P::kSequential> {};
+
 template <typename P, typename I>
 void launch_reduce_kernels(b200_ctx* ctx, const View& out, const float* src, const RedGeo& g64, int64_t n_out,
                            int64_t n_red, int post) {
     using Acc = typename P::Acc;
     RedGeoT<I> g = narrow_geo<I>(g64);
+    if constexpr (is_sequential<P>::value) {
+        // one thread per output, the reduced index space in order, no slices to regroup
+        dim3 grid(static_cast<unsigned>(ceil_div(n_out, 256)), 1);
+        launch_kernel(ctx, reduce_thread_kernel<P, I>, grid, 256, 0, out.data, static_cast<Acc*>(nullptr),
+                      static_cast<unsigned*>(nullptr), src, g, n_out, static_cast<I>(n_red), post);
+        ctx->count_launch();
+        check_last_launch("reduce (sequential)");
+        return;
+    }
     const int64_t r_inner = g64.rstride[kMaxDims - 1];
     const int64_t k_inner = g64.kstride[kMaxDims - 1];
     const bool column = (n_red <= 16) || (k_inner == 1 && r_inner != 1 && n_out >= 32);
@@ -1176,6 +1204,7 @@ void launch_reduce(b200_ctx* ctx, const b200_node& node) {
         case B200_OP_MEAN: run_reduce<SumP>(ctx, out, in, mask4, kPostMean); return;
         case B200_OP_MAX: run_reduce<MaxP>(ctx, out, in, mask4, kPostNone); return;
         case B200_OP_MIN: run_reduce<MinP>(ctx, out, in, mask4, kPostNone); return;
+        case B200_OP_PROD: run_reduce<ProdP>(ctx, out, in, mask4, kPostNone); return;
         case B200_OP_ARGMAX: run_reduce<ArgMaxP>(ctx, out, in, mask4, kPostNone); return;
         case B200_OP_ARGMIN: run_reduce<ArgMinP>(ctx, out, in, mask4, kPostNone); return;
         default: fail(B200_NOT_IMPLEMENTED, "reduce: unhandled op");
