@@ -285,6 +285,10 @@ def run_b200(args, rank, local_rank, world):
                     "traffic": TRAFFIC_BYTES_PER_LAUNCH if (size == 8192 and args.precision == "3xtf32") else None,
                     "avg_launch_ms": avg_ms,
                     "tensor_pipe_tflops": achieved * passes, "tensor_pipe_frac": achieved * passes / peak,
+                    # back-to-back launches run under the power cap: the sustained yardstick beside the burst one
+                    "peak_sustained": (pk["bf16_tflops_sustained"] / 2.0) if pk.get("bf16_tflops_sustained") else None,
+                    "tensor_pipe_frac_of_sustained": (achieved * passes / (pk["bf16_tflops_sustained"] / 2.0))
+                    if pk.get("bf16_tflops_sustained") else None,
                     "peak_source": f"{pk['source']}: bf16_tflops/2 (TF32 runs at half the bf16 rate)",
                     "note": "achieved counts the algorithmic 2*M*N*K once; 3xTF32 issues it three times on "
                             "the tensor pipe (tensor_pipe_*), so frac cannot exceed 1/3"}
