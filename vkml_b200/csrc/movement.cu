@@ -682,25 +682,50 @@ index_select_kernel(T* __restrict__ out, const T* __restrict__ a, const int64_t*
     }
 }
 
-// Dense source rows of 16-byte multiples: one thread per 16 bytes.
+// Dense source rows of 16-byte multiples: one thread per 16 bytes, four independent
+// index -> row -> vector chains in flight per thread, divisions by multiply-high.
 __global__ void __launch_bounds__(kThreads)
 index_select_rows_kernel(uint4* __restrict__ out, const uint4* __restrict__ a, const int64_t* __restrict__ idx,
-                         int64_t idx_stride, unsigned inner16, unsigned extent, unsigned a_extent,
+                         int64_t idx_stride, FastDiv div_inner16, FastDiv div_extent, unsigned a_extent,
                          unsigned total16, uint32_t* status) {
     pdl_prologue();
+    constexpr int U = 4;
     const int64_t stride = int64_t(gridDim.x) * blockDim.x;
-    for (int64_t li = int64_t(blockIdx.x) * blockDim.x + threadIdx.x; li < int64_t(total16); li += stride) {
-        const unsigned i = static_cast<unsigned>(li);
-        const unsigned q = i / inner16;
-        const unsigned rest = i - q * inner16;
-        const unsigned outer = q / extent;
-        const unsigned k = q - outer * extent;
-        int64_t j = idx[int64_t(k) * idx_stride];
-        if (j < 0 || j >= int64_t(a_extent)) {
-            atomicOr(status, kStatusIndexOutOfRange);
-            j = j < 0 ? 0 : int64_t(a_extent) - 1;
+    const unsigned inner16 = div_inner16.d;
+    for (int64_t base = int64_t(blockIdx.x) * blockDim.x + threadIdx.x; base < int64_t(total16); base += U * stride) {
+        int64_t j[U];
+        uint32_t outer[U], rest[U];
+        bool live[U];
+#pragma unroll
+        for (int u = 0; u < U; ++u) {
+            const int64_t li = base + u * stride;
+            live[u] = li < int64_t(total16);
+            j[u] = 0;
+            outer[u] = rest[u] = 0;
+            if (live[u]) {
+                uint32_t q, k;
+                div_inner16.divmod(static_cast<uint32_t>(li), q, rest[u]);
+                div_extent.divmod(q, outer[u], k);
+                j[u] = idx[int64_t(k) * idx_stride];
+            }
         }
-        out[i] = a[(int64_t(outer) * a_extent + j) * inner16 + rest];
+        uint4 v[U];
+#pragma unroll
+        for (int u = 0; u < U; ++u) {
+            if (live[u]) {
+                if (j[u] < 0 || j[u] >= int64_t(a_extent)) {
+                    atomicOr(status, kStatusIndexOutOfRange);
+                    j[u] = j[u] < 0 ? 0 : int64_t(a_extent) - 1;
+                }
+                v[u] = a[(int64_t(outer[u]) * a_extent + j[u]) * inner16 + rest[u]];
+            }
+        }
+#pragma unroll
+        for (int u = 0; u < U; ++u) {
+            if (live[u]) {
+                out[base + u * stride] = v[u];
+            }
+        }
     }
 }
 
@@ -1060,9 +1085,11 @@ void launch_movement(b200_ctx* ctx, const b200_node& node) {
             if (a.contiguous && row_bytes % 16 == 0 && small && reinterpret_cast<uintptr_t>(a.data) % 16 == 0 &&
                 reinterpret_cast<uintptr_t>(out.data) % 16 == 0) {
                 const int64_t total16 = total * static_cast<int64_t>(esz) / 16;
-                launch_kernel(ctx, index_select_rows_kernel, grid_for(total16, kThreads), kThreads, 0, reinterpret_cast<uint4*>(out.data), reinterpret_cast<const uint4*>(a.data), ip, istride,
-                    static_cast<unsigned>(row_bytes / 16), static_cast<unsigned>(out.dim[axis]),
-                    static_cast<unsigned>(a.dim[axis]), static_cast<unsigned>(total16), ctx->d_status);
+                launch_kernel(ctx, index_select_rows_kernel, grid_for(ceil_div(total16, 4), kThreads), kThreads, 0,
+                              reinterpret_cast<uint4*>(out.data), reinterpret_cast<const uint4*>(a.data), ip, istride,
+                              FastDiv(static_cast<uint32_t>(row_bytes / 16)),
+                              FastDiv(static_cast<uint32_t>(out.dim[axis])), static_cast<unsigned>(a.dim[axis]),
+                              static_cast<unsigned>(total16), ctx->d_status);
                 break;
             }
             const unsigned grid = grid_for(total, kThreads);
