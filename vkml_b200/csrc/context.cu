@@ -550,6 +550,9 @@ int b200_create(int cuda_ordinal, b200_ctx** out) {
         *ctx->h_status = 0;
         // VKML_B200_GEMM_PRECISION = 3xtf32 (default) | tf32 | fp32, read once per context:
         // the counterpart of the VKML_GEMM_* switches (vulkan_backend.cpp:2160-2178)
+        if (const char* e = std::getenv("VKML_B200_GEMM_GROUP_M")) {
+            ctx->gemm_group_m = std::max(0, std::min(1024, std::atoi(e)));
+        }
         if (const char* e = std::getenv("VKML_B200_GEMM_BN")) {
             ctx->gemm_bn_override = std::atoi(e);
         }

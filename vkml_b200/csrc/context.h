@@ -112,6 +112,7 @@ struct b200_ctx {
     // VKML_B200_GEMM_OPERANDS: planes (0) = split each operand into TF32 planes in HBM first; direct (1)
     // = the GEMM kernel reads fp32 operands and splits them on the way into shared memory; auto (-1).
     int gemm_operands = -1;
+    int gemm_group_m = 0;      // VKML_B200_GEMM_GROUP_M: M-tiles per L2 group of the tile walk (0: the built-in 16)
     int gemm_bn_override = 0;  // VKML_B200_GEMM_BN: force the N extent of the tensor-core tile (tuning aid)
     // SMs the persistent GEMM kernel leaves free while a span's gradients are being all-reduced,
     // so the communication kernels always find room (VKML_B200_COMM_SMS, default 0: measured no gain at 2 GPUs).

@@ -393,6 +393,7 @@ struct TcArgs {
     int splits;
     int64_t split_stride;  // elements between partial planes
     int64_t tiles_m, tiles_n;
+    int group_m;           // M-tiles walked together before moving along N (L2 reuse of the B tiles)
     uint32_t* status;
     // Dynamic tile order: null = every CTA walks units blockIdx.x, +gridDim.x, ... ; otherwise a
     // zeroed counter from which CTAs draw their units after the first, so a CTA that starts late
@@ -490,10 +491,10 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a_hi, const __grid_consta
         int64_t t = u / g.splits;
         batch = t / tiles_per_batch;
         t -= batch * tiles_per_batch;
-        const int64_t group_size = int64_t(kGroupM) * g.tiles_n;
+        const int64_t group_size = int64_t(g.group_m) * g.tiles_n;
         const int64_t group = t / group_size;
-        const int64_t first_m = group * kGroupM;
-        const int64_t rows_in_group = min(int64_t(kGroupM), g.tiles_m - first_m);
+        const int64_t first_m = group * g.group_m;
+        const int64_t rows_in_group = min(int64_t(g.group_m), g.tiles_m - first_m);
         const int64_t in_group = t - group * group_size;
         tm = first_m + in_group % rows_in_group;
         tn = in_group / rows_in_group;
@@ -1108,6 +1109,7 @@ void gemm_tc(b200_ctx* ctx, const GemmProblem& p, bool three_pass) {
         g.split_stride = out_elems;
         g.tiles_m = tiles_m;
         g.tiles_n = tiles_n;
+        g.group_m = ctx->gemm_group_m > 0 ? ctx->gemm_group_m : kGroupM;
         g.status = ctx->d_status;
         const int grid = static_cast<int>(std::min<int64_t>(tiles * splits, ctx->prop.multiProcessorCount));
         {
@@ -1216,6 +1218,7 @@ void gemm_tc(b200_ctx* ctx, const GemmProblem& p, bool three_pass) {
     g.split_stride = out_elems;
     g.tiles_m = tiles_m;
     g.tiles_n = tiles_n;
+    g.group_m = ctx->gemm_group_m > 0 ? ctx->gemm_group_m : kGroupM;
     g.status = ctx->d_status;
     int sms = ctx->prop.multiProcessorCount;
     if (ctx->in_grad_sync_span && ctx->comm_pending) {
