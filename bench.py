@@ -655,6 +655,11 @@ def run_gemm_sweep(args, local_rank):
               ("conv2 fwd W[128x576] bcast . cols[256][576x256]", 256, 128, 576, 256, "bn"),
               ("conv3 fwd W[256x1152] bcast . cols[256][1152x64]", 256, 256, 1152, 64, "bn"),
               ("conv1 fwd W[64x27] bcast . cols[256][27x1024]", 256, 64, 27, 1024, "bn"),
+              ("conv2 dcols W^T[576x128] bcast . g[256][128x256]", 256, 576, 128, 256, "Bn"),
+              ("conv2 dW g[256][128x256] . cols^T[256][256x576]", 256, 128, 256, 576, "nT"),
+              ("conv3 dcols W^T[1152x256] bcast . g[256][256x64]", 256, 1152, 256, 64, "Bn"),
+              ("conv3 dW g[256][256x64] . cols^T[256][64x1152]", 256, 256, 64, 1152, "nT"),
+              ("CNN head 256x4096 . W^T(100)", 1, 256, 4096, 100, "nt"),
               ("MNIST MLP 64x784 . W^T(128)", 1, 64, 784, 128, "nt")]
     for name, batch, m, k, n, kind in shapes:
         if args.filter and args.filter not in name:
@@ -663,6 +668,14 @@ def run_gemm_sweep(args, local_rank):
             a = DeviceTensor.from_host(backend, rng.standard_normal((m, k), dtype=np.float32)).reshape(
                 (1, 1, m, k)).broadcast_to((1, batch, m, k))
             b = DeviceTensor.from_host(backend, rng.standard_normal((1, batch, k, n), dtype=np.float32))
+        elif kind == "Bn":   # A = a transposed view of a broadcast [k, m] matrix (dcols = W^T . g)
+            a = DeviceTensor.from_host(backend, rng.standard_normal((k, m), dtype=np.float32)).transpose(0, 1)
+            a = DeviceTensor(backend, a.storage, (1, 1) + a.dims, (0, 0) + a.strides, a.dtype).broadcast_to(
+                (1, batch, m, k))
+            b = DeviceTensor.from_host(backend, rng.standard_normal((1, batch, k, n), dtype=np.float32))
+        elif kind == "nT":   # batched A, B = a transposed view of batched [n, k] storage (dW = g . cols^T)
+            a = DeviceTensor.from_host(backend, rng.standard_normal((1, batch, m, k), dtype=np.float32))
+            b = DeviceTensor.from_host(backend, rng.standard_normal((1, batch, n, k), dtype=np.float32)).transpose(2, 3)
         else:
             a = DeviceTensor.from_host(backend, rng.standard_normal((k, m) if kind[0] == "t" else (m, k),
                                                                     dtype=np.float32))
