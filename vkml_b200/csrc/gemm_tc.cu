@@ -52,6 +52,7 @@ constexpr int kThreads = 192;
 constexpr int kProducerThreads = 256;  // direct-operand variant: two groups of four warps
 constexpr int kThreadsDirect = kThreads + kProducerThreads;
 constexpr int kGroupM = 16;
+constexpr int kEpiPitch = 36;   // words per row of the epilogue's staging patch (16-byte aligned rows)
 constexpr int kSchedRing = 4;  // published-but-unconsumed tile numbers per CTA
 constexpr uint64_t kWaitLimitNs = 4000000000ULL;  // 4 s
 
@@ -447,6 +448,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a_hi, const __grid_consta
     __shared__ int sched_ring[kSchedRing];
     __shared__ uint32_t tmem_base_slot;
     __shared__ int abort_flag;
+    __shared__ __align__(16) float epi_patch[4][32][kEpiPitch];  // one transposing patch per epilogue warp
 
     const int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
@@ -746,16 +748,49 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a_hi, const __grid_consta
             const bool row_ok = row < g.m;
             const bool vec_ok = (g.n % 4 == 0) && ((reinterpret_cast<uintptr_t>(g.out) & 15) == 0) &&
                                 ((g.split_stride % 4) == 0);
-#pragma unroll 1
+            const bool warp_rows_live = tm * BM + quarter * 32 < g.m;  // else nothing of this warp's is stored
+#pragma unroll 2
             for (int c = 0; c < BN / 32; ++c) {
-                if (col0 + c * 32 >= g.n) {
+                if (col0 + c * 32 >= g.n || !warp_rows_live) {
                     break;  // uniform across the warp
                 }
                 uint32_t r[32];
                 tmem_ld32(tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + acc * BN + c * 32, r);
+                const int64_t left = g.n - (col0 + c * 32);
+                if (vec_ok && left >= 32) {
+                    // Each lane holds 32 columns of ITS row, so storing from here makes every warp
+                    // instruction touch 32 different rows (32 wavefronts for 512 bytes).  The chunk
+                    // goes through a 32 x 36-word patch of shared memory instead and leaves as four
+                    // 128-byte row segments per instruction; both the row-wise writes and the
+                    // quarter-warp-per-row reads of the patch are conflict-free.
+                    float* patch = &epi_patch[quarter][0][0];
+#pragma unroll
+                    for (int j = 0; j < 8; ++j) {
+                        float4 v;
+                        v.x = __uint_as_float(r[4 * j]);
+                        v.y = __uint_as_float(r[4 * j + 1]);
+                        v.z = __uint_as_float(r[4 * j + 2]);
+                        v.w = __uint_as_float(r[4 * j + 3]);
+                        *reinterpret_cast<float4*>(patch + lane * kEpiPitch + 4 * j) = v;
+                    }
+                    __syncwarp();
+                    const int sub = lane >> 3, seg = lane & 7;
+                    const int64_t row_base = tm * BM + quarter * 32;
+                    float* tile_dst = g.out + int64_t(split) * g.split_stride + (batch * g.m + row_base) * g.n + col0 +
+                                      c * 32 + seg * 4;
+#pragma unroll
+                    for (int i = 0; i < 8; ++i) {
+                        const int rl = i * 4 + sub;
+                        if (row_base + rl < g.m) {
+                            const float4 v = *reinterpret_cast<const float4*>(patch + rl * kEpiPitch + seg * 4);
+                            *reinterpret_cast<float4*>(tile_dst + int64_t(rl) * g.n) = v;
+                        }
+                    }
+                    __syncwarp();
+                    continue;
+                }
                 if (row_ok) {
                     float* p = dst + c * 32;
-                    const int64_t left = g.n - (col0 + c * 32);
                     if (vec_ok && left >= 32) {
 #pragma unroll
                         for (int j = 0; j < 8; ++j) {
