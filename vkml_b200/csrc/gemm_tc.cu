@@ -790,23 +790,12 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a_hi, const __grid_consta
                     continue;
                 }
                 if (row_ok) {
+                    // ragged right edge, or an output that cannot take 128-bit stores
                     float* p = dst + c * 32;
-                    if (vec_ok && left >= 32) {
 #pragma unroll
-                        for (int j = 0; j < 8; ++j) {
-                            float4 v;
-                            v.x = __uint_as_float(r[4 * j]);
-                            v.y = __uint_as_float(r[4 * j + 1]);
-                            v.z = __uint_as_float(r[4 * j + 2]);
-                            v.w = __uint_as_float(r[4 * j + 3]);
-                            reinterpret_cast<float4*>(p)[j] = v;
-                        }
-                    } else {
-#pragma unroll
-                        for (int j = 0; j < 32; ++j) {
-                            if (j < left) {
-                                p[j] = __uint_as_float(r[j]);
-                            }
+                    for (int j = 0; j < 32; ++j) {
+                        if (j < left) {
+                            p[j] = __uint_as_float(r[j]);
                         }
                     }
                 }
