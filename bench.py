@@ -483,7 +483,7 @@ def train_section(args, backend, rank, world, dist, barrier, max_over_ranks):
     if use_graphs:
         # replayed graphs launch the step's kernels as graph nodes, which the library's launch
         # counter does not see: count the same step's kernels from the profiled (eager) pass
-        launches = sum(counts.values())
+        launches = round(sum(counts.values()), 2)
     out = {"workload": f"{desc}, per-GPU batch {batch}, fp32, cross-entropy, SGD momentum 0.9: the framework's "
                        f"recorded step ({args.train}) replayed by the library's step tape",
            "samples_per_s": batch * world * k / (dev_ms * 1e-3), "ms_per_step": dev_ms / k,
