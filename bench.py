@@ -33,9 +33,25 @@ ROOT = os.path.dirname(os.path.abspath(__file__))
 sys.path.insert(0, ROOT)
 
 SEED_DATA = 20260728
-# dram__bytes_read.sum + dram__bytes_write.sum of one launch of the tensor-core kernel,
-# from profiles/ (None until a capture of this kernel has been taken).
-TRAFFIC_BYTES_PER_LAUNCH = 4820527104  # 4.565 GB read + 0.256 GB written at 8192^3 (profiles/gemm_tc_3xtf32.md)
+# dram__bytes_read.sum + dram__bytes_write.sum of ONE launch of the tensor-core kernel at 8192^3,
+# quoted from an ncu capture of that kernel (4.565 GB read + 0.256 GB written); it is not
+# re-measured in the run that prints it, and the line says so.
+TRAFFIC_BYTES_PER_LAUNCH = 4820527104
+
+
+def gemm_config(size, precision, world):
+    """The `config` object of the contract line; both arms print the same one."""
+    return {"workload": f"fp32 GEMM C=A.B, M=N=K={size}, A,B ~ N(0,1) seed {SEED_DATA}, one matmul node "
+                        "through Backend.compute",
+            "m": size, "n": size, "k": size, "precision": precision,  # the arithmetic of the B200 arm
+            "cache": "operands (268 MB each at 8192) exceed L2; no flush needed",
+            "parallelism": "independent replicas" if world > 1 else "single GPU"}
+
+
+def reference_rows(size, cores):
+    """Rows of A in one bounded sample of the reference CPU product: the same slab for the
+    `cpu_baseline` object and for every step of `--impl reference`."""
+    return int(min(size, 4 * cores))
 
 
 def parse():
@@ -135,8 +151,8 @@ def reference_lib():
     return lib
 
 
-def reference_slab_seconds(lib, a, b, rows: int, threads: int) -> float:
-    """Seconds the reference matmul kernel takes for A[:rows] . B on `threads` host threads."""
+def reference_slab(lib, a, b, rows: int, threads: int):
+    """(seconds, C[:rows]) of the reference matmul kernel for A[:rows] . B on `threads` host threads."""
     from vkml_b200.graph import DType, NodeDesc, Op, TensorDesc
     k, n = b.shape
     out = np.empty((rows, n), dtype=np.float32)
@@ -149,25 +165,27 @@ def reference_slab_seconds(lib, a, b, rows: int, threads: int) -> float:
     dt = time.perf_counter() - t0
     if rc != 0:
         raise RuntimeError(f"reference matmul failed with status {rc}")
-    return dt
+    return dt, out
 
 
-def cpu_baseline(a, b, budget_s: float = 12.0):
+def cpu_baseline(a, b, passes: int = 2):
+    """The reference CPU kernel on a bounded sample of the workload (the first rows of the product),
+    timed on all host threads; also returns those rows of C, which the caller compares with the GPU's."""
     lib = reference_lib()
     cores = os.cpu_count() or 1
     size = a.shape[0]
     if lib is None:
-        return None
-    probe_rows = cores
-    t = reference_slab_seconds(lib, a, b, probe_rows, cores)
-    rows = int(max(cores, min(size, probe_rows * budget_s / max(t, 1e-6))))
-    rows = max(cores, rows // cores * cores)
-    t = reference_slab_seconds(lib, a, b, rows, cores)
-    flops = 2.0 * rows * size * size
+        return None, None
+    rows = reference_rows(size, cores)
+    t, out = 0.0, None
+    for _ in range(passes):
+        dt, out = reference_slab(lib, a, b, rows, cores)
+        t += dt
+    flops = 2.0 * rows * size * size * passes
     return {"value": flops / t / 1e12, "unit": "TFLOP/s", "cores": cores, "kind": "reference",
             "sample": f"rows 0..{rows} of A: a {rows}x{size}x{size} slab of the {size}^3 product through the "
-                      f"reference matmul kernel, {cores} host threads over row slabs, {t:.1f} s",
-            "seconds": t, "full_size_seconds_extrapolated": t * size / rows}
+                      f"reference matmul kernel, {cores} host threads over row slabs, {passes} passes, {t:.1f} s",
+            "seconds": t, "full_size_seconds_extrapolated": t / passes * size / rows}, out
 
 
 def run_reference(args, rank, world):
@@ -178,28 +196,23 @@ def run_reference(args, rank, world):
     base = {"impl": "reference", "metric": "fp32_gemm_tflops", "unit": "TFLOP/s", "n_gpus": args.gpus,
             "steps": args.steps, "warmup": args.warmup, "higher_is_better": True, "scaling": "weak",
             "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-            "config": {"workload": f"fp32 GEMM {args.size}^3, A,B ~ N(0,1)", "m": args.size, "n": args.size,
-                       "k": args.size}}
+            "config": gemm_config(args.size, args.precision, world)}
     if lib is None:
         print(json.dumps({"impl": "reference", "unavailable": "oracle/_ref/libvkml_ref.so is not built"}))
         return
     cores = os.cpu_count() or 1
-    # size one step at ~2 s of CPU work so steps+warmup stay within minutes
-    t_probe = reference_slab_seconds(lib, a, b, cores, cores)
-    total = max(1, args.steps + args.warmup)
-    rows = int(max(cores, min(args.size, cores * min(2.0, 150.0 / total) / max(t_probe, 1e-6))))
-    rows = max(cores, rows // cores * cores)
+    rows = reference_rows(args.size, cores)
     for _ in range(args.warmup):
-        reference_slab_seconds(lib, a, b, rows, cores)
+        reference_slab(lib, a, b, rows, cores)
     t = 0.0
     for _ in range(args.steps):
-        t += reference_slab_seconds(lib, a, b, rows, cores)
+        t += reference_slab(lib, a, b, rows, cores)[0]
     flops = 2.0 * rows * args.size * args.size * args.steps
     v = flops / t / 1e12
-    base.update({"value": v, "ms_per_step": t / args.steps * 1e3,
-                 "cpu_baseline": {"value": v, "unit": "TFLOP/s", "cores": cores, "kind": "reference",
-                                  "sample": f"each step: rows 0..{rows} of A ({rows}x{args.size}x{args.size} slab) "
-                                            f"through the reference CPU matmul kernel on {cores} threads"},
+    sample = (f"each step: rows 0..{rows} of A ({rows}x{args.size}x{args.size} slab of the product) through the "
+              f"reference CPU matmul kernel on {cores} host threads")
+    base.update({"value": v, "ms_per_step": t / args.steps * 1e3, "sample": sample,
+                 "cpu_baseline": {"value": v, "unit": "TFLOP/s", "cores": cores, "kind": "reference", "sample": sample},
                  "e2e": {"value": v, "unit": "TFLOP/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}})
     print(json.dumps(base))
 
@@ -251,7 +264,6 @@ def run_b200(args, rank, local_rank, world):
     barrier()
     sampler = ClockSampler(local_rank)
     sampler.start()
-    backend.set_profiling(True)
     launches0 = backend.stats()["kernel_launches"]
     backend.timer_begin()
     for _ in range(args.steps):
@@ -259,11 +271,21 @@ def run_b200(args, rank, local_rank, world):
     ms = backend.timer_end()
     barrier()
     launches = backend.stats()["kernel_launches"] - launches0
+    # a second pass of the same steps with an event pair around every launch: the per-kernel
+    # durations behind `roofline` (kept out of the timed region, whose figure they would inflate)
+    backend.set_profiling(True)
+    for _ in range(args.steps):
+        backend.compute_packed(packed, 1)
     records = backend.last_profile()
     backend.set_profiling(False)
     clocks = sampler.stop()
     ms = max_over_ranks(ms)
     value = flops_per_step * args.steps * world / (ms * 1e-3) / 1e12
+    # the first rows of C as the timed launches left them, for the parity object below
+    cores = os.cpu_count() or 1
+    check_rows = reference_rows(size, cores)
+    c_rows = np.empty((check_rows, size), dtype=np.float32)
+    backend.copy_to_host(c_rows, c.storage, 0, c_rows.nbytes)
 
     # ---- roofline of the dominant kernel ----
     pk = peaks()
@@ -283,12 +305,9 @@ def run_b200(args, rank, local_rank, world):
         roofline = {"bound": "tensor", "kernel": main_label, "achieved": achieved, "peak": peak,
                     "unit": "TFLOP/s", "frac": achieved / peak,
                     "traffic": TRAFFIC_BYTES_PER_LAUNCH if (size == 8192 and args.precision == "3xtf32") else None,
-                    "avg_launch_ms": avg_ms,
+                    "traffic_source": "quoted from one ncu capture of this kernel at this size; not measured in this run",
+                    "avg_launch_ms": avg_ms, "launches_timed": len(by_label[main_label]),
                     "tensor_pipe_tflops": achieved * passes, "tensor_pipe_frac": achieved * passes / peak,
-                    # back-to-back launches run under the power cap: the sustained yardstick beside the burst one
-                    "peak_sustained": (pk["bf16_tflops_sustained"] / 2.0) if pk.get("bf16_tflops_sustained") else None,
-                    "tensor_pipe_frac_of_sustained": (achieved * passes / (pk["bf16_tflops_sustained"] / 2.0))
-                    if pk.get("bf16_tflops_sustained") else None,
                     "peak_source": f"{pk['source']}: bf16_tflops/2 (TF32 runs at half the bf16 rate)",
                     "note": "achieved counts the algorithmic 2*M*N*K once; 3xTF32 issues it three times on "
                             "the tensor pipe (tensor_pipe_*), so frac cannot exceed 1/3"}
@@ -329,9 +348,17 @@ def run_b200(args, rank, local_rank, world):
         for p in (pin_a, pin_b, pin_c):
             backend.free_host(p)
 
-    cpu = None
+    cpu, parity = None, None
     if rank == 0 and world == 1 and not args.no_cpu_baseline:
-        cpu = cpu_baseline(a_host, b_host)
+        cpu, ref_rows = cpu_baseline(a_host, b_host)
+        if ref_rows is not None:
+            # the rows the CPU baseline computed anyway, against the same rows of the timed result
+            want = ref_rows.astype(np.float64)
+            diff = c_rows.astype(np.float64) - want
+            parity = {"rows": int(check_rows), "outputs": int(c_rows.size),
+                      "rel_frobenius": float(np.linalg.norm(diff) / np.linalg.norm(want)),
+                      "bound": 1e-5 * float(np.sqrt(size)), "max_abs": float(np.max(np.abs(diff))),
+                      "against": "the reference CPU matmul kernel on the same operands (rows 0..%d of C)" % check_rows}
 
     del a, b, c, packed
     backend.trim()
@@ -345,12 +372,8 @@ def run_b200(args, rank, local_rank, world):
             "dtype": {"3xtf32": "f32 (3xTF32 split on tcgen05, fp32 accumulate)", "tf32": "tf32",
                       "fp32": "f32"}[args.precision],
             "data": "synthetic",
-            "config": {"workload": f"fp32 GEMM C=A.B, M=N=K={size}, A,B ~ N(0,1) seed {SEED_DATA}, one matmul node "
-                                   "through Backend.compute (operand split + tensor-core kernel)",
-                       "m": size, "n": size, "k": size, "precision": args.precision,
-                       "cache": "operands (268 MB each at 8192) exceed L2; no flush needed",
-                       "parallelism": "independent replicas" if world > 1 else "single GPU"},
-            "roofline": roofline, "cpu_baseline": cpu, "e2e": e2e, "gpu_launches": launches,
+            "config": gemm_config(size, args.precision, world),
+            "roofline": roofline, "cpu_baseline": cpu, "parity": parity, "e2e": e2e, "gpu_launches": launches,
             "kernels": kernel_share, "clocks": clocks, "train": train,
         }
         print(json.dumps(line))

@@ -523,4 +523,25 @@ int vkml_ref_train_cnn(int device, int64_t cin, int64_t hw, int64_t c1, int64_t 
     }
 }
 
+// Cross-entropy forward and backward through the reference API (src/api/ops.cpp:417-441 and the
+// autograd rules of src/autograd/autograd.cpp:528-546): loss = cross_entropy(logits, labels),
+// backward(loss).  Returns the scalar loss and d loss / d logits ([b, c]).  The device sees
+// exactly the node sequence the framework emits for this composite.
+int vkml_ref_cross_entropy(int device, const float* logits, const int64_t* labels, int64_t b, int64_t c,
+                           float* loss_out, float* grad_out) {
+    try {
+        const vkml::Device dev = pick_device(device);
+        vkml::Tensor x = vkml::Tensor::from_host(logits, {b, c}, vkml::DType::F32, dev);
+        const vkml::Tensor y = vkml::Tensor::from_host(labels, {b}, vkml::DType::I64, dev);
+        x.set_requires_grad(true);
+        const vkml::Tensor loss = vkml::cross_entropy(x, y);
+        vkml::backward(loss);
+        *loss_out = loss.item();
+        x.grad().contiguous().to_host(grad_out);
+        return B200_OK;
+    } catch (const std::exception& e) {
+        return status_of(e);
+    }
+}
+
 }  // extern "C"

@@ -193,17 +193,21 @@ def test_known_answers(cuda, backend):
 
 
 def test_out_of_range_index_is_reported(cuda, backend):
-    """The CPU backend throws IndexError (kernels_movement.cpp:362,419); the device
-    clamps, records it, and the next synchronize reports an index error."""
+    """The CPU backend throws IndexError before any value is visible
+    (kernels_movement.cpp:362,419); the device clamps, records it, and the error reaches the
+    caller with the first read of a result -- copy_to_host alone, the framework's normal way
+    of observing a tensor -- or at the next synchronize, whichever comes first."""
     table = np.arange(12, dtype=np.float32).reshape(4, 3)
     idx = np.array([0, 4], dtype=np.int64)
-    cuda.run(Op.INDEX_SELECT, [table, idx], (2, 3), DType.F32, graph.axis_params(0), sync_check=False)
-    with pytest.raises(IndexError):
-        backend.synchronize()
+    with pytest.raises(IndexError):  # run() ends in copy_to_host, nothing else synchronises
+        cuda.run(Op.INDEX_SELECT, [table, idx], (2, 3), DType.F32, graph.axis_params(0), sync_check=False)
     backend.synchronize()  # the word is cleared: the context stays usable
-    cuda.run(Op.SCATTER_ADD, [table[:2], np.array([0, -1], dtype=np.int64)], (4, 3), DType.F32,
-             graph.axis_params(0), sync_check=False)
-    with pytest.raises(IndexError):
+    from vkml_b200 import DeviceTensor, NodeDesc
+    src = DeviceTensor.from_host(backend, table[:2].copy())
+    bad = DeviceTensor.from_host(backend, np.array([0, -1], dtype=np.int64))
+    out = DeviceTensor.empty(backend, (4, 3))
+    backend.compute([NodeDesc(Op.SCATTER_ADD, out.desc, [src.desc, bad.desc], graph.axis_params(0))])
+    with pytest.raises(IndexError):  # no read in between: reported by synchronize
         backend.synchronize()
     got = cuda.run(Op.INDEX_SELECT, [table, np.array([3, 0], dtype=np.int64)], (2, 3), DType.F32,
                    graph.axis_params(0))

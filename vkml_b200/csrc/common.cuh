@@ -13,7 +13,21 @@
 namespace b200 {
 
 constexpr int kMaxDims = B200_MAX_DIMS;
-constexpr int kSmCount = 148;  // B200: 2 dies x 74 SMs; grids are sized in multiples of this
+
+// SMs of the CURRENT device (a B200 has 148: 2 dies x 74); grids, wave counts and split
+// decisions are sized in multiples of this.  Every entry point makes its context's device
+// current before it launches, so the current device is the one the launch goes to.
+inline int sm_count() {
+    static int cached[64] = {};
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return 148;
+    if (cached[dev] == 0) {
+        int n = 0;
+        if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0) n = 148;
+        cached[dev] = n;
+    }
+    return cached[dev];
+}
 
 // Bits of the device status word (b200_ctx::d_status). Kernels never trap:
 // they record the problem here, skip or clamp the access, and the host turns
@@ -296,7 +310,7 @@ inline int64_t ceil_div(int64_t a, int64_t b) { return (a + b - 1) / b; }
 // capped at a whole number of waves across the 148 SMs.
 inline unsigned grid_for(int64_t work, int threads, int blocks_per_sm = 8) {
     const int64_t need = ceil_div(work, threads);
-    const int64_t cap = int64_t(kSmCount) * blocks_per_sm;
+    const int64_t cap = int64_t(sm_count()) * blocks_per_sm;
     int64_t g = need < cap ? need : cap;
     if (g < 1) {
         g = 1;

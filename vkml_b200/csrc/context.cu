@@ -137,6 +137,12 @@ void CachingAllocator::release(void* ptr) {
     live_.erase(it);
 }
 
+size_t CachingAllocator::size_of(void* ptr) {
+    std::lock_guard<std::mutex> lock(mu_);
+    auto it = live_.find(ptr);
+    return it == live_.end() ? 0 : it->second;
+}
+
 void CachingAllocator::trim() {
     std::lock_guard<std::mutex> lock(mu_);
     for (auto& kv : free_) {
@@ -544,8 +550,8 @@ int b200_create(int cuda_ordinal, b200_ctx** out) {
         B200_CUDA_CHECK(cudaStreamCreateWithFlags(&ctx->stream, cudaStreamNonBlocking));
         B200_CUDA_CHECK(cudaMalloc(&ctx->d_status, sizeof(uint32_t)));
         B200_CUDA_CHECK(cudaMemset(ctx->d_status, 0, sizeof(uint32_t)));
-        B200_CUDA_CHECK(cudaMalloc(&ctx->d_counters, sizeof(unsigned) * (4096 + 64)));
-        B200_CUDA_CHECK(cudaMemset(ctx->d_counters, 0, sizeof(unsigned) * (4096 + 64)));
+        B200_CUDA_CHECK(cudaMalloc(&ctx->d_counters, sizeof(unsigned) * kArrivalCounters));
+        B200_CUDA_CHECK(cudaMemset(ctx->d_counters, 0, sizeof(unsigned) * kArrivalCounters));
         B200_CUDA_CHECK(cudaMallocHost(&ctx->h_status, sizeof(uint32_t)));
         *ctx->h_status = 0;
         // VKML_B200_GEMM_PRECISION = 3xtf32 (default) | tf32 | fp32, read once per context:
@@ -646,7 +652,7 @@ int b200_free(b200_ctx* ctx, void* ptr) {
     return guarded(ctx, [&] {
         if (ptr != nullptr && dist_has_pending(ctx)) {
             // a buffer still being all-reduced: later work that reuses the block must come after it
-            dist_wait_range(ctx, ptr, static_cast<const char*>(ptr) + 1);
+            dist_wait_range(ctx, ptr, static_cast<const char*>(ptr) + std::max<size_t>(ctx->alloc.size_of(ptr), 1));
         }
         ctx->alloc.release(ptr);
     });
@@ -884,6 +890,8 @@ static int report_device_status(b200_ctx* ctx) {
     if (bits == 0) return B200_OK;
     *ctx->h_status = 0;
     cudaMemsetAsync(ctx->d_status, 0, sizeof(uint32_t), ctx->stream);
+    // a kernel that gave up may have left arrival counters of a split reduction half-counted
+    cudaMemsetAsync(ctx->d_counters, 0, sizeof(unsigned) * kArrivalCounters, ctx->stream);
     if (bits & kStatusIndexOutOfRange) {
         set_error(ctx, "an index passed to index_select / scatter_add was out of range");
         return B200_INDEX_ERROR;
@@ -900,11 +908,22 @@ int b200_copy_to_host(b200_ctx* ctx, void* dst_host, const void* src_device, siz
     if (ctx == nullptr) return B200_INVALID_ARGUMENT;
     if (nbytes == 0) return B200_OK;
     if (dst_host == nullptr || src_device == nullptr) return B200_INVALID_ARGUMENT;
-    return guarded(ctx, [&] {
+    // Reading a tensor back is the framework's normal way of observing a result, so an error the
+    // device recorded while producing it (an out-of-range index that was clamped) is reported
+    // here, with the bytes, and not only at a later explicit synchronize: the CPU backend rejects
+    // such an index before any value is visible (src/backend/cpu/kernels_movement.cpp:362,419).
+    int device_rc = B200_OK;
+    const int rc = guarded(ctx, [&] {
         dist_wait_range(ctx, src_device, static_cast<const char*>(src_device) + nbytes);
         B200_CUDA_CHECK(cudaMemcpyAsync(dst_host, src_device, nbytes, cudaMemcpyDeviceToHost, ctx->stream));
+        if (!ctx->capturing) {
+            B200_CUDA_CHECK(cudaMemcpyAsync(ctx->h_status, ctx->d_status, sizeof(uint32_t),
+                                            cudaMemcpyDeviceToHost, ctx->stream));
+        }
         B200_CUDA_CHECK(cudaStreamSynchronize(ctx->stream));
+        if (!ctx->capturing) device_rc = report_device_status(ctx);
     });
+    return rc != B200_OK ? rc : device_rc;
 }
 
 int b200_copy_device_to_device(b200_ctx* ctx, const b200_copy* copies, size_t n) {

@@ -27,6 +27,7 @@ class CachingAllocator {
 public:
     void* allocate(size_t nbytes);
     void release(void* ptr);
+    size_t size_of(void* ptr);  // bytes of a block that is currently handed out (0 if unknown)
     void trim();
     ~CachingAllocator();
 
@@ -39,6 +40,10 @@ private:
     std::unordered_map<void*, size_t> sizes_;     // every block ever handed out
     std::unordered_map<void*, size_t> live_;      // blocks currently out (ptr -> size)
 };
+
+// Words behind b200_ctx::d_counters: 4096 arrival counters of split reductions, then 64 words
+// for the persistent GEMM's tile counter.
+constexpr size_t kArrivalCounters = 4096 + 64;
 
 struct DistState;  // dist.cu
 

@@ -140,8 +140,8 @@ void gemm_simt(b200_ctx* ctx, const GemmProblem& p) {
     int64_t splits = 1;
     // few tiles and a long K: spread K over the idle SMs in chunks of at least 48 (three
     // K-blocks, enough for the register prefetch to overlap anything)
-    if (tiles < kSmCount && p.k >= 192) {
-        splits = std::min<int64_t>(ceil_div(2 * kSmCount, tiles), p.k / 48);
+    if (tiles < sm_count() && p.k >= 192) {
+        splits = std::min<int64_t>(ceil_div(2 * sm_count(), tiles), p.k / 48);
         splits = std::max<int64_t>(1, std::min<int64_t>(splits, 64));
     }
     int64_t k_chunk = ceil_div(ceil_div(p.k, splits), BK) * BK;

@@ -1071,10 +1071,10 @@ void gemm_tc(b200_ctx* ctx, const GemmProblem& p, bool three_pass) {
     // tiles against 7 half-cost waves of 128-wide ones).
     int bn = 64;
     if (p.n > 64) bn = 128;
-    if (p.n > 128 && p.m * p.n * batches >= int64_t(128) * 256 * kSmCount) {
+    if (p.n > 128 && p.m * p.n * batches >= int64_t(128) * 256 * sm_count()) {
         const int64_t tm = ceil_div(p.m, BM);
-        const double cost256 = double(ceil_div(tm * ceil_div(p.n, 256) * batches, kSmCount));
-        const double cost128 = double(ceil_div(tm * ceil_div(p.n, 128) * batches, kSmCount)) * 0.5275;
+        const double cost256 = double(ceil_div(tm * ceil_div(p.n, 256) * batches, sm_count()));
+        const double cost128 = double(ceil_div(tm * ceil_div(p.n, 128) * batches, sm_count())) * 0.5275;
         bn = cost128 < cost256 ? 128 : 256;
     }
     if (ctx->gemm_bn_override == 64 || ctx->gemm_bn_override == 128 || ctx->gemm_bn_override == 256) {
@@ -1087,10 +1087,10 @@ void gemm_tc(b200_ctx* ctx, const GemmProblem& p, bool three_pass) {
 
     // split K when the tiles alone cannot fill the machine
     int64_t splits = 1;
-    if (tiles < kSmCount && k_blocks >= 16) {
+    if (tiles < sm_count() && k_blocks >= 16) {
         // as many K-slices as keep every unit in ONE wave of the persistent grid: rounding up
         // instead (32 tiles x 5 slices = 160 units on 148 SMs) runs a second, nearly empty wave
-        splits = std::min<int64_t>(kSmCount / tiles, k_blocks / 8);
+        splits = std::min<int64_t>(sm_count() / tiles, k_blocks / 8);
         splits = std::max<int64_t>(1, std::min<int64_t>(splits, 64));
     }
     int64_t kb_per_split = ceil_div(k_blocks, splits);

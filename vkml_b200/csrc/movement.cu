@@ -816,7 +816,7 @@ bool aligned16(const void* p) { return reinterpret_cast<uintptr_t>(p) % 16 == 0;
 int planes_per_block(int64_t items_per_plane, int64_t bytes_per_plane, int64_t byte_limit, int64_t planes) {
     int64_t group = ceil_div(int64_t(2) * kThreads, std::max<int64_t>(items_per_plane, 1));
     group = std::min(group, std::max<int64_t>(byte_limit / std::max<int64_t>(bytes_per_plane, 1), 1));
-    group = std::min(group, std::max<int64_t>(planes / (int64_t(kSmCount) * 8), 1));
+    group = std::min(group, std::max<int64_t>(planes / (int64_t(sm_count()) * 8), 1));
     return static_cast<int>(std::max<int64_t>(group, 1));
 }
 

@@ -517,7 +517,7 @@ void launch_reduce_kernels(b200_ctx* ctx, const View& out, const float* src, con
     if (column) {
         int64_t splits = 1;
         if (n_red >= 64) {
-            splits = ceil_div(int64_t(kSmCount) * 2048, n_out);
+            splits = ceil_div(int64_t(sm_count()) * 2048, n_out);
             splits = std::min<int64_t>(splits, n_red / 16);
             splits = std::max<int64_t>(1, std::min<int64_t>(splits, 1024));
         }
@@ -537,7 +537,7 @@ void launch_reduce_kernels(b200_ctx* ctx, const View& out, const float* src, con
                 if (n_red >= 64) {
                     // eight vectors per thread in flight, so half as many K-slices (and half the
                     // partial rows the last block has to fold) keep the memory system as busy
-                    sp = ceil_div(int64_t(kSmCount) * 512, n_out4);
+                    sp = ceil_div(int64_t(sm_count()) * 512, n_out4);
                     sp = std::max<int64_t>(1, std::min<int64_t>(std::min<int64_t>(sp, n_red / 16), 1024));
                 }
                 RedGeoT<I> g4 = g;
@@ -592,8 +592,8 @@ void launch_reduce_kernels(b200_ctx* ctx, const View& out, const float* src, con
     const bool warp = n_units <= 1024 && n_out >= 1024;
     const int64_t groups_per_block = warp ? 8 : 1;
     int64_t splits = 1;
-    if (!warp && n_out < int64_t(kSmCount) * 8 && n_units >= 4096) {
-        splits = ceil_div(int64_t(kSmCount) * 8, n_out);
+    if (!warp && n_out < int64_t(sm_count()) * 8 && n_units >= 4096) {
+        splits = ceil_div(int64_t(sm_count()) * 8, n_out);
         splits = std::min<int64_t>(splits, n_units / 2048);
         splits = std::max<int64_t>(1, std::min<int64_t>(splits, 65535));
     }
@@ -1053,13 +1053,11 @@ softmax_bulk_kernel(float* __restrict__ out, const float* __restrict__ in, SoftG
 template <bool LOG>
 void launch_softmax_bulk(b200_ctx* ctx, float* dst, const float* src, const SoftGeo& g, int64_t n_rows) {
     const size_t smem = static_cast<size_t>(g.n_axis) * sizeof(float);
-    static bool raised[2] = {false, false};
-    if (!raised[LOG ? 1 : 0]) {
-        B200_CUDA_CHECK(cudaFuncSetAttribute(softmax_bulk_kernel<LOG>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                             160 * 1024));
-        raised[LOG ? 1 : 0] = true;
-    }
-    const unsigned grid = static_cast<unsigned>(std::min<int64_t>(n_rows, kSmCount));
+    // the limit is a per-device attribute of the kernel and a process may hold several contexts:
+    // set it at every launch (it is a cheap host-side call)
+    B200_CUDA_CHECK(cudaFuncSetAttribute(softmax_bulk_kernel<LOG>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                         160 * 1024));
+    const unsigned grid = static_cast<unsigned>(std::min<int64_t>(n_rows, sm_count()));
     launch_kernel(ctx, softmax_bulk_kernel<LOG>, grid, 1024, smem, dst, src, g, n_rows, ctx->d_status);
     ctx->count_launch();
     check_last_launch("softmax (bulk prefetch)");
@@ -1070,7 +1068,7 @@ void launch_softmax_reg(b200_ctx* ctx, float* dst, const float* src, const SoftG
     constexpr int kBlock = GROUP == 32 ? 256 : GROUP;
     constexpr int kRows = kBlock / GROUP;
     const int64_t blocks = ceil_div(n_rows, kRows);
-    const unsigned grid = static_cast<unsigned>(std::min<int64_t>(blocks, int64_t(kSmCount) * (2048 / kBlock) * 4));
+    const unsigned grid = static_cast<unsigned>(std::min<int64_t>(blocks, int64_t(sm_count()) * (2048 / kBlock) * 4));
     launch_kernel(ctx, softmax_reg_kernel<LOG, GROUP, ITEMS, VEC4>, grid, kBlock, 0, dst, src, g, n_rows);
     ctx->count_launch();
     check_last_launch("softmax (registers)");
@@ -1134,7 +1132,7 @@ void run_softmax(b200_ctx* ctx, const View& out, const View& in, int axis4) {
             if (u <= 2048) return launch_softmax_reg<LOG, 256, 8, true>(ctx, dst, src, g, n_rows);
             // enough rows to keep every SM busy with more than one: prefetch the next row while
             // the current one is processed
-            if (u <= 8192 && n_rows >= 2 * int64_t(kSmCount)) return launch_softmax_bulk<LOG>(ctx, dst, src, g, n_rows);
+            if (u <= 8192 && n_rows >= 2 * int64_t(sm_count())) return launch_softmax_bulk<LOG>(ctx, dst, src, g, n_rows);
             if (u <= 8192) return launch_softmax_reg<LOG, 1024, 8, true>(ctx, dst, src, g, n_rows);
         } else {
             if (n <= 256) return launch_softmax_reg<LOG, 32, 8, false>(ctx, dst, src, g, n_rows);
@@ -1159,13 +1157,9 @@ void run_softmax(b200_ctx* ctx, const View& out, const View& in, int axis4) {
     }
     const size_t smem = staged ? row_bytes : 0;
     if (smem > 48 * 1024) {
-        static bool raised[2] = {false, false};
-        if (!raised[LOG ? 1 : 0]) {
-            B200_CUDA_CHECK(cudaFuncSetAttribute(softmax_block_kernel<LOG>,
-                                                 cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                                 160 * 1024));
-            raised[LOG ? 1 : 0] = true;
-        }
+        // per device, so per launch (see launch_softmax_bulk)
+        B200_CUDA_CHECK(cudaFuncSetAttribute(softmax_block_kernel<LOG>,
+                                             cudaFuncAttributeMaxDynamicSharedMemorySize, 160 * 1024));
     }
     // resident blocks per SM: limited by shared memory and by 2048 threads
     int per_sm = 2048 / threads;
@@ -1173,7 +1167,7 @@ void run_softmax(b200_ctx* ctx, const View& out, const View& in, int axis4) {
         per_sm = std::min<int>(per_sm, static_cast<int>((200 * 1024) / (smem + 1024)));
     }
     per_sm = std::max(per_sm, 1);
-    const unsigned grid = static_cast<unsigned>(std::min<int64_t>(n_rows, int64_t(kSmCount) * per_sm));
+    const unsigned grid = static_cast<unsigned>(std::min<int64_t>(n_rows, int64_t(sm_count()) * per_sm));
     launch_kernel(ctx, softmax_block_kernel<LOG>, grid, threads, smem, dst, src, g, n_rows, staged,
                                                                    vec4 ? 1 : 0);
     ctx->count_launch();
@@ -1356,7 +1350,7 @@ extern "C" int b200_sum_columns_f32_noalloc(const float* in, int64_t rows, int64
     // as many splits as fill the machine, as few as fit the partial planes
     int64_t splits = 1;
     if (rows >= 64) {
-        splits = ceil_div(int64_t(kSmCount) * 2048, cols);
+        splits = ceil_div(int64_t(sm_count()) * 2048, cols);
         splits = std::min<int64_t>(splits, rows / 16);
         splits = std::min<int64_t>(splits, B200_NOALLOC_MAX_COLUMNS / cols);
         splits = std::max<int64_t>(1, std::min<int64_t>(splits, 1024));
