@@ -463,6 +463,16 @@ def matmul_tc_cases(seed=12):
     yield mk("conv1-k27-bcast-a", rnd(1, 1, 64, 27), rnd(1, 16, 27, 1024))     # K below one K-block
     big = rnd(1, 1, 700, 1200)
     yield mk("sliced", big[:, :, 5:605, 16:1016], rnd(1, 1, 1000, 300))
+    # a small left operand and a right operand with n contiguous: the streamed-operand kernel
+    yield mk("stream-skinny-splitk", rnd(1, 1, 64, 2048), rnd(1, 1, 2048, 512))
+    yield mk("stream-ragged-m-n-k", rnd(1, 1, 100, 1333), rnd(1, 1, 1333, 260))
+    yield mk("stream-two-m-tiles", rnd(1, 1, 256, 320), rnd(1, 3, 320, 384))
+    yield mk("stream-batches-in-a-tile", rnd(1, 1, 256, 1152), rnd(1, 8, 1152, 64))       # conv3 forward: N = 64
+    yield mk("stream-batches-in-a-tile-n32", rnd(1, 1, 48, 1024), rnd(2, 8, 1024, 32))
+    yield mk("stream-w-transposed", t(rnd(1, 1, 200, 96)), rnd(1, 4, 96, 256))            # conv dcols: W^T view
+    yield mk("stream-w-batched", rnd(1, 4, 128, 256), rnd(1, 4, 256, 192))
+    wide = rnd(1, 1, 512, 640)
+    yield mk("stream-pitched-s", rnd(1, 1, 96, 512), wide[:, :, :, 64:576])                # S is a column slice
 
 
 def movement_cases(seed=21, quick=False):

@@ -569,6 +569,12 @@ int b200_create(int cuda_ordinal, b200_ctx** out) {
             else if (v == "auto") ctx->gemm_operands = -1;
             else fail(B200_INVALID_ARGUMENT, "VKML_B200_GEMM_OPERANDS must be auto, planes or direct");
         }
+        if (const char* e = std::getenv("VKML_B200_GEMM_STREAM")) {
+            const std::string v(e);
+            if (v == "auto") ctx->gemm_stream = -1;
+            else if (v == "0" || v == "1") ctx->gemm_stream = v == "1" ? 1 : 0;
+            else fail(B200_INVALID_ARGUMENT, "VKML_B200_GEMM_STREAM must be auto, 0 or 1");
+        }
         if (const char* e = std::getenv("VKML_B200_GEMM_SCHEDULE")) {
             const std::string v(e);
             if (v == "static") ctx->gemm_schedule = 0;

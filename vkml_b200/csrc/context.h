@@ -41,9 +41,9 @@ private:
     std::unordered_map<void*, size_t> live_;      // blocks currently out (ptr -> size)
 };
 
-// Words behind b200_ctx::d_counters: 4096 arrival counters of split reductions, then 64 words
-// for the persistent GEMM's tile counter.
-constexpr size_t kArrivalCounters = 4096 + 64;
+// Words behind b200_ctx::d_counters: 4096 arrival counters of split reductions, 64 words for the
+// persistent GEMM's tile counter, 1024 arrival counters of the streamed-operand GEMM's split-K fold.
+constexpr size_t kArrivalCounters = 4096 + 64 + 1024;
 
 struct DistState;  // dist.cu
 
@@ -117,6 +117,10 @@ struct b200_ctx {
     // VKML_B200_GEMM_OPERANDS: planes (0) = split each operand into TF32 planes in HBM first; direct (1)
     // = the GEMM kernel reads fp32 operands and splits them on the way into shared memory; auto (-1).
     int gemm_operands = -1;
+    // VKML_B200_GEMM_STREAM: the streamed-operand kernel for products bound by HBM (a small left
+    // operand, a large right one read exactly once).  auto (-1): wherever the layout allows it and
+    // no other operand scheme was asked for by name; 0 / 1: never / wherever the layout allows.
+    int gemm_stream = -1;
     int gemm_group_m = 0;      // VKML_B200_GEMM_GROUP_M: M-tiles per L2 group of the tile walk (0: the built-in 16)
     int gemm_bn_override = 0;  // VKML_B200_GEMM_BN: force the N extent of the tensor-core tile (tuning aid)
     // SMs the persistent GEMM kernel leaves free while a span's gradients are being all-reduced,

@@ -2,7 +2,8 @@
 // does not take (tiny or ragged problems such as the 64x10 logits of the MNIST
 // MLP or conv1's K = 27) and for B200_GEMM_FP32.
 //
-// 64x64 output tile, K in steps of 16, 256 threads with a 4x4 register block;
+// 64x64 output tile, K in steps of 16, 256 threads with a 4x4 register block, products
+// rounded before they are summed (no fused multiply-add: this is the exactness path);
 // operands are read through their element strides, the staging index order is
 // picked per operand so the global reads follow whichever axis has unit stride
 // (a transposed view is read along its own rows).  A long K with too few tiles
@@ -84,7 +85,13 @@ gemm_simt_kernel(GemmProblem p, float* __restrict__ dst, int64_t k_chunk, int64_
             for (int i = 0; i < 4; ++i) {
 #pragma unroll
                 for (int j = 0; j < 4; ++j) {
-                    acc[i][j] = fmaf(a[i], b[j], acc[i][j]);
+                    // a rounded product, then a rounded add -- never a fused multiply-add.  vkML's
+                    // kernels round every product (shaders/gemm_reg.comp:215 `precise`; the CPU
+                    // backend multiplies, then sums), and its adversarial inputs tell the two apart:
+                    // alternating +-1e7 sums to exactly zero only if each 1e14 is rounded before it
+                    // is added, and an overflowing product must become an infinity of its own sign
+                    // so that +inf and -inf meet as NaN (tests/python/test_invariants.py:496-531).
+                    acc[i][j] = __fadd_rn(__fmul_rn(a[i], b[j]), acc[i][j]);
                 }
             }
         }

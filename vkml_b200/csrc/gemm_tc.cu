@@ -822,6 +822,389 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a_hi, const __grid_consta
     }
 }
 
+// ---------------------------------------------------------------------------
+// Streamed-operand kernel: products bound by HBM, not by the tensor pipe
+// ---------------------------------------------------------------------------
+//
+// C[b][m][n] = sum_k W[b][m][k] * S[b][k][n] with a SMALL W (few rows: a skinny left operand,
+// convolution weights broadcast over the batch) and a LARGE S whose n axis is contiguous
+// (a row-major [K][N] matrix, the column tensor of a convolution).  The plane scheme reads S,
+// writes its two TF32 planes and reads them again -- five times S's bytes -- which is what
+// bounds such a product.  Here S crosses HBM exactly once, as fp32:
+//
+//   * the product is computed transposed, D[n][m] = sum_k S[k][n] W[m][k], so that S is the
+//     tensor core's A operand, and A may come from TENSOR MEMORY instead of shared memory;
+//   * warp 0 brings [32 k][128 n] fp32 tiles of S (tensor map over the caller's own matrix,
+//     zero fill past the edges) and the matching K-block of W's planes into a 4-deep ring;
+//   * eight converter warps read their lane's column of the S tile (lane = n, conflict-free),
+//     split every value into hi/lo in registers and put both into tensor memory with
+//     tcgen05.st -- 64 columns per stage: the streamed operand never touches shared memory
+//     again and no converted copy of it exists anywhere;
+//   * warp 1 issues tcgen05.mma with A = [tmem] (128 lanes x 8 columns per K-step) and B = W's
+//     plane tile in shared memory, three passes into one fp32 accumulator as above;
+//   * warps 2-5 read the accumulator (lane = n, columns = m): for every m one warp instruction
+//     stores 32 consecutive n, 128 bytes, straight from registers.
+//
+// When N is shorter than 128 and W is broadcast over the batch, one tile spans several batches
+// (lanes = batch x n).  K is split across CTAs when the tiles alone cannot fill the machine;
+// the warp that arrives last at its quarter of a tile folds the partial planes in split order in
+// the same launch (deterministic, no atomics on data).
+constexpr int kStreamStages = 4;
+constexpr int kStreamThreads = 448;       // 14 warps: TMA, MMA, 4 epilogue, 8 converters
+constexpr int kStreamTileBytes = BK * 128 * 4;  // one fp32 tile of S: 32 K-rows x 128 lanes
+constexpr uint32_t kStreamTmemCols = 512;
+constexpr int kStreamCounters = 1024;     // arrival counters of the in-kernel split-K fold: 4 per tile
+constexpr int kStreamCounterBase = 4096 + 64;  // their place behind b200_ctx::d_counters
+
+struct StreamArgs {
+    float* out;            // C, or the partial planes when splits > 1
+    float* folded;         // C when splits > 1 (target of the in-kernel fold)
+    int64_t m, n;          // per batch
+    int64_t batches;
+    int64_t w_batch_rows;  // rows between consecutive batches in W's planes (0: broadcast)
+    int64_t k_blocks, kb_per_split;
+    int splits;
+    int64_t split_stride;  // elements between partial planes
+    int64_t tiles_m, tiles_n;
+    int nt;                // n extent of one batch inside a tile (128, or N when N < 128)
+    int bpt;               // batches per tile (nt * bpt == 128 when bpt > 1)
+    int64_t batch_groups;  // ceil(batches / bpt)
+    uint32_t* status;
+    unsigned int* counters;
+};
+
+__device__ __forceinline__ void umma_tf32_ts(uint32_t tmem_d, uint32_t tmem_a, uint64_t bdesc, uint32_t idesc,
+                                             uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::tf32 [%0], [%1], %2, %3, p;\n\t}"
+        ::"r"(tmem_d), "r"(tmem_a), "l"(bdesc), "r"(idesc), "r"(accumulate)
+        : "memory");
+}
+
+__device__ __forceinline__ void tmem_st16(uint32_t taddr, const uint32_t (&r)[16]) {
+    asm volatile(
+        "tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], "
+        "{%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16};"
+        ::"r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]),
+          "r"(r[8]), "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15])
+        : "memory");
+}
+
+__device__ __forceinline__ void tma_load_3d(uint32_t dst, const CUtensorMap* map, uint32_t bar, int c0, int c1,
+                                            int c2) {
+    asm volatile(
+        "cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5}], [%2];"
+        ::"r"(dst), "l"(reinterpret_cast<uint64_t>(map)), "r"(bar), "r"(c0), "r"(c1), "r"(c2)
+        : "memory");
+}
+
+template <int BNW>
+struct StreamSmem {
+    static constexpr int kWBytes = BNW * BK * 4;  // one plane tile of W
+    static constexpr int kStageBytes = kStreamTileBytes + 2 * kWBytes;
+    static constexpr int kTotal = kStreamStages * kStageBytes + 256 + 1024;
+};
+
+template <int BNW, bool THREE_PASS, bool W_MN>
+__global__ void __launch_bounds__(kStreamThreads, 1)
+gemm_stream_kernel(const __grid_constant__ CUtensorMap map_s, const __grid_constant__ CUtensorMap map_w_hi,
+                   const __grid_constant__ CUtensorMap map_w_lo, StreamArgs g) {
+    using S = StreamSmem<BNW>;
+    constexpr int STAGES = kStreamStages;
+    constexpr uint32_t kIdesc = make_idesc(BM, BNW, false, W_MN);
+    constexpr uint32_t kStageTx = kStreamTileBytes + (THREE_PASS ? 2 : 1) * S::kWBytes;
+    constexpr uint32_t kStageCol0 = 2 * BNW;  // tensor-memory columns: two accumulators, then the S stages
+
+    extern __shared__ uint8_t smem_raw[];
+    const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+    uint8_t* base_ptr = smem_raw + (base - smem_u32(smem_raw));
+    const uint32_t bars = base + STAGES * S::kStageBytes;
+    auto full_bar = [&](int s) { return bars + 8u * s; };                    // S tile and W planes landed
+    auto empty_bar = [&](int s) { return bars + 8u * (STAGES + s); };        // the stage's MMAs are done
+    auto conv_bar = [&](int s) { return bars + 8u * (2 * STAGES + s); };     // S is in tensor memory
+    auto acc_full = [&](int a) { return bars + 8u * (3 * STAGES + a); };
+    auto acc_empty = [&](int a) { return bars + 8u * (3 * STAGES + 2 + a); };
+    __shared__ uint32_t tmem_base_slot;
+    __shared__ int abort_flag;
+
+    const int warp = threadIdx.x >> 5;
+    const int lane = threadIdx.x & 31;
+
+    if (threadIdx.x == 0) {
+        abort_flag = 0;
+        for (int s = 0; s < STAGES; ++s) {
+            mbar_init(full_bar(s), 1);
+            mbar_init(empty_bar(s), 1);
+            mbar_init(conv_bar(s), 8);  // one arrival per converter warp
+        }
+        for (int a = 0; a < 2; ++a) {
+            mbar_init(acc_full(a), 1);
+            mbar_init(acc_empty(a), 4);
+        }
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+    }
+    if (warp == 1) {
+        tmem_alloc(smem_u32(&tmem_base_slot), kStreamTmemCols);
+        tc_fence_before();
+    }
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = tmem_base_slot;
+    volatile int* abort_p = &abort_flag;
+    pdl_prologue();
+
+    const int64_t n_units = g.tiles_m * g.splits * g.tiles_n * g.batch_groups;
+    // unit -> (m tile, K split, n tile, batch group): the m tiles of one S tile run side by side
+    auto decode = [&](int64_t u, int64_t& tm, int& split, int64_t& tn, int64_t& bg) {
+        tm = u % g.tiles_m;
+        int64_t t = u / g.tiles_m;
+        split = static_cast<int>(t % g.splits);
+        t /= g.splits;
+        tn = t % g.tiles_n;
+        bg = t / g.tiles_n;
+    };
+
+    if (warp == 0) {
+        // ---------------- TMA producer ----------------
+        if (lane == 0) {
+            uint32_t it = 0;
+            bool ok = true;
+            for (int64_t u = blockIdx.x; u < n_units && ok; u += gridDim.x) {
+                int64_t tm, tn, bg;
+                int split;
+                decode(u, tm, split, tn, bg);
+                const int batch0 = static_cast<int>(bg * g.bpt);
+                const int n0 = static_cast<int>(tn * g.nt);
+                const int m0 = static_cast<int>(tm * BNW);
+                const int w_base = static_cast<int>(batch0 * g.w_batch_rows);
+                const int64_t kb0 = int64_t(split) * g.kb_per_split;
+                const int64_t kb1 = min(kb0 + g.kb_per_split, g.k_blocks);
+                for (int64_t kb = kb0; kb < kb1; ++kb, ++it) {
+                    const int s = it % STAGES;
+                    const uint32_t ph = (it / STAGES) & 1;
+                    if (!mbar_wait(empty_bar(s), ph ^ 1, abort_p, g.status)) {
+                        ok = false;
+                        break;
+                    }
+                    const uint32_t stage = base + s * S::kStageBytes;
+                    const uint32_t bar = full_bar(s);
+                    const int kc = static_cast<int>(kb * BK);
+                    mbar_arrive_expect_tx(bar, kStageTx);
+                    tma_load_3d(stage, &map_s, bar, n0, kc, batch0);
+                    auto load_w = [&](uint32_t dst, const CUtensorMap* map) {
+                        if (W_MN) {
+#pragma unroll
+                            for (int atom = 0; atom < BNW / 32; ++atom) {
+                                tma_load_2d(dst + atom * kMnAtomBytes, map, bar, m0 + 32 * atom, w_base + kc);
+                            }
+                        } else {
+                            tma_load_2d(dst, map, bar, kc, w_base + m0);
+                        }
+                    };
+                    load_w(stage + kStreamTileBytes, &map_w_hi);
+                    if (THREE_PASS) {
+                        load_w(stage + kStreamTileBytes + S::kWBytes, &map_w_lo);
+                    }
+                }
+            }
+        }
+    } else if (warp == 1) {
+        // ---------------- MMA issuer ----------------
+        if (lane == 0) {
+            uint32_t it = 0;
+            uint32_t tile_it = 0;
+            bool ok = true;
+            for (int64_t u = blockIdx.x; u < n_units && ok; u += gridDim.x, ++tile_it) {
+                int64_t tm, tn, bg;
+                int split;
+                decode(u, tm, split, tn, bg);
+                const int acc = tile_it & 1;
+                const uint32_t aph = (tile_it >> 1) & 1;
+                if (!mbar_wait(acc_empty(acc), aph ^ 1, abort_p, g.status)) {
+                    break;
+                }
+                tc_fence_after();
+                const uint32_t d_tmem = tmem_base + acc * BNW;
+                const int64_t kb0 = int64_t(split) * g.kb_per_split;
+                const int64_t kb1 = min(kb0 + g.kb_per_split, g.k_blocks);
+                for (int64_t kb = kb0; kb < kb1; ++kb, ++it) {
+                    const int s = it % STAGES;
+                    const uint32_t ph = (it / STAGES) & 1;
+                    if (!mbar_wait(full_bar(s), ph, abort_p, g.status) ||
+                        !mbar_wait(conv_bar(s), ph, abort_p, g.status)) {
+                        ok = false;
+                        break;
+                    }
+                    tc_fence_after();
+                    const uint32_t stage = base + s * S::kStageBytes;
+                    const uint64_t w_hi = operand_desc<W_MN>(stage + kStreamTileBytes);
+                    const uint64_t w_lo = operand_desc<W_MN>(stage + kStreamTileBytes + S::kWBytes);
+                    const uint32_t s_hi = tmem_base + kStageCol0 + s * 64;
+                    const uint32_t s_lo = s_hi + 32;
+#pragma unroll
+                    for (int kk = 0; kk < BK / UMMA_K; ++kk) {
+                        const uint64_t adv_w = static_cast<uint64_t>((W_MN ? kk * 1024 : kk * UMMA_K * 4) >> 4);
+                        const uint32_t first = (kb == kb0 && kk == 0) ? 0u : 1u;
+                        if (THREE_PASS) {
+                            umma_tf32_ts(d_tmem, s_lo + kk * UMMA_K, w_hi + adv_w, kIdesc, first);
+                            umma_tf32_ts(d_tmem, s_hi + kk * UMMA_K, w_lo + adv_w, kIdesc, 1u);
+                            umma_tf32_ts(d_tmem, s_hi + kk * UMMA_K, w_hi + adv_w, kIdesc, 1u);
+                        } else {
+                            umma_tf32_ts(d_tmem, s_hi + kk * UMMA_K, w_hi + adv_w, kIdesc, first);
+                        }
+                    }
+                    umma_commit(empty_bar(s));  // shared-memory stage and tensor-memory stage are both free then
+                }
+                if (ok) {
+                    umma_commit(acc_full(acc));
+                }
+            }
+        }
+    } else if (warp < 6) {
+        // ---------------- epilogue (warps 2..5) ----------------
+        const int quarter = warp & 3;
+        const int l = quarter * 32 + lane;  // tensor-memory lane = position along (batch, n) of the tile
+        const int bl = l / g.nt;
+        const int nn = l - bl * g.nt;
+        uint32_t tile_it = 0;
+        for (int64_t u = blockIdx.x; u < n_units; u += gridDim.x, ++tile_it) {
+            int64_t tm, tn, bg;
+            int split;
+            decode(u, tm, split, tn, bg);
+            const int acc = tile_it & 1;
+            const uint32_t aph = (tile_it >> 1) & 1;
+            if (!mbar_wait(acc_full(acc), aph, abort_p, g.status)) {
+                break;
+            }
+            tc_fence_after();
+            const int64_t batch = bg * g.bpt + bl;
+            const int64_t n = tn * g.nt + nn;
+            const bool lane_ok = batch < g.batches && n < g.n;
+            const int64_t m0 = tm * BNW;
+            const int64_t col = (batch * g.m) * g.n + n;  // + m * N
+            float* dst = g.out + int64_t(split) * g.split_stride + col;
+#pragma unroll 1
+            for (int c = 0; c < BNW / 32; ++c) {
+                if (m0 + c * 32 >= g.m) {
+                    break;  // uniform
+                }
+                uint32_t r[32];
+                tmem_ld32(tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + acc * BNW + c * 32, r);
+                if (lane_ok) {
+                    const int64_t left = g.m - (m0 + c * 32);
+#pragma unroll
+                    for (int j = 0; j < 32; ++j) {
+                        if (j < left) {
+                            dst[(m0 + c * 32 + j) * g.n] = __uint_as_float(r[j]);
+                        }
+                    }
+                }
+            }
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) {
+                mbar_arrive(acc_empty(acc));
+            }
+            if (g.splits > 1) {
+                // Split K: each epilogue warp owns 32 lanes of the tile in every K-slice.  The warp
+                // that completes its lanes' last slice folds the slices, in split order -- a
+                // per-warp arrival counter, so no warp ever waits for another one.
+                __threadfence();
+                __syncwarp();
+                unsigned old = 0;
+                if (lane == 0) {
+                    const int64_t tile = (bg * g.tiles_n + tn) * g.tiles_m + tm;
+                    old = atomicInc(g.counters + tile * 4 + quarter, static_cast<unsigned>(g.splits - 1));
+                }
+                old = __shfl_sync(0xffffffffu, old, 0);
+                if (old == static_cast<unsigned>(g.splits - 1)) {
+                    __threadfence();
+                    if (lane_ok) {
+                        const int64_t rows = min(int64_t(BNW), g.m - m0);
+                        for (int64_t j = 0; j < rows; ++j) {
+                            const int64_t o = col + (m0 + j) * g.n;
+                            float sum = __ldcg(g.out + o);
+                            for (int sp = 1; sp < g.splits; ++sp) {
+                                sum += __ldcg(g.out + int64_t(sp) * g.split_stride + o);
+                            }
+                            g.folded[o] = sum;
+                        }
+                    }
+                }
+            }
+        }
+    } else {
+        // ---------------- converters (warps 6..13): S tile -> hi / lo in tensor memory ----------------
+        const int quarter = warp & 3;
+        const int half = (warp - 6) >> 2;  // which 16 of the stage's 32 K columns
+        const int l = quarter * 32 + lane;
+        const int bl = l / g.nt;
+        const int nn = l - bl * g.nt;
+        const uint32_t first_off = static_cast<uint32_t>(((bl * BK + half * 16) * g.nt + nn) * 4);
+        const uint32_t k_step = static_cast<uint32_t>(g.nt * 4);
+        const uint32_t lane_field = static_cast<uint32_t>(quarter * 32) << 16;
+        uint32_t it = 0;
+        bool ok = true;
+        for (int64_t u = blockIdx.x; u < n_units && ok; u += gridDim.x) {
+            int64_t tm, tn, bg;
+            int split;
+            decode(u, tm, split, tn, bg);
+            const int64_t kb0 = int64_t(split) * g.kb_per_split;
+            const int64_t kb1 = min(kb0 + g.kb_per_split, g.k_blocks);
+            for (int64_t kb = kb0; kb < kb1; ++kb, ++it) {
+                const int s = it % STAGES;
+                const uint32_t ph = (it / STAGES) & 1;
+                // the producer refilled this stage only after its previous MMAs had finished, so the
+                // stage's tensor-memory columns are free as well
+                if (!mbar_wait(full_bar(s), ph, abort_p, g.status)) {
+                    ok = false;
+                    break;
+                }
+                const float* tile = reinterpret_cast<const float*>(base_ptr + s * S::kStageBytes + first_off);
+                float v[16];
+#pragma unroll
+                for (int j = 0; j < 16; ++j) {
+                    v[j] = *reinterpret_cast<const float*>(reinterpret_cast<const uint8_t*>(tile) + j * k_step);
+                }
+                uint32_t hi[16], lo[16];
+#pragma unroll
+                for (int j = 0; j < 16; ++j) {
+                    float h, lw;
+                    split_tf32_fast(v[j], h, lw);
+                    hi[j] = __float_as_uint(h);
+                    lo[j] = __float_as_uint(lw);
+                }
+                const uint32_t t_hi = tmem_base + lane_field + kStageCol0 + s * 64 + half * 16;
+                tmem_st16(t_hi, hi);
+                if (THREE_PASS) {
+                    tmem_st16(t_hi + 32, lo);
+                }
+                asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
+                tc_fence_before();
+                __syncwarp();
+                if (lane == 0) {
+                    mbar_arrive(conv_bar(s));
+                }
+            }
+        }
+    }
+
+    __syncthreads();
+    if (abort_flag != 0) {
+        for (int i = 0; i < 200; ++i) {
+            __nanosleep(1000);
+        }
+        __syncthreads();
+    }
+    if (warp == 1) {
+        tc_fence_after();
+        tmem_dealloc(tmem_base, kStreamTmemCols);
+    }
+}
+
 __global__ void __launch_bounds__(256)
 fold_partials_kernel(float* __restrict__ out, const float* __restrict__ partial, int64_t n, int splits) {
     pdl_prologue();
@@ -1037,6 +1420,184 @@ void release_use(b200_ctx* ctx, const Operand& o) {
     }
 }
 
+// ---- streamed-operand kernel: eligibility and launch ----
+
+struct StreamPlan {
+    bool ok = false;
+    int nt = 128, bpt = 1, bnw = 64;
+    int64_t batch_stride = 0;  // elements between consecutive batches of S
+};
+
+// The product qualifies when its right operand can be read by TMA as it lies in memory (n
+// contiguous, 16-byte pitches, batches one constant stride apart) and its left operand is small:
+// with at most 256 rows the streamed operand is worth 128 flops per byte at most, and one pass
+// over it beats reading it once, writing two planes and reading those.
+StreamPlan plan_stream(const b200_ctx* ctx, const GemmProblem& p) {
+    StreamPlan sp;
+    if (ctx->gemm_stream == 0 || (ctx->gemm_stream < 0 && ctx->gemm_operands >= 0)) {
+        return sp;  // switched off, or another operand scheme was asked for by name
+    }
+    const int64_t batches = p.b0 * p.b1;
+    if (p.m > 256 || p.n < 32 || batches < 1) return sp;
+    if (p.b_s[3] != 1 || p.b_s[2] % 4 != 0 || p.b_s[2] < p.n) return sp;
+    if (reinterpret_cast<uintptr_t>(p.b) % 16 != 0) return sp;
+    int64_t sb = std::max<int64_t>(p.k * p.b_s[2], 4);
+    if (batches > 1) {
+        if (p.b0 == 1) sb = p.b_s[1];
+        else if (p.b1 == 1) sb = p.b_s[0];
+        else if (p.b_s[0] == p.b1 * p.b_s[1]) sb = p.b_s[1];
+        else return sp;
+        if (sb <= 0 || sb % 4 != 0) return sp;
+    }
+    const bool a_bcast = (p.a_s[0] == 0 || p.b0 == 1) && (p.a_s[1] == 0 || p.b1 == 1);
+    if (p.n >= 128) {
+        sp.nt = 128;
+        sp.bpt = 1;
+    } else if ((p.n == 32 || p.n == 64) && a_bcast && batches % (128 / p.n) == 0) {
+        sp.nt = static_cast<int>(p.n);  // a tile spans several batches: lanes = batch x n
+        sp.bpt = static_cast<int>(128 / p.n);
+    } else {
+        return sp;
+    }
+    if (batches >= (int64_t(1) << 31) || p.n >= (int64_t(1) << 31) || sb * 4 >= (int64_t(1) << 40)) return sp;
+    sp.bnw = p.m <= 64 ? 64 : 128;
+    sp.batch_stride = sb;
+    sp.ok = true;
+    return sp;
+}
+
+CUtensorMap make_stream_map(const float* base, int64_t n, int64_t k, int64_t pitch, int64_t batches,
+                            int64_t batch_stride, int nt, int bpt) {
+    CUtensorMap m;
+    const cuuint64_t dims[3] = {static_cast<cuuint64_t>(n), static_cast<cuuint64_t>(k),
+                                static_cast<cuuint64_t>(batches)};
+    const cuuint64_t strides[2] = {static_cast<cuuint64_t>(pitch) * sizeof(float),
+                                   static_cast<cuuint64_t>(batch_stride) * sizeof(float)};
+    const cuuint32_t box[3] = {static_cast<cuuint32_t>(nt), BK, static_cast<cuuint32_t>(bpt)};
+    const cuuint32_t elem[3] = {1, 1, 1};
+    const CUresult rc = encode_tiled()(&m, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 3, const_cast<float*>(base), dims, strides,
+                                       box, elem, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE,
+                                       CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (rc != CUDA_SUCCESS) {
+        fail(B200_INTERNAL_ERROR, "cuTensorMapEncodeTiled (streamed operand) failed with code " + std::to_string(rc));
+    }
+    return m;
+}
+
+template <int BNW>
+void launch_stream(b200_ctx* ctx, bool three_pass, bool w_mn, const CUtensorMap& ms, const CUtensorMap& wh,
+                   const CUtensorMap& wl, const StreamArgs& g, int grid) {
+    using S = StreamSmem<BNW>;
+#define B200_STREAM_CASE(T, W)                                                                             \
+    if (three_pass == T && w_mn == W) {                                                                    \
+        auto kernel = gemm_stream_kernel<BNW, T, W>;                                                       \
+        B200_CUDA_CHECK(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, S::kTotal)); \
+        launch_kernel(ctx, kernel, grid, kStreamThreads, S::kTotal, ms, wh, wl, g);                        \
+        return;                                                                                            \
+    }
+    B200_STREAM_CASE(true, false)
+    B200_STREAM_CASE(true, true)
+    B200_STREAM_CASE(false, false)
+    B200_STREAM_CASE(false, true)
+#undef B200_STREAM_CASE
+}
+
+void gemm_stream(b200_ctx* ctx, const GemmProblem& p, bool three_pass, const StreamPlan& sp) {
+    const int64_t batches = p.b0 * p.b1;
+    const bool a_bcast = (p.a_s[0] == 0 || p.b0 == 1) && (p.a_s[1] == 0 || p.b1 == 1);
+    Operand ow = plan_operand(p.a, p.a_s[0], p.a_s[1], p.a_s[2], p.a_s[3], p.m, p.k, a_bcast, p);
+    const int64_t k_blocks = align_up(p.k, BK) / BK;
+    const int64_t tiles_m = ceil_div(p.m, sp.bnw);
+    const int64_t tiles_n = sp.bpt > 1 ? 1 : ceil_div(p.n, 128);
+    const int64_t batch_groups = ceil_div(batches, sp.bpt);
+    const int64_t tiles = tiles_m * tiles_n * batch_groups;
+    const int sms = ctx->prop.multiProcessorCount;
+    int64_t splits = 1;
+    if (tiles < sms && k_blocks >= 16 && tiles * 4 <= kStreamCounters) {
+        splits = std::min<int64_t>(sms / tiles, k_blocks / 8);
+        splits = std::max<int64_t>(1, std::min<int64_t>(splits, 64));
+    }
+    const int64_t kb_per_split = ceil_div(k_blocks, splits);
+    splits = ceil_div(k_blocks, kb_per_split);
+    const int64_t out_elems = batches * p.m * p.n;
+    const size_t partial_bytes = splits > 1 ? static_cast<size_t>(align_up(out_elems * splits * 4, 1024)) : 0;
+
+    // W's planes: from this span's cache, into it, or into the workspace
+    const size_t planes = three_pass ? 2 : 1;
+    bool hit = false;
+    if (auto it = ctx->plane_cache.find(ow.key); it != ctx->plane_cache.end()) {
+        ow.hi = it->second.hi;
+        ow.lo = it->second.lo;
+        ow.cached = hit = true;
+        ++ctx->plane_hits;
+    } else {
+        auto uses = ctx->plane_uses.find(ow.key);
+        const size_t bytes = planes * ow.plane_bytes;
+        if (uses != ctx->plane_uses.end() && uses->second >= 2 &&
+            ctx->plane_cache_bytes + bytes <= plane_cache_limit(ctx)) {
+            char* block = static_cast<char*>(ctx->scratch.allocate(bytes));
+            ow.hi = reinterpret_cast<float*>(block);
+            ow.lo = three_pass ? reinterpret_cast<float*>(block + ow.plane_bytes) : nullptr;
+            ctx->plane_cache[ow.key] = PlaneEntry{ow.hi, ow.lo, bytes, uses->second, ow.src_begin, ow.src_end};
+            ctx->plane_cache_bytes += bytes;
+            ow.cached = true;
+        }
+    }
+    char* ws = static_cast<char*>(ctx->ensure_workspace(partial_bytes + 2048 + (ow.cached ? 0 : planes * ow.plane_bytes)));
+    ws = reinterpret_cast<char*>(align_up(reinterpret_cast<int64_t>(ws), 1024));
+    if (!ow.cached) {
+        ow.hi = reinterpret_cast<float*>(ws);
+        ow.lo = three_pass ? reinterpret_cast<float*>(ws + ow.plane_bytes) : nullptr;
+        ws += planes * ow.plane_bytes;
+    }
+    float* partial = splits > 1 ? reinterpret_cast<float*>(ws) : nullptr;
+    if (!hit) {
+        ow.split.hi = ow.hi;
+        ow.split.lo = ow.lo;
+        launch_split(ctx, ow.split, "matmul.split_a");
+        check_last_launch("matmul (operand split)");
+    }
+
+    const CUtensorMap ms = make_stream_map(p.b, p.n, p.k, p.b_s[2], batches, sp.batch_stride, sp.nt, sp.bpt);
+    auto map_w = [&](float* plane) {
+        return ow.mn ? make_map(plane, ow.nb * ow.rows_pad, ow.cols_pad, BK, true)
+                     : make_map(plane, ow.nb * ow.rows_pad, ow.cols_pad, sp.bnw, false);
+    };
+    const CUtensorMap wh = map_w(ow.hi);
+    const CUtensorMap wl = three_pass ? map_w(ow.lo) : wh;
+
+    StreamArgs g{};
+    g.out = splits > 1 ? partial : p.out;
+    g.folded = p.out;
+    g.m = p.m;
+    g.n = p.n;
+    g.batches = batches;
+    g.w_batch_rows = a_bcast ? 0 : ow.rows_pad;
+    g.k_blocks = k_blocks;
+    g.kb_per_split = kb_per_split;
+    g.splits = static_cast<int>(splits);
+    g.split_stride = out_elems;
+    g.tiles_m = tiles_m;
+    g.tiles_n = tiles_n;
+    g.nt = sp.nt;
+    g.bpt = sp.bpt;
+    g.batch_groups = batch_groups;
+    g.status = ctx->d_status;
+    g.counters = ctx->d_counters + kStreamCounterBase;
+    const int grid = static_cast<int>(std::min<int64_t>(tiles * splits, sms));
+    {
+        ProfScope scope(ctx, three_pass ? "matmul.tcgen05_3xtf32_stream" : "matmul.tcgen05_tf32_stream");
+        if (sp.bnw == 64) {
+            launch_stream<64>(ctx, three_pass, ow.mn, ms, wh, wl, g, grid);
+        } else {
+            launch_stream<128>(ctx, three_pass, ow.mn, ms, wh, wl, g, grid);
+        }
+    }
+    ctx->count_launch();
+    check_last_launch("matmul (tcgen05, streamed operand)");
+    release_use(ctx, ow);
+}
+
 }  // namespace
 
 bool gemm_tc_eligible(const b200_ctx* ctx, const GemmProblem& p) {
@@ -1060,6 +1621,10 @@ bool gemm_tc_eligible(const b200_ctx* ctx, const GemmProblem& p) {
 }
 
 void gemm_tc(b200_ctx* ctx, const GemmProblem& p, bool three_pass) {
+    if (const StreamPlan sp = plan_stream(ctx, p); sp.ok) {
+        gemm_stream(ctx, p, three_pass, sp);
+        return;
+    }
     const int64_t batches = p.b0 * p.b1;
     const int64_t kp = align_up(p.k, BK);
     const bool a_bcast = (p.a_s[0] == 0 || p.b0 == 1) && (p.a_s[1] == 0 || p.b1 == 1);
@@ -1286,6 +1851,9 @@ void gemm_tc_note_uses(b200_ctx* ctx, const GemmProblem& p) {
     const bool a_bcast = (p.a_s[0] == 0 || p.b0 == 1) && (p.a_s[1] == 0 || p.b1 == 1);
     const bool b_bcast = (p.b_s[0] == 0 || p.b0 == 1) && (p.b_s[1] == 0 || p.b1 == 1);
     ++ctx->plane_uses[plan_operand(p.a, p.a_s[0], p.a_s[1], p.a_s[2], p.a_s[3], p.m, p.k, a_bcast, p).key];
+    if (plan_stream(ctx, p).ok) {
+        return;  // the right operand is streamed as it is: it gets no planes
+    }
     ++ctx->plane_uses[plan_operand(p.b, p.b_s[0], p.b_s[1], p.b_s[3], p.b_s[2], p.n, p.k, b_bcast, p).key];
 }
 
