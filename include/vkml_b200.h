@@ -219,6 +219,11 @@ int b200_free_host(b200_ctx* ctx, void* ptr);
  * (vulkan_backend.cpp:2160-2178). */
 int b200_set_gemm_precision(b200_ctx* ctx, int precision);
 int b200_get_gemm_precision(b200_ctx* ctx);
+/* Which kernel family b200_compute would launch for this matmul node, and why: the fact the
+ * Vulkan backend publishes under the site "matmul.kernel"
+ * (vulkan_backend.cpp:2363-2375) so that a run can be tied to the arithmetic that produced it. */
+int b200_matmul_kernel(b200_ctx* ctx, const b200_node* node, char* name, size_t name_len, char* reason,
+                       size_t reason_len);
 
 /* The CUDA stream (cudaStream_t) every call on this context is ordered on, so
  * a caller that owns other device work can order against it with events. */

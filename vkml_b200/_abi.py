@@ -98,6 +98,7 @@ SYMBOLS = {
     "b200_free_host": (C.c_int, [_P, _P]),
     "b200_set_gemm_precision": (C.c_int, [_P, C.c_int]),
     "b200_get_gemm_precision": (C.c_int, [_P]),
+    "b200_matmul_kernel": (C.c_int, [_P, C.POINTER(Node), C.c_char_p, C.c_size_t, C.c_char_p, C.c_size_t]),
     "b200_stream": (_P, [_P]),
     "b200_dist_unique_id": (C.c_int, [_P]),
     "b200_dist_init": (C.c_int, [_P, C.c_int, C.c_int, _P]),

@@ -2,7 +2,9 @@
 
 #include "vkml_b200.h"
 
+#include "vkml/util/env.h"
 #include "vkml/util/error.h"
+#include "vkml/util/observe.h"
 
 #include <cstring>
 #include <mutex>
@@ -156,6 +158,15 @@ B200Backend::B200Backend(int cuda_ordinal, int device_index)
     caps_.max_shared_memory_bytes = c.max_shared_memory_bytes;
     caps_.asynchronous = true;
     allocator_ = std::make_unique<DeviceAllocator>(ctx_, device_);
+    // The library reads its switches itself when the context is created; consulting them here
+    // through vkML's one env reader (src/util/env.cpp:43-79) puts them into `configuration()`
+    // beside vkML's own, with the values this process saw.
+    for (const char* name : {"VKML_B200_GEMM_PRECISION", "VKML_B200_GEMM_OPERANDS", "VKML_B200_GEMM_STREAM",
+                             "VKML_B200_GEMM_SCHEDULE", "VKML_B200_SHARE_PLANES", "VKML_B200_PDL",
+                             "VKML_B200_LAZY_JOIN", "VKML_B200_HOIST_GRADIENTS", "VKML_B200_COMM_SMS",
+                             "VKML_B200_FUSE"}) {
+        (void)vkml::env_value(name);
+    }
 }
 
 B200Backend::~B200Backend() {
@@ -191,6 +202,20 @@ void B200Backend::compute(std::span<vkml::Node* const> nodes) {
         }
         flat.emplace_back();
         flatten(*n, flat.back());
+        if (n->op == vkml::OpKind::Matmul && vkml::observe::enabled()) {
+            // a Decision, as the Vulkan backend publishes one per matmul (vulkan_backend.cpp:2363-2375):
+            // which kernel runs decides the arithmetic, and is not derivable from the inputs alone
+            char kernel[48] = "", why[128] = "";
+            if (b200_matmul_kernel(ctx_, &flat.back(), kernel, sizeof(kernel), why, sizeof(why)) == B200_OK) {
+                vkml::observe::publish({.site = "matmul.kernel",
+                                        .op = "matmul",
+                                        .chose = kernel,
+                                        .instead_of = std::string_view(kernel) == "fp32_simt" ? "tcgen05_3xtf32" : "fp32_simt",
+                                        .because = why,
+                                        .required = n->shape.dim(n->shape.ndim() - 2),
+                                        .available = 0});
+            }
+        }
     }
     uint32_t flags = B200_COMPUTE_DEFAULT;
     if (grad_sync_armed_) {

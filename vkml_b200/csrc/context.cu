@@ -1066,6 +1066,31 @@ int b200_set_gemm_precision(b200_ctx* ctx, int precision) {
 
 int b200_get_gemm_precision(b200_ctx* ctx) { return ctx == nullptr ? -1 : ctx->gemm_precision; }
 
+int b200_matmul_kernel(b200_ctx* ctx, const b200_node* node, char* name, size_t name_len, char* reason,
+                       size_t reason_len) {
+    if (ctx == nullptr || node == nullptr || name == nullptr || name_len == 0) return B200_INVALID_ARGUMENT;
+    return guarded(ctx, [&] {
+        if (node->op != B200_OP_MATMUL) fail(B200_INVALID_ARGUMENT, "b200_matmul_kernel: not a matmul node");
+        const GemmProblem p = matmul_problem(*node);
+        const char* kernel = "fp32_simt";
+        const char* why = "the shape is too small or too ragged for a tensor-core tile";
+        if (ctx->gemm_precision == B200_GEMM_FP32) {
+            why = "plain fp32 arithmetic was asked for";
+        } else if (gemm_tc_eligible(ctx, p)) {
+            const bool three = ctx->gemm_precision == B200_GEMM_3XTF32;
+            if (gemm_tc_streams(ctx, p)) {
+                kernel = three ? "tcgen05_3xtf32_stream" : "tcgen05_tf32_stream";
+                why = "a small left operand: the right operand is read once from HBM and split on the way";
+            } else {
+                kernel = three ? "tcgen05_3xtf32" : "tcgen05_tf32";
+                why = "operands split into TF32 planes, tensor-core tiles fed by TMA";
+            }
+        }
+        std::snprintf(name, name_len, "%s", kernel);
+        if (reason != nullptr && reason_len != 0) std::snprintf(reason, reason_len, "%s", why);
+    });
+}
+
 void* b200_stream(b200_ctx* ctx) { return ctx == nullptr ? nullptr : ctx->stream; }
 
 }  // extern "C"

@@ -24,6 +24,9 @@ void gemm_simt(b200_ctx* ctx, const GemmProblem& p);
 // tcgen05 tensor-core path (3xTF32 or single-pass TF32). gemm_tc.cu
 bool gemm_tc_eligible(const b200_ctx* ctx, const GemmProblem& p);
 void gemm_tc(b200_ctx* ctx, const GemmProblem& p, bool three_pass);
+// True when gemm_tc would serve `p` with the streamed-operand kernel (a small left operand, the
+// right operand read once from HBM) rather than from operand planes.
+bool gemm_tc_streams(const b200_ctx* ctx, const GemmProblem& p);
 
 // Reuse of split operand planes inside one compute span: count the operands of every
 // tensor-core matmul before the span runs, drop planes whose source a node overwrites, and

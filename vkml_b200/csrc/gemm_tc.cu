@@ -89,6 +89,21 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
     return ok != 0;
 }
 
+// The same test, but the hardware may park the thread for up to `hint_ns` while the phase is
+// still open (it is woken when the phase completes).  For the many warps that wait for one
+// event, a parked warp leaves the issue slots and the shared-memory pipe to the warps that work.
+__device__ __forceinline__ bool mbar_try_wait_parked(uint32_t bar, uint32_t parity, uint32_t hint_ns) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok)
+        : "r"(bar), "r"(parity), "r"(hint_ns)
+        : "memory");
+    return ok != 0;
+}
+
 __device__ __forceinline__ uint64_t global_ns() {
     uint64_t t;
     asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
@@ -106,6 +121,29 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatil
     uint32_t spins = 0;
     while (!mbar_try_wait(bar, parity)) {
         if ((++spins & 0x3ff) == 0) {
+            if (*abort_flag != 0) {
+                return false;
+            }
+            const uint64_t now = global_ns();
+            if (start == 0) {
+                start = now;
+            } else if (now - start > kWaitLimitNs) {
+                *abort_flag = 1;
+                atomicOr(status, kStatusWaitTimedOut);
+                return false;
+            }
+        }
+    }
+    return true;
+}
+
+// Bounded wait for the warps of a many-waiter role: parked polls, the clock read every 64 of them.
+__device__ __forceinline__ bool mbar_wait_parked(uint32_t bar, uint32_t parity, volatile int* abort_flag,
+                                                 uint32_t* status) {
+    uint64_t start = 0;
+    uint32_t spins = 0;
+    while (!mbar_try_wait_parked(bar, parity, 2000u)) {
+        if ((++spins & 0x3f) == 0) {
             if (*abort_flag != 0) {
                 return false;
             }
@@ -256,6 +294,27 @@ __device__ __forceinline__ void split_tf32_fast(float x, float& hi, float& lo) {
     const uint32_t r = __float_as_uint(x - fh);  // exact
     hi = fh;
     lo = __uint_as_float((r + 0x1000u) & 0xFFFFE000u);
+}
+
+// The same split without a branch, for the converter warps of the streamed-operand kernel: two
+// warps per scheduler cannot hide a taken-or-not decision per element, and sixteen independent
+// elements interleave only if they are one basic block.  hi on the integer pipe (add half a TF32
+// ulp, clear 13 bits; where that reaches the infinity exponent -- x is infinite, NaN, or finite
+// but rounds past the largest TF32 -- truncate instead, keeping a NaN a NaN), lo = tf32(x - hi)
+// on the conversion pipe, forced to zero for a non-finite x.  Same values as split_tf32.
+__device__ __forceinline__ void split_tf32_select(float x, uint32_t& hi, uint32_t& lo) {
+    const uint32_t b = __float_as_uint(x);
+    uint32_t h = (b + 0x1000u) & 0xFFFFE000u;
+    const bool nonfinite = (b & 0x7F800000u) == 0x7F800000u;
+    const bool over = nonfinite || (h & 0x7F800000u) == 0x7F800000u;  // (a NaN's carry can leave the exponent)
+    const bool is_nan = nonfinite && (b & 0x007FFFFFu) != 0u;
+    h = over ? (b & 0xFFFFE000u) : h;
+    h = is_nan ? (h | 0x00400000u) : h;
+    const float rest = x - __uint_as_float(h);  // exact for a finite x
+    uint32_t l;
+    asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(l) : "f"(rest));
+    hi = h;
+    lo = nonfinite ? 0u : l;
 }
 
 struct SplitArgs {
@@ -836,7 +895,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a_hi, const __grid_consta
 //     tensor core's A operand, and A may come from TENSOR MEMORY instead of shared memory;
 //   * warp 0 brings [32 k][128 n] fp32 tiles of S (tensor map over the caller's own matrix,
 //     zero fill past the edges) and the matching K-block of W's planes into a 4-deep ring;
-//   * eight converter warps read their lane's column of the S tile (lane = n, conflict-free),
+//   * sixteen converter warps read their lane's column of the S tile (lane = n, conflict-free),
 //     split every value into hi/lo in registers and put both into tensor memory with
 //     tcgen05.st -- 64 columns per stage: the streamed operand never touches shared memory
 //     again and no converted copy of it exists anywhere;
@@ -850,7 +909,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a_hi, const __grid_consta
 // the warp that arrives last at its quarter of a tile folds the partial planes in split order in
 // the same launch (deterministic, no atomics on data).
 constexpr int kStreamStages = 4;
-constexpr int kStreamThreads = 448;       // 14 warps: TMA, MMA, 4 epilogue, 8 converters
+constexpr int kStreamConverters = 16;     // converter warps: four per tensor-memory lane quarter, 8 K columns each
+constexpr int kStreamThreads = (6 + kStreamConverters) * 32;  // + TMA, MMA and four epilogue warps
 constexpr int kStreamTileBytes = BK * 128 * 4;  // one fp32 tile of S: 32 K-rows x 128 lanes
 constexpr uint32_t kStreamTmemCols = 512;
 constexpr int kStreamCounters = 1024;     // arrival counters of the in-kernel split-K fold: 4 per tile
@@ -873,6 +933,7 @@ struct StreamArgs {
     unsigned int* counters;
 };
 
+
 __device__ __forceinline__ void umma_tf32_ts(uint32_t tmem_d, uint32_t tmem_a, uint64_t bdesc, uint32_t idesc,
                                              uint32_t accumulate) {
     asm volatile(
@@ -889,6 +950,13 @@ __device__ __forceinline__ void tmem_st16(uint32_t taddr, const uint32_t (&r)[16
         "{%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16};"
         ::"r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]),
           "r"(r[8]), "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15])
+        : "memory");
+}
+
+__device__ __forceinline__ void tmem_st8(uint32_t taddr, const uint32_t (&r)[8]) {
+    asm volatile(
+        "tcgen05.st.sync.aligned.32x32b.x8.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8};"
+        ::"r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7])
         : "memory");
 }
 
@@ -937,7 +1005,7 @@ gemm_stream_kernel(const __grid_constant__ CUtensorMap map_s, const __grid_const
         for (int s = 0; s < STAGES; ++s) {
             mbar_init(full_bar(s), 1);
             mbar_init(empty_bar(s), 1);
-            mbar_init(conv_bar(s), 8);  // one arrival per converter warp
+            mbar_init(conv_bar(s), kStreamConverters);  // one arrival per converter warp
         }
         for (int a = 0; a < 2; ++a) {
             mbar_init(acc_full(a), 1);
@@ -1094,11 +1162,24 @@ gemm_stream_kernel(const __grid_constant__ CUtensorMap map_s, const __grid_const
                 uint32_t r[32];
                 tmem_ld32(tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + acc * BNW + c * 32, r);
                 if (lane_ok) {
+                    // one row of C per store: 32 lanes, 128 contiguous bytes.  The row pointer is
+                    // stepped, not recomputed -- a 64-bit multiply per store would cost this
+                    // single warp more than the store does.
                     const int64_t left = g.m - (m0 + c * 32);
+                    float* p = dst + (m0 + c * 32) * g.n;
+                    if (left >= 32) {
 #pragma unroll
-                    for (int j = 0; j < 32; ++j) {
-                        if (j < left) {
-                            dst[(m0 + c * 32 + j) * g.n] = __uint_as_float(r[j]);
+                        for (int j = 0; j < 32; ++j) {
+                            *p = __uint_as_float(r[j]);
+                            p += g.n;
+                        }
+                    } else {
+#pragma unroll
+                        for (int j = 0; j < 32; ++j) {
+                            if (j < left) {
+                                *p = __uint_as_float(r[j]);
+                                p += g.n;
+                            }
                         }
                     }
                 }
@@ -1123,27 +1204,56 @@ gemm_stream_kernel(const __grid_constant__ CUtensorMap map_s, const __grid_const
                 if (old == static_cast<unsigned>(g.splits - 1)) {
                     __threadfence();
                     if (lane_ok) {
+                        // Eight rows and up to four K-slices at a time, all 32 loads issued before
+                        // the first add: the partial planes come from L2, and a chain that waits for
+                        // one load before issuing the next would pay that latency per element.  The
+                        // adds keep the split order.
                         const int64_t rows = min(int64_t(BNW), g.m - m0);
-                        for (int64_t j = 0; j < rows; ++j) {
-                            const int64_t o = col + (m0 + j) * g.n;
-                            float sum = __ldcg(g.out + o);
-                            for (int sp = 1; sp < g.splits; ++sp) {
-                                sum += __ldcg(g.out + int64_t(sp) * g.split_stride + o);
+                        const float* __restrict__ part = g.out + col + m0 * g.n;
+                        float* __restrict__ dstf = g.folded + col + m0 * g.n;
+                        for (int64_t j0 = 0; j0 < rows; j0 += 8) {
+                            float sum[8];
+                            for (int sp0 = 0; sp0 < g.splits; sp0 += 4) {
+                                float t[4][8];
+#pragma unroll
+                                for (int q = 0; q < 4; ++q) {
+#pragma unroll
+                                    for (int j = 0; j < 8; ++j) {
+                                        t[q][j] = (sp0 + q < g.splits && j0 + j < rows)
+                                                      ? __ldcg(part + int64_t(sp0 + q) * g.split_stride + (j0 + j) * g.n)
+                                                      : 0.0F;
+                                    }
+                                }
+#pragma unroll
+                                for (int q = 0; q < 4; ++q) {
+                                    if (sp0 + q < g.splits) {
+#pragma unroll
+                                        for (int j = 0; j < 8; ++j) {
+                                            sum[j] = (sp0 + q == 0) ? t[q][j] : sum[j] + t[q][j];
+                                        }
+                                    }
+                                }
                             }
-                            g.folded[o] = sum;
+#pragma unroll
+                            for (int j = 0; j < 8; ++j) {
+                                if (j0 + j < rows) dstf[(j0 + j) * g.n] = sum[j];
+                            }
                         }
                     }
                 }
             }
         }
     } else {
-        // ---------------- converters (warps 6..13): S tile -> hi / lo in tensor memory ----------------
+        // ---------------- converters (warps 6..21): S tile -> hi / lo in tensor memory ----------------
+        // Sixteen warps, four per tensor-memory lane quarter, each taking 8 of the stage's 32 K
+        // columns: the split is ~7 instructions per element on 4096 elements per K-block, and it is
+        // this loop, not HBM, that a thin set of warps would make the limit.
         const int quarter = warp & 3;
-        const int half = (warp - 6) >> 2;  // which 16 of the stage's 32 K columns
+        const int part = (warp - 6) >> 2;  // which 8 of the stage's 32 K columns
         const int l = quarter * 32 + lane;
         const int bl = l / g.nt;
         const int nn = l - bl * g.nt;
-        const uint32_t first_off = static_cast<uint32_t>(((bl * BK + half * 16) * g.nt + nn) * 4);
+        const uint32_t first_off = static_cast<uint32_t>(((bl * BK + part * 8) * g.nt + nn) * 4);
         const uint32_t k_step = static_cast<uint32_t>(g.nt * 4);
         const uint32_t lane_field = static_cast<uint32_t>(quarter * 32) << 16;
         uint32_t it = 0;
@@ -1159,28 +1269,38 @@ gemm_stream_kernel(const __grid_constant__ CUtensorMap map_s, const __grid_const
                 const uint32_t ph = (it / STAGES) & 1;
                 // the producer refilled this stage only after its previous MMAs had finished, so the
                 // stage's tensor-memory columns are free as well
-                if (!mbar_wait(full_bar(s), ph, abort_p, g.status)) {
+                if (!mbar_wait_parked(full_bar(s), ph, abort_p, g.status)) {
                     ok = false;
                     break;
                 }
-                const float* tile = reinterpret_cast<const float*>(base_ptr + s * S::kStageBytes + first_off);
-                float v[16];
+                const uint8_t* tile = base_ptr + s * S::kStageBytes + first_off;
+                float v[8];
+                uint32_t top = 0;
 #pragma unroll
-                for (int j = 0; j < 16; ++j) {
-                    v[j] = *reinterpret_cast<const float*>(reinterpret_cast<const uint8_t*>(tile) + j * k_step);
+                for (int j = 0; j < 8; ++j) {
+                    v[j] = *reinterpret_cast<const float*>(tile + j * k_step);
+                    top = max(top, __float_as_uint(v[j]) << 1);
                 }
-                uint32_t hi[16], lo[16];
+                uint32_t hi[8], lo[8];
+                if (top < 0xFEFFE000u) {
+                    // every value is finite and rounds inside the TF32 range: add half a TF32 ulp,
+                    // clear 13 bits (round to nearest, ties away), lo = tf32(x - hi)
 #pragma unroll
-                for (int j = 0; j < 16; ++j) {
-                    float h, lw;
-                    split_tf32_fast(v[j], h, lw);
-                    hi[j] = __float_as_uint(h);
-                    lo[j] = __float_as_uint(lw);
+                    for (int j = 0; j < 8; ++j) {
+                        hi[j] = (__float_as_uint(v[j]) + 0x1000u) & 0xFFFFE000u;
+                        const float rest = v[j] - __uint_as_float(hi[j]);
+                        asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(lo[j]) : "f"(rest));
+                    }
+                } else {
+#pragma unroll
+                    for (int j = 0; j < 8; ++j) {
+                        split_tf32_select(v[j], hi[j], lo[j]);  // infinities, NaNs, values that round past the range
+                    }
                 }
-                const uint32_t t_hi = tmem_base + lane_field + kStageCol0 + s * 64 + half * 16;
-                tmem_st16(t_hi, hi);
+                const uint32_t t_hi = tmem_base + lane_field + kStageCol0 + s * 64 + part * 8;
+                tmem_st8(t_hi, hi);
                 if (THREE_PASS) {
-                    tmem_st16(t_hi + 32, lo);
+                    tmem_st8(t_hi + 32, lo);
                 }
                 asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
                 tc_fence_before();
@@ -1619,6 +1739,8 @@ bool gemm_tc_eligible(const b200_ctx* ctx, const GemmProblem& p) {
     }
     return true;
 }
+
+bool gemm_tc_streams(const b200_ctx* ctx, const GemmProblem& p) { return plan_stream(ctx, p).ok; }
 
 void gemm_tc(b200_ctx* ctx, const GemmProblem& p, bool three_pass) {
     if (const StreamPlan sp = plan_stream(ctx, p); sp.ok) {
