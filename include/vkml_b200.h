@@ -199,7 +199,8 @@ int b200_get_stats(b200_ctx* ctx, b200_stats* out);
 typedef struct b200_profile_record {
     char label[48];
     float ms;
-    uint32_t op; /* b200_op of the node the launch belongs to */
+    uint32_t op;         /* b200_op of the node the launch belongs to */
+    uint32_t submission; /* the b200_compute call it was launched by, counted from 1 per context */
 } b200_profile_record;
 int b200_profile_enable(b200_ctx* ctx, int on);
 int b200_profile_read(b200_ctx* ctx, b200_profile_record* out, size_t capacity, size_t* count);

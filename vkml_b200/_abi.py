@@ -67,7 +67,7 @@ class Stats(C.Structure):
 
 class ProfileRecord(C.Structure):
     """b200_profile_record"""
-    _fields_ = [("label", C.c_char * 48), ("ms", C.c_float), ("op", C.c_uint32)]
+    _fields_ = [("label", C.c_char * 48), ("ms", C.c_float), ("op", C.c_uint32), ("submission", C.c_uint32)]
 
 
 # Every symbol include/vkml_b200.h declares: name -> (restype, argtypes).

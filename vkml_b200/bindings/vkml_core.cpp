@@ -38,6 +38,7 @@
 
 #include <array>
 #include <cstring>
+#include <deque>
 #include <map>
 #include <mutex>
 #include <optional>
@@ -199,13 +200,22 @@ vkml_b200::B200Backend& device_backend(int index) {
     return vkml_b200::b200_backend(index);
 }
 
-// Per-dispatch times of the most recent read, kept per device so that last_profile and
-// profile_records describe the same submission.
+// Device times per dispatch, grouped by submission (= one Backend::compute call), as vkML's
+// profiling hooks present them (bindings/module.cpp:222-230, python/vkml/attribution.py:263-365):
+// every submission is a run of dispatch records followed by one "submit" record for the whole
+// window.  The launches of a context run serially on one stream, so a dispatch starts where its
+// predecessor ended and the window is the sum.
+struct ProfileRecord {
+    std::string label;
+    double gpu_ms = 0.0, start_ms = 0.0;
+    uint64_t submission = 0;
+    uint64_t dispatch = 0;
+};
 struct ProfileStore {
-    std::vector<std::pair<std::string, double>> last;
-    std::vector<std::pair<std::string, double>> history;
+    std::vector<ProfileRecord> last;                   // the most recent submission
+    std::deque<std::vector<ProfileRecord>> history;    // the last `keep` submissions, oldest first
     size_t keep = 0;
-    uint64_t reads = 0;
+    uint64_t resolved = 0;                             // submissions seen, including those dropped
 };
 std::map<int, ProfileStore>& profile_stores() {
     static auto* stores = new std::map<int, ProfileStore>();
@@ -220,30 +230,34 @@ ProfileStore& read_profile(int index) {
     if (b200_profile_read(ctx, records.data(), records.size(), &n) != B200_OK) {
         throw vkml::DeviceError(std::string("profile read failed: ") + b200_last_error(ctx));
     }
-    if (n > 0) {
-        store.last.clear();
-        double total = 0.0;
-        for (size_t i = 0; i < n; ++i) {
-            store.last.emplace_back(records[i].label, records[i].ms);
-            total += records[i].ms;
+    size_t i = 0;
+    while (i < n) {
+        std::vector<ProfileRecord> group;
+        const uint32_t submission = records[i].submission;
+        double at = 0.0;
+        for (; i < n && records[i].submission == submission; ++i) {
+            const double ms = records[i].ms > 0.0F ? records[i].ms : 0.0;
+            group.push_back({records[i].label, ms, at, submission, static_cast<uint64_t>(group.size() + 1)});
+            at += ms;
         }
-        // the launches of one stream are serial, so their sum is the submission's device time
-        store.last.emplace_back("submit", total);
-        ++store.reads;
+        group.push_back({"submit", at, 0.0, submission, 0});
         if (store.keep > 0) {
-            store.history.insert(store.history.end(), store.last.begin(), store.last.end());
+            ++store.resolved;  // offered to the retention window, whether or not it is still held
+            store.history.push_back(group);
+            while (store.history.size() > store.keep) store.history.pop_front();
         }
+        store.last = std::move(group);
     }
     return store;
 }
 
-py::dict record_dict(const std::pair<std::string, double>& r, uint64_t submission, size_t dispatch) {
+py::dict record_dict(const ProfileRecord& r) {
     py::dict e;
-    e["label"] = r.first;
-    e["gpu_ms"] = r.second;
-    e["start_ms"] = 0.0;
-    e["submission"] = submission;
-    e["dispatch"] = dispatch;
+    e["label"] = r.label;
+    e["gpu_ms"] = r.gpu_ms;
+    e["start_ms"] = r.start_ms;
+    e["submission"] = r.submission;
+    e["dispatch"] = r.dispatch;
     return e;
 }
 
@@ -643,34 +657,42 @@ PYBIND11_MODULE(_vkml_core, m) {
         "vulkan_set_profiling",
         [](bool on, int index) { b200_profile_enable(device_backend(index).context(), on ? 1 : 0); }, "enabled"_a,
         "index"_a = 0);
-    m.def("vulkan_last_profile", [](int index) { return read_profile(index).last; }, "index"_a = 0);
+    m.def(
+        "vulkan_last_profile",
+        [](int index) {
+            std::vector<std::pair<std::string, double>> out;
+            for (const ProfileRecord& r : read_profile(index).last) out.emplace_back(r.label, r.gpu_ms);
+            return out;
+        },
+        "index"_a = 0);
     m.def(
         "vulkan_profile_records",
         [](int index) {
-            const ProfileStore& store = read_profile(index);
             py::list out;
-            for (size_t i = 0; i < store.last.size(); ++i) out.append(record_dict(store.last[i], store.reads, i + 1));
+            for (const ProfileRecord& r : read_profile(index).last) out.append(record_dict(r));
             return out;
         },
         "index"_a = 0);
     m.def(
         "vulkan_set_profile_history",
         [](size_t submissions, int index) {
-            ProfileStore& store = profile_stores()[index];
+            ProfileStore& store = read_profile(index);  // what ran so far belongs to the old window
             store.keep = submissions;
-            if (submissions == 0) store.history.clear();
+            store.history.clear();
+            store.resolved = 0;
         },
         "submissions"_a, "index"_a = 0);
     m.def(
         "vulkan_profile_history",
         [](int index) {
-            const ProfileStore& store = read_profile(index);
             py::list out;
-            for (size_t i = 0; i < store.history.size(); ++i) out.append(record_dict(store.history[i], store.reads, i + 1));
+            for (const auto& group : read_profile(index).history) {
+                for (const ProfileRecord& r : group) out.append(record_dict(r));
+            }
             return out;
         },
         "index"_a = 0);
-    m.def("vulkan_profile_submissions_resolved", [](int index) { return profile_stores()[index].reads; }, "index"_a = 0);
+    m.def("vulkan_profile_submissions_resolved", [](int index) { return read_profile(index).resolved; }, "index"_a = 0);
     m.def("vulkan_synchronize", [](int index) { device_backend(index).synchronize(); }, "index"_a = 0);
     // A warp is 32 lanes and cannot be resized; accepted so callers written for vkML's device run.
     m.def("vulkan_set_subgroup_override", [](uint32_t, int) {}, "size"_a, "index"_a = 0);

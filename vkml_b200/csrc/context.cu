@@ -23,6 +23,7 @@ ProfScope::ProfScope(b200_ctx* ctx, const char* label) : ctx_(ctx) {
     ProfEntry e{};
     std::snprintf(e.label, sizeof(e.label), "%s", label);
     e.op = ctx->current_op;
+    e.submission = static_cast<uint32_t>(ctx->compute_calls.load(std::memory_order_relaxed));
     // events are recycled: creating a pair per launch would cost more than a small kernel
     for (cudaEvent_t* ev : {&e.begin, &e.end}) {
         if (!ctx->event_pool.empty()) {
@@ -1011,6 +1012,7 @@ int b200_profile_read(b200_ctx* ctx, b200_profile_record* out, size_t capacity, 
                 std::memcpy(out[n].label, e.label, sizeof(out[n].label));
                 out[n].ms = ms;
                 out[n].op = e.op;
+                out[n].submission = e.submission;
                 ++n;
             }
             ctx->event_pool.push_back(e.begin);

@@ -50,6 +50,7 @@ struct DistState;  // dist.cu
 struct ProfEntry {
     char label[48];
     uint32_t op;
+    uint32_t submission;  // which b200_compute call the launch belongs to (counted from 1)
     cudaEvent_t begin, end;
 };
 
