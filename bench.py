@@ -62,9 +62,10 @@ def parse():
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--size", type=int, default=8192, help="M = N = K")
     ap.add_argument("--precision", default="3xtf32", choices=["3xtf32", "tf32", "fp32"])
-    ap.add_argument("--workload", default="gemm", choices=["gemm", "ops", "gemm-sweep"],
+    ap.add_argument("--workload", default="gemm", choices=["gemm", "ops", "gemm-sweep", "adapter-step"],
                     help="gemm: the contract line; ops: per-kernel HBM table of the memory-bound family; "
-                         "gemm-sweep: every GEMM shape of the benchmark's sweep")
+                         "gemm-sweep: every GEMM shape of the benchmark's sweep; adapter-step: full-size training "
+                         "steps driven by the reference framework's own executor through the vkml::Backend adapter")
     ap.add_argument("--no-graphs", action="store_true", help="train object: replay every step eagerly")
     ap.add_argument("--filter", default="", help="ops workload: substring of the case names to run")
     ap.add_argument("--train", default="mlp_wide_b2048",
@@ -720,14 +721,18 @@ def run_gemm_sweep(args, local_rank):
             if prec == "fp32" and flops > 3e11:
                 continue
             backend.set_gemm_precision(code)
-            reps = 20 if flops < 1e11 else 5
+            # small products: ten nodes per submitted span, so that the stream never waits for the
+            # host between them (one Python call per node would be the thing measured)
+            per_span = 10 if flops < 1e10 else 1
+            span = graph.pack_nodes([NodeDesc(int(Op.MATMUL), c.desc, [a.desc, b.desc])] * per_span)
+            reps = (20 if flops < 1e11 else 5) // (2 if per_span > 1 else 1)
             for _ in range(3):
-                backend.compute_packed(packed, 1)
+                backend.compute_packed(span, per_span)
             backend.synchronize()
             backend.timer_begin()
             for _ in range(reps):
-                backend.compute_packed(packed, 1)
-            ms = backend.timer_end() / reps
+                backend.compute_packed(span, per_span)
+            ms = backend.timer_end() / (reps * per_span)
             backend.set_profiling(True)
             backend.compute_packed(packed, 1)
             rec = backend.last_profile()
@@ -739,6 +744,79 @@ def run_gemm_sweep(args, local_rank):
         backend.trim()
 
 
+def run_adapter_steps(args):
+    """The drop-in route itself, timed: vkML's own graph, autograd, executor and optimiser code
+    (compiled from the reference's sources, with the B200 adapter registered as its device) run
+    full-size training steps -- the framework calls Backend::compute / copy_* / allocate exactly
+    as it would on its own GPU backend.  Wall clock per step, uploads and loss read-back included;
+    the `train` object of the contract line replays the same traffic without the framework above."""
+    path = os.path.join(ROOT, "oracle", "_ref", "libvkml_ref_b200.so")
+    if not os.path.exists(path):
+        print(json.dumps({"workload": "adapter-step", "unavailable": "oracle/_ref/libvkml_ref_b200.so is not built"}))
+        return
+    lib = C.CDLL(path, mode=C.RTLD_GLOBAL)
+    f32p, i64p = C.POINTER(C.c_float), C.POINTER(C.c_int64)
+    lib.vkml_ref_train_mlp.restype = C.c_int
+    lib.vkml_ref_train_mlp.argtypes = [C.c_int, i64p, C.c_int, f32p, f32p, f32p, i64p, C.c_int64, C.c_int,
+                                       C.c_double, C.c_double, f32p]
+    lib.vkml_ref_train_cnn.restype = C.c_int
+    lib.vkml_ref_train_cnn.argtypes = [C.c_int] + [C.c_int64] * 6 + [f32p, f32p, i64p, C.c_int64, C.c_int,
+                                                                    C.c_double, C.c_double, f32p]
+    lib.vkml_ref_step_seconds.restype = C.c_int
+    lib.vkml_ref_step_seconds.argtypes = [C.POINTER(C.c_double), C.c_int]
+    lib.vkml_ref_last_error.restype = C.c_char_p
+    steps = max(6, args.train_steps)
+    rng = np.random.default_rng(SEED_DATA + 1)
+
+    def ptr(a, t):
+        return a.ctypes.data_as(C.POINTER(t))
+
+    def report(name, rc, batch):
+        if rc != 0:
+            print(json.dumps({"workload": "adapter-step", "model": name, "error": lib.vkml_ref_last_error().decode()}))
+            return
+        buf = (C.c_double * steps)()
+        n = lib.vkml_ref_step_seconds(buf, steps)
+        ms = [buf[i] * 1e3 for i in range(n)]
+        steady = sorted(ms[3:])
+        med = steady[len(steady) // 2]
+        print(json.dumps({"workload": "adapter-step", "model": name, "per_gpu_batch": batch, "steps": n,
+                          "ms_per_step": med, "samples_per_s": batch / (med * 1e-3), "first_steps_ms": ms[:3],
+                          "path": "reference executor -> vkml::Backend adapter -> C ABI -> CUDA; wall clock per step "
+                                  "with the batch uploaded and the loss read back"}), flush=True)
+
+    widths = np.array([4096, 8192, 8192, 8192, 1000], dtype=np.int64)
+    batch = 2048
+    w = np.concatenate([rng.uniform(-1, 1, a * b).astype(np.float32) / np.float32(np.sqrt(a))
+                        for a, b in zip(widths[:-1], widths[1:])])
+    b = np.zeros(int(widths[1:].sum()), dtype=np.float32)
+    x = rng.standard_normal((batch * steps, int(widths[0])), dtype=np.float32)
+    y = rng.integers(0, int(widths[-1]), batch * steps).astype(np.int64)
+    losses = np.zeros(steps, dtype=np.float32)
+    rc = lib.vkml_ref_train_mlp(1, ptr(widths, C.c_int64), len(widths) - 1, ptr(w, C.c_float), ptr(b, C.c_float),
+                                ptr(x, C.c_float), ptr(y, C.c_int64), batch, steps, 0.1, 0.9, ptr(losses, C.c_float))
+    report("MLP 4096-8192-8192-8192-1000", rc, batch)
+    del w, x
+    batch, c1, c2, c3, classes = 256, 64, 128, 256, 100
+    n_p = c1 * 27 + c1 + c2 * c1 * 9 + c2 + c3 * c2 * 9 + c3 + classes * c3 * 16 + classes
+    params = (rng.uniform(-1, 1, n_p) * 0.05).astype(np.float32)
+    x = rng.random((batch * steps, 3, 32, 32), dtype=np.float32)
+    y = rng.integers(0, classes, batch * steps).astype(np.int64)
+    rc = lib.vkml_ref_train_cnn(1, 3, 32, c1, c2, c3, classes, ptr(params, C.c_float), ptr(x, C.c_float),
+                                ptr(y, C.c_int64), batch, steps, 0.05, 0.9, ptr(losses, C.c_float))
+    report("CNN conv3x3 64-128-256 + Linear 4096->100", rc, batch)
+    widths = np.array([784, 128, 10], dtype=np.int64)
+    batch = 64
+    steps_small = steps
+    w = (rng.uniform(-1, 1, 784 * 128 + 128 * 10) * 0.03).astype(np.float32)
+    b = np.zeros(138, dtype=np.float32)
+    x = rng.random((batch * steps_small, 784), dtype=np.float32)
+    y = rng.integers(0, 10, batch * steps_small).astype(np.int64)
+    rc = lib.vkml_ref_train_mlp(1, ptr(widths, C.c_int64), 2, ptr(w, C.c_float), ptr(b, C.c_float), ptr(x, C.c_float),
+                                ptr(y, C.c_int64), batch, steps_small, 0.1, 0.9, ptr(losses, C.c_float))
+    report("MLP 784-128-10", rc, batch)
+
+
 def main():
     args = parse()
     rank = int(os.environ.get("RANK", "0"))
@@ -748,6 +826,8 @@ def main():
         run_ops(args, local_rank)
     elif args.workload == "gemm-sweep":
         run_gemm_sweep(args, local_rank)
+    elif args.workload == "adapter-step":
+        run_adapter_steps(args)
     elif args.impl == "reference":
         run_reference(args, rank, world)
     else:

@@ -230,11 +230,25 @@ int b200_matmul_kernel(b200_ctx* ctx, const b200_node* node, char* name, size_t 
  * a caller that owns other device work can order against it with events. */
 void* b200_stream(b200_ctx* ctx);
 
+/* Diagnostic (no counterpart in vkML): queues one block that waits `limit_ns` (at most one second)
+ * on a barrier nobody arrives on, through the bounded wait the GEMM kernels use.  The wait gives
+ * up, the kernel returns by itself, and the next b200_synchronize / b200_copy_to_host reports
+ * B200_TIMEOUT; the context stays usable.  Nothing faults and nothing hangs: it lets a caller's
+ * handling of an expired device wait be tested. */
+int b200_debug_expire_wait(b200_ctx* ctx, uint64_t limit_ns);
+
 /* -- data-parallel training (no counterpart in vkML, which is single-device:
  *    src/dispatch/executor.cpp:96-103). One process per GPU. -- */
 #define B200_UNIQUE_ID_BYTES 128
 int b200_dist_unique_id(void* out_id /* B200_UNIQUE_ID_BYTES */);
 int b200_dist_init(b200_ctx* ctx, int rank, int world_size, const void* id);
+/* The same with an explicit deadline: the communicator is created in NCCL's non-blocking mode and
+ * polled; if the ranks have not all joined after `timeout_ms` it is aborted and the call returns
+ * B200_TIMEOUT (0 = wait for ever, as ncclCommInitRank does).  b200_dist_init uses
+ * VKML_B200_DIST_INIT_TIMEOUT_MS, default two minutes.  Once initialised, b200_synchronize also
+ * polls NCCL's asynchronous error state and, with VKML_B200_COMM_TIMEOUT_MS set, gives outstanding
+ * collectives that long before it aborts the communicator and reports B200_TIMEOUT. */
+int b200_dist_init_deadline(b200_ctx* ctx, int rank, int world_size, const void* id, int timeout_ms);
 int b200_dist_destroy(b200_ctx* ctx);
 /* Average `count` f32 values in place across ranks on the communication
  * stream; ordered after everything submitted so far and before everything

@@ -39,6 +39,7 @@
 #include "b200_backend.h"
 #endif
 
+#include <chrono>
 #include <cstdio>
 #include <cstring>
 #include <mutex>
@@ -252,8 +253,19 @@ void before_backward(int device) {
 #endif
 }
 
+// Wall-clock time of every step of the last training run (forward, backward(), optimiser,
+// loss.item()): how long the framework's own executor takes per step on the chosen device.
+thread_local std::vector<double> g_step_seconds;
+thread_local std::chrono::steady_clock::time_point g_step_begin;
+
 void mark_step(int device, int index) {
     if (device == 2) recorder().mark("step", index);
+    if (index == 0) g_step_seconds.clear();
+    g_step_begin = std::chrono::steady_clock::now();
+}
+
+void end_step() {
+    g_step_seconds.push_back(std::chrono::duration<double>(std::chrono::steady_clock::now() - g_step_begin).count());
 }
 
 vkml::Device pick_device(int which) {
@@ -339,6 +351,14 @@ int vkml_ref_has_b200(void) {
 #else
     return 0;
 #endif
+}
+
+// Per-step wall-clock seconds of the last vkml_ref_train_* call on this thread; returns how many
+// steps were timed (at most `capacity` are copied).
+int vkml_ref_step_seconds(double* out, int capacity) {
+    const int n = static_cast<int>(g_step_seconds.size());
+    for (int i = 0; i < n && i < capacity; ++i) out[i] = g_step_seconds[static_cast<size_t>(i)];
+    return n;
 }
 
 // Install (or clear, with NULL) the host-side gradient exchange used by the trainers below.
@@ -455,6 +475,7 @@ int vkml_ref_train_mlp(int device, const int64_t* widths, int n_layers, float* w
             exchange_grads(params);
             opt.step(params);
             losses[s] = loss.item();
+            end_step();
         }
         wo = bo = 0;
         for (int l = 0; l < n_layers; ++l) {
@@ -511,6 +532,7 @@ int vkml_ref_train_cnn(int device, int64_t cin, int64_t hw, int64_t c1, int64_t 
             exchange_grads(params);
             opt.step(params);
             losses[s] = loss.item();
+            end_step();
         }
         off = 0;
         for (size_t i = 0; i < params.size(); ++i) {

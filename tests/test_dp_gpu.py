@@ -43,3 +43,30 @@ def test_two_gpus_follow_the_cpu_global_batch(tmp_path):
     # the ranks really exchanged: without it their curves would not add up to the global one,
     # and a single rank's curve differs from the global curve
     assert np.max(np.abs(r0["losses"] - cpu_l) / cpu_l) > 1e-4
+
+
+def test_a_rank_that_never_joins_ends_init_with_a_timeout():
+    """Failure made on the host: rank 0 of a two-rank job starts, rank 1 never does.  The
+    communicator is created in NCCL's non-blocking mode and polled against a deadline; when it runs
+    out the communicator is aborted and the call returns B200_TIMEOUT (vkML's DeviceError).  No
+    kernel or collective is in flight at any point, and the context keeps working afterwards."""
+    import time
+
+    import vkml_b200
+    from vkml_b200 import DeviceTensor
+    from vkml_b200.backend import DeviceError
+    b = vkml_b200.Backend(0)
+    uid = b.dist_unique_id()
+    t0 = time.perf_counter()
+    with pytest.raises(DeviceError, match="did not all join"):
+        b.dist_init(0, 2, uid, timeout_ms=1500)
+    waited = time.perf_counter() - t0
+    assert 1.0 < waited < 20.0, waited
+    x = DeviceTensor.from_host(b, np.arange(100, dtype=np.float32))
+    np.testing.assert_array_equal(x.numpy(), np.arange(100, dtype=np.float32))
+    # a one-rank job on the same context still initialises and reduces
+    b.dist_init(0, 1, b.dist_unique_id(), timeout_ms=20000)
+    b.dist_all_reduce_mean(x.storage.data, 100)
+    b.dist_wait()
+    np.testing.assert_array_equal(x.numpy(), np.arange(100, dtype=np.float32))
+    b.close()

@@ -363,6 +363,22 @@ def test_errors_leave_the_backend_usable(backend):
     backend.synchronize()
 
 
+def test_an_expired_device_wait_becomes_a_timeout_and_the_context_survives(backend):
+    """Every device-side wait is bounded.  A block that waits one millisecond on a barrier nobody
+    arrives on gives up by itself; the host reports B200_TIMEOUT (vkML's DeviceError) at the next
+    synchronisation, and the context keeps working afterwards."""
+    from vkml_b200 import DeviceTensor
+    from vkml_b200.backend import DeviceError
+    backend.synchronize()
+    rc = backend._lib.b200_debug_expire_wait(backend._ctx, 1_000_000)
+    assert rc == 0
+    with pytest.raises(DeviceError, match="timeout"):
+        backend.synchronize()
+    backend.synchronize()  # reported once, then cleared
+    w = DeviceTensor.from_host(backend, np.arange(1000, dtype=np.float32))
+    np.testing.assert_array_equal(w.numpy(), np.arange(1000, dtype=np.float32))
+
+
 def test_device_copies(backend):
     from vkml_b200 import DeviceTensor
     rng = np.random.default_rng(4)

@@ -205,3 +205,67 @@ def test_graph_replay_is_bit_identical_to_eager_replay(backend, name):
     assert np.array_equal(eager.view(np.uint32), graph.view(np.uint32)), (eager, graph)
     backend.free_host(pin_x)
     backend.free_host(pin_y)
+
+
+@pytest.mark.parametrize("name", ["mlp_784_128_10_b64", "cnn_reduced_b16"])
+def test_fused_groups_compute_what_the_separate_kernels_do(monkeypatch, name):
+    """In-span fusion (bias add + ReLU mask + ReLU, the one-hot mask of cross_entropy, the backward
+    of log_softmax) against the same recorded steps with VKML_B200_FUSE=0: fewer launches, and the
+    same loss curve -- bit for bit wherever no sum is involved; the fused log_softmax backward adds
+    its row in a different (fixed) order, so the curves are held to 1e-6 relative."""
+    import vkml_b200
+    from vkml_b200.replay import load_program
+    from vkml_b200.tape import Tape
+    program = load_program(os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden", "programs",
+                                        name + ".json.gz"))
+    meta = program["meta"]
+    batch, steps = meta["batch"], 12
+    rng = np.random.default_rng(5)
+    if meta["model"] == "mlp":
+        widths = meta["widths"]
+        params = []
+        for fin, fout in zip(widths[:-1], widths[1:]):
+            bound = 1.0 / np.sqrt(fin)
+            params += [rng.uniform(-bound, bound, (fout, fin)).astype(np.float32),
+                       rng.uniform(-bound, bound, (fout,)).astype(np.float32)]
+        x = rng.random((steps, batch, widths[0])).astype(np.float32)
+        classes = widths[-1]
+    else:
+        cin, hw, classes = meta["cin"], meta["hw"], meta["classes"]
+        feat = meta["c3"] * (hw // 8) ** 2
+        params = []
+        for cout, ci in ((meta["c1"], cin), (meta["c2"], meta["c1"]), (meta["c3"], meta["c2"])):
+            bound = 1.0 / np.sqrt(ci * 9)
+            params += [rng.uniform(-bound, bound, (cout, ci, 3, 3)).astype(np.float32),
+                       rng.uniform(-bound, bound, (cout,)).astype(np.float32)]
+        bound = 1.0 / np.sqrt(feat)
+        params += [rng.uniform(-bound, bound, (classes, feat)).astype(np.float32),
+                   rng.uniform(-bound, bound, (classes,)).astype(np.float32)]
+        x = rng.random((steps, batch, cin, hw, hw)).astype(np.float32)
+    y = rng.integers(0, classes, (steps, batch)).astype(np.int64)
+
+    def run(fuse):
+        monkeypatch.setenv("VKML_B200_FUSE", "1" if fuse else "0")
+        b = vkml_b200.Backend(0)
+        tape = Tape(b, program)
+        tape.run_prologue(params)
+        b.set_profiling(True)
+        losses = []
+        for s in range(steps):
+            tape.step([np.ascontiguousarray(x[s]), np.ascontiguousarray(y[s])])
+            losses.append(tape.downloads[0].view(np.float32)[0].copy())
+        labels = [l for l, _ in b.last_profile()]
+        b.set_profiling(False)
+        tape.close()
+        return np.array(losses, dtype=np.float32), labels
+
+    plain, plain_labels = run(False)
+    fused, fused_labels = run(True)
+    assert not any(l.startswith("fused.") for l in plain_labels)
+    for kind in ("fused.one_hot_mul", "fused.log_softmax_backward"):
+        assert kind in fused_labels, sorted(set(fused_labels))
+    # the bias / mask / relu group appears in whichever form the span holds it
+    assert any(l in ("fused.bias_mask_relu", "fused.bias_mask", "fused.bias_relu", "fused.mask") for l in fused_labels)
+    assert len(fused_labels) <= len(plain_labels) - 7 * steps, (len(fused_labels), len(plain_labels))
+    assert np.all(np.isfinite(plain))
+    np.testing.assert_allclose(fused, plain, rtol=1e-6, atol=0)

@@ -100,8 +100,10 @@ SYMBOLS = {
     "b200_get_gemm_precision": (C.c_int, [_P]),
     "b200_matmul_kernel": (C.c_int, [_P, C.POINTER(Node), C.c_char_p, C.c_size_t, C.c_char_p, C.c_size_t]),
     "b200_stream": (_P, [_P]),
+    "b200_debug_expire_wait": (C.c_int, [_P, C.c_uint64]),
     "b200_dist_unique_id": (C.c_int, [_P]),
     "b200_dist_init": (C.c_int, [_P, C.c_int, C.c_int, _P]),
+    "b200_dist_init_deadline": (C.c_int, [_P, C.c_int, C.c_int, _P, C.c_int]),
     "b200_dist_destroy": (C.c_int, [_P]),
     "b200_dist_all_reduce_mean": (C.c_int, [_P, _P, C.c_size_t]),
     "b200_dist_wait": (C.c_int, [_P]),

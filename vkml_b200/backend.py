@@ -221,9 +221,14 @@ class Backend:
         self._check(self._lib.b200_dist_unique_id(buf), "dist_unique_id")
         return buf.raw
 
-    def dist_init(self, rank: int, world: int, unique_id: bytes) -> None:
+    def dist_init(self, rank: int, world: int, unique_id: bytes, timeout_ms: int | None = None) -> None:
+        """Join a data-parallel job.  With `timeout_ms`, ranks that do not all arrive in time end
+        the call with DeviceError (timeout) and an aborted communicator instead of blocking."""
         buf = C.create_string_buffer(unique_id, _abi.UNIQUE_ID_BYTES)
-        self._check(self._lib.b200_dist_init(self._ctx, rank, world, buf), "dist_init")
+        if timeout_ms is None:
+            self._check(self._lib.b200_dist_init(self._ctx, rank, world, buf), "dist_init")
+        else:
+            self._check(self._lib.b200_dist_init_deadline(self._ctx, rank, world, buf, timeout_ms), "dist_init")
 
     def dist_all_reduce_mean(self, data: int, count: int) -> None:
         self._check(self._lib.b200_dist_all_reduce_mean(self._ctx, data, count), "all_reduce")

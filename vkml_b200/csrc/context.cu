@@ -586,8 +586,14 @@ int b200_create(int cuda_ordinal, b200_ctx** out) {
         if (const char* e = std::getenv("VKML_B200_SHARE_PLANES")) {
             ctx->share_planes = std::atoi(e) != 0;
         }
+        if (const char* e = std::getenv("VKML_B200_FUSE")) {
+            ctx->fuse = std::atoi(e) != 0;
+        }
         if (const char* e = std::getenv("VKML_B200_PDL")) {
             ctx->pdl = std::atoi(e) != 0;
+        }
+        if (const char* e = std::getenv("VKML_B200_BUCKET")) {
+            ctx->bucket_grads = std::atoi(e) != 0;
         }
         if (const char* e = std::getenv("VKML_B200_LAZY_JOIN")) {
             ctx->lazy_join = std::atoi(e) != 0;
@@ -813,20 +819,9 @@ int b200_compute(b200_ctx* ctx, const b200_node* nodes, size_t n_nodes, uint32_t
             }
             std::stable_sort(order.begin(), order.end(), [&](size_t a, size_t b) { return key[a] < key[b]; });
         }
-        for (const size_t i : order) {
+        // What a node needs before its kernel may be queued, and what follows it.
+        auto prepare = [&](size_t i) {
             const b200_node& node = nodes[i];
-            if (is_view_or_leaf(node.op)) {
-                continue;  // resolved by the executor through aliasing (backend.h:34-45)
-            }
-            if (node.op >= B200_OP_COUNT) {
-                fail(B200_NOT_IMPLEMENTED, "unknown op " + std::to_string(node.op));
-            }
-            // zero-element tensors are legal and need no work (vulkan_backend.cpp:1233-1236)
-            int64_t numel = 1;
-            for (int d = 0; d < node.out.ndim; ++d) numel *= node.out.dims[d];
-            if (numel == 0) {
-                continue;
-            }
             if (node.out.data == nullptr) {
                 fail(B200_INVALID_ARGUMENT, "node has no storage");
             }
@@ -847,20 +842,99 @@ int b200_compute(b200_ctx* ctx, const b200_node* nodes, size_t n_nodes, uint32_t
             if (!ctx->plane_cache.empty()) {
                 // cannot happen under the caller's contract (outputs are fresh buffers), but a
                 // plane must never outlive the data it was split from
-                gemm_tc_invalidate(ctx, node.out.data,
-                                   static_cast<const char*>(node.out.data) + numel * dtype_size(node.out.dtype));
+                gemm_tc_invalidate(ctx, node.out.data, static_cast<const char*>(node.out.data) + tensor_bytes(node.out));
             }
-            dispatch_node(ctx, node);
+        };
+        auto finish = [&](size_t i) {
+            const b200_node& node = nodes[i];
             ctx->nodes_computed.fetch_add(1, std::memory_order_relaxed);
             if (grad_sync) {
                 if (!is_sink.empty()) {
                     if (is_sink[i]) {
+                        int64_t numel = 1;
+                        for (int d = 0; d < node.out.ndim; ++d) numel *= node.out.dims[d];
                         dist_all_reduce_now(ctx, node.out.data, static_cast<size_t>(numel));
                     }
                 } else {
                     dist_after_node(ctx, node);
                 }
             }
+        };
+        // the nodes that need a kernel, in execution order
+        std::vector<size_t> exec;
+        exec.reserve(order.size());
+        for (const size_t i : order) {
+            const b200_node& node = nodes[i];
+            if (is_view_or_leaf(node.op)) {
+                continue;  // resolved by the executor through aliasing (backend.h:34-45)
+            }
+            if (node.op >= B200_OP_COUNT) {
+                fail(B200_NOT_IMPLEMENTED, "unknown op " + std::to_string(node.op));
+            }
+            // zero-element tensors are legal and need no work (vulkan_backend.cpp:1233-1236)
+            int64_t numel = 1;
+            for (int d = 0; d < node.out.ndim; ++d) numel *= node.out.dims[d];
+            if (numel != 0) exec.push_back(i);
+        }
+        // Buffers a `full` node of this span filled with one value: a later elementwise node that
+        // reads such a buffer whole is handed a stride-0 view of its first element instead, and
+        // reads 4 bytes where it would have read the tensor (ReLU's backward mask compares against,
+        // and its `where` selects from, activation-sized tensors of zeros).
+        std::map<const void*, size_t> constants;
+        for (size_t p = 0; p < exec.size();) {
+            const size_t i = exec[p];
+            const b200_node& node = nodes[i];
+            if (ctx->fuse && exec.size() - p >= 2 &&
+                (node.op == B200_OP_ADD || node.op == B200_OP_FULL || node.op == B200_OP_EQUAL ||
+                 node.op == B200_OP_EXP)) {
+                const size_t avail = std::min<size_t>(exec.size() - p, 5);
+                const b200_node* seq[5];
+                bool eligible = true;
+                for (size_t k = 0; k < avail; ++k) {
+                    seq[k] = &nodes[exec[p + k]];
+                    // a gradient that this span all-reduces is exchanged as soon as its own kernel is queued
+                    eligible = eligible && (is_sink.empty() || !is_sink[exec[p + k]]) && seq[k]->out.data != nullptr;
+                    eligible = eligible && (!grad_sync || !is_sink.empty() || ctx->grads.empty());
+                }
+                if (eligible) {
+                    for (size_t k = 0; k < avail; ++k) prepare(exec[p + k]);
+                    ctx->current_op = node.op;
+                    const size_t taken = launch_fused(ctx, seq, avail);
+                    if (taken > 0) {
+                        for (size_t k = 0; k < taken; ++k) {
+                            if (seq[k]->op == B200_OP_FULL && seq[k]->out.dtype == B200_F32) {
+                                constants[seq[k]->out.data] = tensor_bytes(seq[k]->out);
+                            }
+                            finish(exec[p + k]);
+                        }
+                        p += taken;
+                        continue;
+                    }
+                }
+            }
+            prepare(i);
+            const bool elementwise = node.op == B200_OP_WHERE || (node.op >= B200_OP_ADD && node.op <= B200_OP_NOT_EQUAL);
+            if (ctx->fuse && elementwise && !constants.empty()) {
+                b200_node lean = node;
+                bool changed = false;
+                for (uint32_t s = 0; s < node.n_src && s < B200_MAX_SRC; ++s) {
+                    const auto it = constants.find(node.src[s].data);
+                    if (it != constants.end() && node.src[s].dtype == B200_F32 && it->second == tensor_bytes(node.src[s])) {
+                        for (int d = 0; d < lean.src[s].ndim; ++d) lean.src[s].strides[d] = 0;
+                        changed = true;
+                    }
+                }
+                dispatch_node(ctx, changed ? lean : node);
+            } else {
+                dispatch_node(ctx, node);
+            }
+            if (node.op == B200_OP_FULL && node.out.dtype == B200_F32) {
+                constants[node.out.data] = tensor_bytes(node.out);
+            } else {
+                constants.erase(node.out.data);  // (outputs are fresh buffers; kept exact regardless)
+            }
+            finish(i);
+            ++p;
         }
         if (grad_sync) {
             dist_join(ctx);
@@ -953,6 +1027,7 @@ int b200_synchronize(b200_ctx* ctx) {
     if (ctx == nullptr) return B200_INVALID_ARGUMENT;
     int device_rc = B200_OK;
     const int rc = guarded(ctx, [&] {
+        dist_check_health(ctx);
         dist_wait_range(ctx, nullptr, nullptr);  // "everything submitted" includes the all-reduces
         B200_CUDA_CHECK(cudaMemcpyAsync(ctx->h_status, ctx->d_status, sizeof(uint32_t),
                                         cudaMemcpyDeviceToHost, ctx->stream));
@@ -1094,5 +1169,10 @@ int b200_matmul_kernel(b200_ctx* ctx, const b200_node* node, char* name, size_t 
 }
 
 void* b200_stream(b200_ctx* ctx) { return ctx == nullptr ? nullptr : ctx->stream; }
+
+int b200_debug_expire_wait(b200_ctx* ctx, uint64_t limit_ns) {
+    if (ctx == nullptr || limit_ns == 0 || limit_ns > 1000000000ULL) return B200_INVALID_ARGUMENT;
+    return guarded(ctx, [&] { gemm_tc_wait_probe(ctx, limit_ns); });
+}
 
 }  // extern "C"

@@ -135,6 +135,8 @@ struct b200_ctx {
     // nodes of a later span are taken in the order their gradients arrive, so the optimiser's
     // updates of the early-reduced parameters run under the tail of the communication.
     bool lazy_join = true;
+    bool bucket_grads = true;  // small gradients of a span leave as one grouped NCCL launch (VKML_B200_BUCKET)
+    bool fuse = true;  // in-span fusion of the node sequences autograd always emits (VKML_B200_FUSE, fuse.cu)
     bool pdl = true;  // programmatic dependent launch between consecutive kernels (VKML_B200_PDL)
     bool in_grad_sync_span = false;
     bool comm_pending = false;  // an all-reduce was issued in this span and has not been joined yet
@@ -199,6 +201,10 @@ void launch_matmul(b200_ctx* ctx, const b200_node& node);       // matmul (all k
 
 bool supports_node(const b200_node& node);
 
+// fuse.cu: serves the head of `seq` (the span's remaining computed nodes, in execution order)
+// with one fused launch if it matches a known pattern; returns how many nodes it covered, or 0.
+size_t launch_fused(b200_ctx* ctx, const b200_node* const* seq, size_t avail);
+
 // dist.cu
 void dist_destroy(b200_ctx* ctx);
 void dist_after_node(b200_ctx* ctx, const b200_node& node);  // all-reduce a registered gradient once its producer is queued
@@ -207,6 +213,7 @@ void dist_join(b200_ctx* ctx);                                // make the comput
 void dist_wait_range(b200_ctx* ctx, const void* lo, const void* hi);  // ... for those touching [lo, hi) (nullptr: all)
 int dist_pending_index(const b200_ctx* ctx, const void* lo, const void* hi);
 bool dist_has_pending(const b200_ctx* ctx);
+void dist_check_health(b200_ctx* ctx);  // asynchronous NCCL errors and the host deadline for collectives
 
 void check_last_launch(const char* what);
 

@@ -14,6 +14,10 @@
 #include "context.h"
 
 #include <dlfcn.h>
+#include <nccl.h>  // types and initialisers only (ncclConfig_t): the library itself is opened with dlopen
+
+#include <chrono>
+#include <thread>
 
 namespace b200 {
 
@@ -31,6 +35,9 @@ struct NcclApi {
     void* handle = nullptr;
     int (*GetUniqueId)(NcclUniqueId*) = nullptr;
     int (*CommInitRank)(NcclComm*, int, NcclUniqueId, int) = nullptr;
+    int (*CommInitRankConfig)(NcclComm*, int, NcclUniqueId, int, ncclConfig_t*) = nullptr;
+    int (*CommGetAsyncError)(NcclComm, int*) = nullptr;
+    int (*CommAbort)(NcclComm) = nullptr;
     int (*CommDestroy)(NcclComm) = nullptr;
     int (*AllReduce)(const void*, void*, size_t, int, int, NcclComm, cudaStream_t) = nullptr;
     int (*GroupStart)() = nullptr;
@@ -48,6 +55,11 @@ NcclApi& nccl() {
         if (a.handle != nullptr) {
             a.GetUniqueId = reinterpret_cast<decltype(a.GetUniqueId)>(dlsym(a.handle, "ncclGetUniqueId"));
             a.CommInitRank = reinterpret_cast<decltype(a.CommInitRank)>(dlsym(a.handle, "ncclCommInitRank"));
+            a.CommInitRankConfig =
+                reinterpret_cast<decltype(a.CommInitRankConfig)>(dlsym(a.handle, "ncclCommInitRankConfig"));
+            a.CommGetAsyncError =
+                reinterpret_cast<decltype(a.CommGetAsyncError)>(dlsym(a.handle, "ncclCommGetAsyncError"));
+            a.CommAbort = reinterpret_cast<decltype(a.CommAbort)>(dlsym(a.handle, "ncclCommAbort"));
             a.CommDestroy = reinterpret_cast<decltype(a.CommDestroy)>(dlsym(a.handle, "ncclCommDestroy"));
             a.AllReduce = reinterpret_cast<decltype(a.AllReduce)>(dlsym(a.handle, "ncclAllReduce"));
             a.GroupStart = reinterpret_cast<decltype(a.GroupStart)>(dlsym(a.handle, "ncclGroupStart"));
@@ -93,30 +105,80 @@ struct DistState {
     std::vector<Lazy> lazy;
     std::vector<cudaEvent_t> event_pool;
     std::mutex lazy_mu;  // b200_free may arrive from any thread (a Storage deleter) and looks at `lazy`
+    // Small gradients of the running span, held back so that they leave as ONE grouped NCCL
+    // launch: eight biases and 3x3 kernels of a few KB each would otherwise be eight launches of
+    // a latency-bound collective on a step that takes a millisecond.
+    struct Deferred {
+        void* data;
+        size_t count;
+    };
+    std::vector<Deferred> bucket;
+    size_t bucket_bytes = 0;
+    bool aborted = false;
+    int comm_timeout_ms = 0;  // host deadline for outstanding collectives at a synchronisation (0: none)
 };
 
-static void all_reduce_mean(b200_ctx* ctx, void* data, size_t count) {
+constexpr size_t kBucketEachBytes = size_t(4) << 20;    // gradients below this are grouped
+constexpr size_t kBucketFlushBytes = size_t(32) << 20;  // ... and the group leaves when it holds this much
+
+// Issues the all-reduces of `items` on the communication stream, ordered after everything queued
+// on the compute stream so far; more than one item goes out as one NCCL group (one launch).
+static void issue_all_reduces(b200_ctx* ctx, const DistState::Deferred* items, size_t n) {
     DistState* d = ctx->dist;
+    if (n == 0) return;
+    if (d->aborted) fail(B200_DEVICE_ERROR, "the communicator was aborted after an error or a timeout");
     B200_CUDA_CHECK(cudaEventRecord(d->produced, ctx->stream));
     B200_CUDA_CHECK(cudaStreamWaitEvent(d->comm_stream, d->produced, 0));
-    nccl_check(nccl().AllReduce(data, data, count, kNcclFloat32, kNcclAvg, d->comm, d->comm_stream),
-               "ncclAllReduce");
+    const bool group = n > 1 && nccl().GroupStart != nullptr && nccl().GroupEnd != nullptr;
+    if (group) nccl_check(nccl().GroupStart(), "ncclGroupStart");
+    for (size_t i = 0; i < n; ++i) {
+        nccl_check(nccl().AllReduce(items[i].data, items[i].data, items[i].count, kNcclFloat32, kNcclAvg, d->comm,
+                                    d->comm_stream),
+                   "ncclAllReduce");
+        ctx->comm_bytes.fetch_add(items[i].count * sizeof(float), std::memory_order_relaxed);
+    }
+    if (group) nccl_check(nccl().GroupEnd(), "ncclGroupEnd");
     d->pending = true;
     ctx->comm_pending = true;
-    ctx->comm_bytes.fetch_add(count * sizeof(float), std::memory_order_relaxed);
     if (ctx->lazy_join) {
         std::lock_guard<std::mutex> lock(d->lazy_mu);
-        cudaEvent_t ev = nullptr;
-        if (!d->event_pool.empty()) {
-            ev = d->event_pool.back();
-            d->event_pool.pop_back();
-        } else {
-            B200_CUDA_CHECK(cudaEventCreateWithFlags(&ev, cudaEventDisableTiming));
+        for (size_t i = 0; i < n; ++i) {
+            cudaEvent_t ev = nullptr;
+            if (!d->event_pool.empty()) {
+                ev = d->event_pool.back();
+                d->event_pool.pop_back();
+            } else {
+                B200_CUDA_CHECK(cudaEventCreateWithFlags(&ev, cudaEventDisableTiming));
+            }
+            B200_CUDA_CHECK(cudaEventRecord(ev, d->comm_stream));
+            d->lazy.push_back(DistState::Lazy{static_cast<const char*>(items[i].data),
+                                              static_cast<const char*>(items[i].data) + items[i].count * sizeof(float), ev});
         }
-        B200_CUDA_CHECK(cudaEventRecord(ev, d->comm_stream));
-        d->lazy.push_back(DistState::Lazy{static_cast<const char*>(data),
-                                          static_cast<const char*>(data) + count * sizeof(float), ev});
     }
+}
+
+static void flush_bucket(b200_ctx* ctx) {
+    DistState* d = ctx->dist;
+    if (d == nullptr || d->bucket.empty()) return;
+    std::vector<DistState::Deferred> items;
+    items.swap(d->bucket);
+    d->bucket_bytes = 0;
+    issue_all_reduces(ctx, items.data(), items.size());
+}
+
+// `may_defer`: inside a gradient span a small buffer waits for its neighbours (flushed when the
+// group is large enough, when anything touches one of its buffers, and at the end of the span).
+static void all_reduce_mean(b200_ctx* ctx, void* data, size_t count, bool may_defer = false) {
+    DistState* d = ctx->dist;
+    const size_t bytes = count * sizeof(float);
+    if (may_defer && ctx->bucket_grads && bytes < kBucketEachBytes) {
+        d->bucket.push_back(DistState::Deferred{data, count});
+        d->bucket_bytes += bytes;
+        if (d->bucket_bytes >= kBucketFlushBytes) flush_bucket(ctx);
+        return;
+    }
+    const DistState::Deferred one{data, count};
+    issue_all_reduces(ctx, &one, 1);
 }
 
 // Makes the compute stream wait for the pending all-reduces that overlap [lo, hi) and for every
@@ -124,6 +186,15 @@ static void all_reduce_mean(b200_ctx* ctx, void* data, size_t count) {
 void dist_wait_range(b200_ctx* ctx, const void* lo, const void* hi) {
     DistState* d = ctx->dist;
     if (d == nullptr) return;
+    if (!d->bucket.empty()) {
+        // a held-back gradient that something is about to touch must be on its way first
+        bool touches = lo == nullptr;
+        for (const DistState::Deferred& e : d->bucket) {
+            const char* b0 = static_cast<const char*>(e.data);
+            touches = touches || (static_cast<const char*>(lo) < b0 + e.count * sizeof(float) && b0 < static_cast<const char*>(hi));
+        }
+        if (touches) flush_bucket(ctx);
+    }
     std::lock_guard<std::mutex> lock(d->lazy_mu);
     if (d->lazy.empty()) return;
     const char* a = static_cast<const char*>(lo);
@@ -156,13 +227,14 @@ int dist_pending_index(const b200_ctx* ctx, const void* lo, const void* hi) {
 bool dist_has_pending(const b200_ctx* ctx) {
     DistState* d = ctx->dist;
     if (d == nullptr) return false;
+    if (!d->bucket.empty()) return true;
     std::lock_guard<std::mutex> lock(d->lazy_mu);
     return !d->lazy.empty();
 }
 
 void dist_all_reduce_now(b200_ctx* ctx, void* data, size_t count) {
     if (ctx->dist != nullptr && count != 0) {
-        all_reduce_mean(ctx, data, count);
+        all_reduce_mean(ctx, data, count, /*may_defer=*/true);
     }
 }
 
@@ -183,7 +255,7 @@ void dist_after_node(b200_ctx* ctx, const b200_node& node) {
     for (size_t i = 0; i < ctx->grads.size(); ++i) {
         const char* g = static_cast<const char*>(ctx->grads[i].data);
         if (!d->done[i] && g >= lo && g < hi) {
-            all_reduce_mean(ctx, ctx->grads[i].data, ctx->grads[i].count);
+            all_reduce_mean(ctx, ctx->grads[i].data, ctx->grads[i].count, /*may_defer=*/true);
             d->done[i] = 1;
         }
     }
@@ -201,6 +273,7 @@ void dist_join(b200_ctx* ctx) {
         }
     }
     d->done.clear();
+    flush_bucket(ctx);
     if (d->pending && !ctx->lazy_join) {
         B200_CUDA_CHECK(cudaEventRecord(d->reduced, d->comm_stream));
         B200_CUDA_CHECK(cudaStreamWaitEvent(ctx->stream, d->reduced, 0));
@@ -215,8 +288,8 @@ void dist_destroy(b200_ctx* ctx) {
     if (d == nullptr) {
         return;
     }
-    if (d->comm_stream != nullptr) cudaStreamSynchronize(d->comm_stream);
-    if (d->comm != nullptr && nccl().CommDestroy != nullptr) nccl().CommDestroy(d->comm);
+    if (d->comm_stream != nullptr && !d->aborted) cudaStreamSynchronize(d->comm_stream);
+    if (d->comm != nullptr && !d->aborted && nccl().CommDestroy != nullptr) nccl().CommDestroy(d->comm);
     for (auto& l : d->lazy) cudaEventDestroy(l.done);
     for (cudaEvent_t e : d->event_pool) cudaEventDestroy(e);
     if (d->produced != nullptr) cudaEventDestroy(d->produced);
@@ -224,6 +297,54 @@ void dist_destroy(b200_ctx* ctx) {
     if (d->comm_stream != nullptr) cudaStreamDestroy(d->comm_stream);
     delete d;
     ctx->dist = nullptr;
+}
+
+// Gives up on the communicator: NCCL's kernels are told to stop, nothing further is issued on it.
+static void abort_comm(b200_ctx* ctx) {
+    DistState* d = ctx->dist;
+    if (d == nullptr || d->aborted) return;
+    d->aborted = true;
+    if (d->comm != nullptr && nccl().CommAbort != nullptr) nccl().CommAbort(d->comm);
+    d->comm = nullptr;
+    std::lock_guard<std::mutex> lock(d->lazy_mu);
+    for (auto& l : d->lazy) d->event_pool.push_back(l.done);
+    d->lazy.clear();
+    d->bucket.clear();
+    d->pending = false;
+}
+
+// Called where the host is about to block on device work that may include collectives: an error
+// NCCL noticed by itself (a peer that went away) or a collective that outlives the host deadline
+// ends with the communicator aborted and an error code, not with a process that waits for ever.
+void dist_check_health(b200_ctx* ctx) {
+    DistState* d = ctx->dist;
+    if (d == nullptr || d->aborted || d->comm == nullptr) return;
+    flush_bucket(ctx);
+    auto async_error = [&]() -> int {
+        int state = 0;
+        if (nccl().CommGetAsyncError == nullptr) return 0;
+        if (nccl().CommGetAsyncError(d->comm, &state) != 0) return -1;
+        return state == static_cast<int>(ncclInProgress) ? 0 : state;
+    };
+    if (const int e = async_error()) {
+        abort_comm(ctx);
+        fail(B200_DEVICE_ERROR, "NCCL reported an asynchronous error (" + std::to_string(e) + "); the communicator was aborted");
+    }
+    if (d->comm_timeout_ms <= 0) return;
+    const auto deadline = std::chrono::steady_clock::now() + std::chrono::milliseconds(d->comm_timeout_ms);
+    while (cudaStreamQuery(d->comm_stream) == cudaErrorNotReady) {
+        if (const int e = async_error()) {
+            abort_comm(ctx);
+            fail(B200_DEVICE_ERROR, "NCCL reported an asynchronous error (" + std::to_string(e) + "); the communicator was aborted");
+        }
+        if (std::chrono::steady_clock::now() > deadline) {
+            abort_comm(ctx);
+            fail(B200_TIMEOUT, "a collective did not finish within " + std::to_string(d->comm_timeout_ms) +
+                                   " ms (VKML_B200_COMM_TIMEOUT_MS); the communicator was aborted");
+        }
+        std::this_thread::sleep_for(std::chrono::microseconds(200));
+    }
+    cudaGetLastError();
 }
 
 namespace {
@@ -268,8 +389,8 @@ int b200_dist_unique_id(void* out_id) {
     });
 }
 
-int b200_dist_init(b200_ctx* ctx, int rank, int world_size, const void* id) {
-    if (ctx == nullptr || id == nullptr || world_size < 1 || rank < 0 || rank >= world_size) {
+int b200_dist_init_deadline(b200_ctx* ctx, int rank, int world_size, const void* id, int timeout_ms) {
+    if (ctx == nullptr || id == nullptr || world_size < 1 || rank < 0 || rank >= world_size || timeout_ms < 0) {
         return B200_INVALID_ARGUMENT;
     }
     return guarded_dist(ctx, [&] {
@@ -281,6 +402,7 @@ int b200_dist_init(b200_ctx* ctx, int rank, int world_size, const void* id) {
         ctx->dist = d;
         d->rank = rank;
         d->world = world_size;
+        if (const char* e = std::getenv("VKML_B200_COMM_TIMEOUT_MS")) d->comm_timeout_ms = std::max(0, std::atoi(e));
         // highest priority: when SMs free up, the all-reduce's blocks are placed before the next
         // compute blocks, so communication is never starved by a queue of GEMM tiles
         int least = 0, greatest = 0;
@@ -290,8 +412,48 @@ int b200_dist_init(b200_ctx* ctx, int rank, int world_size, const void* id) {
         B200_CUDA_CHECK(cudaEventCreateWithFlags(&d->reduced, cudaEventDisableTiming));
         NcclUniqueId uid;
         std::memcpy(&uid, id, sizeof(uid));
-        nccl_check(nccl().CommInitRank(&d->comm, world_size, uid, rank), "ncclCommInitRank");
+        const bool can_poll = nccl().CommInitRankConfig != nullptr && nccl().CommGetAsyncError != nullptr &&
+                              nccl().CommAbort != nullptr;
+        if (timeout_ms == 0 || !can_poll) {
+            nccl_check(nccl().CommInitRank(&d->comm, world_size, uid, rank), "ncclCommInitRank");
+            return;
+        }
+        // Non-blocking initialisation: the call returns while the ranks are still finding each
+        // other, and the host polls with a deadline -- a rank that never joins ends this one with
+        // B200_TIMEOUT and an aborted communicator instead of a process stuck inside NCCL.
+        ncclConfig_t config = NCCL_CONFIG_INITIALIZER;
+        config.blocking = 0;
+        int rc = nccl().CommInitRankConfig(&d->comm, world_size, uid, rank, &config);
+        const auto deadline = std::chrono::steady_clock::now() + std::chrono::milliseconds(timeout_ms);
+        int state = rc;
+        while (rc == 0 || rc == static_cast<int>(ncclInProgress)) {
+            if (d->comm == nullptr || nccl().CommGetAsyncError(d->comm, &state) != 0) {
+                state = -1;
+                break;
+            }
+            if (state != static_cast<int>(ncclInProgress)) break;
+            if (std::chrono::steady_clock::now() > deadline) {
+                nccl().CommAbort(d->comm);
+                d->comm = nullptr;
+                dist_destroy(ctx);
+                fail(B200_TIMEOUT, "the ranks did not all join within " + std::to_string(timeout_ms) +
+                                       " ms; the communicator was aborted");
+            }
+            std::this_thread::sleep_for(std::chrono::milliseconds(1));
+        }
+        if (state != 0) {
+            if (d->comm != nullptr) nccl().CommAbort(d->comm);
+            d->comm = nullptr;
+            dist_destroy(ctx);
+            nccl_check(state > 0 ? state : 1, "ncclCommInitRankConfig");
+        }
     });
+}
+
+int b200_dist_init(b200_ctx* ctx, int rank, int world_size, const void* id) {
+    int timeout_ms = 120000;
+    if (const char* e = std::getenv("VKML_B200_DIST_INIT_TIMEOUT_MS")) timeout_ms = std::max(0, std::atoi(e));
+    return b200_dist_init_deadline(ctx, rank, world_size, id, timeout_ms);
 }
 
 int b200_dist_destroy(b200_ctx* ctx) {

@@ -113,7 +113,7 @@ __device__ __forceinline__ uint64_t global_ns() {
 // Bounded wait. Returns false (and raises the abort flag) when the limit ran out
 // or another role already aborted.
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag,
-                                          uint32_t* status) {
+                                          uint32_t* status, uint64_t limit_ns = kWaitLimitNs) {
     // The clock is only consulted every 1024 polls (reading %globaltimer costs far more than a
     // poll, and the converter warps wait here once per K-block), so the limit is the stated time
     // plus at most 1024 polls.
@@ -127,7 +127,7 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatil
             const uint64_t now = global_ns();
             if (start == 0) {
                 start = now;
-            } else if (now - start > kWaitLimitNs) {
+            } else if (now - start > limit_ns) {
                 *abort_flag = 1;
                 atomicOr(status, kStatusWaitTimedOut);
                 return false;
@@ -158,6 +158,21 @@ __device__ __forceinline__ bool mbar_wait_parked(uint32_t bar, uint32_t parity, 
         }
     }
     return true;
+}
+
+// One block that waits, through the very mbar_wait the GEMM kernels use, on a barrier nobody will
+// ever arrive on: the wait runs out after `limit_ns`, records kStatusWaitTimedOut and the kernel
+// returns by itself.  Nothing is in flight, nothing faults; it exists so that the path from a
+// bounded device wait to B200_TIMEOUT on the host can be exercised.
+__global__ void wait_probe_kernel(uint32_t* status, uint64_t limit_ns) {
+    __shared__ uint64_t barrier;
+    __shared__ int abort_flag;
+    if (threadIdx.x == 0) {
+        abort_flag = 0;
+        mbar_init(smem_u32(&barrier), 1);
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        (void)mbar_wait(smem_u32(&barrier), 0, &abort_flag, status, limit_ns);
+    }
 }
 
 __device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, uint32_t bar, int c0,
@@ -1741,6 +1756,12 @@ bool gemm_tc_eligible(const b200_ctx* ctx, const GemmProblem& p) {
 }
 
 bool gemm_tc_streams(const b200_ctx* ctx, const GemmProblem& p) { return plan_stream(ctx, p).ok; }
+
+void gemm_tc_wait_probe(b200_ctx* ctx, uint64_t limit_ns) {
+    wait_probe_kernel<<<1, 32, 0, ctx->stream>>>(ctx->d_status, limit_ns);
+    ctx->count_launch();
+    check_last_launch("wait probe");
+}
 
 void gemm_tc(b200_ctx* ctx, const GemmProblem& p, bool three_pass) {
     if (const StreamPlan sp = plan_stream(ctx, p); sp.ok) {
