@@ -86,6 +86,27 @@ void nccl_check(int rc, const char* what) {
     }
 }
 
+// A communicator created in non-blocking mode (b200_dist_init_deadline) stays non-blocking: any
+// call on it may return ncclInProgress, and the work is only known to be ENQUEUED on its stream
+// once ncclCommGetAsyncError stops saying so.  Events recorded behind a collective must come
+// after that point, so every call is settled before the host goes on.
+void nccl_settle(NcclComm comm, int rc, const char* what) {
+    if (rc == static_cast<int>(ncclInProgress) && nccl().CommGetAsyncError != nullptr) {
+        const auto deadline = std::chrono::steady_clock::now() + std::chrono::seconds(60);
+        int state = rc;
+        do {
+            if (nccl().CommGetAsyncError(comm, &state) != 0) {
+                state = 1;
+                break;
+            }
+            if (state != static_cast<int>(ncclInProgress)) break;
+            std::this_thread::yield();
+        } while (std::chrono::steady_clock::now() < deadline);
+        rc = state;
+    }
+    nccl_check(rc, what);
+}
+
 }  // namespace
 
 struct DistState {
@@ -132,12 +153,17 @@ static void issue_all_reduces(b200_ctx* ctx, const DistState::Deferred* items, s
     const bool group = n > 1 && nccl().GroupStart != nullptr && nccl().GroupEnd != nullptr;
     if (group) nccl_check(nccl().GroupStart(), "ncclGroupStart");
     for (size_t i = 0; i < n; ++i) {
-        nccl_check(nccl().AllReduce(items[i].data, items[i].data, items[i].count, kNcclFloat32, kNcclAvg, d->comm,
-                                    d->comm_stream),
-                   "ncclAllReduce");
+        const int rc = nccl().AllReduce(items[i].data, items[i].data, items[i].count, kNcclFloat32, kNcclAvg, d->comm,
+                                        d->comm_stream);
+        if (group) {
+            // inside a group nothing is launched yet: in-progress is the expected answer
+            if (rc != static_cast<int>(ncclInProgress)) nccl_check(rc, "ncclAllReduce");
+        } else {
+            nccl_settle(d->comm, rc, "ncclAllReduce");
+        }
         ctx->comm_bytes.fetch_add(items[i].count * sizeof(float), std::memory_order_relaxed);
     }
-    if (group) nccl_check(nccl().GroupEnd(), "ncclGroupEnd");
+    if (group) nccl_settle(d->comm, nccl().GroupEnd(), "ncclGroupEnd");
     d->pending = true;
     ctx->comm_pending = true;
     if (ctx->lazy_join) {
