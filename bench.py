@@ -692,39 +692,49 @@ def run_gemm_sweep(args, local_rank):
     for name, batch, m, k, n, kind in shapes:
         if args.filter and args.filter not in name:
             continue
-        if kind == "bn":   # A broadcast over the batch
-            a = DeviceTensor.from_host(backend, rng.standard_normal((m, k), dtype=np.float32)).reshape(
-                (1, 1, m, k)).broadcast_to((1, batch, m, k))
-            b = DeviceTensor.from_host(backend, rng.standard_normal((1, batch, k, n), dtype=np.float32))
-        elif kind == "Bn":   # A = a transposed view of a broadcast [k, m] matrix (dcols = W^T . g)
-            a = DeviceTensor.from_host(backend, rng.standard_normal((k, m), dtype=np.float32)).transpose(0, 1)
-            a = DeviceTensor(backend, a.storage, (1, 1) + a.dims, (0, 0) + a.strides, a.dtype).broadcast_to(
-                (1, batch, m, k))
-            b = DeviceTensor.from_host(backend, rng.standard_normal((1, batch, k, n), dtype=np.float32))
-        elif kind == "nT":   # batched A, B = a transposed view of batched [n, k] storage (dW = g . cols^T)
-            a = DeviceTensor.from_host(backend, rng.standard_normal((1, batch, m, k), dtype=np.float32))
-            b = DeviceTensor.from_host(backend, rng.standard_normal((1, batch, n, k), dtype=np.float32)).transpose(2, 3)
-        else:
-            a = DeviceTensor.from_host(backend, rng.standard_normal((k, m) if kind[0] == "t" else (m, k),
-                                                                    dtype=np.float32))
-            b = DeviceTensor.from_host(backend, rng.standard_normal((n, k) if kind[1] == "t" else (k, n),
-                                                                    dtype=np.float32))
-            a = (a.transpose(0, 1) if kind[0] == "t" else a)
-            b = (b.transpose(0, 1) if kind[1] == "t" else b)
-            a = DeviceTensor(backend, a.storage, (1, 1) + a.dims, (0, 0) + a.strides, a.dtype)
-            b = DeviceTensor(backend, b.storage, (1, 1) + b.dims, (0, 0) + b.strides, b.dtype)
-        c = DeviceTensor.empty(backend, (1, batch, m, n))
-        packed = graph.pack_nodes([NodeDesc(int(Op.MATMUL), c.desc, [a.desc, b.desc])])
         flops = 2.0 * batch * m * n * k
-        row = {"gemm": name, "batch": batch, "m": m, "k": k, "n": n, "layout": kind}
+        # small products: ten nodes per submitted span, so that the stream never waits for the host
+        # between them (one Python call per node would be the thing measured).  Every node of the span
+        # has operands and a result of its OWN: nothing is shared between the nodes (no operand plane is
+        # reused) and the ten operand sets together are larger than L2, so no node finds its input there.
+        per_span = 10 if flops < 1e10 else 1
+        if kind in ("bn", "Bn"):
+            host_a = rng.standard_normal((k, m) if kind == "Bn" else (m, k), dtype=np.float32)
+            host_b = rng.standard_normal((1, batch, k, n), dtype=np.float32)
+        elif kind == "nT":
+            host_a = rng.standard_normal((1, batch, m, k), dtype=np.float32)
+            host_b = rng.standard_normal((1, batch, n, k), dtype=np.float32)
+        else:
+            host_a = rng.standard_normal((k, m) if kind[0] == "t" else (m, k), dtype=np.float32)
+            host_b = rng.standard_normal((n, k) if kind[1] == "t" else (k, n), dtype=np.float32)
+
+        def operands():
+            a = DeviceTensor.from_host(backend, host_a)
+            b = DeviceTensor.from_host(backend, host_b)
+            if kind == "bn":   # A broadcast over the batch
+                a = a.reshape((1, 1, m, k)).broadcast_to((1, batch, m, k))
+            elif kind == "Bn":   # A = a transposed view of a broadcast [k, m] matrix (dcols = W^T . g)
+                a = a.transpose(0, 1)
+                a = DeviceTensor(backend, a.storage, (1, 1) + a.dims, (0, 0) + a.strides, a.dtype).broadcast_to(
+                    (1, batch, m, k))
+            elif kind == "nT":   # batched A, B = a transposed view of batched [n, k] storage (dW = g . cols^T)
+                b = b.transpose(2, 3)
+            else:
+                a = (a.transpose(0, 1) if kind[0] == "t" else a)
+                b = (b.transpose(0, 1) if kind[1] == "t" else b)
+                a = DeviceTensor(backend, a.storage, (1, 1) + a.dims, (0, 0) + a.strides, a.dtype)
+                b = DeviceTensor(backend, b.storage, (1, 1) + b.dims, (0, 0) + b.strides, b.dtype)
+            return a, b, DeviceTensor.empty(backend, (1, batch, m, n))
+
+        sets = [operands() for _ in range(per_span)]
+        nodes = [NodeDesc(int(Op.MATMUL), c.desc, [a.desc, b.desc]) for a, b, c in sets]
+        packed = graph.pack_nodes(nodes[:1])
+        span = graph.pack_nodes(nodes)
+        row = {"gemm": name, "batch": batch, "m": m, "k": k, "n": n, "layout": kind, "nodes_per_span": per_span}
         for prec, code in (("3xtf32", 0), ("tf32", 1), ("fp32", 2)):
             if prec == "fp32" and flops > 3e11:
                 continue
             backend.set_gemm_precision(code)
-            # small products: ten nodes per submitted span, so that the stream never waits for the
-            # host between them (one Python call per node would be the thing measured)
-            per_span = 10 if flops < 1e10 else 1
-            span = graph.pack_nodes([NodeDesc(int(Op.MATMUL), c.desc, [a.desc, b.desc])] * per_span)
             reps = (20 if flops < 1e11 else 5) // (2 if per_span > 1 else 1)
             for _ in range(3):
                 backend.compute_packed(span, per_span)
@@ -740,7 +750,7 @@ def run_gemm_sweep(args, local_rank):
             row[prec] = {"ms": round(ms, 4), "tflops": round(flops / (ms * 1e-3) / 1e12, 2),
                          "kernel_ms": {l: round(t, 4) for l, t in rec}}
         print(json.dumps(row), flush=True)
-        del a, b, c, packed
+        del sets, nodes, packed, span
         backend.trim()
 
 
