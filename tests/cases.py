@@ -473,6 +473,16 @@ def matmul_tc_cases(seed=12):
     yield mk("stream-w-batched", rnd(1, 4, 128, 256), rnd(1, 4, 256, 192))
     wide = rnd(1, 1, 512, 640)
     yield mk("stream-pitched-s", rnd(1, 1, 96, 512), wide[:, :, :, 64:576])                # S is a column slice
+    # ... and a right operand with K contiguous (a transposed view: a Linear weight, the column tensor
+    # in a convolution's weight gradient), ragged in every extent, pitched, batched, several chunks of W
+    yield mk("stream-kmajor-ragged", rnd(1, 1, 100, 652), t(rnd(1, 1, 652, 520)))
+    yield mk("stream-kmajor-conv3-dw", rnd(1, 4, 256, 64), t(rnd(1, 4, 64, 1152)))
+    tall = rnd(1, 4, 400, 300)                                                              # storage [n][k], k sliced
+    yield mk("stream-kmajor-pitched", rnd(1, 4, 60, 256), tall[:, :, 8:392, 20:276].swapaxes(-1, -2))
+    yield mk("stream-kmajor-splitk", rnd(1, 1, 48, 4096), t(rnd(1, 1, 4096, 256)))
+    # a tall W against a short K: the column gradient of a convolution (W^T broadcast, N = 64: two batches per tile)
+    yield mk("stream-tall-w-conv3-dcols", t(rnd(1, 1, 1152, 256)), rnd(1, 8, 256, 64))
+    yield mk("stream-tall-w-ragged", rnd(1, 1, 700, 130), rnd(1, 3, 130, 200))
 
 
 def movement_cases(seed=21, quick=False):

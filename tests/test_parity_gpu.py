@@ -100,9 +100,14 @@ def test_matmul_tensor_core_3xtf32(cuda, oracle, backend):
         n += 1
     labels = [l for l, _ in backend.last_profile()]
     backend.set_profiling(False)
-    # every case really ran on the tensor cores (operand planes or direct operands)
+    # every case really ran on the tensor cores (operand planes or the streamed operand)
     assert sum(l.startswith("matmul.tcgen05_3xtf32") for l in labels) == n, labels
     assert not any(l == "matmul.fp32_simt" for l in labels)
+    # ... and the products bound by memory on the streamed-operand kernel: every case named for it,
+    # both operand layouts, a tall W against a short K
+    streamed = sum(l == "matmul.tcgen05_3xtf32_stream" for l in labels)
+    named = sum("/stream-" in c.name for c in cases.matmul_tc_cases())
+    assert named >= 14 and streamed >= named + 4, (streamed, named)
 
 
 def test_matmul_tensor_core_both_operand_schemes(oracle, monkeypatch):

@@ -1157,7 +1157,7 @@ int b200_matmul_kernel(b200_ctx* ctx, const b200_node* node, char* name, size_t 
             const bool three = ctx->gemm_precision == B200_GEMM_3XTF32;
             if (gemm_tc_streams(ctx, p)) {
                 kernel = three ? "tcgen05_3xtf32_stream" : "tcgen05_tf32_stream";
-                why = "a small left operand: the right operand is read once from HBM and split on the way";
+                why = "bound by memory (a small left operand or a short K): the right operand is read as fp32 and split on the way";
             } else {
                 kernel = three ? "tcgen05_3xtf32" : "tcgen05_tf32";
                 why = "operands split into TF32 planes, tensor-core tiles fed by TMA";

@@ -908,8 +908,11 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a_hi, const __grid_consta
 //
 //   * the product is computed transposed, D[n][m] = sum_k S[k][n] W[m][k], so that S is the
 //     tensor core's A operand, and A may come from TENSOR MEMORY instead of shared memory;
-//   * warp 0 brings [32 k][128 n] fp32 tiles of S (tensor map over the caller's own matrix,
-//     zero fill past the edges) and the matching K-block of W's planes into a 4-deep ring;
+//   * two producer warps: one brings [32 k][128 n] fp32 tiles of S (tensor map over the caller's
+//     own matrix, zero fill past the edges) into a ring of 6 to 8 slots, the other the matching
+//     K-blocks of W's planes into a ring of 4.  The rings are separate because their latencies
+//     are: S comes from HBM and its slot is free again as soon as the converters have read it,
+//     W comes from L2 and stays until the MMAs that read it have finished;
 //   * sixteen converter warps read their lane's column of the S tile (lane = n, conflict-free),
 //     split every value into hi/lo in registers and put both into tensor memory with
 //     tcgen05.st -- 64 columns per stage: the streamed operand never touches shared memory
@@ -919,13 +922,21 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a_hi, const __grid_consta
 //   * warps 2-5 read the accumulator (lane = n, columns = m): for every m one warp instruction
 //     stores 32 consecutive n, 128 bytes, straight from registers.
 //
+// S may also lie with its K axis contiguous (the transposed view of an [N][K] matrix: a Linear
+// layer's weight in the forward product, the column tensor in a convolution's weight gradient).
+// Then the tile is [128 n][32 k], fetched with the 128-byte swizzle so that a lane reading its own
+// row (lane = n) meets no bank conflict, and everything after the converter is unchanged.
+//
+// W may have more rows than one accumulator holds: its 128-row chunks are separate units that run
+// side by side on neighbouring SMs, so S's tile is fetched from HBM once and from L2 after that.
+//
 // When N is shorter than 128 and W is broadcast over the batch, one tile spans several batches
 // (lanes = batch x n).  K is split across CTAs when the tiles alone cannot fill the machine;
 // the warp that arrives last at its quarter of a tile folds the partial planes in split order in
 // the same launch (deterministic, no atomics on data).
-constexpr int kStreamStages = 4;
+constexpr int kStreamStages = 4;          // W's ring in shared memory and S's ring in tensor memory
 constexpr int kStreamConverters = 16;     // converter warps: four per tensor-memory lane quarter, 8 K columns each
-constexpr int kStreamThreads = (6 + kStreamConverters) * 32;  // + TMA, MMA and four epilogue warps
+constexpr int kStreamThreads = (7 + kStreamConverters) * 32;  // + two TMA warps, MMA and four epilogue warps
 constexpr int kStreamTileBytes = BK * 128 * 4;  // one fp32 tile of S: 32 K-rows x 128 lanes
 constexpr uint32_t kStreamTmemCols = 512;
 constexpr int kStreamCounters = 1024;     // arrival counters of the in-kernel split-K fold: 4 per tile
@@ -959,15 +970,6 @@ __device__ __forceinline__ void umma_tf32_ts(uint32_t tmem_d, uint32_t tmem_a, u
         : "memory");
 }
 
-__device__ __forceinline__ void tmem_st16(uint32_t taddr, const uint32_t (&r)[16]) {
-    asm volatile(
-        "tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], "
-        "{%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16};"
-        ::"r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]),
-          "r"(r[8]), "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15])
-        : "memory");
-}
-
 __device__ __forceinline__ void tmem_st8(uint32_t taddr, const uint32_t (&r)[8]) {
     asm volatile(
         "tcgen05.st.sync.aligned.32x32b.x8.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8};"
@@ -986,29 +988,36 @@ __device__ __forceinline__ void tma_load_3d(uint32_t dst, const CUtensorMap* map
 template <int BNW>
 struct StreamSmem {
     static constexpr int kWBytes = BNW * BK * 4;  // one plane tile of W
-    static constexpr int kStageBytes = kStreamTileBytes + 2 * kWBytes;
-    static constexpr int kTotal = kStreamStages * kStageBytes + 256 + 1024;
+    static constexpr int kWStage = 2 * kWBytes;   // hi and lo
+    static constexpr int kSlots = BNW <= 64 ? 8 : 6;  // fp32 tiles of S in flight (besides the 4 in tensor memory)
+    static constexpr int kWBase = kSlots * kStreamTileBytes;
+    static constexpr int kBars = kWBase + kStreamStages * kWStage;
+    static constexpr int kTotal = kBars + 256 + 1024;
 };
 
-template <int BNW, bool THREE_PASS, bool W_MN>
+template <int BNW, bool THREE_PASS, bool W_MN, bool S_KM>
 __global__ void __launch_bounds__(kStreamThreads, 1)
 gemm_stream_kernel(const __grid_constant__ CUtensorMap map_s, const __grid_constant__ CUtensorMap map_w_hi,
                    const __grid_constant__ CUtensorMap map_w_lo, StreamArgs g) {
     using S = StreamSmem<BNW>;
     constexpr int STAGES = kStreamStages;
     constexpr uint32_t kIdesc = make_idesc(BM, BNW, false, W_MN);
-    constexpr uint32_t kStageTx = kStreamTileBytes + (THREE_PASS ? 2 : 1) * S::kWBytes;
+    constexpr int SLOTS = S::kSlots;
+    constexpr uint32_t kWTx = (THREE_PASS ? 2 : 1) * S::kWBytes;
     constexpr uint32_t kStageCol0 = 2 * BNW;  // tensor-memory columns: two accumulators, then the S stages
+    static_assert(8 * (2 * SLOTS + 3 * STAGES + 4) <= 256, "barrier block");
 
     extern __shared__ uint8_t smem_raw[];
     const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
     uint8_t* base_ptr = smem_raw + (base - smem_u32(smem_raw));
-    const uint32_t bars = base + STAGES * S::kStageBytes;
-    auto full_bar = [&](int s) { return bars + 8u * s; };                    // S tile and W planes landed
+    const uint32_t bars = base + S::kBars;
+    auto full_bar = [&](int s) { return bars + 8u * s; };                    // W's planes landed
     auto empty_bar = [&](int s) { return bars + 8u * (STAGES + s); };        // the stage's MMAs are done
     auto conv_bar = [&](int s) { return bars + 8u * (2 * STAGES + s); };     // S is in tensor memory
     auto acc_full = [&](int a) { return bars + 8u * (3 * STAGES + a); };
     auto acc_empty = [&](int a) { return bars + 8u * (3 * STAGES + 2 + a); };
+    auto s_full = [&](int j) { return bars + 8u * (3 * STAGES + 4 + j); };            // an fp32 tile of S landed
+    auto s_empty = [&](int j) { return bars + 8u * (3 * STAGES + 4 + SLOTS + j); };   // the converters have read it
     __shared__ uint32_t tmem_base_slot;
     __shared__ int abort_flag;
 
@@ -1021,6 +1030,10 @@ gemm_stream_kernel(const __grid_constant__ CUtensorMap map_s, const __grid_const
             mbar_init(full_bar(s), 1);
             mbar_init(empty_bar(s), 1);
             mbar_init(conv_bar(s), kStreamConverters);  // one arrival per converter warp
+        }
+        for (int j = 0; j < SLOTS; ++j) {
+            mbar_init(s_full(j), 1);
+            mbar_init(s_empty(j), kStreamConverters);
         }
         for (int a = 0; a < 2; ++a) {
             mbar_init(acc_full(a), 1);
@@ -1050,8 +1063,8 @@ gemm_stream_kernel(const __grid_constant__ CUtensorMap map_s, const __grid_const
         bg = t / g.tiles_n;
     };
 
-    if (warp == 0) {
-        // ---------------- TMA producer ----------------
+    if (warp == kStreamThreads / 32 - 1) {
+        // ---------------- TMA producer of S ----------------
         if (lane == 0) {
             uint32_t it = 0;
             bool ok = true;
@@ -1061,6 +1074,37 @@ gemm_stream_kernel(const __grid_constant__ CUtensorMap map_s, const __grid_const
                 decode(u, tm, split, tn, bg);
                 const int batch0 = static_cast<int>(bg * g.bpt);
                 const int n0 = static_cast<int>(tn * g.nt);
+                const int64_t kb0 = int64_t(split) * g.kb_per_split;
+                const int64_t kb1 = min(kb0 + g.kb_per_split, g.k_blocks);
+                for (int64_t kb = kb0; kb < kb1; ++kb, ++it) {
+                    const int j = it % SLOTS;
+                    const uint32_t ph = (it / SLOTS) & 1;
+                    if (!mbar_wait(s_empty(j), ph ^ 1, abort_p, g.status)) {
+                        ok = false;
+                        break;
+                    }
+                    const uint32_t slot = base + j * kStreamTileBytes;
+                    const uint32_t bar = s_full(j);
+                    const int kc = static_cast<int>(kb * BK);
+                    mbar_arrive_expect_tx(bar, kStreamTileBytes);
+                    if (S_KM) {
+                        tma_load_3d(slot, &map_s, bar, kc, n0, batch0);  // [128 n][32 k], k contiguous
+                    } else {
+                        tma_load_3d(slot, &map_s, bar, n0, kc, batch0);  // [32 k][128 n], n contiguous
+                    }
+                }
+            }
+        }
+    } else if (warp == 0) {
+        // ---------------- TMA producer of W's planes ----------------
+        if (lane == 0) {
+            uint32_t it = 0;
+            bool ok = true;
+            for (int64_t u = blockIdx.x; u < n_units && ok; u += gridDim.x) {
+                int64_t tm, tn, bg;
+                int split;
+                decode(u, tm, split, tn, bg);
+                const int batch0 = static_cast<int>(bg * g.bpt);
                 const int m0 = static_cast<int>(tm * BNW);
                 const int w_base = static_cast<int>(batch0 * g.w_batch_rows);
                 const int64_t kb0 = int64_t(split) * g.kb_per_split;
@@ -1072,11 +1116,10 @@ gemm_stream_kernel(const __grid_constant__ CUtensorMap map_s, const __grid_const
                         ok = false;
                         break;
                     }
-                    const uint32_t stage = base + s * S::kStageBytes;
+                    const uint32_t stage = base + S::kWBase + s * S::kWStage;
                     const uint32_t bar = full_bar(s);
                     const int kc = static_cast<int>(kb * BK);
-                    mbar_arrive_expect_tx(bar, kStageTx);
-                    tma_load_3d(stage, &map_s, bar, n0, kc, batch0);
+                    mbar_arrive_expect_tx(bar, kWTx);
                     auto load_w = [&](uint32_t dst, const CUtensorMap* map) {
                         if (W_MN) {
 #pragma unroll
@@ -1087,9 +1130,9 @@ gemm_stream_kernel(const __grid_constant__ CUtensorMap map_s, const __grid_const
                             tma_load_2d(dst, map, bar, kc, w_base + m0);
                         }
                     };
-                    load_w(stage + kStreamTileBytes, &map_w_hi);
+                    load_w(stage, &map_w_hi);
                     if (THREE_PASS) {
-                        load_w(stage + kStreamTileBytes + S::kWBytes, &map_w_lo);
+                        load_w(stage + S::kWBytes, &map_w_lo);
                     }
                 }
             }
@@ -1122,9 +1165,9 @@ gemm_stream_kernel(const __grid_constant__ CUtensorMap map_s, const __grid_const
                         break;
                     }
                     tc_fence_after();
-                    const uint32_t stage = base + s * S::kStageBytes;
-                    const uint64_t w_hi = operand_desc<W_MN>(stage + kStreamTileBytes);
-                    const uint64_t w_lo = operand_desc<W_MN>(stage + kStreamTileBytes + S::kWBytes);
+                    const uint32_t stage = base + S::kWBase + s * S::kWStage;
+                    const uint64_t w_hi = operand_desc<W_MN>(stage);
+                    const uint64_t w_lo = operand_desc<W_MN>(stage + S::kWBytes);
                     const uint32_t s_hi = tmem_base + kStageCol0 + s * 64;
                     const uint32_t s_lo = s_hi + 32;
 #pragma unroll
@@ -1139,7 +1182,7 @@ gemm_stream_kernel(const __grid_constant__ CUtensorMap map_s, const __grid_const
                             umma_tf32_ts(d_tmem, s_hi + kk * UMMA_K, w_hi + adv_w, kIdesc, first);
                         }
                     }
-                    umma_commit(empty_bar(s));  // shared-memory stage and tensor-memory stage are both free then
+                    umma_commit(empty_bar(s));  // W's stage and S's tensor-memory stage are both free then
                 }
                 if (ok) {
                     umma_commit(acc_full(acc));
@@ -1258,7 +1301,7 @@ gemm_stream_kernel(const __grid_constant__ CUtensorMap map_s, const __grid_const
                 }
             }
         }
-    } else {
+    } else if (warp < 6 + kStreamConverters) {
         // ---------------- converters (warps 6..21): S tile -> hi / lo in tensor memory ----------------
         // Sixteen warps, four per tensor-memory lane quarter, each taking 8 of the stage's 32 K
         // columns: the split is ~7 instructions per element on 4096 elements per K-block, and it is
@@ -1268,8 +1311,13 @@ gemm_stream_kernel(const __grid_constant__ CUtensorMap map_s, const __grid_const
         const int l = quarter * 32 + lane;
         const int bl = l / g.nt;
         const int nn = l - bl * g.nt;
-        const uint32_t first_off = static_cast<uint32_t>(((bl * BK + part * 8) * g.nt + nn) * 4);
+        const uint32_t first_off = S_KM ? static_cast<uint32_t>(l * 128)
+                                        : static_cast<uint32_t>(((bl * BK + part * 8) * g.nt + nn) * 4);
         const uint32_t k_step = static_cast<uint32_t>(g.nt * 4);
+        // K-major tile: the row of lane l is 128 bytes, its 16-byte chunks permuted by the 128-byte
+        // swizzle (chunk ^ (row & 7)); this warp's eight K values are chunks 2*part and 2*part + 1
+        const uint32_t chunk0 = static_cast<uint32_t>(((2 * part) ^ (l & 7)) * 16);
+        const uint32_t chunk1 = static_cast<uint32_t>(((2 * part + 1) ^ (l & 7)) * 16);
         const uint32_t lane_field = static_cast<uint32_t>(quarter * 32) << 16;
         uint32_t it = 0;
         bool ok = true;
@@ -1282,18 +1330,31 @@ gemm_stream_kernel(const __grid_constant__ CUtensorMap map_s, const __grid_const
             for (int64_t kb = kb0; kb < kb1; ++kb, ++it) {
                 const int s = it % STAGES;
                 const uint32_t ph = (it / STAGES) & 1;
-                // the producer refilled this stage only after its previous MMAs had finished, so the
-                // stage's tensor-memory columns are free as well
-                if (!mbar_wait_parked(full_bar(s), ph, abort_p, g.status)) {
+                const int j = it % SLOTS;
+                const uint32_t sph = (it / SLOTS) & 1;
+                // the tile has landed, and the MMAs that read this tensor-memory stage last are done
+                if (!mbar_wait_parked(s_full(j), sph, abort_p, g.status) ||
+                    !mbar_wait(empty_bar(s), ph ^ 1, abort_p, g.status)) {
                     ok = false;
                     break;
                 }
-                const uint8_t* tile = base_ptr + s * S::kStageBytes + first_off;
+                tc_fence_after();
+                const uint8_t* tile = base_ptr + j * kStreamTileBytes + first_off;
                 float v[8];
                 uint32_t top = 0;
+                if (S_KM) {
+                    const float4 q0 = *reinterpret_cast<const float4*>(tile + chunk0);
+                    const float4 q1 = *reinterpret_cast<const float4*>(tile + chunk1);
+                    v[0] = q0.x; v[1] = q0.y; v[2] = q0.z; v[3] = q0.w;
+                    v[4] = q1.x; v[5] = q1.y; v[6] = q1.z; v[7] = q1.w;
+                } else {
+#pragma unroll
+                    for (int j = 0; j < 8; ++j) {
+                        v[j] = *reinterpret_cast<const float*>(tile + j * k_step);
+                    }
+                }
 #pragma unroll
                 for (int j = 0; j < 8; ++j) {
-                    v[j] = *reinterpret_cast<const float*>(tile + j * k_step);
                     top = max(top, __float_as_uint(v[j]) << 1);
                 }
                 uint32_t hi[8], lo[8];
@@ -1322,6 +1383,7 @@ gemm_stream_kernel(const __grid_constant__ CUtensorMap map_s, const __grid_const
                 __syncwarp();
                 if (lane == 0) {
                     mbar_arrive(conv_bar(s));
+                    mbar_arrive(s_empty(j));  // the values are in registers and tensor memory: the slot may be refilled
                 }
             }
         }
@@ -1559,24 +1621,37 @@ void release_use(b200_ctx* ctx, const Operand& o) {
 
 struct StreamPlan {
     bool ok = false;
+    bool s_km = false;         // S's K axis is the contiguous one
     int nt = 128, bpt = 1, bnw = 64;
+    int64_t pitch = 0;         // elements between consecutive rows of S (K rows, or N rows when s_km)
     int64_t batch_stride = 0;  // elements between consecutive batches of S
 };
 
-// The product qualifies when its right operand can be read by TMA as it lies in memory (n
-// contiguous, 16-byte pitches, batches one constant stride apart) and its left operand is small:
-// with at most 256 rows the streamed operand is worth 128 flops per byte at most, and one pass
-// over it beats reading it once, writing two planes and reading those.
+// The product qualifies when its right operand can be read by TMA as it lies in memory (n or k
+// contiguous, 16-byte pitches, batches one constant stride apart) and the product is bound by
+// memory rather than by the tensor pipe: a left operand of at most 256 rows (the streamed operand
+// is then worth 128 flops per byte at most, and one pass over it beats reading it once, writing
+// two planes and reading those), or a short K (at most 256: the result outweighs the operands --
+// the column gradient of a convolution -- and re-reading S's few tiles from L2 for every 128 rows
+// of W costs less than the plane passes).
 StreamPlan plan_stream(const b200_ctx* ctx, const GemmProblem& p) {
     StreamPlan sp;
     if (ctx->gemm_stream == 0 || (ctx->gemm_stream < 0 && ctx->gemm_operands >= 0)) {
         return sp;  // switched off, or another operand scheme was asked for by name
     }
     const int64_t batches = p.b0 * p.b1;
-    if (p.m > 256 || p.n < 32 || batches < 1) return sp;
-    if (p.b_s[3] != 1 || p.b_s[2] % 4 != 0 || p.b_s[2] < p.n) return sp;
+    if ((p.m > 256 && (p.k > 256 || p.m > 4096)) || p.n < 32 || batches < 1) return sp;
+    if (p.b_s[3] == 1 && p.b_s[2] % 4 == 0 && p.b_s[2] >= p.n) {
+        sp.s_km = false;
+        sp.pitch = p.b_s[2];
+    } else if (p.b_s[2] == 1 && p.b_s[3] % 4 == 0 && p.b_s[3] >= p.k && p.n >= 128) {
+        sp.s_km = true;
+        sp.pitch = p.b_s[3];
+    } else {
+        return sp;
+    }
     if (reinterpret_cast<uintptr_t>(p.b) % 16 != 0) return sp;
-    int64_t sb = std::max<int64_t>(p.k * p.b_s[2], 4);
+    int64_t sb = std::max<int64_t>((sp.s_km ? p.n : p.k) * sp.pitch, 4);
     if (batches > 1) {
         if (p.b0 == 1) sb = p.b_s[1];
         else if (p.b1 == 1) sb = p.b_s[0];
@@ -1602,16 +1677,20 @@ StreamPlan plan_stream(const b200_ctx* ctx, const GemmProblem& p) {
 }
 
 CUtensorMap make_stream_map(const float* base, int64_t n, int64_t k, int64_t pitch, int64_t batches,
-                            int64_t batch_stride, int nt, int bpt) {
+                            int64_t batch_stride, int nt, int bpt, bool s_km) {
     CUtensorMap m;
-    const cuuint64_t dims[3] = {static_cast<cuuint64_t>(n), static_cast<cuuint64_t>(k),
+    // n contiguous: tiles of [32 k][nt n] as they lie; k contiguous: tiles of [128 n][32 k], whose
+    // 128-byte rows take the 128-byte swizzle
+    const cuuint64_t dims[3] = {static_cast<cuuint64_t>(s_km ? k : n), static_cast<cuuint64_t>(s_km ? n : k),
                                 static_cast<cuuint64_t>(batches)};
     const cuuint64_t strides[2] = {static_cast<cuuint64_t>(pitch) * sizeof(float),
                                    static_cast<cuuint64_t>(batch_stride) * sizeof(float)};
-    const cuuint32_t box[3] = {static_cast<cuuint32_t>(nt), BK, static_cast<cuuint32_t>(bpt)};
+    const cuuint32_t box[3] = {s_km ? cuuint32_t(BK) : static_cast<cuuint32_t>(nt), s_km ? cuuint32_t(128) : cuuint32_t(BK),
+                               static_cast<cuuint32_t>(bpt)};
     const cuuint32_t elem[3] = {1, 1, 1};
     const CUresult rc = encode_tiled()(&m, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 3, const_cast<float*>(base), dims, strides,
-                                       box, elem, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE,
+                                       box, elem, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                                       s_km ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_NONE,
                                        CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     if (rc != CUDA_SUCCESS) {
         fail(B200_INTERNAL_ERROR, "cuTensorMapEncodeTiled (streamed operand) failed with code " + std::to_string(rc));
@@ -1620,12 +1699,18 @@ CUtensorMap make_stream_map(const float* base, int64_t n, int64_t k, int64_t pit
 }
 
 template <int BNW>
-void launch_stream(b200_ctx* ctx, bool three_pass, bool w_mn, const CUtensorMap& ms, const CUtensorMap& wh,
+void launch_stream(b200_ctx* ctx, bool three_pass, bool w_mn, bool s_km, const CUtensorMap& ms, const CUtensorMap& wh,
                    const CUtensorMap& wl, const StreamArgs& g, int grid) {
     using S = StreamSmem<BNW>;
 #define B200_STREAM_CASE(T, W)                                                                             \
+    if (three_pass == T && w_mn == W && s_km) {                                                            \
+        auto kernel = gemm_stream_kernel<BNW, T, W, true>;                                                 \
+        B200_CUDA_CHECK(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, S::kTotal)); \
+        launch_kernel(ctx, kernel, grid, kStreamThreads, S::kTotal, ms, wh, wl, g);                        \
+        return;                                                                                            \
+    }                                                                                                      \
     if (three_pass == T && w_mn == W) {                                                                    \
-        auto kernel = gemm_stream_kernel<BNW, T, W>;                                                       \
+        auto kernel = gemm_stream_kernel<BNW, T, W, false>;                                                \
         B200_CUDA_CHECK(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, S::kTotal)); \
         launch_kernel(ctx, kernel, grid, kStreamThreads, S::kTotal, ms, wh, wl, g);                        \
         return;                                                                                            \
@@ -1693,7 +1778,7 @@ void gemm_stream(b200_ctx* ctx, const GemmProblem& p, bool three_pass, const Str
         check_last_launch("matmul (operand split)");
     }
 
-    const CUtensorMap ms = make_stream_map(p.b, p.n, p.k, p.b_s[2], batches, sp.batch_stride, sp.nt, sp.bpt);
+    const CUtensorMap ms = make_stream_map(p.b, p.n, p.k, sp.pitch, batches, sp.batch_stride, sp.nt, sp.bpt, sp.s_km);
     auto map_w = [&](float* plane) {
         return ow.mn ? make_map(plane, ow.nb * ow.rows_pad, ow.cols_pad, BK, true)
                      : make_map(plane, ow.nb * ow.rows_pad, ow.cols_pad, sp.bnw, false);
@@ -1723,9 +1808,9 @@ void gemm_stream(b200_ctx* ctx, const GemmProblem& p, bool three_pass, const Str
     {
         ProfScope scope(ctx, three_pass ? "matmul.tcgen05_3xtf32_stream" : "matmul.tcgen05_tf32_stream");
         if (sp.bnw == 64) {
-            launch_stream<64>(ctx, three_pass, ow.mn, ms, wh, wl, g, grid);
+            launch_stream<64>(ctx, three_pass, ow.mn, sp.s_km, ms, wh, wl, g, grid);
         } else {
-            launch_stream<128>(ctx, three_pass, ow.mn, ms, wh, wl, g, grid);
+            launch_stream<128>(ctx, three_pass, ow.mn, sp.s_km, ms, wh, wl, g, grid);
         }
     }
     ctx->count_launch();
