@@ -632,6 +632,11 @@ def run_ops(args, local_rank):
     case("index_select rows [50000,1024][8192]", Op.INDEX_SELECT, (8192, 1024), F32,
          lambda: [dev((50000, 1024)), DeviceTensor.from_host(backend, rng.integers(0, 50000, 8192).astype(np.int64))],
          graph.axis_params(0), bytes_alg=8 * 8192 * 1024)
+    # an Embedding's backward: 8192 gradient rows added into a 50000-row table (every row of the
+    # result is written, each source row is read once)
+    case("scatter_add rows [8192,1024] -> [50000,1024]", Op.SCATTER_ADD, (50000, 1024), F32,
+         lambda: [dev((8192, 1024)), DeviceTensor.from_host(backend, rng.integers(0, 50000, 8192).astype(np.int64))],
+         graph.axis_params(0), bytes_alg=4 * 1024 * (8192 + 50000))
 
     results = []
     for name, op, out_shape, out_dtype, make_srcs, params, bytes_alg in cases:

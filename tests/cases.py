@@ -552,6 +552,21 @@ def movement_cases(seed=21, quick=False):
                graph.axis_params(0))
     src3 = rng.standard_normal((4, 7, 6)).astype(np.float32)
     yield Case("scatter_add/middle", Op.SCATTER_ADD, [src3, idx3], (4, 10, 6), DType.F32, graph.axis_params(1))
+    # long index lists (an Embedding backward): bucketed by destination on the device, several
+    # chunks of 1024 indices, one destination that takes a third of them, a strided index tensor
+    # (a generator of their own: the cases after these keep the inputs their golden outputs were made from)
+    rng2 = np.random.default_rng(seed + 1000)
+    big_idx = rng2.integers(0, 2000, 3000).astype(np.int64)
+    big_idx[rng2.random(3000) < 0.3] = 777
+    big_src = (rng2.standard_normal((3000, 32)) * 10.0 ** rng2.integers(-3, 4, (3000, 1))).astype(np.float32)
+    yield Case("scatter_add/embedding-backward", Op.SCATTER_ADD, [big_src, big_idx], (2000, 32), DType.F32,
+               graph.axis_params(0))
+    yield Case("scatter_add/embedding-backward-strided-index", Op.SCATTER_ADD,
+               [big_src, np.repeat(big_idx, 3)[::3]], (2000, 32), DType.F32, graph.axis_params(0))
+    mid_idx = rng2.integers(0, 1000, 2500).astype(np.int64)
+    mid_src = rng2.standard_normal((4, 2500, 16)).astype(np.float32)
+    yield Case("scatter_add/long-middle", Op.SCATTER_ADD, [mid_src, mid_idx], (4, 1000, 16), DType.F32,
+               graph.axis_params(1))
     yield Case("scatter_add/empty", Op.SCATTER_ADD, [np.zeros((0, 16), np.float32), np.zeros((0,), np.int64)],
                (5, 16), DType.F32, graph.axis_params(0))
     # cat / slice_backward

@@ -402,6 +402,28 @@ def test_device_copies(backend):
     assert z.data == 0 and z.nbytes == 0
 
 
+def test_large_uploads_from_pageable_memory_arrive_intact(backend):
+    """copy_from_host of pageable memory above a few MB is staged through pinned slots by several
+    threads: sizes that are not a multiple of the chunk, sources that change between calls (every
+    slot is reused), the source overwritten as soon as the call returns, and a kernel queued
+    right behind the copy -- the bytes on the device are the bytes that were passed."""
+    from vkml_b200 import DeviceTensor, NodeDesc
+    rng = np.random.default_rng(17)
+    for n in (3_000_001, 8_400_000 // 4, 40_000_003):
+        dev = DeviceTensor.empty(backend, (1, 1, 1, n))
+        out = DeviceTensor.empty(backend, (1, 1, 1, n))
+        for _ in range(3):
+            src = rng.standard_normal(n).astype(np.float32)
+            want = src.copy()
+            backend.copy_from_host(dev.storage, 0, src)
+            src[:] = -1.0                                   # the call has returned: the source is the caller's again
+            backend.compute([NodeDesc(Op.NEG, out.desc, [dev.desc])])
+            assert np.array_equal(out.numpy().ravel(), -want)
+            back = np.empty(n, np.float32)
+            backend.copy_to_host(back, dev.storage, 0)
+            assert np.array_equal(back, want)
+
+
 def test_profiling_stats_timer_and_pinned_memory(backend):
     """The auxiliary ABI: per-launch device times, counters, the stream stopwatch, page-locked buffers."""
     from vkml_b200 import DeviceTensor, NodeDesc

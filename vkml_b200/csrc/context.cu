@@ -5,6 +5,7 @@
 #include <algorithm>
 #include <cstdlib>
 #include <new>
+#include <thread>
 
 namespace b200 {
 
@@ -589,6 +590,10 @@ int b200_create(int cuda_ordinal, b200_ctx** out) {
         if (const char* e = std::getenv("VKML_B200_FUSE")) {
             ctx->fuse = std::atoi(e) != 0;
         }
+        ctx->upload_threads = std::max(2, std::min(8, static_cast<int>(std::thread::hardware_concurrency()) / 2));
+        if (const char* e = std::getenv("VKML_B200_UPLOAD_THREADS")) {
+            ctx->upload_threads = std::max(0, std::min(16, std::atoi(e)));
+        }
         if (const char* e = std::getenv("VKML_B200_PDL")) {
             ctx->pdl = std::atoi(e) != 0;
         }
@@ -626,12 +631,12 @@ void b200_destroy(b200_ctx* ctx) {
     if (ctx == nullptr) return;
     cudaSetDevice(ctx->device);
     if (ctx->stream != nullptr) cudaStreamSynchronize(ctx->stream);
+    destroy_uploader(ctx);
     dist_destroy(ctx);
     if (ctx->stream != nullptr) cudaStreamDestroy(ctx->stream);
     if (ctx->d_status != nullptr) cudaFree(ctx->d_status);
     if (ctx->d_counters != nullptr) cudaFree(ctx->d_counters);
     if (ctx->h_status != nullptr) cudaFreeHost(ctx->h_status);
-    if (ctx->staging != nullptr) cudaFreeHost(ctx->staging);
     for (cudaEvent_t ev : ctx->event_pool) cudaEventDestroy(ev);
     if (ctx->timer_begin != nullptr) cudaEventDestroy(ctx->timer_begin);
     if (ctx->timer_end != nullptr) cudaEventDestroy(ctx->timer_end);
@@ -954,10 +959,14 @@ int b200_copy_from_host(b200_ctx* ctx, void* dst_device, const void* src_host, s
         // the caller may reuse `src_host` immediately; pinned memory is read
         // asynchronously, in stream order.
         dist_wait_range(ctx, dst_device, static_cast<const char*>(dst_device) + nbytes);
-        B200_CUDA_CHECK(cudaMemcpyAsync(dst_device, src_host, nbytes, cudaMemcpyHostToDevice, ctx->stream));
         cudaPointerAttributes attr{};
         const cudaError_t e = cudaPointerGetAttributes(&attr, src_host);
         if (e != cudaSuccess) cudaGetLastError();
+        const bool pageable = e != cudaSuccess || attr.type == cudaMemoryTypeUnregistered;
+        if (pageable && staged_upload(ctx, dst_device, src_host, nbytes)) {
+            return;  // large and pageable: staged by several threads, `src_host` has been read
+        }
+        B200_CUDA_CHECK(cudaMemcpyAsync(dst_device, src_host, nbytes, cudaMemcpyHostToDevice, ctx->stream));
         if (e == cudaSuccess && attr.type == cudaMemoryTypeHost) {
             // pinned source: the copy is truly asynchronous; wait so the
             // "caller may reuse the buffer" contract of copy_from_host holds

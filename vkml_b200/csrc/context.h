@@ -86,6 +86,10 @@ struct PlaneEntry {
 
 }  // namespace b200
 
+namespace b200 {
+class Uploader;
+}
+
 struct b200_ctx {
     int device = 0;
     cudaStream_t stream = nullptr;
@@ -105,9 +109,10 @@ struct b200_ctx {
     void* workspace = nullptr;
     size_t workspace_bytes = 0;
 
-    // Pinned staging for host copies.
-    void* staging = nullptr;
-    size_t staging_bytes = 0;
+    // Uploads from pageable host memory, staged through pinned slots by a few threads (upload.cu).
+    // VKML_B200_UPLOAD_THREADS: 0 or 1 leave such copies to the runtime's own single-threaded staging.
+    b200::Uploader* uploader = nullptr;
+    int upload_threads = 4;  // set from the host's core count at creation (2..8)
 
     int gemm_precision = B200_GEMM_3XTF32;
     // VKML_B200_GEMM_SCHEDULE: how the persistent GEMM's CTAs get their tiles. -1 (auto): a fixed
@@ -210,6 +215,9 @@ void dist_destroy(b200_ctx* ctx);
 void dist_after_node(b200_ctx* ctx, const b200_node& node);  // all-reduce a registered gradient once its producer is queued
 void dist_all_reduce_now(b200_ctx* ctx, void* data, size_t count);  // average across ranks on the comm stream
 void dist_join(b200_ctx* ctx);                                // make the compute stream wait for outstanding all-reduces
+// upload.cu: true when the copy was served by the threaded staging (src is reusable on return)
+bool staged_upload(b200_ctx* ctx, void* dst, const void* src, size_t nbytes);
+void destroy_uploader(b200_ctx* ctx);
 void dist_wait_range(b200_ctx* ctx, const void* lo, const void* hi);  // ... for those touching [lo, hi) (nullptr: all)
 int dist_pending_index(const b200_ctx* ctx, const void* lo, const void* hi);
 bool dist_has_pending(const b200_ctx* ctx);

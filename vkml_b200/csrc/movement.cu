@@ -752,6 +752,207 @@ scatter_add_kernel(float* __restrict__ out, const float* __restrict__ src, const
     }
 }
 
+// ---- scatter_add for long index lists -------------------------------------
+// The pull form above reads every index for every output element: exact, in the reference's
+// order, and O(outputs x indices) -- an Embedding backward over a 50 000-row table with 8192
+// indices would be 4e11 index reads.  Here the indices are bucketed by destination first:
+//   1. count the sources of every destination,
+//   2. exclusive scan -> where each destination's list starts,
+//   3. place every k into its destination's list AT ITS RANK among the earlier k with the same
+//      destination, so every list is in ascending k: the rank inside a chunk of 512 indices comes
+//      from comparing the chunk's indices in shared memory (all chunks in parallel), the rank
+//      before the chunk from a per-destination cursor that one block advances chunk by chunk,
+//   4. every output element adds the sources of its list in list order.
+// Same sums in the same order as the pull form, bit for bit; each source element is read once.
+constexpr int kScatterChunk = 512;
+
+__global__ void __launch_bounds__(kThreads)
+scatter_count_kernel(int* __restrict__ count, const int64_t* __restrict__ idx, int64_t idx_stride, int n,
+                     int64_t extent) {
+    pdl_prologue();
+    const int k = blockIdx.x * blockDim.x + threadIdx.x;
+    if (k < n) {
+        const int64_t t = idx[k * idx_stride];
+        if (t >= 0 && t < extent) {
+            atomicAdd(count + t, 1);  // integer counts: the result does not depend on the order
+        }
+    }
+}
+
+// One block: offsets[j] = number of sources of destinations < j; offsets[extent] = their total.
+// cursor[j] starts as a copy of offsets[j].  Eight consecutive destinations per thread and step.
+__global__ void __launch_bounds__(1024)
+scatter_scan_kernel(int* __restrict__ offsets, int* __restrict__ cursor, const int* __restrict__ count, int extent) {
+    pdl_prologue();
+    constexpr int PER = 8;
+    __shared__ int warp_sums[32];
+    __shared__ int carry;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    if (threadIdx.x == 0) carry = 0;
+    __syncthreads();
+    for (int base = 0; base < extent; base += 1024 * PER) {
+        const int j0 = base + threadIdx.x * PER;
+        int c[PER];
+        int mine = 0;
+#pragma unroll
+        for (int u = 0; u < PER; ++u) {
+            c[u] = j0 + u < extent ? count[j0 + u] : 0;
+            mine += c[u];
+        }
+        int incl = mine;
+#pragma unroll
+        for (int d = 1; d < 32; d <<= 1) {
+            const int up = __shfl_up_sync(0xffffffffU, incl, d);
+            if (lane >= d) incl += up;
+        }
+        if (lane == 31) warp_sums[warp] = incl;
+        __syncthreads();
+        if (warp == 0) {
+            int w = warp_sums[lane];
+#pragma unroll
+            for (int d = 1; d < 32; d <<= 1) {
+                const int up = __shfl_up_sync(0xffffffffU, w, d);
+                if (lane >= d) w += up;
+            }
+            warp_sums[lane] = w;  // inclusive over the warps
+        }
+        __syncthreads();
+        int before = carry + (warp > 0 ? warp_sums[warp - 1] : 0) + incl - mine;
+        const int block_total = warp_sums[31];
+#pragma unroll
+        for (int u = 0; u < PER; ++u) {
+            if (j0 + u < extent) {
+                offsets[j0 + u] = before;
+                cursor[j0 + u] = before;
+            }
+            before += c[u];
+        }
+        __syncthreads();
+        if (threadIdx.x == 0) carry += block_total;
+        __syncthreads();
+    }
+    if (threadIdx.x == 0) offsets[extent] = carry;
+}
+
+// rank[k] = how many EARLIER indices of k's chunk have k's destination, bit 30 set when no LATER
+// index of the chunk has it; -1 for an index out of range.  All chunks at once.
+__global__ void __launch_bounds__(kScatterChunk)
+scatter_rank_kernel(int* __restrict__ rank, const int64_t* __restrict__ idx, int64_t idx_stride, int n,
+                    int64_t extent) {
+    pdl_prologue();
+    __shared__ int keys[kScatterChunk];
+    const int k = blockIdx.x * kScatterChunk + threadIdx.x;
+    int key = -1;
+    if (k < n) {
+        const int64_t t = idx[k * idx_stride];
+        if (t >= 0 && t < extent) key = static_cast<int>(t);
+    }
+    keys[threadIdx.x] = key;
+    __syncthreads();
+    if (k >= n) return;
+    int before = 0, later = 0;
+    if (key >= 0) {
+        const int me = static_cast<int>(threadIdx.x);
+#pragma unroll 8
+        for (int t = 0; t < kScatterChunk; ++t) {
+            const int same = keys[t] == key;   // every lane reads the same word: a broadcast
+            before += same & (t < me);
+            later |= same & (t > me);
+        }
+    }
+    rank[k] = key < 0 ? -1 : (before | (later ? 0 : (1 << 30)));
+}
+
+// One block walks the chunks in order: an index goes to its destination's cursor plus its rank
+// inside the chunk, and the chunk's last index of a destination moves that cursor on.
+__global__ void __launch_bounds__(kScatterChunk)
+scatter_place_kernel(int* __restrict__ perm, int* __restrict__ cursor, const int* __restrict__ rank,
+                     const int64_t* __restrict__ idx, int64_t idx_stride, int n) {
+    pdl_prologue();
+    for (int k0 = 0; k0 < n; k0 += kScatterChunk) {
+        const int k = k0 + static_cast<int>(threadIdx.x);
+        const int r = k < n ? rank[k] : -1;
+        int64_t key = 0;
+        int start = 0;
+        if (r >= 0) {
+            key = idx[k * idx_stride];
+            start = __ldcg(cursor + key);  // written by this block's earlier steps only
+        }
+        __syncthreads();
+        if (r >= 0) {
+            const int pos = start + (r & ((1 << 30) - 1));
+            perm[pos] = k;
+            if (r >> 30) __stcg(cursor + key, pos + 1);
+        }
+        __syncthreads();
+    }
+}
+
+template <typename I>
+__global__ void __launch_bounds__(kThreads)
+scatter_gather_kernel(float* __restrict__ out, const float* __restrict__ src, const int* __restrict__ perm,
+                      const int* __restrict__ offsets, GeoT<I> gsrc, I inner, I src_extent, I out_extent, I total) {
+    pdl_prologue();
+    const int64_t stride = int64_t(gridDim.x) * blockDim.x;
+    for (int64_t li = int64_t(blockIdx.x) * blockDim.x + threadIdx.x; li < int64_t(total); li += stride) {
+        const I i = static_cast<I>(li);
+        const I q = i / inner;
+        const I rest = i - q * inner;
+        const I outer = q / out_extent;
+        const I j = q - outer * out_extent;
+        const int t0 = offsets[j], t1 = offsets[j + 1];
+        float acc = 0.0F;
+        for (int t = t0; t < t1; ++t) {
+            acc += src[geo_off<I>(gsrc, (outer * src_extent + static_cast<I>(perm[t])) * inner + rest)];
+        }
+        out[i] = acc;
+    }
+}
+
+// Dense source, rows of 16-byte multiples: four adjacent elements per thread and four such items
+// in flight, so the (list bounds -> source index -> source row) chains of different items overlap.
+__global__ void __launch_bounds__(kThreads)
+scatter_gather4_kernel(float4* __restrict__ out, const float4* __restrict__ src, const int* __restrict__ perm,
+                       const int* __restrict__ offsets, FastDiv div_inner4, FastDiv div_extent, unsigned src_extent,
+                       unsigned total4) {
+    pdl_prologue();
+    constexpr int U = 4;
+    const int64_t stride = int64_t(gridDim.x) * blockDim.x;
+    const unsigned inner4 = div_inner4.d;
+    for (int64_t base = int64_t(blockIdx.x) * blockDim.x + threadIdx.x; base < int64_t(total4); base += U * stride) {
+        int t0[U], t1[U];
+        uint32_t outer[U], rest[U];
+#pragma unroll
+        for (int u = 0; u < U; ++u) {
+            const int64_t li = base + u * stride;
+            t0[u] = t1[u] = 0;
+            outer[u] = rest[u] = 0;
+            if (li < int64_t(total4)) {
+                uint32_t q, j;
+                div_inner4.divmod(static_cast<uint32_t>(li), q, rest[u]);
+                div_extent.divmod(q, outer[u], j);
+                t0[u] = offsets[j];
+                t1[u] = offsets[j + 1];
+            }
+        }
+#pragma unroll
+        for (int u = 0; u < U; ++u) {
+            const int64_t li = base + u * stride;
+            if (li < int64_t(total4)) {
+                float4 acc = make_float4(0.0F, 0.0F, 0.0F, 0.0F);
+                for (int t = t0[u]; t < t1[u]; ++t) {
+                    const float4 v = src[(int64_t(outer[u]) * src_extent + perm[t]) * inner4 + rest[u]];
+                    acc.x += v.x;
+                    acc.y += v.y;
+                    acc.z += v.z;
+                    acc.w += v.w;
+                }
+                out[li] = acc;
+            }
+        }
+    }
+}
+
 // Flags any index outside [0, extent): scatter_add's pull form would otherwise
 // just never match it.
 __global__ void __launch_bounds__(kThreads)
@@ -1132,7 +1333,38 @@ void launch_movement(b200_ctx* ctx, const b200_node& node) {
             const unsigned grid = grid_for(total, kThreads);
             const float* sp = reinterpret_cast<const float*>(src.data);
             const bool small = total < kMax32 && fits32(src) && istride >= 0 && istride * std::max<int64_t>(n_idx, 1) < kMax32;
-            if (small) {
+            const int64_t extent = out.dim[axis];
+            if (n_idx >= 64 && n_idx < (int64_t(1) << 30) && extent < (int64_t(1) << 30) &&
+                double(total) * double(n_idx) >= 1e8) {
+                // bucket the indices by destination first (see above): five small launches and the gather
+                const size_t ints = static_cast<size_t>(3 * extent + 1 + 2 * n_idx);
+                int* count = static_cast<int*>(ctx->ensure_workspace(ints * sizeof(int) + 16));
+                int* offsets = count + extent;  // extent + 1 entries
+                int* cursor = offsets + extent + 1;
+                int* perm = cursor + extent;
+                int* rank = perm + n_idx;
+                B200_CUDA_CHECK(cudaMemsetAsync(count, 0, static_cast<size_t>(extent) * sizeof(int), ctx->stream));
+                const int n = static_cast<int>(n_idx);
+                launch_kernel(ctx, scatter_count_kernel, static_cast<unsigned>(ceil_div(n_idx, kThreads)), kThreads, 0, count, ip, istride, n, extent);
+                launch_kernel(ctx, scatter_scan_kernel, 1u, 1024, 0, offsets, cursor, static_cast<const int*>(count), static_cast<int>(extent));
+                launch_kernel(ctx, scatter_rank_kernel, static_cast<unsigned>(ceil_div(n_idx, kScatterChunk)), kScatterChunk, 0, rank, ip, istride, n, extent);
+                launch_kernel(ctx, scatter_place_kernel, 1u, kScatterChunk, 0, perm, cursor, static_cast<const int*>(rank), ip, istride, n);
+                ctx->count_launch(4);
+                if (src.contiguous && inner % 4 == 0 && total / 4 < kMax32 && reinterpret_cast<uintptr_t>(sp) % 16 == 0 &&
+                    reinterpret_cast<uintptr_t>(o) % 16 == 0) {
+                    const unsigned total4 = static_cast<unsigned>(total / 4);
+                    launch_kernel(ctx, scatter_gather4_kernel, grid_for(ceil_div(int64_t(total4), 4), kThreads), kThreads, 0, reinterpret_cast<float4*>(o),
+                                  reinterpret_cast<const float4*>(sp), static_cast<const int*>(perm), static_cast<const int*>(offsets),
+                                  FastDiv(static_cast<uint32_t>(inner / 4)), FastDiv(static_cast<uint32_t>(extent)),
+                                  static_cast<unsigned>(n_idx), total4);
+                } else if (small) {
+                    launch_kernel(ctx, scatter_gather_kernel<uint32_t>, grid, kThreads, 0, o, sp, static_cast<const int*>(perm), static_cast<const int*>(offsets),
+                        geo_t<uint32_t>(src), static_cast<uint32_t>(inner), static_cast<uint32_t>(n_idx), static_cast<uint32_t>(extent), static_cast<uint32_t>(total));
+                } else {
+                    launch_kernel(ctx, scatter_gather_kernel<int64_t>, grid, kThreads, 0, o, sp, static_cast<const int*>(perm), static_cast<const int*>(offsets),
+                        geo_t<int64_t>(src), inner, n_idx, extent, total);
+                }
+            } else if (small) {
                 launch_kernel(ctx, scatter_add_kernel<uint32_t>, grid, kThreads, 0, o, sp, ip, geo_t<uint32_t>(src), static_cast<uint32_t>(istride), static_cast<uint32_t>(inner),
                     static_cast<uint32_t>(n_idx), static_cast<uint32_t>(out.dim[axis]), static_cast<uint32_t>(total));
             } else {
