@@ -886,7 +886,12 @@ int b200_compute(b200_ctx* ctx, const b200_node* nodes, size_t n_nodes, uint32_t
         // reads 4 bytes where it would have read the tensor (ReLU's backward mask compares against,
         // and its `where` selects from, activation-sized tensors of zeros).
         std::map<const void*, size_t> constants;
+        std::vector<char> done(exec.size(), 0);  // served ahead of its turn by a grouped launch
         for (size_t p = 0; p < exec.size();) {
+            if (done[p]) {
+                ++p;
+                continue;
+            }
             const size_t i = exec[p];
             const b200_node& node = nodes[i];
             if (ctx->fuse && exec.size() - p >= 2 &&
@@ -914,6 +919,36 @@ int b200_compute(b200_ctx* ctx, const b200_node* nodes, size_t n_nodes, uint32_t
                         }
                         p += taken;
                         continue;
+                    }
+                }
+            }
+            if (ctx->fuse && node.op == B200_OP_SCALED_ADD && exec.size() - p >= 2 && !grad_sync) {
+                // the optimiser's spans: independent scaled_add nodes, one launch for the dense ones among
+                // the next 24 nodes (a transposed gradient in between keeps its own kernel)
+                constexpr size_t kLook = 24;
+                const size_t avail = std::min<size_t>(exec.size() - p, kLook);
+                const b200_node* seq[kLook];
+                bool picked[kLook];
+                size_t run = 0;
+                while (run < avail && !done[p + run]) {
+                    seq[run] = &nodes[exec[p + run]];
+                    ++run;
+                }
+                if (run >= 2) {
+                    for (size_t k = 0; k < run; ++k) prepare(exec[p + k]);
+                    ctx->current_op = node.op;
+                    if (launch_scaled_add_group(ctx, seq, run, picked) > 0) {
+                        for (size_t k = 0; k < run; ++k) {
+                            if (picked[k]) {
+                                constants.erase(seq[k]->out.data);
+                                finish(exec[p + k]);
+                                done[p + k] = 1;
+                            }
+                        }
+                        if (done[p]) {
+                            ++p;
+                            continue;
+                        }
                     }
                 }
             }

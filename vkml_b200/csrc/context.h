@@ -209,6 +209,7 @@ bool supports_node(const b200_node& node);
 // fuse.cu: serves the head of `seq` (the span's remaining computed nodes, in execution order)
 // with one fused launch if it matches a known pattern; returns how many nodes it covered, or 0.
 size_t launch_fused(b200_ctx* ctx, const b200_node* const* seq, size_t avail);
+size_t launch_scaled_add_group(b200_ctx* ctx, const b200_node* const* seq, size_t avail, bool* picked);
 
 // dist.cu
 void dist_destroy(b200_ctx* ctx);

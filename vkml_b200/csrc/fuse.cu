@@ -377,6 +377,147 @@ size_t fuse_lsm_backward(b200_ctx* ctx, const b200_node* const* seq, size_t avai
 
 }  // namespace
 
+namespace {
+
+// ---------------------------------------------------------------------------
+// scaled_add over several tensors: the optimiser's spans
+// ---------------------------------------------------------------------------
+// An optimiser step reaches the backend as spans of nothing but scaled_add nodes, one per parameter
+// tensor (python/vkml/optim.py: the velocity update of every parameter in one span, the parameter
+// update in the next).  The nodes are independent, so one launch serves them all: every block takes
+// one 4096-element tile of one tensor.  Same arithmetic as the single-tensor kernel (two rounded
+// products, one rounded sum).
+constexpr int kGroupTensors = 16;
+constexpr int kGroupTile = 4096;
+
+struct ScaledAddGroup {
+    float* out[kGroupTensors];
+    const float* a[kGroupTensors];
+    const float* b[kGroupTensors];
+    int64_t count[kGroupTensors];
+    float alpha[kGroupTensors], beta[kGroupTensors];
+    uint32_t first_block[kGroupTensors + 1];
+    uint32_t vec_mask;  // bit t: tensor t may be walked in 16-byte quads
+    int n;
+};
+
+__global__ void __launch_bounds__(kThreads) scaled_add_group_kernel(const __grid_constant__ ScaledAddGroup g) {
+    pdl_prologue();
+    int t = 0;
+    while (t + 1 < g.n && blockIdx.x >= g.first_block[t + 1]) ++t;
+    const int64_t base = int64_t(blockIdx.x - g.first_block[t]) * kGroupTile;
+    const int64_t count = g.count[t];
+    const float alpha = g.alpha[t], beta = g.beta[t];
+    if ((g.vec_mask >> t) & 1u) {
+        const float4* __restrict__ a = reinterpret_cast<const float4*>(g.a[t] + base);
+        const float4* __restrict__ b = reinterpret_cast<const float4*>(g.b[t] + base);
+        float4* __restrict__ o = reinterpret_cast<float4*>(g.out[t] + base);
+        const int quads = static_cast<int>(min(int64_t(kGroupTile), count - base) / 4);
+        float4 x[4], y[4];
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+            const int q = threadIdx.x + u * kThreads;
+            if (q < quads) {
+                x[u] = a[q];
+                y[u] = b[q];
+            }
+        }
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+            const int q = threadIdx.x + u * kThreads;
+            if (q < quads) {
+                float4 r;
+                r.x = __fadd_rn(__fmul_rn(x[u].x, alpha), __fmul_rn(y[u].x, beta));
+                r.y = __fadd_rn(__fmul_rn(x[u].y, alpha), __fmul_rn(y[u].y, beta));
+                r.z = __fadd_rn(__fmul_rn(x[u].z, alpha), __fmul_rn(y[u].z, beta));
+                r.w = __fadd_rn(__fmul_rn(x[u].w, alpha), __fmul_rn(y[u].w, beta));
+                o[q] = r;
+            }
+        }
+    } else {
+        const int n = static_cast<int>(min(int64_t(kGroupTile), count - base));
+        for (int i = threadIdx.x; i < n; i += kThreads) {
+            g.out[t][base + i] = __fadd_rn(__fmul_rn(g.a[t][base + i], alpha), __fmul_rn(g.b[t][base + i], beta));
+        }
+    }
+}
+
+bool overlaps(const void* p, size_t pn, const void* q, size_t qn) {
+    const char* a = static_cast<const char*>(p);
+    const char* b = static_cast<const char*>(q);
+    return a < b + qn && b < a + pn;
+}
+
+}  // namespace
+
+// `seq`: the next nodes of a span in execution order, the first a scaled_add.  Picks the scaled_add
+// nodes over dense f32 tensors among them that are independent of every other node of `seq` up to
+// the last one picked (none writes what another reads or writes, so running them first changes
+// nothing), marks them in `picked` and serves them with one launch.  Returns how many it served
+// (0: fewer than two qualified).
+size_t launch_scaled_add_group(b200_ctx* ctx, const b200_node* const* seq, size_t avail, bool* picked) {
+    ScaledAddGroup g{};
+    uint64_t blocks = 0;
+    size_t n = 0;
+    auto bytes_of = [](const b200_tensor& t) {
+        // the span of addresses the tensor can touch (strided views included)
+        int64_t hi = static_cast<int64_t>(dtype_size(t.dtype));
+        for (int d = 0; d < t.ndim; ++d) {
+            if (t.dims[d] > 1) hi += (t.dims[d] - 1) * std::abs(t.strides[d]);
+        }
+        return static_cast<size_t>(hi);
+    };
+    auto independent = [&](const b200_node& x, const b200_node& y) {
+        // x and y may run in either order: neither writes what the other reads or writes
+        for (uint32_t s = 0; s < y.n_src && s < B200_MAX_SRC; ++s) {
+            if (y.src[s].data != nullptr && overlaps(x.out.data, bytes_of(x.out), y.src[s].data, bytes_of(y.src[s]))) return false;
+        }
+        for (uint32_t s = 0; s < x.n_src && s < B200_MAX_SRC; ++s) {
+            if (x.src[s].data != nullptr && overlaps(y.out.data, bytes_of(y.out), x.src[s].data, bytes_of(x.src[s]))) return false;
+        }
+        return !overlaps(x.out.data, bytes_of(x.out), y.out.data, bytes_of(y.out));
+    };
+    for (size_t k = 0; k < avail; ++k) picked[k] = false;
+    for (size_t k = 0; k < avail && n < static_cast<size_t>(kGroupTensors); ++k) {
+        const b200_node& node = *seq[k];
+        if (node.op != B200_OP_SCALED_ADD || node.n_src != 2) continue;
+        const b200_tensor& o = node.out;
+        bool ok = o.dtype == B200_F32 && dense_tensor(o) && o.data != nullptr;
+        for (int s = 0; s < 2 && ok; ++s) {
+            ok = node.src[s].dtype == B200_F32 && same_shape(node.src[s], o) && dense_tensor(node.src[s]) &&
+                 node.src[s].data != nullptr;
+        }
+        for (int d = 0; d < o.ndim && ok; ++d) ok = o.strides[d] >= 0;
+        for (size_t e = 0; e < k && ok; ++e) ok = independent(node, *seq[e]);  // members and the nodes it jumps over
+        const int64_t count = numel_of(o);
+        ok = ok && blocks + static_cast<uint64_t>((count + kGroupTile - 1) / kGroupTile) < (uint64_t(1) << 31);
+        if (!ok) continue;
+        const ScaledAddParams prm = get_params<ScaledAddParams>(node);
+        g.out[n] = static_cast<float*>(o.data);
+        g.a[n] = static_cast<const float*>(node.src[0].data);
+        g.b[n] = static_cast<const float*>(node.src[1].data);
+        g.count[n] = count;
+        g.alpha[n] = prm.alpha;
+        g.beta[n] = prm.beta;
+        g.first_block[n] = static_cast<uint32_t>(blocks);
+        if (count % 4 == 0 && aligned16(g.out[n]) && aligned16(g.a[n]) && aligned16(g.b[n])) g.vec_mask |= 1u << n;
+        blocks += static_cast<uint64_t>((count + kGroupTile - 1) / kGroupTile);
+        picked[k] = true;
+        ++n;
+    }
+    if (n < 2) {
+        for (size_t k = 0; k < avail; ++k) picked[k] = false;
+        return 0;
+    }
+    g.first_block[n] = static_cast<uint32_t>(blocks);
+    g.n = static_cast<int>(n);
+    ProfScope scope(ctx, "fused.scaled_add_group");
+    launch_kernel(ctx, scaled_add_group_kernel, static_cast<unsigned>(blocks), kThreads, 0, g);
+    ctx->count_launch();
+    check_last_launch("fused scaled_add group");
+    return n;
+}
+
 // Tries every pattern at the head of `seq` (the span's remaining computed nodes, in execution
 // order); returns how many nodes one fused launch served, or 0.
 size_t launch_fused(b200_ctx* ctx, const b200_node* const* seq, size_t avail) {
