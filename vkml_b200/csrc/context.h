@@ -124,8 +124,9 @@ struct b200_ctx {
     // = the GEMM kernel reads fp32 operands and splits them on the way into shared memory; auto (-1).
     int gemm_operands = -1;
     // VKML_B200_GEMM_STREAM: the streamed-operand kernel for products bound by HBM (a small left
-    // operand, a large right one read exactly once).  auto (-1): wherever the layout allows it and
-    // no other operand scheme was asked for by name; 0 / 1: never / wherever the layout allows.
+    // operand or a short K, the large right operand read exactly once).  auto (-1): such products,
+    // where the layout allows it and no other operand scheme was asked for by name; 0: never; 1:
+    // every product whose layout allows it, whatever its size (A/B runs).
     int gemm_stream = -1;
     int gemm_group_m = 0;      // VKML_B200_GEMM_GROUP_M: M-tiles per L2 group of the tile walk (0: the built-in 16)
     int gemm_bn_override = 0;  // VKML_B200_GEMM_BN: force the N extent of the tensor-core tile (tuning aid)

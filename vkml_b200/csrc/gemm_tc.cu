@@ -1640,7 +1640,8 @@ StreamPlan plan_stream(const b200_ctx* ctx, const GemmProblem& p) {
         return sp;  // switched off, or another operand scheme was asked for by name
     }
     const int64_t batches = p.b0 * p.b1;
-    if ((p.m > 256 && (p.k > 256 || p.m > 4096)) || p.n < 32 || batches < 1) return sp;
+    // (VKML_B200_GEMM_STREAM=1 lifts the size rule: every product whose layout allows it, for A/B runs)
+    if ((ctx->gemm_stream < 1 && p.m > 256 && (p.k > 256 || p.m > 4096)) || p.n < 32 || batches < 1) return sp;
     if (p.b_s[3] == 1 && p.b_s[2] % 4 == 0 && p.b_s[2] >= p.n) {
         sp.s_km = false;
         sp.pitch = p.b_s[2];
