@@ -12,7 +12,10 @@ a fixed seed) after the last step -- they depend on every gradient and on the op
 The problems are the seeded ones of tests/training.py, so the GPU side regenerates the
 same inputs instead of storing them.
 
-Run from the repository root:  python tests/golden/make_full_size_steps.py [cnn] [mlp]
+  mlp1_*  the same MLP, ONE step on a problem of its own (half the time), stored in a file of its
+          own, full_size_steps_mlp1.npz, so that it can be generated beside the two-step run.
+
+Run from the repository root:  python tests/golden/make_full_size_steps.py [cnn] [mlp] [mlp1]
 """
 import os
 import sys
@@ -27,6 +30,7 @@ sys.path.insert(0, os.path.dirname(os.path.dirname(HERE)))
 import training  # noqa: E402
 
 OUT = os.path.join(HERE, "full_size_steps.npz")
+OUT_MLP1 = os.path.join(HERE, "full_size_steps_mlp1.npz")
 SAMPLE = 4096
 SAMPLE_SEED = 20260730
 
@@ -61,6 +65,13 @@ def main():
         out.update(mlp_losses=losses, mlp_positions=pos, mlp_weights=w[pos], mlp_biases=b)
         print(f"mlp: losses {losses} in {time.time() - t0:.0f} s", flush=True)
         np.savez(OUT, **out)
+    if "mlp1" in which:
+        t0 = time.time()
+        ws, bs, x, y = training.mlp_problem(MLP_WIDTHS, MLP_BATCH, 1, data="normal")
+        losses, w, b = training.train_mlp(lib, training.CPU, MLP_WIDTHS, ws, bs, x, y, MLP_BATCH, 1, lr=MLP_LR)
+        pos = sample_positions(w.size)
+        print(f"mlp1: losses {losses} in {time.time() - t0:.0f} s", flush=True)
+        np.savez(OUT_MLP1, mlp1_losses=losses, mlp1_positions=pos, mlp1_weights=w[pos], mlp1_biases=b)
 
 
 if __name__ == "__main__":

@@ -305,3 +305,21 @@ def test_full_size_wide_mlp_steps(lib):
     assert rel(losses, fx["mlp_losses"]) < 1e-4
     np.testing.assert_allclose(w[fx["mlp_positions"]], fx["mlp_weights"], rtol=0, atol=1e-4)
     np.testing.assert_allclose(b, fx["mlp_biases"], rtol=0, atol=1e-4)
+
+
+def test_full_size_wide_mlp_one_step(lib):
+    """The same configuration, one step on a problem of its own: the loss checks the forward pass, the
+    sampled weights and every bias after the update check every gradient and the optimiser."""
+    import make_full_size_steps as gen
+    if not os.path.exists(gen.OUT_MLP1):
+        pytest.skip("the one-step wide-MLP fixture has not been generated")
+    fx = np.load(gen.OUT_MLP1)
+    ws, bs, x, y = training.mlp_problem(gen.MLP_WIDTHS, gen.MLP_BATCH, 1, data="normal")
+    losses, w, b = training.train_mlp(lib, training.B200, gen.MLP_WIDTHS, ws, bs, x, y, gen.MLP_BATCH, 1, lr=gen.MLP_LR)
+    record(test="full_size_wide_mlp_one_step", gpu_losses=[float(v) for v in losses],
+           cpu_losses=[float(v) for v in fx["mlp1_losses"]],
+           weights_max_abs=float(np.max(np.abs(w[fx["mlp1_positions"]] - fx["mlp1_weights"]))),
+           biases_max_abs=float(np.max(np.abs(b - fx["mlp1_biases"]))))
+    assert rel(losses, fx["mlp1_losses"]) < 1e-4
+    np.testing.assert_allclose(w[fx["mlp1_positions"]], fx["mlp1_weights"], rtol=0, atol=1e-4)
+    np.testing.assert_allclose(b, fx["mlp1_biases"], rtol=0, atol=1e-4)

@@ -19,8 +19,8 @@ namespace b200 {
 
 class Uploader {
 public:
-    static constexpr size_t kChunk = size_t(2) << 20;
-    static constexpr int kSlotsPerThread = 3;
+    static constexpr size_t kChunk = size_t(1) << 20;
+    static constexpr int kSlotsPerThread = 4;
 
     Uploader(int device, cudaStream_t stream, int threads)
         : device_(device), stream_(stream), threads_(threads), slots_(static_cast<size_t>(threads) * kSlotsPerThread) {
