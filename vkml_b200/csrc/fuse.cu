@@ -15,9 +15,12 @@
 //   * one-hot mask of cross_entropy:  equal(labels, arange)  cast(bool->f32)  mul(w, mask)
 //     (src/api/ops.cpp:347-354,417-441);
 //   * backward of log_softmax:  exp(l)  sum(g, axis=-1, keepdim)  mul(exp, sum)  sub(g, mul)
-//     (src/autograd/autograd.cpp:528-546), one block per row.
+//     (src/autograd/autograd.cpp:528-546), one block per row;
+//   * the optimiser's spans: independent scaled_add nodes, one per parameter tensor
+//     (python/vkml/optim.py), served by one multi-tensor launch.
 //
-// A group is taken only when its nodes are consecutive in execution order, every operand has the
+// A group is taken only when its nodes are consecutive in execution order (the scaled_add group
+// may jump over nodes it is independent of), every operand has the
 // layout the kernel reads (dense outputs, a bias that is one contiguous vector), and none of its
 // members is a gradient that a data-parallel span all-reduces.  VKML_B200_FUSE=0 turns it off.
 #include "context.h"

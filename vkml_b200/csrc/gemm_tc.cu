@@ -910,9 +910,11 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a_hi, const __grid_consta
 //     tensor core's A operand, and A may come from TENSOR MEMORY instead of shared memory;
 //   * two producer warps: one brings [32 k][128 n] fp32 tiles of S (tensor map over the caller's
 //     own matrix, zero fill past the edges) into a ring of 6 to 8 slots, the other the matching
-//     K-blocks of W's planes into a ring of 4.  The rings are separate because their latencies
-//     are: S comes from HBM and its slot is free again as soon as the converters have read it,
-//     W comes from L2 and stays until the MMAs that read it have finished;
+//     K-blocks of W's planes into a ring of 4.  The rings are separate because their lifetimes
+//     are: S's slot is free again as soon as the converters have read it, W's stays until the
+//     MMAs that read it have finished.  (Measured: the deeper ring for S changes no time -- the
+//     loop is bound by the rate at which tcgen05.mma instructions issue, about 98 cycles each
+//     with A in tensor memory, twelve per K-block -- so its depth is headroom, not a tuning knob.)
 //   * sixteen converter warps read their lane's column of the S tile (lane = n, conflict-free),
 //     split every value into hi/lo in registers and put both into tensor memory with
 //     tcgen05.st -- 64 columns per stage: the streamed operand never touches shared memory
