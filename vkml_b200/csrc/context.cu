@@ -922,6 +922,47 @@ int b200_compute(b200_ctx* ctx, const b200_node* nodes, size_t n_nodes, uint32_t
                     }
                 }
             }
+            if (ctx->fuse && node.op == B200_OP_MAX_POOL2D_BACKWARD && p + 1 < exec.size() && !done[p + 1]) {
+                // ReLU's backward rule behind a pooling layer: where(mask, zeros, pooling gradient)
+                const b200_node& wn = nodes[exec[p + 1]];
+                auto same_tensor = [](const b200_tensor& a, const b200_tensor& b) {
+                    if (a.data != b.data || a.dtype != b.dtype || a.ndim != b.ndim) return false;
+                    for (int d = 0; d < a.ndim; ++d) {
+                        if (a.dims[d] != b.dims[d] || (a.dims[d] > 1 && a.strides[d] != b.strides[d])) return false;
+                    }
+                    return true;
+                };
+                auto filled = [&](const b200_tensor& t) {
+                    if (t.dtype != B200_F32 || t.data == nullptr) return false;
+                    const auto it = constants.find(t.data);
+                    if (it != constants.end() && it->second == tensor_bytes(t)) return true;
+                    for (int d = 0; d < t.ndim; ++d) {
+                        if (t.dims[d] > 1 && t.strides[d] != 0) return false;
+                    }
+                    return true;
+                };
+                bool eligible = wn.op == B200_OP_WHERE && wn.n_src == 3 && node.out.data != nullptr && wn.out.data != nullptr;
+                for (const size_t k : {p, p + 1}) {
+                    eligible = eligible && (is_sink.empty() || !is_sink[exec[k]]);
+                }
+                eligible = eligible && (!grad_sync || !is_sink.empty() || ctx->grads.empty());
+                int side = -1;
+                if (eligible && same_tensor(wn.src[1], node.out) && filled(wn.src[2])) side = 1;
+                if (eligible && same_tensor(wn.src[2], node.out) && filled(wn.src[1])) side = 0;
+                if (side >= 0) {
+                    prepare(exec[p]);
+                    prepare(exec[p + 1]);
+                    ctx->current_op = node.op;
+                    if (launch_pool_backward_where(ctx, node, wn, side, wn.src[side == 1 ? 2 : 1].data)) {
+                        constants.erase(node.out.data);
+                        constants.erase(wn.out.data);
+                        finish(exec[p]);
+                        finish(exec[p + 1]);
+                        p += 2;
+                        continue;
+                    }
+                }
+            }
             if (ctx->fuse && node.op == B200_OP_SCALED_ADD && exec.size() - p >= 2 && !grad_sync) {
                 // the optimiser's spans: independent scaled_add nodes, one launch for the dense ones among
                 // the next 24 nodes (a transposed gradient in between keeps its own kernel)

@@ -210,6 +210,9 @@ bool supports_node(const b200_node& node);
 // fuse.cu: serves the head of `seq` (the span's remaining computed nodes, in execution order)
 // with one fused launch if it matches a known pattern; returns how many nodes it covered, or 0.
 size_t launch_fused(b200_ctx* ctx, const b200_node* const* seq, size_t avail);
+// movement.cu: max_pool2d_backward + the where() of ReLU's backward rule behind it, one launch; false: not that case
+bool launch_pool_backward_where(b200_ctx* ctx, const b200_node& pool, const b200_node& where, int result_is_x,
+                                const void* constant);
 size_t launch_scaled_add_group(b200_ctx* ctx, const b200_node* const* seq, size_t avail, bool* picked);
 
 // dist.cu

@@ -16,6 +16,8 @@
 //     (src/api/ops.cpp:347-354,417-441);
 //   * backward of log_softmax:  exp(l)  sum(g, axis=-1, keepdim)  mul(exp, sum)  sub(g, mul)
 //     (src/autograd/autograd.cpp:528-546), one block per row;
+//   * max_pool2d_backward followed by the where() of ReLU's backward rule: served by the pooling
+//     kernel itself (movement.cu, launch_pool_backward_where);
 //   * the optimiser's spans: independent scaled_add nodes, one per parameter tensor
 //     (python/vkml/optim.py), served by one multi-tensor launch.
 //

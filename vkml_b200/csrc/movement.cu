@@ -395,9 +395,21 @@ max_pool2d_dense2_kernel(float* __restrict__ out, const float* __restrict__ in, 
 // Its adjoint under the same conditions (image exactly 2 out_h x 2 out_w): the thread that
 // owns four windows writes their 2 x 8 patch, the gradient (as 0 + g) at each window's first
 // maximum and zero elsewhere.
+// With WHERE, the `where(mask, x, y)` that ReLU's backward rule puts behind the pooling's adjoint
+// (src/autograd/autograd.cpp:397-409) is served from the same registers: one of x / y is this
+// kernel's own result, the other a tensor filled with one value (read from its first element).
+struct PoolWhere {
+    float* out;            // the where node's result
+    const uint8_t* mask;   // dense, the shape of the image
+    const float* constant; // first element of the filled operand
+    int result_is_x;       // the pooling gradient is where's x (taken where the mask is set)
+};
+
+template <bool WHERE>
 __global__ void __launch_bounds__(kThreads)
 max_pool2d_backward_dense2_kernel(float* __restrict__ out, const float* __restrict__ grad,
-                                  const float* __restrict__ in, int w, uint32_t items, FastDiv div_ow4) {
+                                  const float* __restrict__ in, int w, uint32_t items, FastDiv div_ow4,
+                                  PoolWhere pw) {
     pdl_prologue();
     const uint32_t step = gridDim.x * kThreads;
     const int out_w = w / 2;
@@ -442,6 +454,21 @@ max_pool2d_backward_dense2_kernel(float* __restrict__ out, const float* __restri
         for (int ki = 0; ki < 2; ++ki) {
             *reinterpret_cast<float4*>(out + base + ki * w) = make_float4(r[ki][0], r[ki][1], r[ki][2], r[ki][3]);
             *reinterpret_cast<float4*>(out + base + ki * w + 4) = make_float4(r[ki][4], r[ki][5], r[ki][6], r[ki][7]);
+        }
+        if (WHERE) {
+            const float c = *pw.constant;
+#pragma unroll
+            for (int ki = 0; ki < 2; ++ki) {
+                const uint2 m8 = *reinterpret_cast<const uint2*>(pw.mask + base + ki * w);
+                float s[8];
+#pragma unroll
+                for (int j = 0; j < 8; ++j) {
+                    const bool set = (((j < 4 ? m8.x : m8.y) >> (8 * (j & 3))) & 0xffu) != 0;
+                    s[j] = (set == (pw.result_is_x != 0)) ? r[ki][j] : c;
+                }
+                *reinterpret_cast<float4*>(pw.out + base + ki * w) = make_float4(s[0], s[1], s[2], s[3]);
+                *reinterpret_cast<float4*>(pw.out + base + ki * w + 4) = make_float4(s[4], s[5], s[6], s[7]);
+            }
         }
     }
 }
@@ -1028,6 +1055,49 @@ void allow_large_smem(K kernel) {
     B200_CUDA_CHECK(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kDenseSmemLimit));
 }
 
+// max_pool2d_backward followed by where(mask, x, y) with one of x / y the pooling gradient and the
+// other a tensor filled with one value: one launch when the pooling is the dense 2x2 case, false otherwise.
+bool launch_pool_backward_where(b200_ctx* ctx, const b200_node& pool, const b200_node& where, int result_is_x,
+                                const void* constant) {
+    const View out = make_view(pool.out);
+    const View grad = make_view(pool.src[0]);
+    const View in = make_view(pool.src[1]);
+    const View wout = make_view(where.out);
+    const View mask = make_view(where.src[0]);
+    if (out.dtype != B200_F32 || in.dtype != B200_F32 || grad.dtype != B200_F32 || wout.dtype != B200_F32 ||
+        mask.dtype != B200_BOOL || pool.out.ndim != 4 || pool.src[0].ndim != 4 || pool.src[1].ndim != 4) {
+        return false;
+    }
+    if (!out.contiguous || !in.contiguous || !grad.contiguous || !wout.contiguous || !mask.contiguous ||
+        wout.numel != out.numel || mask.numel != out.numel) {
+        return false;
+    }
+    const Win w = make_win(get_params<UnfoldParams>(pool), 1);
+    const int out_h = static_cast<int>(grad.dim[2]), out_w = static_cast<int>(grad.dim[3]);
+    const int64_t planes = out.dim[0] * out.dim[1];
+    const int64_t total = out.numel;
+    const bool dense2 = w.sh == 2 && w.sw == 2 && w.kh == 2 && w.kw == 2 && w.ph == 0 && w.pw == 0 && w.dh == 1 && w.dw == 1 &&
+                        in.dim[2] == w.image_h && in.dim[3] == w.image_w && out.dim[2] == w.image_h && out.dim[3] == w.image_w &&
+                        in.dim[0] == out.dim[0] && in.dim[1] == out.dim[1] && grad.dim[0] == out.dim[0] && grad.dim[1] == out.dim[1] &&
+                        w.image_w % 8 == 0 && w.image_h % 2 == 0 && out_h * 2 == w.image_h && out_w * 2 == w.image_w &&
+                        total > 0 && total / 16 < (int64_t(1) << 31);
+    const auto aligned = [](const void* p, size_t a) { return reinterpret_cast<uintptr_t>(p) % a == 0; };
+    if (!dense2 || !aligned(out.data, 16) || !aligned(in.data, 16) || !aligned(grad.data, 16) || !aligned(wout.data, 16) ||
+        !aligned(mask.data, 8)) {
+        return false;
+    }
+    const uint32_t items = static_cast<uint32_t>(planes * out_h * (out_w / 4));
+    PoolWhere pw{reinterpret_cast<float*>(wout.data), reinterpret_cast<const uint8_t*>(mask.data),
+                 static_cast<const float*>(constant), result_is_x};
+    ProfScope scope(ctx, "fused.pool_backward_where");
+    launch_kernel(ctx, max_pool2d_backward_dense2_kernel<true>, grid_for(items, kThreads), kThreads, 0,
+                  reinterpret_cast<float*>(out.data), reinterpret_cast<const float*>(grad.data),
+                  reinterpret_cast<const float*>(in.data), w.image_w, items, FastDiv(static_cast<uint32_t>(out_w / 4)), pw);
+    ctx->count_launch();
+    check_last_launch("max_pool2d_backward + where");
+    return true;
+}
+
 void launch_movement(b200_ctx* ctx, const b200_node& node) {
     const View out = make_view(node.out);
     const int64_t total = out.numel;
@@ -1238,7 +1308,7 @@ void launch_movement(b200_ctx* ctx, const b200_node& node) {
                 total / 16 < kMax32) {
                 const uint32_t items = static_cast<uint32_t>(planes * out_h * (out_w / 4));
                 const FastDiv div_ow4(static_cast<uint32_t>(out_w / 4));
-                launch_kernel(ctx, max_pool2d_backward_dense2_kernel, grid_for(items, kThreads), kThreads, 0, o, g, src, w.image_w, items, div_ow4);
+                launch_kernel(ctx, max_pool2d_backward_dense2_kernel<false>, grid_for(items, kThreads), kThreads, 0, o, g, src, w.image_w, items, div_ow4, PoolWhere{});
                 break;
             }
             if (tiled) {
