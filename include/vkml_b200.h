@@ -237,6 +237,13 @@ void* b200_stream(b200_ctx* ctx);
  * handling of an expired device wait be tested. */
 int b200_debug_expire_wait(b200_ctx* ctx, uint64_t limit_ns);
 
+/* b200_compute replays a span that comes back unchanged (same nodes, same addresses, same library
+ * state) as one CUDA graph: captured at its second sighting, launched from then on -- vkML's
+ * planned "re-submit the cached command buffer" (docs/ARCHITECTURE.md:565-569) without any change
+ * above the backend interface.  How many spans were served by a launch of a kept graph, and how
+ * many graphs were captured.  VKML_B200_SPAN_GRAPHS=0 turns the cache off. */
+int b200_span_graph_stats(b200_ctx* ctx, uint64_t* hits, uint64_t* captures);
+
 /* -- data-parallel training (no counterpart in vkML, which is single-device:
  *    src/dispatch/executor.cpp:96-103). One process per GPU. -- */
 #define B200_UNIQUE_ID_BYTES 128

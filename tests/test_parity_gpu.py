@@ -402,6 +402,56 @@ def test_device_copies(backend):
     assert z.data == 0 and z.nbytes == 0
 
 
+def test_a_span_that_comes_back_is_replayed_as_a_graph_with_fresh_data(oracle, monkeypatch):
+    """The same span on the same buffers, seven times with new input data each time: from the third
+    submission on it is one CUDA graph launch, and every result is the one the eager path gives
+    (bit for bit) and the oracle confirms.  A different span on the same buffers is not mistaken for it."""
+    import vkml_b200
+    from vkml_b200 import DeviceTensor, NodeDesc
+    rng = np.random.default_rng(23)
+    results = {}
+    for mode in ("1", "0"):
+        monkeypatch.setenv("VKML_B200_SPAN_GRAPHS", mode)
+        b = vkml_b200.Backend(0)
+        x = DeviceTensor.empty(b, (1, 1, 96, 160))
+        w = DeviceTensor.from_host(b, (np.random.default_rng(3).standard_normal((1, 1, 160, 64)) * 0.05).astype(np.float32))
+        bias = DeviceTensor.from_host(b, np.random.default_rng(4).standard_normal((1, 1, 1, 64)).astype(np.float32))
+        h, hb, r, e, sm, s = (DeviceTensor.empty(b, (1, 1, 96, 64)) for _ in range(6))
+        tot = DeviceTensor.empty(b, (1, 1, 96, 1))
+        bias_b = bias.broadcast_to((1, 1, 96, 64))
+        span = [NodeDesc(Op.MATMUL, h.desc, [x.desc, w.desc]), NodeDesc(Op.ADD, hb.desc, [h.desc, bias_b.desc]),
+                NodeDesc(Op.RELU, r.desc, [hb.desc]), NodeDesc(Op.EXP, e.desc, [r.desc]),
+                NodeDesc(Op.LOG_SOFTMAX, sm.desc, [e.desc], graph.axis_params(3)),
+                NodeDesc(Op.NEG, s.desc, [sm.desc]),
+                NodeDesc(Op.SUM, tot.desc, [s.desc], graph.reduce_params([3], 4, keepdim=True))]
+        outs = []
+        data = np.random.default_rng(5)
+        for _ in range(7):
+            xs = data.standard_normal((1, 1, 96, 160)).astype(np.float32)
+            b.copy_from_host(x.storage, 0, xs)
+            b.compute(span)
+            outs.append((xs, tot.numpy().copy(), sm.numpy().copy()))
+        other = span[:3] + [NodeDesc(Op.NEG, e.desc, [r.desc])] + span[4:]   # same buffers, another function
+        b.compute(other)
+        outs.append((None, tot.numpy().copy(), sm.numpy().copy()))
+        hits, captures = b.span_graph_stats()
+        if mode == "1":
+            assert captures == 1 and hits == 5, (hits, captures)
+        else:
+            assert captures == 0 and hits == 0
+        results[mode] = outs
+    for (xs, t1, s1), (_, t0, s0) in zip(results["1"], results["0"]):
+        assert np.array_equal(t1.view(np.uint32), t0.view(np.uint32)) and np.array_equal(s1.view(np.uint32), s0.view(np.uint32))
+    xs, t1, s1 = results["1"][6]
+    wh = (np.random.default_rng(3).standard_normal((160, 64)) * 0.05).astype(np.float32)
+    bh = np.random.default_rng(4).standard_normal((64,)).astype(np.float32)
+    z = np.maximum(xs.reshape(96, 160).astype(np.float64) @ wh + bh, 0)
+    ez = np.exp(z)
+    want = ez - np.log(np.exp(ez - ez.max(1, keepdims=True)).sum(1, keepdims=True)) - ez.max(1, keepdims=True)
+    assert np.allclose(s1.reshape(96, 64), want, rtol=2e-4, atol=2e-4)
+    assert not np.array_equal(results["1"][7][2], results["1"][6][2])
+
+
 def test_large_uploads_from_pageable_memory_arrive_intact(backend):
     """copy_from_host of pageable memory above a few MB is staged through pinned slots by several
     threads: sizes that are not a multiple of the chunk, sources that change between calls (every

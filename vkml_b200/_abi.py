@@ -101,6 +101,7 @@ SYMBOLS = {
     "b200_matmul_kernel": (C.c_int, [_P, C.POINTER(Node), C.c_char_p, C.c_size_t, C.c_char_p, C.c_size_t]),
     "b200_stream": (_P, [_P]),
     "b200_debug_expire_wait": (C.c_int, [_P, C.c_uint64]),
+    "b200_span_graph_stats": (C.c_int, [_P, C.POINTER(C.c_uint64), C.POINTER(C.c_uint64)]),
     "b200_dist_unique_id": (C.c_int, [_P]),
     "b200_dist_init": (C.c_int, [_P, C.c_int, C.c_int, _P]),
     "b200_dist_init_deadline": (C.c_int, [_P, C.c_int, C.c_int, _P, C.c_int]),

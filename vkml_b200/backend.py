@@ -185,6 +185,12 @@ class Backend:
         self._check(self._lib.b200_profile_read(self._ctx, buf, capacity, C.byref(n)), "profile_read")
         return [(buf[i].label.decode(), float(buf[i].ms)) for i in range(n.value)]
 
+    def span_graph_stats(self) -> tuple:
+        """(spans served by launching a kept CUDA graph, graphs captured) since the context was created."""
+        hits, captures = C.c_uint64(0), C.c_uint64(0)
+        self._check(self._lib.b200_span_graph_stats(self._ctx, C.byref(hits), C.byref(captures)), "span_graph_stats")
+        return int(hits.value), int(captures.value)
+
     def timer_begin(self) -> None:
         self._check(self._lib.b200_timer_begin(self._ctx), "timer_begin")
 

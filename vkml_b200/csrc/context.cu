@@ -101,6 +101,7 @@ void* CachingAllocator::allocate(size_t nbytes) {
                     cudaFree(block);
                     reserved -= kv.first;
                     sizes_.erase(block);
+                    ++driver_frees;
                 }
             }
             free_.clear();
@@ -152,6 +153,7 @@ void CachingAllocator::trim() {
             cudaFree(block);
             reserved -= kv.first;
             sizes_.erase(block);
+            ++driver_frees;
         }
     }
     free_.clear();
@@ -594,6 +596,9 @@ int b200_create(int cuda_ordinal, b200_ctx** out) {
         if (const char* e = std::getenv("VKML_B200_UPLOAD_THREADS")) {
             ctx->upload_threads = std::max(0, std::min(16, std::atoi(e)));
         }
+        if (const char* e = std::getenv("VKML_B200_SPAN_GRAPHS")) {
+            ctx->span_graph_cache = std::atoi(e) != 0;
+        }
         if (const char* e = std::getenv("VKML_B200_PDL")) {
             ctx->pdl = std::atoi(e) != 0;
         }
@@ -632,6 +637,9 @@ void b200_destroy(b200_ctx* ctx) {
     cudaSetDevice(ctx->device);
     if (ctx->stream != nullptr) cudaStreamSynchronize(ctx->stream);
     destroy_uploader(ctx);
+    for (auto& kv : ctx->span_graphs) {
+        if (kv.second.exec != nullptr) cudaGraphExecDestroy(kv.second.exec);
+    }
     dist_destroy(ctx);
     if (ctx->stream != nullptr) cudaStreamDestroy(ctx->stream);
     if (ctx->d_status != nullptr) cudaFree(ctx->d_status);
@@ -676,10 +684,13 @@ int b200_free(b200_ctx* ctx, void* ptr) {
     });
 }
 
+static void drop_span_graphs(b200_ctx* ctx);
+
 int b200_trim(b200_ctx* ctx) {
     if (ctx == nullptr) return B200_INVALID_ARGUMENT;
     return guarded(ctx, [&] {
         B200_CUDA_CHECK(cudaStreamSynchronize(ctx->stream));
+        drop_span_graphs(ctx);
         ctx->alloc.trim();
         ctx->scratch.trim();
     });
@@ -690,10 +701,9 @@ int b200_supports(const b200_node* node) {
     return supports_node(*node) ? 1 : 0;
 }
 
-int b200_compute(b200_ctx* ctx, const b200_node* nodes, size_t n_nodes, uint32_t flags) {
-    if (ctx == nullptr || (nodes == nullptr && n_nodes != 0)) return B200_INVALID_ARGUMENT;
-    return guarded(ctx, [&] {
-        ctx->compute_calls.fetch_add(1, std::memory_order_relaxed);
+// Queues one span, node by node (fused groups aside).
+static void compute_span(b200_ctx* ctx, const b200_node* nodes, size_t n_nodes, uint32_t flags) {
+    {
         const bool grad_sync = (flags & B200_COMPUTE_GRAD_SYNC) != 0 && ctx->dist != nullptr;
         // With no buffers registered, the gradients are the span's SINKS: f32 outputs that
         // no later node of the span reads.  backward() realises exactly the leaf gradients
@@ -1023,6 +1033,127 @@ int b200_compute(b200_ctx* ctx, const b200_node* nodes, size_t n_nodes, uint32_t
         if ((flags & B200_COMPUTE_SYNC) && !ctx->capturing) {
             B200_CUDA_CHECK(cudaStreamSynchronize(ctx->stream));
         }
+    }
+}
+
+// ---- spans replayed as CUDA graphs ----
+//
+// What a span queues is a function of its nodes (ops, shapes, strides, ADDRESSES, parameters) and
+// of a little library state: the GEMM precision, the workspace and the scratch pool the planes
+// come from.  When all of that comes back unchanged, so do the launches -- and vkML's training
+// loops do come back: the caching allocator hands a loop the same addresses again every few steps.
+// The second time a span of at least kSpanGraphMinNodes nodes is seen in the same state, its
+// launches are captured from the stream (relaxed mode, the same code path as the eager run) and
+// kept; from then on the span is one cudaGraphLaunch.  A graph is only ever launched for a span
+// that matches the captured one byte for byte, and everything is dropped when device memory goes
+// back to the driver.  Spans that exchange gradients, spans queued while an all-reduce is still
+// pending, and profiled spans always run eagerly.
+constexpr size_t kSpanGraphMinNodes = 6;
+constexpr size_t kSpanGraphMax = 256;
+static_assert(sizeof(b200_node) % 8 == 0 && alignof(b200_node) >= 8, "spans are hashed in 8-byte words");
+
+static uint64_t span_graph_state(const b200_ctx* ctx) {
+    uint64_t h = 1469598103934665603ull;
+    auto mix = [&](uint64_t v) { h = (h ^ v) * 1099511628211ull; };
+    mix(static_cast<uint64_t>(ctx->gemm_precision));
+    mix(reinterpret_cast<uintptr_t>(ctx->workspace));
+    mix(ctx->workspace_bytes);
+    mix(ctx->scratch.driver_allocs);
+    mix(ctx->alloc.driver_frees + ctx->scratch.driver_frees);
+    return h;
+}
+
+static void drop_span_graphs(b200_ctx* ctx) {
+    for (auto& kv : ctx->span_graphs) {
+        if (kv.second.exec != nullptr) cudaGraphExecDestroy(kv.second.exec);
+    }
+    ctx->span_graphs.clear();
+    ctx->span_seen.clear();
+}
+
+// True when the span was served by a graph (launched, or captured and launched).
+static bool span_graph_run(b200_ctx* ctx, const b200_node* nodes, size_t n_nodes, uint32_t flags) {
+    if (!ctx->span_graph_cache || ctx->capturing || ctx->profiling || n_nodes < kSpanGraphMinNodes ||
+        (flags & ~static_cast<uint32_t>(B200_COMPUTE_SYNC)) != 0 || dist_has_pending(ctx)) {
+        return false;
+    }
+    const size_t bytes = n_nodes * sizeof(b200_node);
+    const unsigned char* raw = reinterpret_cast<const unsigned char*>(nodes);
+    uint64_t key = 1469598103934665603ull;
+    {
+        const uint64_t* w = reinterpret_cast<const uint64_t*>(raw);  // b200_node is a multiple of 8 bytes, 8-aligned
+        for (size_t i = 0; i < bytes / 8; ++i) key = (key ^ w[i]) * 1099511628211ull;
+    }
+    const uint64_t state = span_graph_state(ctx);
+    key = (key ^ state) * 1099511628211ull;
+    auto finish = [&](b200_ctx::SpanGraph& g) {
+        B200_CUDA_CHECK(cudaGraphLaunch(g.exec, ctx->stream));
+        ctx->kernel_launches.fetch_add(g.launches, std::memory_order_relaxed);
+        ctx->nodes_computed.fetch_add(g.node_count, std::memory_order_relaxed);
+        if (flags & B200_COMPUTE_SYNC) B200_CUDA_CHECK(cudaStreamSynchronize(ctx->stream));
+    };
+    if (auto it = ctx->span_graphs.find(key); it != ctx->span_graphs.end()) {
+        b200_ctx::SpanGraph& g = it->second;
+        if (g.state == state && g.nodes.size() == bytes && std::memcmp(g.nodes.data(), raw, bytes) == 0) {
+            finish(g);
+            ++ctx->span_graph_hits;
+            return true;
+        }
+        return false;  // a different span under the same key: leave it to the eager path
+    }
+    if (ctx->span_seen.size() > 65536) ctx->span_seen.clear();  // a caller whose addresses never come back
+    if (++ctx->span_seen[key] < 2 || ctx->span_graphs.size() >= kSpanGraphMax) {
+        return false;
+    }
+    // second sighting: capture what the eager path queues for this span
+    const uint64_t launches0 = ctx->kernel_launches.load(), nodes0 = ctx->nodes_computed.load();
+    cudaGraph_t graph = nullptr;
+    B200_CUDA_CHECK(cudaStreamBeginCapture(ctx->stream, cudaStreamCaptureModeRelaxed));
+    ctx->capturing = true;
+    bool ok = true;
+    try {
+        compute_span(ctx, nodes, n_nodes, flags);
+    } catch (const Error&) {
+        ok = false;
+    }
+    ctx->capturing = false;
+    if (cudaStreamEndCapture(ctx->stream, &graph) != cudaSuccess || graph == nullptr) {
+        cudaGetLastError();
+        ok = false;
+    }
+    b200_ctx::SpanGraph g;
+    ok = ok && span_graph_state(ctx) == state;  // nothing grew while capturing
+    if (ok && cudaGraphInstantiate(&g.exec, graph, 0) != cudaSuccess) {
+        cudaGetLastError();
+        ok = false;
+    }
+    if (graph != nullptr) cudaGraphDestroy(graph);
+    // the capture pass counted the span once; a launch counts it again below
+    const uint64_t launches = ctx->kernel_launches.load() - launches0, node_count = ctx->nodes_computed.load() - nodes0;
+    ctx->kernel_launches.fetch_sub(launches, std::memory_order_relaxed);
+    ctx->nodes_computed.fetch_sub(node_count, std::memory_order_relaxed);
+    if (!ok) {
+        ctx->span_seen[key] = 0x40000000u;  // never try this one again; the eager path reports whatever is wrong
+        if (g.exec != nullptr) cudaGraphExecDestroy(g.exec);
+        return false;
+    }
+    g.nodes.assign(raw, raw + bytes);
+    g.launches = launches;
+    g.node_count = node_count;
+    g.state = state;
+    auto placed = ctx->span_graphs.emplace(key, std::move(g));
+    ++ctx->span_graph_captures;
+    finish(placed.first->second);
+    return true;
+}
+
+int b200_compute(b200_ctx* ctx, const b200_node* nodes, size_t n_nodes, uint32_t flags) {
+    if (ctx == nullptr || (nodes == nullptr && n_nodes != 0)) return B200_INVALID_ARGUMENT;
+    return guarded(ctx, [&] {
+        ctx->compute_calls.fetch_add(1, std::memory_order_relaxed);
+        if (!span_graph_run(ctx, nodes, n_nodes, flags)) {
+            compute_span(ctx, nodes, n_nodes, flags);
+        }
     });
 }
 
@@ -1254,6 +1385,13 @@ int b200_matmul_kernel(b200_ctx* ctx, const b200_node* node, char* name, size_t 
 }
 
 void* b200_stream(b200_ctx* ctx) { return ctx == nullptr ? nullptr : ctx->stream; }
+
+int b200_span_graph_stats(b200_ctx* ctx, uint64_t* hits, uint64_t* captures) {
+    if (ctx == nullptr) return B200_INVALID_ARGUMENT;
+    if (hits != nullptr) *hits = ctx->span_graph_hits;
+    if (captures != nullptr) *captures = ctx->span_graph_captures;
+    return B200_OK;
+}
 
 int b200_debug_expire_wait(b200_ctx* ctx, uint64_t limit_ns) {
     if (ctx == nullptr || limit_ns == 0 || limit_ns > 1000000000ULL) return B200_INVALID_ARGUMENT;

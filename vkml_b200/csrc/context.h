@@ -32,6 +32,7 @@ public:
     ~CachingAllocator();
 
     uint64_t reserved = 0, in_use = 0, peak = 0, live = 0, total = 0, driver_allocs = 0;
+    uint64_t driver_frees = 0;  // blocks handed back to the driver (trim, or making room after a failed allocation)
 
 private:
     static size_t round_size(size_t n);
@@ -158,6 +159,21 @@ struct b200_ctx {
     uint32_t current_op = 0;
     std::vector<b200::ProfEntry> prof;
     std::vector<cudaEvent_t> event_pool;
+
+    // Spans that come back unchanged -- same nodes, same addresses, same library state -- are replayed
+    // as one CUDA graph each (context.cu, span_graph_*): a training loop driven through
+    // Backend::compute is handed the same addresses again every few steps, so after a short
+    // warm-up its large spans cost one launch.  VKML_B200_SPAN_GRAPHS=0 turns it off.
+    struct SpanGraph {
+        cudaGraphExec_t exec = nullptr;
+        std::vector<unsigned char> nodes;  // the span it was captured from, byte for byte
+        uint64_t launches = 0, node_count = 0;
+        uint64_t state = 0;                // library state it depends on (see span_graph_state)
+    };
+    std::unordered_map<uint64_t, SpanGraph> span_graphs;
+    std::unordered_map<uint64_t, uint32_t> span_seen;
+    bool span_graph_cache = true;
+    uint64_t span_graph_hits = 0, span_graph_captures = 0;
 
     b200::DistState* dist = nullptr;
     std::vector<b200::GradBuffer> grads;
