@@ -541,7 +541,7 @@ def run_ops(args, local_rank):
     backend = vkml_b200.Backend(local_rank)
     pk = peaks()
     rng = np.random.default_rng(SEED_DATA)
-    F32, I64, BOOL = DType.F32, DType.I64, DType.BOOL
+    F32, I64, BOOL, F16 = DType.F32, DType.I64, DType.BOOL, DType.F16
 
     def dev(shape, dtype=F32, kind="normal"):
         n = int(np.prod(shape)) if len(shape) else 1
@@ -549,6 +549,8 @@ def run_ops(args, local_rank):
             host = rng.standard_normal(n, dtype=np.float32) if kind == "normal" else rng.random(n, dtype=np.float32)
         elif dtype == I64:
             host = rng.integers(0, 10, n).astype(np.int64)
+        elif dtype == F16:
+            host = rng.standard_normal(n, dtype=np.float32).astype(np.float16)
         else:
             host = (rng.random(n) < 0.5).astype(np.uint8)
         return DeviceTensor.from_host(backend, host.reshape(shape))
@@ -569,6 +571,10 @@ def run_ops(args, local_rank):
          lambda: [dev((256, 64, 32, 32)), dev((64, 1, 1)).broadcast_to((256, 64, 32, 32))],
          bytes_alg=8 * 256 * 64 * 1024)
     case("relu [2048,8192]", Op.RELU, (B, H), F32, lambda: [dev((B, H))], bytes_alg=8 * B * H)
+    # half storage: the elementwise families read and write it directly (2 bytes per element each way)
+    case("add f16 dense [4096,8192]", Op.ADD, (4096, H), F16, lambda: [dev((4096, H), F16), dev((4096, H), F16)],
+         bytes_alg=6 * 4096 * H)
+    case("relu f16 [4096,8192]", Op.RELU, (4096, H), F16, lambda: [dev((4096, H), F16)], bytes_alg=4 * 4096 * H)
     case("less_equal vs scalar [2048,8192] -> bool", Op.LESS_EQUAL, (B, H), BOOL,
          lambda: [dev((B, H)), dev(()).broadcast_to((B, H))], bytes_alg=5 * B * H)
     case("where(mask, g, 0) [2048,8192]", Op.WHERE, (B, H), F32,

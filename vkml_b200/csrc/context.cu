@@ -359,7 +359,20 @@ void dispatch_node(b200_ctx* ctx, const b200_node& node) {
     const uint32_t op = node.op;
     ctx->current_op = op;
     if (touches_f16(node)) {
-        dispatch_f16(ctx, node);
+        // the elementwise families read and write half storage themselves (elementwise.cu, HalfIO);
+        // everything else runs on widened copies
+        const bool elementwise = op == B200_OP_WHERE || op == B200_OP_SCALED_ADD || op == B200_OP_CLAMP ||
+                                 (op >= B200_OP_ADD && op <= B200_OP_NOT_EQUAL) || (op >= B200_OP_NEG && op <= B200_OP_SILU);
+        bool all_half = true;
+        for (uint32_t s = 0; s < node.n_src && s < B200_MAX_SRC; ++s) {
+            all_half = all_half && node.src[s].dtype != B200_F32;
+        }
+        if (elementwise && all_half && node.out.dtype != B200_F32) {
+            ProfScope scope(ctx, op_label(op));
+            launch_elementwise(ctx, node);
+        } else {
+            dispatch_f16(ctx, node);
+        }
         return;
     }
     if (op == B200_OP_MATMUL) {

@@ -20,6 +20,7 @@
 #include <cuda_fp16.h>
 
 #include <algorithm>
+#include <type_traits>
 
 namespace b200 {
 namespace {
@@ -234,6 +235,38 @@ struct FCastF16F32 {
         return __half2float(__ushort_as_half(x));
     }
 };
+// F16 is storage, never arithmetic (src/backend/cpu/kernels_elementwise.cpp:89-99): the same
+// functor, with every float operand widened from half bits on load and a float result narrowed
+// once, round-to-nearest-even, on store.  What the widened-copy path computes, without the copies.
+template <typename T>
+using HalfIf = std::conditional_t<std::is_same_v<T, float>, uint16_t, T>;
+
+template <typename F>
+struct HalfIO {
+    static constexpr int NIN = F::NIN;
+    using In0 = HalfIf<typename F::In0>;
+    using In1 = HalfIf<typename F::In1>;
+    using In2 = HalfIf<typename F::In2>;
+    using Out = HalfIf<typename F::Out>;
+    using P = typename F::P;
+    template <typename Want, typename Got>
+    __device__ __forceinline__ static Want widen(Got x) {
+        if constexpr (std::is_same_v<Want, float>) {
+            return __half2float(__ushort_as_half(x));
+        } else {
+            return x;
+        }
+    }
+    __device__ __forceinline__ static Out apply(const P& p, In0 a, In1 b, In2 c) {
+        const auto r = F::apply(p, widen<typename F::In0>(a), widen<typename F::In1>(b), widen<typename F::In2>(c));
+        if constexpr (std::is_same_v<typename F::Out, float>) {
+            return f32_to_f16_bits(r);
+        } else {
+            return r;
+        }
+    }
+};
+
 template <typename To>
 struct FCastBool {
     static constexpr int NIN = 1;
@@ -1063,6 +1096,34 @@ void require_f32(const b200_node& node, const char* what) {
     }
 }
 
+// Every floating tensor of the node is F16 (and there is at least one).
+bool all_half(const b200_node& node) {
+    auto floating = [](int dt) { return dt == B200_F32 || dt == B200_F16; };
+    bool any = false;
+    if (floating(node.out.dtype)) {
+        if (node.out.dtype != B200_F16) return false;
+        any = true;
+    }
+    for (uint32_t s = 0; s < node.n_src && s < B200_MAX_SRC; ++s) {
+        if (floating(node.src[s].dtype)) {
+            if (node.src[s].dtype != B200_F16) return false;
+            any = true;
+        }
+    }
+    return any;
+}
+
+// The f32 functor F on f32 tensors, or on half storage through HalfIO.
+template <typename F>
+void run_float(b200_ctx* ctx, const b200_node& node, const typename F::P& p, const char* what) {
+    if (all_half(node)) {
+        run<HalfIO<F>>(ctx, node, p);
+    } else {
+        require_f32(node, what);
+        run<F>(ctx, node, p);
+    }
+}
+
 }  // namespace
 
 void launch_elementwise(b200_ctx* ctx, const b200_node& node) {
@@ -1152,63 +1213,58 @@ void launch_elementwise(b200_ctx* ctx, const b200_node& node) {
             check_last_launch("slice_backward");
             return;
         }
-        case B200_OP_WHERE:
-            require_f32(node, "where");
-            run<FWhere>(ctx, node, {});
-            return;
-        case B200_OP_SCALED_ADD:
-            require_f32(node, "scaled_add");
-            run<FScaledAdd>(ctx, node, get_params<ScaledAddParams>(node));
-            return;
-        case B200_OP_CLAMP:
-            require_f32(node, "clamp");
-            run<FClamp>(ctx, node, get_params<ClampParams>(node));
-            return;
+        case B200_OP_WHERE: run_float<FWhere>(ctx, node, {}, "where"); return;
+        case B200_OP_SCALED_ADD: run_float<FScaledAdd>(ctx, node, get_params<ScaledAddParams>(node), "scaled_add"); return;
+        case B200_OP_CLAMP: run_float<FClamp>(ctx, node, get_params<ClampParams>(node), "clamp"); return;
         default: break;
     }
 
     if (node.op >= B200_OP_EQUAL && node.op <= B200_OP_NOT_EQUAL) {
-        if (node.out.dtype != B200_BOOL || node.src[0].dtype != B200_F32 ||
-            node.src[1].dtype != B200_F32) {
-            fail(B200_DTYPE_ERROR, "comparison: expects f32 operands and a bool result");
+        const bool half = node.src[0].dtype == B200_F16 && node.src[1].dtype == B200_F16;
+        if (node.out.dtype != B200_BOOL || (!half && (node.src[0].dtype != B200_F32 || node.src[1].dtype != B200_F32))) {
+            fail(B200_DTYPE_ERROR, "comparison: expects f32 (or f16) operands and a bool result");
         }
+#define B200_COMPARE(F)                         \
+    if (half) run<HalfIO<F>>(ctx, node, {});    \
+    else run<F>(ctx, node, {});                 \
+    return
         switch (node.op) {
-            case B200_OP_EQUAL: run<FEqual>(ctx, node, {}); return;
-            case B200_OP_LESS: run<FLess>(ctx, node, {}); return;
-            case B200_OP_GREATER: run<FGreater>(ctx, node, {}); return;
-            case B200_OP_LESS_EQUAL: run<FLessEqual>(ctx, node, {}); return;
-            case B200_OP_GREATER_EQUAL: run<FGreaterEqual>(ctx, node, {}); return;
-            case B200_OP_NOT_EQUAL: run<FNotEqual>(ctx, node, {}); return;
+            case B200_OP_EQUAL: B200_COMPARE(FEqual);
+            case B200_OP_LESS: B200_COMPARE(FLess);
+            case B200_OP_GREATER: B200_COMPARE(FGreater);
+            case B200_OP_LESS_EQUAL: B200_COMPARE(FLessEqual);
+            case B200_OP_GREATER_EQUAL: B200_COMPARE(FGreaterEqual);
+            case B200_OP_NOT_EQUAL: B200_COMPARE(FNotEqual);
         }
+#undef B200_COMPARE
     }
 
-    require_f32(node, "elementwise");
     switch (node.op) {
-        case B200_OP_ADD: run<FAdd>(ctx, node, {}); return;
-        case B200_OP_SUB: run<FSub>(ctx, node, {}); return;
-        case B200_OP_MUL: run<FMul>(ctx, node, {}); return;
-        case B200_OP_DIV: run<FDiv>(ctx, node, {}); return;
-        case B200_OP_POW: run<FPow>(ctx, node, {}); return;
-        case B200_OP_MAXIMUM: run<FMaximum>(ctx, node, {}); return;
-        case B200_OP_MINIMUM: run<FMinimum>(ctx, node, {}); return;
-        case B200_OP_NEG: run<FNeg>(ctx, node, {}); return;
-        case B200_OP_ABS: run<FAbs>(ctx, node, {}); return;
-        case B200_OP_SIGN: run<FSign>(ctx, node, {}); return;
-        case B200_OP_SQUARE: run<FSquare>(ctx, node, {}); return;
-        case B200_OP_SQRT: run<FSqrt>(ctx, node, {}); return;
-        case B200_OP_RSQRT: run<FRsqrt>(ctx, node, {}); return;
-        case B200_OP_RECIPROCAL: run<FReciprocal>(ctx, node, {}); return;
-        case B200_OP_EXP: run<FExp>(ctx, node, {}); return;
-        case B200_OP_LOG: run<FLog>(ctx, node, {}); return;
-        case B200_OP_ERF: run<FErf>(ctx, node, {}); return;
-        case B200_OP_ERFC: run<FErfc>(ctx, node, {}); return;
-        case B200_OP_SIN: run<FSin>(ctx, node, {}); return;
-        case B200_OP_COS: run<FCos>(ctx, node, {}); return;
-        case B200_OP_TANH: run<FTanh>(ctx, node, {}); return;
-        case B200_OP_SIGMOID: run<FSigmoid>(ctx, node, {}); return;
-        case B200_OP_RELU: run<FRelu>(ctx, node, {}); return;
-        case B200_OP_GELU: run<FGelu>(ctx, node, {}); return;
-        case B200_OP_SILU: run<FSilu>(ctx, node, {}); return;
+        case B200_OP_ADD: run_float<FAdd>(ctx, node, {}, "elementwise"); return;
+        case B200_OP_SUB: run_float<FSub>(ctx, node, {}, "elementwise"); return;
+        case B200_OP_MUL: run_float<FMul>(ctx, node, {}, "elementwise"); return;
+        case B200_OP_DIV: run_float<FDiv>(ctx, node, {}, "elementwise"); return;
+        case B200_OP_POW: run_float<FPow>(ctx, node, {}, "elementwise"); return;
+        case B200_OP_MAXIMUM: run_float<FMaximum>(ctx, node, {}, "elementwise"); return;
+        case B200_OP_MINIMUM: run_float<FMinimum>(ctx, node, {}, "elementwise"); return;
+        case B200_OP_NEG: run_float<FNeg>(ctx, node, {}, "elementwise"); return;
+        case B200_OP_ABS: run_float<FAbs>(ctx, node, {}, "elementwise"); return;
+        case B200_OP_SIGN: run_float<FSign>(ctx, node, {}, "elementwise"); return;
+        case B200_OP_SQUARE: run_float<FSquare>(ctx, node, {}, "elementwise"); return;
+        case B200_OP_SQRT: run_float<FSqrt>(ctx, node, {}, "elementwise"); return;
+        case B200_OP_RSQRT: run_float<FRsqrt>(ctx, node, {}, "elementwise"); return;
+        case B200_OP_RECIPROCAL: run_float<FReciprocal>(ctx, node, {}, "elementwise"); return;
+        case B200_OP_EXP: run_float<FExp>(ctx, node, {}, "elementwise"); return;
+        case B200_OP_LOG: run_float<FLog>(ctx, node, {}, "elementwise"); return;
+        case B200_OP_ERF: run_float<FErf>(ctx, node, {}, "elementwise"); return;
+        case B200_OP_ERFC: run_float<FErfc>(ctx, node, {}, "elementwise"); return;
+        case B200_OP_SIN: run_float<FSin>(ctx, node, {}, "elementwise"); return;
+        case B200_OP_COS: run_float<FCos>(ctx, node, {}, "elementwise"); return;
+        case B200_OP_TANH: run_float<FTanh>(ctx, node, {}, "elementwise"); return;
+        case B200_OP_SIGMOID: run_float<FSigmoid>(ctx, node, {}, "elementwise"); return;
+        case B200_OP_RELU: run_float<FRelu>(ctx, node, {}, "elementwise"); return;
+        case B200_OP_GELU: run_float<FGelu>(ctx, node, {}, "elementwise"); return;
+        case B200_OP_SILU: run_float<FSilu>(ctx, node, {}, "elementwise"); return;
         default: fail(B200_NOT_IMPLEMENTED, "elementwise: unhandled op");
     }
 }
