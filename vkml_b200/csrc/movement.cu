@@ -1404,7 +1404,9 @@ void launch_movement(b200_ctx* ctx, const b200_node& node) {
             const float* sp = reinterpret_cast<const float*>(src.data);
             const bool small = total < kMax32 && fits32(src) && istride >= 0 && istride * std::max<int64_t>(n_idx, 1) < kMax32;
             const int64_t extent = out.dim[axis];
-            if (n_idx >= 64 && n_idx < (int64_t(1) << 30) && extent < (int64_t(1) << 30) &&
+            // (worth its five small launches and its one-block scan over the destinations only when the
+            // pull form's outputs x indices reads are many and the destination axis is not enormous)
+            if (n_idx >= 256 && n_idx < (int64_t(1) << 30) && extent <= (int64_t(1) << 26) &&
                 double(total) * double(n_idx) >= 1e8) {
                 // bucket the indices by destination first (see above): five small launches and the gather
                 const size_t ints = static_cast<size_t>(3 * extent + 1 + 2 * n_idx);
