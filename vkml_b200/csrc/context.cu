@@ -716,336 +716,334 @@ int b200_supports(const b200_node* node) {
 
 // Queues one span, node by node (fused groups aside).
 static void compute_span(b200_ctx* ctx, const b200_node* nodes, size_t n_nodes, uint32_t flags) {
-    {
-        const bool grad_sync = (flags & B200_COMPUTE_GRAD_SYNC) != 0 && ctx->dist != nullptr;
-        // With no buffers registered, the gradients are the span's SINKS: f32 outputs that
-        // no later node of the span reads.  backward() realises exactly the leaf gradients
-        // (src/autograd/autograd.cpp:627-666), so every other output is consumed in-span.
-        ctx->in_grad_sync_span = grad_sync && ctx->dist != nullptr;
-        struct SpanGuard {
-            b200_ctx* c;
-            ~SpanGuard() {
-                c->in_grad_sync_span = false;
-                gemm_tc_end_span(c);
-            }
-        } span_guard{ctx};
-        count_matmul_operands(ctx, nodes, n_nodes);
-        std::vector<char> is_sink;
-        if (grad_sync && ctx->grads.empty()) {
-            is_sink.assign(n_nodes, 0);
-            auto bytes_of = [](const b200_tensor& t) {
-                size_t n = dtype_size(t.dtype);
-                for (int d = 0; d < t.ndim; ++d) n *= static_cast<size_t>(t.dims[d]);
-                return n;
-            };
-            for (size_t i = 0; i < n_nodes; ++i) {
-                const b200_node& node = nodes[i];
-                if (is_view_or_leaf(node.op) || node.out.dtype != B200_F32 || node.out.data == nullptr) continue;
-                const char* lo = static_cast<const char*>(node.out.data);
-                const char* hi = lo + bytes_of(node.out);
-                bool consumed = false;
-                for (size_t j = i + 1; j < n_nodes && !consumed; ++j) {
-                    for (uint32_t k = 0; k < nodes[j].n_src && k < B200_MAX_SRC; ++k) {
-                        const char* p = static_cast<const char*>(nodes[j].src[k].data);
-                        if (p >= lo && p < hi) {
-                            consumed = true;
-                            break;
-                        }
-                    }
-                }
-                is_sink[i] = consumed ? 0 : 1;
-            }
+    const bool grad_sync = (flags & B200_COMPUTE_GRAD_SYNC) != 0 && ctx->dist != nullptr;
+    // With no buffers registered, the gradients are the span's SINKS: f32 outputs that
+    // no later node of the span reads.  backward() realises exactly the leaf gradients
+    // (src/autograd/autograd.cpp:627-666), so every other output is consumed in-span.
+    ctx->in_grad_sync_span = grad_sync && ctx->dist != nullptr;
+    struct SpanGuard {
+        b200_ctx* c;
+        ~SpanGuard() {
+            c->in_grad_sync_span = false;
+            gemm_tc_end_span(c);
         }
-        // Execution order.  Only dependency order is contractual (backend.h:34-45), and the
-        // executor's depth-first order puts every parameter gradient at the tail of the span.
-        // When gradients are exchanged, each sink is hoisted to just after the last node it
-        // reads from, so its all-reduce runs under the remaining backward work instead of
-        // after it.  Every node still computes the same values from the same inputs.
-        std::vector<size_t> order;
-        order.reserve(n_nodes);
-        if (!is_sink.empty() && ctx->hoist_gradients) {
-            std::vector<std::vector<size_t>> deps(n_nodes);
-            std::vector<size_t> pending;
-            auto bytes_of = [](const b200_tensor& t) {
-                size_t n = dtype_size(t.dtype);
-                for (int d = 0; d < t.ndim; ++d) n *= static_cast<size_t>(t.dims[d]);
-                return n;
-            };
-            for (size_t j = 0; j < n_nodes; ++j) {
-                if (!is_sink[j]) continue;
-                pending.push_back(j);
-                for (uint32_t k = 0; k < nodes[j].n_src && k < B200_MAX_SRC; ++k) {
-                    const char* p = static_cast<const char*>(nodes[j].src[k].data);
-                    for (size_t i = j; i-- > 0;) {  // latest earlier writer of that address
-                        if (is_view_or_leaf(nodes[i].op) || nodes[i].out.data == nullptr) continue;
-                        const char* lo = static_cast<const char*>(nodes[i].out.data);
-                        if (p >= lo && p < lo + bytes_of(nodes[i].out)) {
-                            deps[j].push_back(i);
-                            break;
-                        }
-                    }
-                }
-            }
-            std::vector<char> emitted(n_nodes, 0);
-            auto flush = [&] {
-                for (size_t q = 0; q < pending.size();) {
-                    const size_t j = pending[q];
-                    bool ready = true;
-                    for (size_t d : deps[j]) ready = ready && emitted[d];
-                    if (ready) {
-                        order.push_back(j);
-                        emitted[j] = 1;
-                        pending.erase(pending.begin() + static_cast<std::ptrdiff_t>(q));
-                    } else {
-                        ++q;
-                    }
-                }
-            };
-            flush();
-            for (size_t i = 0; i < n_nodes; ++i) {
-                if (is_sink[i]) continue;
-                order.push_back(i);
-                emitted[i] = 1;
-                flush();
-            }
-        } else {
-            for (size_t i = 0; i < n_nodes; ++i) order.push_back(i);
-        }
-        auto tensor_bytes = [](const b200_tensor& t) {
+    } span_guard{ctx};
+    count_matmul_operands(ctx, nodes, n_nodes);
+    std::vector<char> is_sink;
+    if (grad_sync && ctx->grads.empty()) {
+        is_sink.assign(n_nodes, 0);
+        auto bytes_of = [](const b200_tensor& t) {
             size_t n = dtype_size(t.dtype);
             for (int d = 0; d < t.ndim; ++d) n *= static_cast<size_t>(t.dims[d]);
             return n;
         };
-        // All-reduces of an earlier gradient span may still be running.  Nodes are taken in the
-        // order their inputs become available: key = the latest pending all-reduce a node depends
-        // on, directly or through producers inside this span; a stable sort by that key keeps
-        // every producer before its consumers and leaves a span that touches no gradient as it is.
-        if (dist_has_pending(ctx) && n_nodes > 1) {
-            std::vector<int> key(n_nodes, -1);
-            for (size_t j = 0; j < n_nodes; ++j) {
-                const b200_node& node = nodes[j];
-                if (is_view_or_leaf(node.op)) continue;
-                int k = -1;
-                if (node.out.data != nullptr) {
-                    k = std::max(k, dist_pending_index(ctx, node.out.data,
-                                                       static_cast<const char*>(node.out.data) + tensor_bytes(node.out)));
-                }
-                for (uint32_t s = 0; s < node.n_src && s < B200_MAX_SRC; ++s) {
-                    const char* p = static_cast<const char*>(node.src[s].data);
-                    if (p == nullptr) continue;
-                    k = std::max(k, dist_pending_index(ctx, p, p + 1));
-                    for (size_t i = j; i-- > 0;) {  // latest earlier writer of that address
-                        if (is_view_or_leaf(nodes[i].op) || nodes[i].out.data == nullptr) continue;
-                        const char* lo = static_cast<const char*>(nodes[i].out.data);
-                        if (p >= lo && p < lo + tensor_bytes(nodes[i].out)) {
-                            k = std::max(k, key[i]);
-                            break;
-                        }
+        for (size_t i = 0; i < n_nodes; ++i) {
+            const b200_node& node = nodes[i];
+            if (is_view_or_leaf(node.op) || node.out.dtype != B200_F32 || node.out.data == nullptr) continue;
+            const char* lo = static_cast<const char*>(node.out.data);
+            const char* hi = lo + bytes_of(node.out);
+            bool consumed = false;
+            for (size_t j = i + 1; j < n_nodes && !consumed; ++j) {
+                for (uint32_t k = 0; k < nodes[j].n_src && k < B200_MAX_SRC; ++k) {
+                    const char* p = static_cast<const char*>(nodes[j].src[k].data);
+                    if (p >= lo && p < hi) {
+                        consumed = true;
+                        break;
                     }
                 }
-                key[j] = k;
             }
-            std::stable_sort(order.begin(), order.end(), [&](size_t a, size_t b) { return key[a] < key[b]; });
+            is_sink[i] = consumed ? 0 : 1;
         }
-        // What a node needs before its kernel may be queued, and what follows it.
-        auto prepare = [&](size_t i) {
-            const b200_node& node = nodes[i];
-            if (node.out.data == nullptr) {
-                fail(B200_INVALID_ARGUMENT, "node has no storage");
+    }
+    // Execution order.  Only dependency order is contractual (backend.h:34-45), and the
+    // executor's depth-first order puts every parameter gradient at the tail of the span.
+    // When gradients are exchanged, each sink is hoisted to just after the last node it
+    // reads from, so its all-reduce runs under the remaining backward work instead of
+    // after it.  Every node still computes the same values from the same inputs.
+    std::vector<size_t> order;
+    order.reserve(n_nodes);
+    if (!is_sink.empty() && ctx->hoist_gradients) {
+        std::vector<std::vector<size_t>> deps(n_nodes);
+        std::vector<size_t> pending;
+        auto bytes_of = [](const b200_tensor& t) {
+            size_t n = dtype_size(t.dtype);
+            for (int d = 0; d < t.ndim; ++d) n *= static_cast<size_t>(t.dims[d]);
+            return n;
+        };
+        for (size_t j = 0; j < n_nodes; ++j) {
+            if (!is_sink[j]) continue;
+            pending.push_back(j);
+            for (uint32_t k = 0; k < nodes[j].n_src && k < B200_MAX_SRC; ++k) {
+                const char* p = static_cast<const char*>(nodes[j].src[k].data);
+                for (size_t i = j; i-- > 0;) {  // latest earlier writer of that address
+                    if (is_view_or_leaf(nodes[i].op) || nodes[i].out.data == nullptr) continue;
+                    const char* lo = static_cast<const char*>(nodes[i].out.data);
+                    if (p >= lo && p < lo + bytes_of(nodes[i].out)) {
+                        deps[j].push_back(i);
+                        break;
+                    }
+                }
+            }
+        }
+        std::vector<char> emitted(n_nodes, 0);
+        auto flush = [&] {
+            for (size_t q = 0; q < pending.size();) {
+                const size_t j = pending[q];
+                bool ready = true;
+                for (size_t d : deps[j]) ready = ready && emitted[d];
+                if (ready) {
+                    order.push_back(j);
+                    emitted[j] = 1;
+                    pending.erase(pending.begin() + static_cast<std::ptrdiff_t>(q));
+                } else {
+                    ++q;
+                }
+            }
+        };
+        flush();
+        for (size_t i = 0; i < n_nodes; ++i) {
+            if (is_sink[i]) continue;
+            order.push_back(i);
+            emitted[i] = 1;
+            flush();
+        }
+    } else {
+        for (size_t i = 0; i < n_nodes; ++i) order.push_back(i);
+    }
+    auto tensor_bytes = [](const b200_tensor& t) {
+        size_t n = dtype_size(t.dtype);
+        for (int d = 0; d < t.ndim; ++d) n *= static_cast<size_t>(t.dims[d]);
+        return n;
+    };
+    // All-reduces of an earlier gradient span may still be running.  Nodes are taken in the
+    // order their inputs become available: key = the latest pending all-reduce a node depends
+    // on, directly or through producers inside this span; a stable sort by that key keeps
+    // every producer before its consumers and leaves a span that touches no gradient as it is.
+    if (dist_has_pending(ctx) && n_nodes > 1) {
+        std::vector<int> key(n_nodes, -1);
+        for (size_t j = 0; j < n_nodes; ++j) {
+            const b200_node& node = nodes[j];
+            if (is_view_or_leaf(node.op)) continue;
+            int k = -1;
+            if (node.out.data != nullptr) {
+                k = std::max(k, dist_pending_index(ctx, node.out.data,
+                                                   static_cast<const char*>(node.out.data) + tensor_bytes(node.out)));
             }
             for (uint32_t s = 0; s < node.n_src && s < B200_MAX_SRC; ++s) {
-                int64_t sn = 1;
-                for (int d = 0; d < node.src[s].ndim; ++d) sn *= node.src[s].dims[d];
-                if (sn != 0 && node.src[s].data == nullptr) {
-                    fail(B200_INVALID_ARGUMENT, "source " + std::to_string(s) + " has no storage");
-                }
-            }
-            if (dist_has_pending(ctx)) {
-                dist_wait_range(ctx, node.out.data, static_cast<const char*>(node.out.data) + tensor_bytes(node.out));
-                for (uint32_t s = 0; s < node.n_src && s < B200_MAX_SRC; ++s) {
-                    const char* p = static_cast<const char*>(node.src[s].data);
-                    if (p != nullptr) dist_wait_range(ctx, p, p + 1);
-                }
-            }
-            if (!ctx->plane_cache.empty()) {
-                // cannot happen under the caller's contract (outputs are fresh buffers), but a
-                // plane must never outlive the data it was split from
-                gemm_tc_invalidate(ctx, node.out.data, static_cast<const char*>(node.out.data) + tensor_bytes(node.out));
-            }
-        };
-        auto finish = [&](size_t i) {
-            const b200_node& node = nodes[i];
-            ctx->nodes_computed.fetch_add(1, std::memory_order_relaxed);
-            if (grad_sync) {
-                if (!is_sink.empty()) {
-                    if (is_sink[i]) {
-                        int64_t numel = 1;
-                        for (int d = 0; d < node.out.ndim; ++d) numel *= node.out.dims[d];
-                        dist_all_reduce_now(ctx, node.out.data, static_cast<size_t>(numel));
+                const char* p = static_cast<const char*>(node.src[s].data);
+                if (p == nullptr) continue;
+                k = std::max(k, dist_pending_index(ctx, p, p + 1));
+                for (size_t i = j; i-- > 0;) {  // latest earlier writer of that address
+                    if (is_view_or_leaf(nodes[i].op) || nodes[i].out.data == nullptr) continue;
+                    const char* lo = static_cast<const char*>(nodes[i].out.data);
+                    if (p >= lo && p < lo + tensor_bytes(nodes[i].out)) {
+                        k = std::max(k, key[i]);
+                        break;
                     }
-                } else {
-                    dist_after_node(ctx, node);
                 }
             }
-        };
-        // the nodes that need a kernel, in execution order
-        std::vector<size_t> exec;
-        exec.reserve(order.size());
-        for (const size_t i : order) {
-            const b200_node& node = nodes[i];
-            if (is_view_or_leaf(node.op)) {
-                continue;  // resolved by the executor through aliasing (backend.h:34-45)
-            }
-            if (node.op >= B200_OP_COUNT) {
-                fail(B200_NOT_IMPLEMENTED, "unknown op " + std::to_string(node.op));
-            }
-            // zero-element tensors are legal and need no work (vulkan_backend.cpp:1233-1236)
-            int64_t numel = 1;
-            for (int d = 0; d < node.out.ndim; ++d) numel *= node.out.dims[d];
-            if (numel != 0) exec.push_back(i);
+            key[j] = k;
         }
-        // Buffers a `full` node of this span filled with one value: a later elementwise node that
-        // reads such a buffer whole is handed a stride-0 view of its first element instead, and
-        // reads 4 bytes where it would have read the tensor (ReLU's backward mask compares against,
-        // and its `where` selects from, activation-sized tensors of zeros).
-        std::map<const void*, size_t> constants;
-        std::vector<char> done(exec.size(), 0);  // served ahead of its turn by a grouped launch
-        for (size_t p = 0; p < exec.size();) {
-            if (done[p]) {
-                ++p;
-                continue;
-            }
-            const size_t i = exec[p];
-            const b200_node& node = nodes[i];
-            if (ctx->fuse && exec.size() - p >= 2 &&
-                (node.op == B200_OP_ADD || node.op == B200_OP_FULL || node.op == B200_OP_EQUAL ||
-                 node.op == B200_OP_EXP)) {
-                const size_t avail = std::min<size_t>(exec.size() - p, 5);
-                const b200_node* seq[5];
-                bool eligible = true;
-                for (size_t k = 0; k < avail; ++k) {
-                    seq[k] = &nodes[exec[p + k]];
-                    // a gradient that this span all-reduces is exchanged as soon as its own kernel is queued
-                    eligible = eligible && (is_sink.empty() || !is_sink[exec[p + k]]) && seq[k]->out.data != nullptr;
-                    eligible = eligible && (!grad_sync || !is_sink.empty() || ctx->grads.empty());
-                }
-                if (eligible) {
-                    for (size_t k = 0; k < avail; ++k) prepare(exec[p + k]);
-                    ctx->current_op = node.op;
-                    const size_t taken = launch_fused(ctx, seq, avail);
-                    if (taken > 0) {
-                        for (size_t k = 0; k < taken; ++k) {
-                            if (seq[k]->op == B200_OP_FULL && seq[k]->out.dtype == B200_F32) {
-                                constants[seq[k]->out.data] = tensor_bytes(seq[k]->out);
-                            }
-                            finish(exec[p + k]);
-                        }
-                        p += taken;
-                        continue;
-                    }
-                }
-            }
-            if (ctx->fuse && node.op == B200_OP_MAX_POOL2D_BACKWARD && p + 1 < exec.size() && !done[p + 1]) {
-                // ReLU's backward rule behind a pooling layer: where(mask, zeros, pooling gradient)
-                const b200_node& wn = nodes[exec[p + 1]];
-                auto same_tensor = [](const b200_tensor& a, const b200_tensor& b) {
-                    if (a.data != b.data || a.dtype != b.dtype || a.ndim != b.ndim) return false;
-                    for (int d = 0; d < a.ndim; ++d) {
-                        if (a.dims[d] != b.dims[d] || (a.dims[d] > 1 && a.strides[d] != b.strides[d])) return false;
-                    }
-                    return true;
-                };
-                auto filled = [&](const b200_tensor& t) {
-                    if (t.dtype != B200_F32 || t.data == nullptr) return false;
-                    const auto it = constants.find(t.data);
-                    if (it != constants.end() && it->second == tensor_bytes(t)) return true;
-                    for (int d = 0; d < t.ndim; ++d) {
-                        if (t.dims[d] > 1 && t.strides[d] != 0) return false;
-                    }
-                    return true;
-                };
-                bool eligible = wn.op == B200_OP_WHERE && wn.n_src == 3 && node.out.data != nullptr && wn.out.data != nullptr;
-                for (const size_t k : {p, p + 1}) {
-                    eligible = eligible && (is_sink.empty() || !is_sink[exec[k]]);
-                }
-                eligible = eligible && (!grad_sync || !is_sink.empty() || ctx->grads.empty());
-                int side = -1;
-                if (eligible && same_tensor(wn.src[1], node.out) && filled(wn.src[2])) side = 1;
-                if (eligible && same_tensor(wn.src[2], node.out) && filled(wn.src[1])) side = 0;
-                if (side >= 0) {
-                    prepare(exec[p]);
-                    prepare(exec[p + 1]);
-                    ctx->current_op = node.op;
-                    if (launch_pool_backward_where(ctx, node, wn, side, wn.src[side == 1 ? 2 : 1].data)) {
-                        constants.erase(node.out.data);
-                        constants.erase(wn.out.data);
-                        finish(exec[p]);
-                        finish(exec[p + 1]);
-                        p += 2;
-                        continue;
-                    }
-                }
-            }
-            if (ctx->fuse && node.op == B200_OP_SCALED_ADD && exec.size() - p >= 2 && !grad_sync) {
-                // the optimiser's spans: independent scaled_add nodes, one launch for the dense ones among
-                // the next 24 nodes (a transposed gradient in between keeps its own kernel)
-                constexpr size_t kLook = 24;
-                const size_t avail = std::min<size_t>(exec.size() - p, kLook);
-                const b200_node* seq[kLook];
-                bool picked[kLook];
-                size_t run = 0;
-                while (run < avail && !done[p + run]) {
-                    seq[run] = &nodes[exec[p + run]];
-                    ++run;
-                }
-                if (run >= 2) {
-                    for (size_t k = 0; k < run; ++k) prepare(exec[p + k]);
-                    ctx->current_op = node.op;
-                    if (launch_scaled_add_group(ctx, seq, run, picked) > 0) {
-                        for (size_t k = 0; k < run; ++k) {
-                            if (picked[k]) {
-                                constants.erase(seq[k]->out.data);
-                                finish(exec[p + k]);
-                                done[p + k] = 1;
-                            }
-                        }
-                        if (done[p]) {
-                            ++p;
-                            continue;
-                        }
-                    }
-                }
-            }
-            prepare(i);
-            const bool elementwise = node.op == B200_OP_WHERE || (node.op >= B200_OP_ADD && node.op <= B200_OP_NOT_EQUAL);
-            if (ctx->fuse && elementwise && !constants.empty()) {
-                b200_node lean = node;
-                bool changed = false;
-                for (uint32_t s = 0; s < node.n_src && s < B200_MAX_SRC; ++s) {
-                    const auto it = constants.find(node.src[s].data);
-                    if (it != constants.end() && node.src[s].dtype == B200_F32 && it->second == tensor_bytes(node.src[s])) {
-                        for (int d = 0; d < lean.src[s].ndim; ++d) lean.src[s].strides[d] = 0;
-                        changed = true;
-                    }
-                }
-                dispatch_node(ctx, changed ? lean : node);
-            } else {
-                dispatch_node(ctx, node);
-            }
-            if (node.op == B200_OP_FULL && node.out.dtype == B200_F32) {
-                constants[node.out.data] = tensor_bytes(node.out);
-            } else {
-                constants.erase(node.out.data);  // (outputs are fresh buffers; kept exact regardless)
-            }
-            finish(i);
-            ++p;
+        std::stable_sort(order.begin(), order.end(), [&](size_t a, size_t b) { return key[a] < key[b]; });
+    }
+    // What a node needs before its kernel may be queued, and what follows it.
+    auto prepare = [&](size_t i) {
+        const b200_node& node = nodes[i];
+        if (node.out.data == nullptr) {
+            fail(B200_INVALID_ARGUMENT, "node has no storage");
         }
+        for (uint32_t s = 0; s < node.n_src && s < B200_MAX_SRC; ++s) {
+            int64_t sn = 1;
+            for (int d = 0; d < node.src[s].ndim; ++d) sn *= node.src[s].dims[d];
+            if (sn != 0 && node.src[s].data == nullptr) {
+                fail(B200_INVALID_ARGUMENT, "source " + std::to_string(s) + " has no storage");
+            }
+        }
+        if (dist_has_pending(ctx)) {
+            dist_wait_range(ctx, node.out.data, static_cast<const char*>(node.out.data) + tensor_bytes(node.out));
+            for (uint32_t s = 0; s < node.n_src && s < B200_MAX_SRC; ++s) {
+                const char* p = static_cast<const char*>(node.src[s].data);
+                if (p != nullptr) dist_wait_range(ctx, p, p + 1);
+            }
+        }
+        if (!ctx->plane_cache.empty()) {
+            // cannot happen under the caller's contract (outputs are fresh buffers), but a
+            // plane must never outlive the data it was split from
+            gemm_tc_invalidate(ctx, node.out.data, static_cast<const char*>(node.out.data) + tensor_bytes(node.out));
+        }
+    };
+    auto finish = [&](size_t i) {
+        const b200_node& node = nodes[i];
+        ctx->nodes_computed.fetch_add(1, std::memory_order_relaxed);
         if (grad_sync) {
-            dist_join(ctx);
+            if (!is_sink.empty()) {
+                if (is_sink[i]) {
+                    int64_t numel = 1;
+                    for (int d = 0; d < node.out.ndim; ++d) numel *= node.out.dims[d];
+                    dist_all_reduce_now(ctx, node.out.data, static_cast<size_t>(numel));
+                }
+            } else {
+                dist_after_node(ctx, node);
+            }
         }
-        if ((flags & B200_COMPUTE_SYNC) && !ctx->capturing) {
-            B200_CUDA_CHECK(cudaStreamSynchronize(ctx->stream));
+    };
+    // the nodes that need a kernel, in execution order
+    std::vector<size_t> exec;
+    exec.reserve(order.size());
+    for (const size_t i : order) {
+        const b200_node& node = nodes[i];
+        if (is_view_or_leaf(node.op)) {
+            continue;  // resolved by the executor through aliasing (backend.h:34-45)
         }
+        if (node.op >= B200_OP_COUNT) {
+            fail(B200_NOT_IMPLEMENTED, "unknown op " + std::to_string(node.op));
+        }
+        // zero-element tensors are legal and need no work (vulkan_backend.cpp:1233-1236)
+        int64_t numel = 1;
+        for (int d = 0; d < node.out.ndim; ++d) numel *= node.out.dims[d];
+        if (numel != 0) exec.push_back(i);
+    }
+    // Buffers a `full` node of this span filled with one value: a later elementwise node that
+    // reads such a buffer whole is handed a stride-0 view of its first element instead, and
+    // reads 4 bytes where it would have read the tensor (ReLU's backward mask compares against,
+    // and its `where` selects from, activation-sized tensors of zeros).
+    std::map<const void*, size_t> constants;
+    std::vector<char> done(exec.size(), 0);  // served ahead of its turn by a grouped launch
+    for (size_t p = 0; p < exec.size();) {
+        if (done[p]) {
+            ++p;
+            continue;
+        }
+        const size_t i = exec[p];
+        const b200_node& node = nodes[i];
+        if (ctx->fuse && exec.size() - p >= 2 &&
+            (node.op == B200_OP_ADD || node.op == B200_OP_FULL || node.op == B200_OP_EQUAL ||
+             node.op == B200_OP_EXP)) {
+            const size_t avail = std::min<size_t>(exec.size() - p, 5);
+            const b200_node* seq[5];
+            bool eligible = true;
+            for (size_t k = 0; k < avail; ++k) {
+                seq[k] = &nodes[exec[p + k]];
+                // a gradient that this span all-reduces is exchanged as soon as its own kernel is queued
+                eligible = eligible && (is_sink.empty() || !is_sink[exec[p + k]]) && seq[k]->out.data != nullptr;
+                eligible = eligible && (!grad_sync || !is_sink.empty() || ctx->grads.empty());
+            }
+            if (eligible) {
+                for (size_t k = 0; k < avail; ++k) prepare(exec[p + k]);
+                ctx->current_op = node.op;
+                const size_t taken = launch_fused(ctx, seq, avail);
+                if (taken > 0) {
+                    for (size_t k = 0; k < taken; ++k) {
+                        if (seq[k]->op == B200_OP_FULL && seq[k]->out.dtype == B200_F32) {
+                            constants[seq[k]->out.data] = tensor_bytes(seq[k]->out);
+                        }
+                        finish(exec[p + k]);
+                    }
+                    p += taken;
+                    continue;
+                }
+            }
+        }
+        if (ctx->fuse && node.op == B200_OP_MAX_POOL2D_BACKWARD && p + 1 < exec.size() && !done[p + 1]) {
+            // ReLU's backward rule behind a pooling layer: where(mask, zeros, pooling gradient)
+            const b200_node& wn = nodes[exec[p + 1]];
+            auto same_tensor = [](const b200_tensor& a, const b200_tensor& b) {
+                if (a.data != b.data || a.dtype != b.dtype || a.ndim != b.ndim) return false;
+                for (int d = 0; d < a.ndim; ++d) {
+                    if (a.dims[d] != b.dims[d] || (a.dims[d] > 1 && a.strides[d] != b.strides[d])) return false;
+                }
+                return true;
+            };
+            auto filled = [&](const b200_tensor& t) {
+                if (t.dtype != B200_F32 || t.data == nullptr) return false;
+                const auto it = constants.find(t.data);
+                if (it != constants.end() && it->second == tensor_bytes(t)) return true;
+                for (int d = 0; d < t.ndim; ++d) {
+                    if (t.dims[d] > 1 && t.strides[d] != 0) return false;
+                }
+                return true;
+            };
+            bool eligible = wn.op == B200_OP_WHERE && wn.n_src == 3 && node.out.data != nullptr && wn.out.data != nullptr;
+            for (const size_t k : {p, p + 1}) {
+                eligible = eligible && (is_sink.empty() || !is_sink[exec[k]]);
+            }
+            eligible = eligible && (!grad_sync || !is_sink.empty() || ctx->grads.empty());
+            int side = -1;
+            if (eligible && same_tensor(wn.src[1], node.out) && filled(wn.src[2])) side = 1;
+            if (eligible && same_tensor(wn.src[2], node.out) && filled(wn.src[1])) side = 0;
+            if (side >= 0) {
+                prepare(exec[p]);
+                prepare(exec[p + 1]);
+                ctx->current_op = node.op;
+                if (launch_pool_backward_where(ctx, node, wn, side, wn.src[side == 1 ? 2 : 1].data)) {
+                    constants.erase(node.out.data);
+                    constants.erase(wn.out.data);
+                    finish(exec[p]);
+                    finish(exec[p + 1]);
+                    p += 2;
+                    continue;
+                }
+            }
+        }
+        if (ctx->fuse && node.op == B200_OP_SCALED_ADD && exec.size() - p >= 2 && !grad_sync) {
+            // the optimiser's spans: independent scaled_add nodes, one launch for the dense ones among
+            // the next 24 nodes (a transposed gradient in between keeps its own kernel)
+            constexpr size_t kLook = 24;
+            const size_t avail = std::min<size_t>(exec.size() - p, kLook);
+            const b200_node* seq[kLook];
+            bool picked[kLook];
+            size_t run = 0;
+            while (run < avail && !done[p + run]) {
+                seq[run] = &nodes[exec[p + run]];
+                ++run;
+            }
+            if (run >= 2) {
+                for (size_t k = 0; k < run; ++k) prepare(exec[p + k]);
+                ctx->current_op = node.op;
+                if (launch_scaled_add_group(ctx, seq, run, picked) > 0) {
+                    for (size_t k = 0; k < run; ++k) {
+                        if (picked[k]) {
+                            constants.erase(seq[k]->out.data);
+                            finish(exec[p + k]);
+                            done[p + k] = 1;
+                        }
+                    }
+                    if (done[p]) {
+                        ++p;
+                        continue;
+                    }
+                }
+            }
+        }
+        prepare(i);
+        const bool elementwise = node.op == B200_OP_WHERE || (node.op >= B200_OP_ADD && node.op <= B200_OP_NOT_EQUAL);
+        if (ctx->fuse && elementwise && !constants.empty()) {
+            b200_node lean = node;
+            bool changed = false;
+            for (uint32_t s = 0; s < node.n_src && s < B200_MAX_SRC; ++s) {
+                const auto it = constants.find(node.src[s].data);
+                if (it != constants.end() && node.src[s].dtype == B200_F32 && it->second == tensor_bytes(node.src[s])) {
+                    for (int d = 0; d < lean.src[s].ndim; ++d) lean.src[s].strides[d] = 0;
+                    changed = true;
+                }
+            }
+            dispatch_node(ctx, changed ? lean : node);
+        } else {
+            dispatch_node(ctx, node);
+        }
+        if (node.op == B200_OP_FULL && node.out.dtype == B200_F32) {
+            constants[node.out.data] = tensor_bytes(node.out);
+        } else {
+            constants.erase(node.out.data);  // (outputs are fresh buffers; kept exact regardless)
+        }
+        finish(i);
+        ++p;
+    }
+    if (grad_sync) {
+        dist_join(ctx);
+    }
+    if ((flags & B200_COMPUTE_SYNC) && !ctx->capturing) {
+        B200_CUDA_CHECK(cudaStreamSynchronize(ctx->stream));
     }
 }
 
