@@ -40,11 +40,12 @@ THREADS = os.cpu_count() or 1
 
 
 def record(**fields):
-    """Measured errors go to stdout and, where a run's output folder exists, into it."""
+    """Measured errors go to stdout and, when VKML_B200_TEST_RECORDS names a directory, into a
+    JSON-lines file there."""
     line = json.dumps(fields)
     print(line)
-    out = os.path.join(ROOT, "gpurun_out")
-    if os.path.isdir(out):
+    out = os.environ.get("VKML_B200_TEST_RECORDS", "")
+    if out and os.path.isdir(out):
         with open(os.path.join(out, "parity_measured.jsonl"), "a") as f:
             f.write(line + "\n")
 

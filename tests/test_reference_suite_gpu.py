@@ -67,8 +67,8 @@ def run_suite(files, timeout, also_deselect=()):
     env = dict(os.environ, PYTHONPATH=os.path.join(REF, "python"), VKML_TEST_DEVICE="0")
     run = subprocess.run(args + files, cwd=SUITE, env=env, capture_output=True, text=True, timeout=timeout)
     tail = run.stdout[-6000:]
-    out = os.path.join(os.path.dirname(HERE), "gpurun_out")
-    if os.path.isdir(out):
+    out = os.environ.get("VKML_B200_TEST_RECORDS", "")  # a directory for the suite's full output, if wanted
+    if out and os.path.isdir(out):
         with open(os.path.join(out, "reference_suite.log"), "a") as f:
             f.write(run.stdout + run.stderr)
     summary = re.search(r"(\d+) passed", run.stdout)
