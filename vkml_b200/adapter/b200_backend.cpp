@@ -164,7 +164,7 @@ B200Backend::B200Backend(int cuda_ordinal, int device_index)
     for (const char* name : {"VKML_B200_GEMM_PRECISION", "VKML_B200_GEMM_OPERANDS", "VKML_B200_GEMM_STREAM",
                              "VKML_B200_GEMM_SCHEDULE", "VKML_B200_SHARE_PLANES", "VKML_B200_PDL",
                              "VKML_B200_LAZY_JOIN", "VKML_B200_HOIST_GRADIENTS", "VKML_B200_COMM_SMS",
-                             "VKML_B200_FUSE", "VKML_B200_BUCKET", "VKML_B200_COMM_TIMEOUT_MS", "VKML_B200_DIST_INIT_TIMEOUT_MS",
+                             "VKML_B200_FUSE", "VKML_B200_BUCKET", "VKML_B200_BUCKET_FLUSH_BYTES", "VKML_B200_COMM_TIMEOUT_MS", "VKML_B200_DIST_INIT_TIMEOUT_MS",
                              "VKML_B200_UPLOAD_THREADS", "VKML_B200_SPAN_GRAPHS"}) {
         (void)vkml::env_value(name);
     }

@@ -618,6 +618,9 @@ int b200_create(int cuda_ordinal, b200_ctx** out) {
         if (const char* e = std::getenv("VKML_B200_BUCKET")) {
             ctx->bucket_grads = std::atoi(e) != 0;
         }
+        if (const char* e = std::getenv("VKML_B200_BUCKET_FLUSH_BYTES")) {
+            ctx->bucket_flush_bytes = static_cast<size_t>(std::max<long long>(1, std::atoll(e)));
+        }
         if (const char* e = std::getenv("VKML_B200_LAZY_JOIN")) {
             ctx->lazy_join = std::atoi(e) != 0;
         }

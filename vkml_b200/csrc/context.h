@@ -143,6 +143,7 @@ struct b200_ctx {
     // updates of the early-reduced parameters run under the tail of the communication.
     bool lazy_join = true;
     bool bucket_grads = true;  // small gradients of a span leave as one grouped NCCL launch (VKML_B200_BUCKET)
+    size_t bucket_flush_bytes = size_t(1) << 20;  // ... which leaves when it holds this much (VKML_B200_BUCKET_FLUSH_BYTES), or at the end of the span
     bool fuse = true;  // in-span fusion of the node sequences autograd always emits (VKML_B200_FUSE, fuse.cu)
     bool pdl = true;  // programmatic dependent launch between consecutive kernels (VKML_B200_PDL)
     bool in_grad_sync_span = false;

@@ -140,7 +140,6 @@ struct DistState {
 };
 
 constexpr size_t kBucketEachBytes = size_t(4) << 20;    // gradients below this are grouped
-constexpr size_t kBucketFlushBytes = size_t(32) << 20;  // ... and the group leaves when it holds this much
 
 // Issues the all-reduces of `items` on the communication stream, ordered after everything queued
 // on the compute stream so far; more than one item goes out as one NCCL group (one launch).
@@ -200,7 +199,7 @@ static void all_reduce_mean(b200_ctx* ctx, void* data, size_t count, bool may_de
     if (may_defer && ctx->bucket_grads && bytes < kBucketEachBytes) {
         d->bucket.push_back(DistState::Deferred{data, count});
         d->bucket_bytes += bytes;
-        if (d->bucket_bytes >= kBucketFlushBytes) flush_bucket(ctx);
+        if (d->bucket_bytes >= ctx->bucket_flush_bytes) flush_bucket(ctx);
         return;
     }
     const DistState::Deferred one{data, count};
