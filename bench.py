@@ -694,6 +694,7 @@ def run_gemm_sweep(args, local_rank):
               ("conv2 fwd W[128x576] bcast . cols[256][576x256]", 256, 128, 576, 256, "bn"),
               ("conv3 fwd W[256x1152] bcast . cols[256][1152x64]", 256, 256, 1152, 64, "bn"),
               ("conv1 fwd W[64x27] bcast . cols[256][27x1024]", 256, 64, 27, 1024, "bn"),
+              ("conv1 dW g[256][64x1024] . cols^T[256][1024x27]", 256, 64, 1024, 27, "nT"),
               ("conv2 dcols W^T[576x128] bcast . g[256][128x256]", 256, 576, 128, 256, "Bn"),
               ("conv2 dW g[256][128x256] . cols^T[256][256x576]", 256, 128, 256, 576, "nT"),
               ("conv3 dcols W^T[1152x256] bcast . g[256][256x64]", 256, 1152, 256, 64, "Bn"),

@@ -1598,11 +1598,22 @@ Operand plan_operand(const float* ptr, int64_t s_b0, int64_t s_b1, int64_t s_mn,
 
 // Whether reading the operands directly beats splitting them into planes first.  Measured: the
 // in-kernel split is bound by shared-memory traffic (the converter's loads and stores contend
-// with the tensor core's operand reads), 7.5 ms against 4.5 ms at 8192^3 and 1.09 ms against
-// 0.97 ms over the GEMMs of the CNN step; it wins only on isolated HBM-bound products whose
-// planes nobody else uses (conv2 forward alone: 0.100 ms against 0.164 ms).  So the automatic
-// choice is always planes, and the direct variant is an opt-in (VKML_B200_GEMM_OPERANDS=direct).
-bool direct_pays(const GemmProblem&, int64_t, int) { return false; }
+// with the tensor core's operand reads) at about 147 TFLOP/s of algorithmic work -- 7.5 ms against
+// 4.5 ms at 8192^3, 0.32 against 0.31 ms at 512 x 65536 x 512 -- while the plane scheme moves each
+// operand five times (read, two planes written, two planes read).  It pays where that traffic is
+// what the product costs and nobody else in the span uses the planes: the CNN's first
+// weight gradient, g[256][64x1024] . cols^T[256][1024x27], 74 us against 105; the CNN's head,
+// 19 against 24 us.
+bool direct_pays(const b200_ctx* ctx, const GemmProblem& p, int64_t batches, const Operand& oa, const Operand& ob) {
+    auto shared = [&](const Operand& o) {
+        const auto it = ctx->plane_uses.find(o.key);
+        return it != ctx->plane_uses.end() && it->second >= 2;
+    };
+    if (shared(oa) || shared(ob)) return false;
+    const double flops = 2.0 * double(p.m) * double(p.n) * double(p.k) * double(batches);
+    const double operand_bytes = double(oa.plane_bytes) + double(ob.plane_bytes);
+    return flops / 147e12 < 4.0 * operand_bytes / 6.5e12;
+}
 
 size_t plane_cache_limit(const b200_ctx* ctx) {
     return std::min<size_t>(size_t(16) << 30, ctx->prop.totalGlobalMem / 8);
@@ -1901,7 +1912,7 @@ void gemm_tc(b200_ctx* ctx, const GemmProblem& p, bool three_pass) {
     // ---- direct operands: no planes at all ----
     const bool want_dynamic = ctx->gemm_schedule == 1 || (ctx->gemm_schedule < 0 && ctx->in_grad_sync_span);
     if (ctx->gemm_operands != 0 && oa.dense && ob.dense && !want_dynamic &&
-        (ctx->gemm_operands == 1 || direct_pays(p, batches, bn))) {
+        (ctx->gemm_operands == 1 || direct_pays(ctx, p, batches, oa, ob))) {
         float* partial = nullptr;
         if (splits > 1) {
             char* ws = static_cast<char*>(ctx->ensure_workspace(partial_bytes + 2048));
