@@ -448,6 +448,105 @@ reduce_thread4_kernel(float* out, float4* partial, unsigned* counters, const flo
     }
 }
 
+// Column sums with a dense kept axis, second form: a block is 64 output quads wide (1 KB of every
+// row) and FOUR row-lanes deep.  Row-lane l of K-slice s takes the reduced indices
+// (g * splits + s) * 32 + l * 8 + u, u < 8 -- eight vectors in flight per thread -- the four lanes
+// meet in shared memory in lane order, and only then does the block hand a partial row to the
+// last block of its column stripe.  Against one quad per thread and no row-lanes this needs a
+// quarter of the K-slices for the same number of blocks: a quarter of the partial rows, and a
+// fold that is two rounds of loads instead of five.
+template <typename P, typename I>
+__global__ void __launch_bounds__(256)
+reduce_lanes4_kernel(float* out, float4* partial, unsigned* counters, const float* __restrict__ in,
+                     RedGeoT<I> g, int64_t n_out4, I n_red, int post) {
+    pdl_prologue();
+    constexpr int U = 8;
+    __shared__ float4 part[4][64];
+    __shared__ int last_flag;
+    const int q = threadIdx.x & 63;
+    const int lane = threadIdx.x >> 6;
+    const int64_t o4 = int64_t(blockIdx.x) * 64 + q;
+    const I split = blockIdx.y;
+    const I splits = gridDim.y;
+    const bool live = o4 < n_out4;
+    float acc[4] = {P::init(), P::init(), P::init(), P::init()};
+    if (live) {
+        const I base = walk<I>(g.kdim, g.kstride, g.kdiv, g.krank, static_cast<I>(o4));
+        for (int64_t kb64 = int64_t(split) * (4 * U) + lane * U; kb64 < int64_t(n_red); kb64 += int64_t(splits) * (4 * U)) {
+            const I kb = static_cast<I>(kb64);
+            float4 v[U];
+#pragma unroll
+            for (int u = 0; u < U; ++u) {
+                if (kb + u < n_red) {
+                    v[u] = *reinterpret_cast<const float4*>(in + base + walk<I>(g.rdim, g.rstride, g.rdiv, g.rrank, kb + u));
+                }
+            }
+#pragma unroll
+            for (int u = 0; u < U; ++u) {
+                if (kb + u < n_red) {
+                    acc[0] = P::step(acc[0], v[u].x, 0);
+                    acc[1] = P::step(acc[1], v[u].y, 0);
+                    acc[2] = P::step(acc[2], v[u].z, 0);
+                    acc[3] = P::step(acc[3], v[u].w, 0);
+                }
+            }
+        }
+    }
+    part[lane][q] = make_float4(acc[0], acc[1], acc[2], acc[3]);
+    __syncthreads();
+    float t[4] = {P::init(), P::init(), P::init(), P::init()};
+    if (lane == 0) {
+#pragma unroll
+        for (int l = 0; l < 4; ++l) {
+            const float4 w = part[l][q];
+            t[0] = P::merge(t[0], w.x);
+            t[1] = P::merge(t[1], w.y);
+            t[2] = P::merge(t[2], w.z);
+            t[3] = P::merge(t[3], w.w);
+        }
+    }
+    auto finish = [&](float v) {
+        if (post == kPostMean) {
+            return n_red == 0 ? __int_as_float(0x7fc00000) : v / static_cast<float>(n_red);
+        }
+        return v;
+    };
+    if (partial == nullptr) {
+        if (lane == 0 && live) {
+            reinterpret_cast<float4*>(out)[o4] = make_float4(finish(t[0]), finish(t[1]), finish(t[2]), finish(t[3]));
+        }
+        return;
+    }
+    if (lane == 0 && live) {
+        partial[int64_t(split) * n_out4 + o4] = make_float4(t[0], t[1], t[2], t[3]);
+    }
+    if (!last_block_of(counters + blockIdx.x, splits, &last_flag)) {
+        return;
+    }
+    if (lane == 0 && live) {
+        float r[4] = {P::init(), P::init(), P::init(), P::init()};
+        for (I s0 = 0; s0 < splits; s0 += 8) {
+            float4 w[8];
+#pragma unroll
+            for (int u = 0; u < 8; ++u) {
+                if (s0 + u < splits) {
+                    w[u] = __ldcg(partial + int64_t(s0 + u) * n_out4 + o4);
+                }
+            }
+#pragma unroll
+            for (int u = 0; u < 8; ++u) {
+                if (s0 + u < splits) {
+                    r[0] = P::merge(r[0], w[u].x);
+                    r[1] = P::merge(r[1], w[u].y);
+                    r[2] = P::merge(r[2], w[u].z);
+                    r[3] = P::merge(r[3], w[u].w);
+                }
+            }
+        }
+        reinterpret_cast<float4*>(out)[o4] = make_float4(finish(r[0]), finish(r[1]), finish(r[2]), finish(r[3]));
+    }
+}
+
 // Fallback fold for launches with more blocks than counters. partial is [split][output].
 template <typename P>
 __global__ void __launch_bounds__(256)
@@ -569,6 +668,23 @@ void launch_reduce_kernels(b200_ctx* ctx, const View& out, const float* src, con
                 g4.kdim[kMaxDims - 1] = static_cast<I>(k_run / 4);
                 set_divisors(g4);
                 g4.kstride[kMaxDims - 1] = 4;
+                const int64_t bx64 = ceil_div(n_out4, 64);
+                if (n_red >= 128 && bx64 <= kMaxCounters) {
+                    // three blocks per SM is what the kernel's registers allow: one full wave (measured at
+                    // 2048 x 8192: 16.6 us with two per SM, 15.4 with three, 17.2 with four; 17.0 before)
+                    int64_t sl = ceil_div(int64_t(sm_count()) * 3, bx64);
+                    sl = std::max<int64_t>(1, std::min<int64_t>(std::min<int64_t>(sl, n_red / 64), 256));
+                    float4* part4 = nullptr;
+                    if (sl > 1) {
+                        part4 = static_cast<float4*>(ctx->ensure_workspace(sizeof(float4) * n_out4 * sl));
+                    }
+                    dim3 gridl(static_cast<unsigned>(bx64), static_cast<unsigned>(sl));
+                    launch_kernel(ctx, reduce_lanes4_kernel<P, I>, gridl, 256, 0, reinterpret_cast<float*>(out.data), part4,
+                                  ctx->d_counters, src, g4, n_out4, static_cast<I>(n_red), post);
+                    ctx->count_launch();
+                    check_last_launch("reduce (row lanes)");
+                    return;
+                }
                 float4* part = nullptr;
                 if (sp > 1) {
                     part = static_cast<float4*>(ctx->ensure_workspace(sizeof(float4) * n_out4 * sp));
