@@ -672,7 +672,13 @@ void launch_reduce_kernels(b200_ctx* ctx, const View& out, const float* src, con
                 if (n_red >= 128 && bx64 <= kMaxCounters) {
                     // three blocks per SM is what the kernel's registers allow: one full wave (measured at
                     // 2048 x 8192: 16.6 us with two per SM, 15.4 with three, 17.2 with four; 17.0 before)
-                    int64_t sl = ceil_div(int64_t(sm_count()) * 3, bx64);
+                    int lanes_per_sm = 0;
+                    if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&lanes_per_sm, reduce_lanes4_kernel<P, I>, 256, 0) != cudaSuccess ||
+                        lanes_per_sm < 1) {
+                        cudaGetLastError();
+                        lanes_per_sm = 3;
+                    }
+                    int64_t sl = ceil_div(int64_t(sm_count()) * lanes_per_sm, bx64);
                     sl = std::max<int64_t>(1, std::min<int64_t>(std::min<int64_t>(sl, n_red / 64), 256));
                     float4* part4 = nullptr;
                     if (sl > 1) {
