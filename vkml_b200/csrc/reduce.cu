@@ -678,7 +678,7 @@ void launch_reduce_kernels(b200_ctx* ctx, const View& out, const float* src, con
                         cudaGetLastError();
                         lanes_per_sm = 3;
                     }
-                    int64_t sl = ceil_div(int64_t(sm_count()) * lanes_per_sm, bx64);
+                    int64_t sl = int64_t(sm_count()) * lanes_per_sm / bx64;  // every block resident at once
                     sl = std::max<int64_t>(1, std::min<int64_t>(std::min<int64_t>(sl, n_red / 64), 256));
                     float4* part4 = nullptr;
                     if (sl > 1) {
