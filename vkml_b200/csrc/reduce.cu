@@ -236,6 +236,10 @@ reduce_group_kernel(void* out, typename P::Acc* partial, unsigned* counters, con
     const bool live = o < n_out;
     if (live) {
         const I base = walk<I>(g.kdim, g.kstride, g.kdiv, g.krank, static_cast<I>(o));
+        // one accumulator per vector component: a thread that walks millions of elements (a mean over
+        // 2^31 of them) then adds four chains a quarter as long, which keeps a float sum's rounding
+        // error well inside the tolerance the CPU's pairwise sums set
+        typename P::Acc acc4[4] = {P::init(), P::init(), P::init(), P::init()};
         for (int64_t kb64 = int64_t(split) * (GROUP * U) + lane; kb64 < int64_t(n_units);
              kb64 += int64_t(splits) * (GROUP * U)) {
             const I kb = static_cast<I>(kb64);
@@ -254,10 +258,10 @@ reduce_group_kernel(void* out, typename P::Acc* partial, unsigned* counters, con
                     if (k < n_units) {
                         // element index of v.x in reduced (row-major) order, for argmax / argmin
                         const int64_t e = int64_t(k) * 4;
-                        acc = P::step(acc, v[u].x, e);
-                        acc = P::step(acc, v[u].y, e + 1);
-                        acc = P::step(acc, v[u].z, e + 2);
-                        acc = P::step(acc, v[u].w, e + 3);
+                        acc4[0] = P::step(acc4[0], v[u].x, e);
+                        acc4[1] = P::step(acc4[1], v[u].y, e + 1);
+                        acc4[2] = P::step(acc4[2], v[u].z, e + 2);
+                        acc4[3] = P::step(acc4[3], v[u].w, e + 3);
                     }
                 }
             } else {
@@ -277,6 +281,9 @@ reduce_group_kernel(void* out, typename P::Acc* partial, unsigned* counters, con
                     }
                 }
             }
+        }
+        if constexpr (VEC4) {
+            acc = P::merge(P::merge(acc4[0], acc4[1]), P::merge(acc4[2], acc4[3]));
         }
     }
     acc = group_fold<P, GROUP>(acc, smem);
