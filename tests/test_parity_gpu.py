@@ -402,6 +402,38 @@ def test_device_copies(backend):
     assert z.data == 0 and z.nbytes == 0
 
 
+def test_which_kernel_a_product_gets(backend):
+    """b200_matmul_kernel names the kernel a product would get, taken by itself, and the profile of
+    the product run by itself agrees: CUDA cores for a tiny product, operand planes for a large
+    square one, the streamed operand for a skinny one and for a convolution's weight gradient, the
+    operands read directly where a byte model says the plane passes would cost more than the product."""
+    from vkml_b200 import DeviceTensor, NodeDesc
+    rng = np.random.default_rng(31)
+
+    def dev(*shape):
+        return DeviceTensor.from_host(backend, rng.standard_normal(shape).astype(np.float32))
+
+    def product(a, b, shape):
+        return NodeDesc(Op.MATMUL, DeviceTensor.empty(backend, shape).desc, [a.desc, b.desc])
+
+    cases = [
+        ("fp32_simt", product(dev(1, 1, 24, 40), dev(1, 1, 40, 24), (1, 1, 24, 24))),
+        ("tcgen05_3xtf32", product(dev(1, 1, 1024, 1024), dev(1, 1, 1024, 1024), (1, 1, 1024, 1024))),
+        ("tcgen05_3xtf32_stream", product(dev(1, 1, 64, 2048), dev(1, 1, 2048, 512), (1, 1, 64, 512))),
+        ("tcgen05_3xtf32_stream", product(dev(1, 4, 128, 256), dev(1, 4, 576, 256).transpose(2, 3), (1, 4, 128, 576))),
+        # the first convolution's weight gradient: N = 27 keeps it off the streamed-operand kernel
+        ("tcgen05_3xtf32_direct", product(dev(1, 16, 64, 1024), dev(1, 16, 27, 1024).transpose(2, 3), (1, 16, 64, 27))),
+    ]
+    for want, node in cases:
+        name, why = backend.matmul_kernel(node)
+        assert name == want and why, (want, name, why)
+        backend.set_profiling(True)
+        backend.compute([node])
+        labels = [l for l, _ in backend.last_profile()]
+        backend.set_profiling(False)
+        assert "matmul." + want in labels, (want, labels)
+
+
 def test_a_span_that_comes_back_is_replayed_as_a_graph_with_fresh_data(oracle, monkeypatch):
     """The same span on the same buffers, seven times with new input data each time: from the third
     submission on it is one CUDA graph launch, and every result is the one the eager path gives

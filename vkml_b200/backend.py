@@ -119,6 +119,14 @@ class Backend:
         c = node.to_c()
         return bool(self._lib.b200_supports(C.byref(c)))
 
+    def matmul_kernel(self, node: NodeDesc) -> tuple:
+        """(kernel, reason) a matmul node would get, taken by itself: fp32_simt, tcgen05_3xtf32 (operand
+        planes), tcgen05_3xtf32_stream (streamed operand) or tcgen05_3xtf32_direct (operands read directly)."""
+        c = node.to_c()
+        name, why = C.create_string_buffer(64), C.create_string_buffer(160)
+        self._check(self._lib.b200_matmul_kernel(self._ctx, C.byref(c), name, 64, why, 160), "matmul_kernel")
+        return name.value.decode(), why.value.decode()
+
     def compute(self, nodes: Sequence[NodeDesc], flags: int = 0) -> None:
         """Backend::compute: ordered when this returns, not necessarily finished."""
         self.compute_packed(pack_nodes(nodes), len(nodes), flags)

@@ -1388,6 +1388,9 @@ int b200_matmul_kernel(b200_ctx* ctx, const b200_node* node, char* name, size_t 
             if (gemm_tc_streams(ctx, p)) {
                 kernel = three ? "tcgen05_3xtf32_stream" : "tcgen05_tf32_stream";
                 why = "bound by memory (a small left operand or a short K): the right operand is read as fp32 and split on the way";
+            } else if (gemm_tc_reads_directly(ctx, p)) {
+                kernel = three ? "tcgen05_3xtf32_direct" : "tcgen05_tf32_direct";
+                why = "the plane passes would cost more than the product: fp32 tiles by TMA, split inside the kernel";
             } else {
                 kernel = three ? "tcgen05_3xtf32" : "tcgen05_tf32";
                 why = "operands split into TF32 planes, tensor-core tiles fed by TMA";

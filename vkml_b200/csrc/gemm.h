@@ -27,6 +27,7 @@ void gemm_tc(b200_ctx* ctx, const GemmProblem& p, bool three_pass);
 // True when gemm_tc would serve `p` with the streamed-operand kernel (a small left operand, the
 // right operand read once from HBM) rather than from operand planes.
 bool gemm_tc_streams(const b200_ctx* ctx, const GemmProblem& p);
+bool gemm_tc_reads_directly(const b200_ctx* ctx, const GemmProblem& p);  // (taken by itself: no shared planes)
 // Diagnostic: one block waits `limit_ns` on a barrier nobody arrives on and gives up (gemm_tc.cu).
 void gemm_tc_wait_probe(b200_ctx* ctx, uint64_t limit_ns);
 

@@ -1856,6 +1856,19 @@ bool gemm_tc_eligible(const b200_ctx* ctx, const GemmProblem& p) {
 
 bool gemm_tc_streams(const b200_ctx* ctx, const GemmProblem& p) { return plan_stream(ctx, p).ok; }
 
+// Whether gemm_tc would read this product's operands directly (no planes), taken by itself: the
+// same conditions as in gemm_tc below, with no other matmul of a span sharing the planes.
+bool gemm_tc_reads_directly(const b200_ctx* ctx, const GemmProblem& p) {
+    if (plan_stream(ctx, p).ok || ctx->gemm_operands == 0) return false;
+    const int64_t batches = p.b0 * p.b1;
+    const bool a_bcast = (p.a_s[0] == 0 || p.b0 == 1) && (p.a_s[1] == 0 || p.b1 == 1);
+    const bool b_bcast = (p.b_s[0] == 0 || p.b0 == 1) && (p.b_s[1] == 0 || p.b1 == 1);
+    const Operand oa = plan_operand(p.a, p.a_s[0], p.a_s[1], p.a_s[2], p.a_s[3], p.m, p.k, a_bcast, p);
+    const Operand ob = plan_operand(p.b, p.b_s[0], p.b_s[1], p.b_s[3], p.b_s[2], p.n, p.k, b_bcast, p);
+    const bool want_dynamic = ctx->gemm_schedule == 1;
+    return oa.dense && ob.dense && !want_dynamic && (ctx->gemm_operands == 1 || direct_pays(ctx, p, batches, oa, ob));
+}
+
 void gemm_tc_wait_probe(b200_ctx* ctx, uint64_t limit_ns) {
     wait_probe_kernel<<<1, 32, 0, ctx->stream>>>(ctx->d_status, limit_ns);
     ctx->count_launch();
