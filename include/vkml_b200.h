@@ -222,7 +222,11 @@ int b200_set_gemm_precision(b200_ctx* ctx, int precision);
 int b200_get_gemm_precision(b200_ctx* ctx);
 /* Which kernel family b200_compute would launch for this matmul node, and why: the fact the
  * Vulkan backend publishes under the site "matmul.kernel"
- * (vulkan_backend.cpp:2363-2375) so that a run can be tied to the arithmetic that produced it. */
+ * (vulkan_backend.cpp:2363-2375) so that a run can be tied to the arithmetic that produced it.
+ * Names: fp32_simt (CUDA cores), tcgen05_3xtf32 (operand planes), tcgen05_3xtf32_stream (the large
+ * operand streamed once through tensor memory), tcgen05_3xtf32_direct (fp32 tiles split inside
+ * the kernel), and the tcgen05_tf32* forms under the plain-TF32 precision.  The node is judged by
+ * itself: inside a span, planes shared with another matmul keep a product on the plane scheme. */
 int b200_matmul_kernel(b200_ctx* ctx, const b200_node* node, char* name, size_t name_len, char* reason,
                        size_t reason_len);
 
