@@ -34,7 +34,8 @@ def test_the_python_package_trains_on_the_device_it_picks():
     assert np.all(np.isfinite(cpu)) and np.all(np.isfinite(dev))  # (random labels: the loss need not fall)
     assert np.max(np.abs(dev - cpu) / np.abs(cpu)) < 1e-4, (dev[:5], cpu[:5])
     assert out["params_max_abs"] < 1e-4
-    assert out["submissions"] >= 300 and out["dispatches"] >= 3000  # the device really did the work
+    # the device really did the work: four submissions and some twenty launches per step (fused groups)
+    assert out["submissions"] >= 300 and out["dispatches"] >= 1500
     assert out["shape_error"] == "ShapeError"
     assert any(label.startswith("matmul.") for label in out["profile"]) and "relu" in out["profile"]
     assert out["profile"][-1] == "submit"

@@ -36,6 +36,7 @@ DESELECT = {
     "test_device_limits.py::test_the_stack_runs_at_the_guaranteed_floor": "VKML_MIN_SPEC makes a Vulkan device report the API's minimum limits",
     "test_attribution.py::test_concurrent_dispatches_make_the_naive_sum_exceed_the_window": "asserts an artefact of Vulkan timestamp brackets (overlapping split-K dispatches); launches on one CUDA stream are serial",
     "test_invariants.py::test_cumulative_gpu_time_accumulates_across_submissions": "vulkan_stats()['gpu_ms'] is fed by Vulkan timestamp queries that are always on; device time here is measured only while profiling is enabled",
+    "test_invariants.py::test_scaled_add_costs_one_dispatch_not_four": "counts three dispatches for a*alpha + b*beta written out as mul, mul, add; a run of tiny elementwise nodes is ONE launch here (the test's own failure message asks for the comparison to be revisited when the composed form gets cheaper)",
     # -- this backend serves MORE than vkML's Vulkan backend does
     "test_backend_parity.py::test_the_declined_set_is_known": "pins the set the Vulkan backend declines to {prod}; prod is served here (in index order, bit-identical to the CPU)",
     "test_layout_and_scale.py::test_prod_has_no_vulkan_kernel": "expects NotImplementedError for prod, which is served here",

@@ -262,10 +262,13 @@ def test_fused_groups_compute_what_the_separate_kernels_do(monkeypatch, name):
     plain, plain_labels = run(False)
     fused, fused_labels = run(True)
     assert not any(l.startswith("fused.") for l in plain_labels)
-    for kind in ("fused.one_hot_mul", "fused.log_softmax_backward"):
-        assert kind in fused_labels, sorted(set(fused_labels))
+    assert "fused.log_softmax_backward" in fused_labels, sorted(set(fused_labels))
+    # the one-hot mask of the loss: a kernel of its own, or part of the single-block chain that serves
+    # the whole prologue when its tensors are tiny
+    assert "fused.one_hot_mul" in fused_labels or "fused.tiny_chain" in fused_labels, sorted(set(fused_labels))
+    assert "fused.tiny_chain" in fused_labels and "fused.scaled_add_group" in fused_labels
     # the bias / mask / relu group appears in whichever form the span holds it
     assert any(l in ("fused.bias_mask_relu", "fused.bias_mask", "fused.bias_relu", "fused.mask") for l in fused_labels)
-    assert len(fused_labels) <= len(plain_labels) - 7 * steps, (len(fused_labels), len(plain_labels))
+    assert len(fused_labels) <= len(plain_labels) - 12 * steps, (len(fused_labels), len(plain_labels))
     assert np.all(np.isfinite(plain))
     np.testing.assert_allclose(fused, plain, rtol=1e-6, atol=0)

@@ -947,6 +947,42 @@ static void compute_span(b200_ctx* ctx, const b200_node* nodes, size_t n_nodes, 
                 }
             }
         }
+        if (ctx->fuse && exec.size() - p >= 3 &&
+            (node.op == B200_OP_FULL || node.op == B200_OP_ARANGE || node.op == B200_OP_CONTIGUOUS || node.op == B200_OP_CAST ||
+             node.op == B200_OP_NEG || node.op == B200_OP_DIV || node.op == B200_OP_MUL || node.op == B200_OP_EQUAL)) {
+            // a run of tiny elementwise nodes (the prologue of a loss): one block walks it
+            constexpr size_t kLook = 12;
+            const size_t avail = std::min<size_t>(exec.size() - p, kLook);
+            const b200_node* seq[kLook];
+            size_t run = 0;
+            while (run < avail && !done[p + run]) {
+                const size_t idx = exec[p + run];
+                const bool sink = !is_sink.empty() && is_sink[idx];
+                if (sink || (grad_sync && is_sink.empty() && !ctx->grads.empty())) break;
+                int64_t numel = 1;
+                for (int d = 0; d < nodes[idx].out.ndim; ++d) numel *= nodes[idx].out.dims[d];
+                if (numel > 4096) break;
+                seq[run] = &nodes[idx];
+                ++run;
+            }
+            if (run >= 3) {
+                for (size_t k = 0; k < run; ++k) prepare(exec[p + k]);
+                ctx->current_op = node.op;
+                const size_t taken = launch_tiny_chain(ctx, seq, run);
+                if (taken > 0) {
+                    for (size_t k = 0; k < taken; ++k) {
+                        if (seq[k]->op == B200_OP_FULL && seq[k]->out.dtype == B200_F32) {
+                            constants[seq[k]->out.data] = tensor_bytes(seq[k]->out);
+                        } else {
+                            constants.erase(seq[k]->out.data);
+                        }
+                        finish(exec[p + k]);
+                    }
+                    p += taken;
+                    continue;
+                }
+            }
+        }
         if (ctx->fuse && node.op == B200_OP_MAX_POOL2D_BACKWARD && p + 1 < exec.size() && !done[p + 1]) {
             // ReLU's backward rule behind a pooling layer: where(mask, zeros, pooling gradient)
             const b200_node& wn = nodes[exec[p + 1]];

@@ -230,6 +230,8 @@ size_t launch_fused(b200_ctx* ctx, const b200_node* const* seq, size_t avail);
 // movement.cu: max_pool2d_backward + the where() of ReLU's backward rule behind it, one launch; false: not that case
 bool launch_pool_backward_where(b200_ctx* ctx, const b200_node& pool, const b200_node& where, int result_is_x,
                                 const void* constant);
+// elementwise.cu: the leading run of tiny elementwise nodes (a loss prologue) as one single-block launch
+size_t launch_tiny_chain(b200_ctx* ctx, const b200_node* const* seq, size_t avail);
 size_t launch_scaled_add_group(b200_ctx* ctx, const b200_node* const* seq, size_t avail, bool* picked);
 
 // dist.cu

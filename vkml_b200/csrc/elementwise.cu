@@ -1126,6 +1126,156 @@ void run_float(b200_ctx* ctx, const b200_node& node, const typename F::P& p, con
 
 }  // namespace
 
+// ---------------------------------------------------------------------------
+// Chains of tiny elementwise nodes: one block, one launch
+// ---------------------------------------------------------------------------
+// A loss prologue is a run of nodes of a few hundred elements each -- scalar fills, a division of
+// scalars, broadcasts made contiguous, the labels cast to float, an arange, the one-hot comparison
+// (src/api/ops.cpp:347-354,417-441) -- eleven launches that each cost more to start than to run.
+// Here one block walks such a run node by node, in span order, with a block barrier between nodes
+// (which also orders its own global writes before the next node's reads).  Every element goes
+// through the functor the stand-alone kernel uses, so the values are the same bits.
+namespace {
+
+constexpr int kTinyNodes = 12;
+constexpr int64_t kTinyElems = 4096;  // one block: beyond a few thousand elements a node is faster as its own launch
+enum TinyKind : int {
+    kTinyFull, kTinyArange, kTinyCopy4, kTinyCastI64, kTinyCastBool, kTinyNeg, kTinyAdd, kTinySub, kTinyMul, kTinyDiv, kTinyEqual
+};
+
+struct TinyNode {
+    int kind;
+    int numel;
+    void* out;
+    const void* src[2];
+    int dim[kMaxDims];
+    int stride[2][kMaxDims];  // elements
+    float value;              // full
+    double start, step;       // arange
+};
+
+struct TinyChain {
+    int n;
+    TinyNode node[kTinyNodes];
+};
+
+__global__ void __launch_bounds__(1024) tiny_chain_kernel(const __grid_constant__ TinyChain c) {
+    pdl_prologue();
+    const NoParams np{};
+    for (int t = 0; t < c.n; ++t) {
+        const TinyNode& nd = c.node[t];
+        for (int i = threadIdx.x; i < nd.numel; i += blockDim.x) {
+            int r = i, o0 = 0, o1 = 0;
+#pragma unroll
+            for (int a = kMaxDims - 1; a >= 0; --a) {
+                const int q = r / nd.dim[a];
+                const int idx = r - q * nd.dim[a];
+                r = q;
+                o0 += idx * nd.stride[0][a];
+                o1 += idx * nd.stride[1][a];
+            }
+            const float* a32 = static_cast<const float*>(nd.src[0]);
+            const float* b32 = static_cast<const float*>(nd.src[1]);
+            float* out32 = static_cast<float*>(nd.out);
+            switch (nd.kind) {
+                case kTinyFull: out32[i] = nd.value; break;
+                case kTinyArange: out32[i] = static_cast<float>(__dadd_rn(nd.start, __dmul_rn(static_cast<double>(i), nd.step))); break;
+                case kTinyCopy4: static_cast<uint32_t*>(nd.out)[i] = static_cast<const uint32_t*>(nd.src[0])[o0]; break;
+                case kTinyCastI64: out32[i] = FCast<int64_t, float>::apply(np, static_cast<const int64_t*>(nd.src[0])[o0], 0, 0); break;
+                case kTinyCastBool: out32[i] = FCastBool<float>::apply(np, static_cast<const uint8_t*>(nd.src[0])[o0], 0, 0); break;
+                case kTinyNeg: out32[i] = FNeg::apply(np, a32[o0], 0.0F, 0.0F); break;
+                case kTinyAdd: out32[i] = FAdd::apply(np, a32[o0], b32[o1], 0.0F); break;
+                case kTinySub: out32[i] = FSub::apply(np, a32[o0], b32[o1], 0.0F); break;
+                case kTinyMul: out32[i] = FMul::apply(np, a32[o0], b32[o1], 0.0F); break;
+                case kTinyDiv: out32[i] = FDiv::apply(np, a32[o0], b32[o1], 0.0F); break;
+                case kTinyEqual: static_cast<uint8_t*>(nd.out)[i] = FEqual::apply(np, a32[o0], b32[o1], 0.0F); break;
+                default: break;
+            }
+        }
+        __syncthreads();
+    }
+}
+
+// Fills `t` when the node is one the chain kernel serves as it stands.
+bool tiny_node(const b200_node& node, TinyNode& t) {
+    const View out = make_view(node.out);
+    if (!out.contiguous || out.numel <= 0 || out.numel > kTinyElems || out.data == nullptr) return false;
+    const int dt = out.dtype;
+    int n_src = 0;
+    int want[2] = {B200_F32, B200_F32};
+    switch (node.op) {
+        case B200_OP_FULL:
+            if (dt != B200_F32) return false;
+            t.kind = kTinyFull;
+            t.value = static_cast<float>(get_params<FullParams>(node).value);
+            break;
+        case B200_OP_ARANGE: {
+            if (dt != B200_F32) return false;
+            const auto p = get_params<ArangeParams>(node);
+            t.kind = kTinyArange;
+            t.start = p.start;
+            t.step = p.step;
+            break;
+        }
+        case B200_OP_CONTIGUOUS:
+            if (dtype_size(dt) != 4 || node.src[0].dtype != dt) return false;
+            t.kind = kTinyCopy4;
+            n_src = 1;
+            want[0] = dt;
+            break;
+        case B200_OP_CAST:
+            if (dt != B200_F32) return false;
+            n_src = 1;
+            if (node.src[0].dtype == B200_I64) { t.kind = kTinyCastI64; want[0] = B200_I64; }
+            else if (node.src[0].dtype == B200_BOOL) { t.kind = kTinyCastBool; want[0] = B200_BOOL; }
+            else return false;
+            break;
+        case B200_OP_NEG: t.kind = kTinyNeg; n_src = 1; if (dt != B200_F32) return false; break;
+        case B200_OP_ADD: t.kind = kTinyAdd; n_src = 2; if (dt != B200_F32) return false; break;
+        case B200_OP_SUB: t.kind = kTinySub; n_src = 2; if (dt != B200_F32) return false; break;
+        case B200_OP_MUL: t.kind = kTinyMul; n_src = 2; if (dt != B200_F32) return false; break;
+        case B200_OP_DIV: t.kind = kTinyDiv; n_src = 2; if (dt != B200_F32) return false; break;
+        case B200_OP_EQUAL: t.kind = kTinyEqual; n_src = 2; if (dt != B200_BOOL) return false; break;
+        default: return false;
+    }
+    if (static_cast<int>(node.n_src) < n_src) return false;
+    t.numel = static_cast<int>(out.numel);
+    t.out = out.data;
+    t.src[0] = t.src[1] = nullptr;
+    for (int a = 0; a < kMaxDims; ++a) {
+        t.dim[a] = static_cast<int>(out.dim[a]);
+        t.stride[0][a] = t.stride[1][a] = 0;
+    }
+    for (int s = 0; s < n_src; ++s) {
+        if (node.src[s].dtype != want[s] || node.src[s].data == nullptr) return false;
+        const View in = make_view(node.src[s]);
+        for (int a = 0; a < kMaxDims; ++a) {
+            if (in.dim[a] != out.dim[a]) return false;
+            if (in.stride[a] < -(int64_t(1) << 30) || in.stride[a] > (int64_t(1) << 30)) return false;
+            t.stride[s][a] = in.dim[a] > 1 ? static_cast<int>(in.stride[a]) : 0;
+        }
+        t.src[s] = in.data;
+    }
+    return true;
+}
+
+}  // namespace
+
+// `seq`: consecutive nodes of a span.  Serves the leading run of tiny elementwise nodes (at least
+// three of them) with one launch; returns how many it served.
+size_t launch_tiny_chain(b200_ctx* ctx, const b200_node* const* seq, size_t avail) {
+    TinyChain chain{};
+    size_t n = 0;
+    while (n < avail && n < static_cast<size_t>(kTinyNodes) && tiny_node(*seq[n], chain.node[n])) ++n;
+    if (n < 3) return 0;
+    chain.n = static_cast<int>(n);
+    ProfScope scope(ctx, "fused.tiny_chain");
+    launch_kernel(ctx, tiny_chain_kernel, 1u, 1024, 0, chain);
+    ctx->count_launch();
+    check_last_launch("chain of tiny elementwise nodes");
+    return n;
+}
+
 void launch_elementwise(b200_ctx* ctx, const b200_node& node) {
     switch (node.op) {
         case B200_OP_FULL: run_full(ctx, node); return;
